@@ -1,0 +1,147 @@
+// Row-wise kernels: embedding gather, residual sum + RMS norm, SwiGLU activation, and
+// the combination of routed and shared expert outputs.
+//
+// Formulas follow the reference's kernels (src/ops/kernels.hip): embed_gather 150-159,
+// rmsnorm 17-41, fused_residual_rmsnorm 100-129, silu_and_mul 131-140; the weighted
+// sum of expert outputs replaces scale_rows (216-223) + scatter_add_rows
+// (src/ops/moe.hip:22-31, which races) by one pass with a fixed order and no atomics.
+// The residual stream is float32 in both modes.
+#include "common.cuh"
+
+namespace nf {
+
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+// h[t] += delta[t] (if delta), out[t] = h[t] * rsqrt(mean(h[t]^2) + eps) * w.
+// With `rows`, row r reads h[rows[r]] / delta[rows[r]], writes out[r] and leaves h alone.
+template <typename T, bool GATHER>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ w,
+                                   float eps, T* __restrict__ out, int hidden) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int src = GATHER ? rows[r] : r;
+  float* hr = h + (size_t)src * hidden;
+  const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  T* o = out + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = hr[i];
+    if (dr) {
+      v += to_float(dr[i]);
+      if (!GATHER) hr[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = hr[i];
+    if (GATHER && dr) v += to_float(dr[i]);
+    o[i] = from_float<T>(v * inv * w[i]);
+  }
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner) {
+  const int m = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= inner) return;
+  const float g = to_float(gu[(size_t)m * 2 * inner + i]);
+  const float u = to_float(gu[(size_t)m * 2 * inner + inner + i]);
+  act[(size_t)m * inner + i] = from_float<T>(g / (1.f + expf(-g)) * u);
+}
+
+// out[t] = sum_j wts[t,j] * y[inv[t*k+j]]  (j ascending)  + sigmoid(gate[t*gate_stride]) * shared[t]
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ inv,
+                                   const float* __restrict__ wts, const T* __restrict__ shared,
+                                   const float* __restrict__ gate, int gate_stride,
+                                   T* __restrict__ out, int hidden, int k) {
+  const int t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= hidden) return;
+  float acc = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const int p = inv[t * k + j];
+    acc += wts[t * k + j] * to_float(y[(size_t)p * hidden + i]);
+  }
+  if (shared) {
+    float s = to_float(shared[(size_t)t * hidden + i]);
+    if (gate) s *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride]));
+    acc += s;
+  }
+  out[(size_t)t * hidden + i] = from_float<T>(acc);
+}
+
+static inline int row_threads(int n) {
+  int t = 32;
+  while (t < n && t < 256) t <<= 1;
+  return t;
+}
+
+}  // namespace nf
+
+using namespace nf;
+
+extern "C" int nf_embed_rows(const void* table, const int* ids, float* out, int T, int hidden,
+                             int vocab, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && hidden > 0 && vocab > 0, "embed_rows: bad sizes T=%d hidden=%d vocab=%d", T, hidden, vocab);
+  if (dtype == kF32)
+    embed_rows_kernel<float><<<T, row_threads(hidden), 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+  else
+    embed_rows_kernel<__nv_bfloat16><<<T, row_threads(hidden), 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+  return check_launch("embed_rows");
+}
+
+extern "C" int nf_add_rmsnorm(float* h, const void* delta, const int* rows, const float* w,
+                              float eps, void* out, int R, int hidden, int dtype,
+                              cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && hidden > 0, "add_rmsnorm: bad sizes R=%d hidden=%d", R, hidden);
+  const int th = row_threads(hidden);
+  if (dtype == kF32) {
+    if (rows) add_rmsnorm_kernel<float, true><<<R, th, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);
+    else add_rmsnorm_kernel<float, false><<<R, th, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);
+  } else {
+    if (rows) add_rmsnorm_kernel<__nv_bfloat16, true><<<R, th, 0, stream>>>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
+    else add_rmsnorm_kernel<__nv_bfloat16, false><<<R, th, 0, stream>>>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
+  }
+  return check_launch("add_rmsnorm");
+}
+
+extern "C" int nf_silu_mul(const void* gu, void* act, int M, int inner, int dtype,
+                           cudaStream_t stream) {
+  if (M == 0) return 0;
+  NF_REQUIRE(M > 0 && inner > 0, "silu_mul: bad sizes M=%d inner=%d", M, inner);
+  dim3 grid(M, (inner + 255) / 256);
+  if (dtype == kF32) silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)act, inner);
+  else silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inner);
+  return check_launch("silu_mul");
+}
+
+extern "C" int nf_moe_combine(const void* y, const int* inv, const float* wts, const void* shared,
+                              const float* gate, int gate_stride, void* out, int T, int hidden,
+                              int k, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && hidden > 0 && k > 0, "moe_combine: bad sizes T=%d hidden=%d k=%d", T, hidden, k);
+  dim3 grid(T, (hidden + 255) / 256);
+  if (dtype == kF32)
+    moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)y, inv, wts, (const float*)shared, gate, gate_stride, (float*)out, hidden, k);
+  else
+    moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
+  return check_launch("moe_combine");
+}

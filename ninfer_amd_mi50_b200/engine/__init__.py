@@ -1,0 +1,5 @@
+from .batch import BatchError, StepEntry, pack_step
+from .step import ModelRunner
+from .loading import build_model, load_runner
+
+__all__ = ["BatchError", "StepEntry", "pack_step", "ModelRunner", "build_model", "load_runner"]

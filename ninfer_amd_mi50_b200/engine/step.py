@@ -1,0 +1,75 @@
+"""The step function: run a batch of (request, its next tokens) from the cache.
+
+Reference: ``Model::forward_batch(tokens, positions, seq_ids)`` (src/models/model.h:74-77,
+src/models/model.hip:994-1032) returns the logits of each group's last row and leaves
+length bookkeeping to its callers (src/api/ninfer_c_api.cpp:190, 210, 239).  This step
+takes whole entries, keeps the lengths in the cache manager, accepts portions of prompts
+beside single decoded tokens cut anywhere, and returns logits at exactly the rows asked
+for.  It runs only the tokens it is given; everything earlier comes from the cache.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.page_pool import OutOfPages
+from ..parts.model import DecoderModel
+from .batch import BatchError, StepEntry, pack_step, validate_entries
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, dtype: torch.dtype, device):
+        self.model, self.cache, self.dtype = model, cache, dtype
+        self.device = torch.device(device)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- requests -------------------------------------------------------------------
+    def open(self, req: Hashable) -> int:
+        return self.cache.open(req)
+
+    def close(self, req: Hashable) -> None:
+        self.cache.close(req)
+
+    # ---- the step -------------------------------------------------------------------
+    def reserve(self, entries: Sequence[StepEntry]) -> None:
+        """Hold pages for every entry's new tokens, or for none of them."""
+        done: List[StepEntry] = []
+        try:
+            for e in entries:
+                self.cache.reserve(e.req, self.cache.length(e.req) + len(e.tokens))
+                done.append(e)
+        except OutOfPages:
+            for e in done:
+                self.cache.truncate(e.req)
+            raise
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """float32 logits [R, vocab] on the device, R = total wanted rows, in entry order."""
+        entries = list(entries)
+        if not entries:
+            return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
+        validate_entries(entries, self.cache, self.model.vocab_size)
+        self.reserve(entries)
+        try:
+            ctx = pack_step(entries, self.cache, self.dtype, self.device)
+            logits = self.run(ctx)
+        except Exception:
+            for e in entries:
+                self.cache.truncate(e.req)
+            raise
+        for e in entries:
+            self.cache.commit(e.req, self.cache.length(e.req) + len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += ctx.T
+        return logits
+
+    def run(self, ctx) -> torch.Tensor:
+        cache = self.cache
+        return self.model.forward(
+            ctx,
+            lambda slot, append: cache.view(slot, ctx.block_tables, append),
+            cache.state_of)

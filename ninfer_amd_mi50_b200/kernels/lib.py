@@ -1,0 +1,50 @@
+"""Loading the kernel library and calling into it.
+
+The library is plain C ABI (``extern "C" int nf_*``), loaded with ctypes like the
+reference's Python wrapper loads ``libninfer.so`` (tools/ninfer_ctypes.py:20-33).  There is
+no other implementation behind these calls: if the library cannot be built or loaded,
+the first call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+from . import build as _build
+
+_lib: Optional[ctypes.CDLL] = None
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Build if needed, then load.  Raises if there is no CUDA library to call."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.build(verbose=True)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from None
+            lib.nf_last_error.restype = ctypes.c_char_p
+            _lib = lib
+    return _lib
+
+
+def call(name: str, *args) -> None:
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name}: {lib.nf_last_error().decode(errors='replace')}")
+
+
+def is_loaded() -> bool:
+    return _lib is not None

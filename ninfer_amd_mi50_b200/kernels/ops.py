@@ -1,0 +1,267 @@
+"""Python faces of the CUDA kernels.  Every function launches on torch's current stream.
+
+One function per operation of the step (reference: the free functions of
+src/ops/ops.h:19-234).  Which kernel serves a call is decided by the dtype and by the
+number of rows only, never by what the rows are (prompt or decode), so that a row's
+result does not depend on its neighbours.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import lib as _lib
+
+c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+# Tunables that tests may override to force a particular kernel.
+TUNING = {
+    "bf16_linear": "auto",        # "simt" | "auto"
+    "bf16_attention": "auto",     # "generic" | "auto"
+    "bf16_moe": "auto",           # "simt" | "auto"
+    "skinny_max_rows": 64,
+}
+
+SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
+MAX_EXPERTS = 8192
+
+
+def check_head_dim(head_dim: int) -> None:
+    if head_dim not in SUPPORTED_HEAD_DIMS:
+        raise ValueError(f"head_dim={head_dim} is not supported by the attention kernels "
+                         f"(multiples of 16 from 16 to 256)")
+
+
+def check_router_sizes(num_experts: int, top_k: int) -> None:
+    if not 1 <= num_experts <= MAX_EXPERTS:
+        raise ValueError(f"num_experts={num_experts} is not supported (1..{MAX_EXPERTS})")
+    if not 1 <= top_k <= num_experts:
+        raise ValueError(f"top_k={top_k} must lie in [1, {num_experts}]")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _chk(t: torch.Tensor, name: str, dtype=None, contiguous=True) -> None:
+    if not t.is_cuda:
+        raise _lib.KernelError(f"{name} must be a CUDA tensor; there is no CPU implementation")
+    if contiguous and not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+# ---------------------------------------------------------------------------------------
+# rows
+# ---------------------------------------------------------------------------------------
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = float32(table[ids[t]])."""
+    _chk(table, "table"); _chk(ids, "ids", torch.int32); _chk(out, "out", torch.float32)
+    _lib.call("nf_embed_rows", _p(table), _p(ids), _p(out), c_int(ids.numel()),
+              c_int(table.shape[1]), c_int(table.shape[0]), c_int(_dt(table)), _stream())
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    """h += delta (float32, in place); out = h * rsqrt(mean(h^2) + eps) * weight."""
+    _chk(h, "h", torch.float32); _chk(weight, "weight", torch.float32); _chk(out, "out")
+    if delta is not None:
+        _chk(delta, "delta", out.dtype)
+    _lib.call("nf_add_rmsnorm", _p(h), _p(delta), None, _p(weight), c_float(eps), _p(out),
+              c_int(h.shape[0]), c_int(h.shape[1]), c_int(_dt(out)), _stream())
+
+
+def add_rmsnorm_rows(h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor,
+                     weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[r] = norm(h[rows[r]] + delta[rows[r]]); h is left as it is."""
+    _chk(h, "h", torch.float32); _chk(rows, "rows", torch.int32); _chk(out, "out")
+    _chk(weight, "weight", torch.float32)
+    if delta is not None:
+        _chk(delta, "delta", out.dtype)
+    _lib.call("nf_add_rmsnorm", _p(h), _p(delta), _p(rows), _p(weight), c_float(eps), _p(out),
+              c_int(rows.numel()), c_int(h.shape[1]), c_int(_dt(out)), _stream())
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[M, 2I] -> [M, I]: silu(first half) * second half."""
+    _chk(gate_up, "gate_up")
+    M, two_i = gate_up.shape
+    out = torch.empty((M, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _lib.call("nf_silu_mul", _p(gate_up), _p(out), c_int(M), c_int(two_i // 2), c_int(_dt(gate_up)),
+              _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# matrix products
+# ---------------------------------------------------------------------------------------
+
+def _gemm_simt(a, lda, b, b_group_stride, c, M, N, K, groups, max_rows, offsets, a_rows, a_div,
+               swiglu) -> None:
+    _lib.call("nf_gemm_simt", _p(a), c_int(lda), _p(b), c_longlong(b_group_stride), _p(c),
+              c_int(c.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
+              _p(offsets), _p(a_rows), c_int(a_div), c_int(1 if swiglu else 0), c_int(_dt(a)),
+              c_int(_dt(c)), _stream())
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] times w [N, K] transposed -> [M, N]; float32 accumulation."""
+    _chk(x, "x"); _chk(w, "w", x.dtype)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError(f"linear: x has {K} columns, w has {w.shape[1]}")
+    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if M == 0:
+        return out
+    _gemm_simt(x, K, w, 0, out, M, N, K, 1, M, None, None, 1, False)
+    return out
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """x [M, K], w [2I, K] (gate rows first) -> silu(x gate^T) * (x up^T)  [M, I]."""
+    _chk(x, "x"); _chk(w_gate_up, "w_gate_up", x.dtype)
+    M, K = x.shape
+    inner = w_gate_up.shape[0] // 2
+    out = torch.empty((M, inner), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out
+    _gemm_simt(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True)
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------
+
+def rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                row_seg: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                Hq: int, Hkv: int, D: int, pages: torch.Tensor, block_table: torch.Tensor,
+                page_size: int, append: bool) -> None:
+    """In place: qkv += bias; rotate q and k heads; write k, v to the cache pages."""
+    _chk(qkv, "qkv"); _chk(pages, "pages", qkv.dtype); _chk(block_table, "block_table", torch.int32)
+    _chk(positions, "positions", torch.int32); _chk(row_seg, "row_seg", torch.int32)
+    if bias is not None:
+        _chk(bias, "bias", torch.float32)
+    if inv_freq is not None:
+        _chk(inv_freq, "inv_freq", torch.float32)
+    if qkv.shape[1] != (Hq + 2 * Hkv) * D:
+        raise ValueError("rope_append: qkv width does not match the head counts")
+    _lib.call("nf_rope_append", _p(qkv), _p(bias), _p(positions), _p(row_seg), _p(inv_freq),
+              c_int(rotary_dim if inv_freq is not None else 0), c_int(qkv.shape[0]), c_int(Hq),
+              c_int(Hkv), c_int(D), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+              c_int(page_size), c_int(pages.shape[0]), c_int(1 if append else 0), c_int(_dt(qkv)),
+              _stream())
+
+
+def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.Tensor,
+                    block_table: torch.Tensor, page_size: int, ctx, window: int, scale: float
+                    ) -> torch.Tensor:
+    """Causal attention of the rows' (rotated) queries in `qkv` over the cache -> [T, Hq*D]."""
+    _chk(qkv, "qkv"); _chk(pages, "pages", qkv.dtype)
+    T = qkv.shape[0]
+    out = torch.empty((T, Hq * D), dtype=qkv.dtype, device=qkv.device)
+    _lib.call("nf_paged_attention_generic", _p(qkv), c_int(qkv.shape[1]), _p(pages),
+              _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg),
+              _p(out), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+              c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(_dt(qkv)), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# routed experts
+# ---------------------------------------------------------------------------------------
+
+@dataclass
+class MoePlan:
+    offsets: torch.Tensor   # int32 [E + 1] rows of each expert in sorted order
+    order: torch.Tensor     # int32 [T * k] pair (t * k + j) at each sorted position
+    inv: torch.Tensor       # int32 [T * k] sorted position of each pair
+    num_experts: int
+    num_tokens: int
+    top_k: int
+
+
+def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool
+                ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Router logits (float32), softmax, top-k.  Rows of `w_router` beyond E give raw
+    logits back (`extra`, [T, rows - E]).  Returns (idx int32 [T, k], weights float32 [T, k], extra)."""
+    _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
+    T, H = x.shape
+    extra = w_router.shape[0] - E
+    idx = torch.empty((T, k), dtype=torch.int32, device=x.device)
+    wts = torch.empty((T, k), dtype=torch.float32, device=x.device)
+    ext = torch.empty((T, extra), dtype=torch.float32, device=x.device) if extra > 0 else None
+    _lib.call("nf_router_topk", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra),
+              c_int(k), c_int(1 if norm_topk else 0), _p(idx), _p(wts), _p(ext), c_int(_dt(x)),
+              _stream())
+    return idx, wts, ext
+
+
+def moe_plan(topk_idx: torch.Tensor, E: int) -> MoePlan:
+    _chk(topk_idx, "topk_idx", torch.int32)
+    T, k = topk_idx.shape
+    dev = topk_idx.device
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    order = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    _lib.call("nf_moe_plan", _p(topk_idx), c_int(T * k), c_int(E), _p(offsets), _p(order), _p(inv),
+              _stream())
+    return MoePlan(offsets, order, inv, E, T, k)
+
+
+def moe_gemm1(x: torch.Tensor, w13: torch.Tensor, plan: MoePlan, k: int) -> torch.Tensor:
+    """Sorted pair p (token order[p] // k, expert e) -> silu(x Wgate_e^T) * (x Wup_e^T)  [T*k, I]."""
+    _chk(x, "x"); _chk(w13, "w13", x.dtype)
+    T, H = x.shape
+    E, two_i, _ = w13.shape
+    inner = two_i // 2
+    act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return act
+    _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
+    return act
+
+
+def moe_gemm2(act: torch.Tensor, w2: torch.Tensor, plan: MoePlan) -> torch.Tensor:
+    """Sorted pair p of expert e -> act[p] Wdown_e^T  [T*k, H]."""
+    _chk(act, "act"); _chk(w2, "w2", act.dtype)
+    n, inner = act.shape
+    E, H, _ = w2.shape
+    y = torch.empty((n, H), dtype=act.dtype, device=act.device)
+    if n == 0:
+        return y
+    _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
+    return y
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optional[torch.Tensor],
+                gate: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """out[t] = sum_j wts[t, j] * y[inv[t, j]] (j ascending) + sigmoid(gate[t]) * shared[t]."""
+    _chk(y, "y"); _chk(wts, "wts", torch.float32)
+    T, k = wts.shape
+    H = y.shape[1]
+    out = torch.empty((T, H), dtype=out_dtype, device=y.device)
+    _lib.call("nf_moe_combine", _p(y), _p(plan.inv), _p(wts), _p(shared), _p(gate),
+              c_int(gate.shape[1] if gate is not None else 0), _p(out), c_int(T), c_int(H), c_int(k),
+              c_int(_dt(y)), _stream())
+    return out

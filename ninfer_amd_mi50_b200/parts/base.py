@@ -1,0 +1,234 @@
+"""Interfaces that every part of a layer implements, and the step's shared metadata.
+
+A part knows its own sizes and constants (constructor arguments that come from the
+configuration through a `PartSpec`) and the names of its own tensors below a prefix.
+It does not know which model it is in, how many layers there are, or what the other
+parts of its block are.
+
+Reference counterpart: ``Shard::layer_start`` / ``layer_mid`` / ``end_layer``
+(src/models/model.hip:206-444) hard-wire one attention and one MLP/MoE into a
+function; here the same stages are objects chosen layer by layer.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+# --------------------------------------------------------------------------------------
+# Tensors a part needs from the checkpoint
+# --------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """One checkpoint tensor a part asks for.
+
+    role:  "matrix" - held in the engine dtype (bfloat16 or float32);
+           "vector" - norm weights and biases, held in float32 in both modes (a
+                      bfloat16 value widens exactly; a tensor stored in 32-bit stays so);
+           "router" - routing matrices, held in float32 for the same reason;
+           "table"  - integer tables, held as int32.
+    init:  distribution for the random-weights mode: "linear" N(0, 0.02),
+           "norm" 1 + N(0, 0.05).
+    """
+    name: str
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    init: str = "linear"
+
+
+Fetch = Callable[[str], torch.Tensor]   # tensor name -> device tensor in its role's dtype
+
+
+# --------------------------------------------------------------------------------------
+# What a mixer asks of the cache manager
+# --------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """Paged keys and values for one cache slot.
+
+    kind "full": every key stays until the request ends.
+    kind "window": only the last `window` keys are read; pages that the window has
+    passed go back to the pool.
+    """
+    kind: str
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+    def group_key(self) -> Tuple:
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size: one tensor of `shape` per live request."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """What a mixer call sees of one cache slot during a step."""
+    spec: CacheSpec
+    pages: torch.Tensor          # [num_pages + 1, 2, kv_heads, page_size, head_dim]
+    block_table: torch.Tensor    # int32 [S, width]: page of (segment, position // page_size)
+    page_size: int
+    append: bool = True
+
+
+# --------------------------------------------------------------------------------------
+# The step's metadata, shared by all parts
+# --------------------------------------------------------------------------------------
+
+@dataclass
+class StepContext:
+    """Everything about a step that is not the hidden state.
+
+    Rows are the step's tokens in order; a *segment* is one request's run of rows
+    (a portion of a prompt, or one decoded token).  All index tensors are int32 on the
+    device.  `seg_len_host` / `seg_pos0_host` are host copies for grid sizing; they are
+    absent in graph mode, where only the bounds `max_rows_per_seg` and `max_context`
+    may shape a launch.
+    """
+    dtype: torch.dtype
+    device: torch.device
+    T: int
+    S: int
+    token_ids: torch.Tensor        # [T]
+    positions: torch.Tensor        # [T] absolute position of each row in its request
+    row_seg: torch.Tensor          # [T] segment of each row
+    seg_row0: torch.Tensor         # [S + 1] first row of each segment
+    seg_pos0: torch.Tensor         # [S] tokens the request held before this step
+    seg_slot: torch.Tensor         # [S] state slot of each segment's request
+    logit_rows: torch.Tensor       # [R] rows whose logits are wanted
+    block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)  # per cache group
+    seg_len_host: Optional[List[int]] = None
+    seg_pos0_host: Optional[List[int]] = None
+    max_rows_per_seg: int = 1
+    max_context: int = 0           # bound on pos0 + rows over the segments of this step
+    graph_mode: bool = False
+    scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
+    _tiles: Dict[int, Tuple[torch.Tensor, int]] = field(default_factory=dict)
+
+    @property
+    def all_single(self) -> bool:
+        """Every segment brings exactly one row (a decode-only step)."""
+        return self.max_rows_per_seg == 1
+
+    def query_tiles(self, rows_per_tile: int) -> Tuple[torch.Tensor, int]:
+        """Tiles of at most `rows_per_tile` consecutive rows of one segment.
+
+        Returns (int32 [n, 2] of (segment, first row), n).  Built on the host from the
+        segment lengths; not available in graph mode.
+        """
+        if rows_per_tile in self._tiles:
+            return self._tiles[rows_per_tile]
+        if self.seg_len_host is None:
+            raise RuntimeError("query_tiles needs host segment lengths (not in graph mode)")
+        flat: List[int] = []
+        row = 0
+        for s, n in enumerate(self.seg_len_host):
+            for r in range(0, n, rows_per_tile):
+                flat += [s, row + r]
+            row += n
+        n_tiles = len(flat) // 2
+        t = torch.tensor(flat, dtype=torch.int32).reshape(n_tiles, 2).to(self.device)
+        self._tiles[rows_per_tile] = (t, n_tiles)
+        return t, n_tiles
+
+
+# --------------------------------------------------------------------------------------
+# Part interfaces
+# --------------------------------------------------------------------------------------
+
+class Part:
+    """Common to all parts: which tensors it needs and how it takes them."""
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return []
+
+    def load(self, fetch: Fetch) -> None:
+        """Pull this part's tensors (`fetch(name)`), fusing or stacking as it likes."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one forward call reads when every row uses everything."""
+        return 0
+
+
+class Norm(Part):
+    """Normalisation fused with the residual sum.
+
+    The residual stream `h` is float32 in both modes; `delta` is the previous part's
+    output in the engine dtype (or None).
+    """
+
+    def add_norm(self, h: torch.Tensor, delta: Optional[torch.Tensor],
+                 out_dtype: torch.dtype) -> torch.Tensor:
+        """h += delta (in place, in 32-bit); return norm(h) in `out_dtype`."""
+        raise NotImplementedError
+
+    def add_norm_rows(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor,
+                      out_dtype: torch.dtype) -> torch.Tensor:
+        """norm(h[rows] + delta[rows]) without changing h."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """How positions enter queries and keys."""
+
+    def rotary_table(self, device: torch.device) -> Optional[Tuple[torch.Tensor, int]]:
+        """(inverse frequencies float32 [rotary_dim // 2], rotary_dim) for the fused
+        rotate-and-append kernel (half-split pairing), or None if the encoding is not of
+        that form; then `apply` is called and the kernel appends without rotating."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        """Encode in place: q [T, heads, D], k [T, kv_heads, D], positions int32 [T]."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request (attention here)."""
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[CacheView],
+                state: Optional[torch.Tensor]) -> torch.Tensor:
+        """x [T, hidden] in the engine dtype -> [T, hidden] in the engine dtype.
+
+        `cache` is the view of the slot this call reads (and appends to when
+        `cache.append`); `state` is the slab [slots, *state_spec.shape] indexed by
+        `ctx.seg_slot`.
+        """
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """x [T, hidden] -> [T, hidden], both in the engine dtype."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of norms, mixer and feed-forward around the residual stream."""
+
+    mixer: Mixer
+
+    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: Optional[CacheView], state: Optional[torch.Tensor]
+                ) -> Optional[torch.Tensor]:
+        """Advance the float32 residual stream `h` in place.
+
+        `pending` is a contribution not yet added to `h` (so that the sum fuses with the
+        next norm); the return value is this block's own pending contribution.
+        """
+        raise NotImplementedError

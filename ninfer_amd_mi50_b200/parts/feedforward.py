@@ -1,0 +1,129 @@
+"""Feed-forward parts: a dense SwiGLU MLP, and routed SwiGLU experts with a gated
+shared expert.
+
+Dense (src/models/model.hip:334-336, gate and up fused to ``[2I, H]`` at load,
+model.hip:586-605): ``ffn = Wdown (silu(Wgate x) * Wup x)``, ``silu(g) = g / (1 + exp(-g))``
+(src/ops/kernels.hip:131-140).
+
+Sparse (model.hip:338-433; routing in ``moe_route_cpu``, src/ops/moe.hip:49-106):
+router logits in float32, softmax over all experts, the k largest probabilities
+(ties to the lower index), weights ``p_e`` or, with ``norm_topk_prob``, ``p_e / sum(selected)``
+(the reference always renormalises, moe.hip:77-82); every selected expert is a SwiGLU
+MLP; ``moe = sum_i w_i y_i`` in selection order.  The shared expert and its sigmoid gate
+(``ffn = moe + sigmoid(w_sg x) * shared(x)``) are Qwen2-MoE's and absent from the
+reference.  Unlike the reference, routing never leaves the device.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import kernels
+from ..registry import register_part
+from .base import FeedForward, Fetch, StepContext, TensorSpec
+
+
+@register_part("feed_forward", "dense_swiglu")
+class DenseSwiglu(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.prefix = prefix
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H, I = self.prefix, self.hidden_size, self.intermediate_size
+        return [TensorSpec(p + "gate_proj.weight", (I, H)),
+                TensorSpec(p + "up_proj.weight", (I, H)),
+                TensorSpec(p + "down_proj.weight", (H, I))]
+
+    def load(self, fetch: Fetch) -> None:
+        p = self.prefix
+        self.w_gate_up = torch.cat([fetch(p + "gate_proj.weight"), fetch(p + "up_proj.weight")],
+                                   dim=0).contiguous()
+        self.w_down = fetch(p + "down_proj.weight")
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up), self.w_down)
+
+
+@register_part("feed_forward", "sparse_moe_swiglu")
+class SparseMoeSwiglu(FeedForward):
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int, norm_topk_prob: bool,
+                 moe_intermediate_size: int, shared_intermediate_size: int, prefix: str):
+        if not 1 <= top_k <= num_experts:
+            raise ValueError(f"top_k={top_k} must lie in [1, num_experts={num_experts}]")
+        kernels.check_router_sizes(num_experts, top_k)
+        self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
+        self.norm_topk_prob = bool(norm_topk_prob)
+        self.moe_intermediate_size = int(moe_intermediate_size)
+        self.shared_intermediate_size = int(shared_intermediate_size)
+        self.prefix = prefix
+        self.w_router = self.w13 = self.w2 = self.ws13 = self.ws2 = None
+
+    @property
+    def has_shared(self) -> bool:
+        return self.shared_intermediate_size > 0
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H, I, Is = self.prefix, self.hidden_size, self.moe_intermediate_size, self.shared_intermediate_size
+        specs = [TensorSpec(p + "gate.weight", (self.num_experts, H), role="router")]
+        for e in range(self.num_experts):
+            q = f"{p}experts.{e}."
+            specs += [TensorSpec(q + "gate_proj.weight", (I, H)),
+                      TensorSpec(q + "up_proj.weight", (I, H)),
+                      TensorSpec(q + "down_proj.weight", (H, I))]
+        if self.has_shared:
+            q = p + "shared_expert."
+            specs += [TensorSpec(q + "gate_proj.weight", (Is, H)),
+                      TensorSpec(q + "up_proj.weight", (Is, H)),
+                      TensorSpec(q + "down_proj.weight", (H, Is)),
+                      TensorSpec(p + "shared_expert_gate.weight", (1, H), role="router")]
+        return specs
+
+    def load(self, fetch: Fetch) -> None:
+        p, H, I, E = self.prefix, self.hidden_size, self.moe_intermediate_size, self.num_experts
+        router = fetch(p + "gate.weight")
+        if self.has_shared:
+            # one matrix yields the router logits and the shared expert's gate logit
+            router = torch.cat([router, fetch(p + "shared_expert_gate.weight")], dim=0)
+        self.w_router = router.contiguous()
+        first = fetch(f"{p}experts.0.gate_proj.weight")
+        self.w13 = torch.empty((E, 2 * I, H), dtype=first.dtype, device=first.device)
+        self.w2 = torch.empty((E, H, I), dtype=first.dtype, device=first.device)
+        for e in range(E):
+            q = f"{p}experts.{e}."
+            self.w13[e, :I].copy_(first if e == 0 else fetch(q + "gate_proj.weight"))
+            self.w13[e, I:].copy_(fetch(q + "up_proj.weight"))
+            self.w2[e].copy_(fetch(q + "down_proj.weight"))
+        del first
+        if self.has_shared:
+            q = p + "shared_expert."
+            self.ws13 = torch.cat([fetch(q + "gate_proj.weight"), fetch(q + "up_proj.weight")],
+                                  dim=0).contiguous()
+            self.ws2 = fetch(q + "down_proj.weight")
+
+    def weight_bytes(self) -> int:
+        n = self.w_router.numel() * 4 + (self.w13.numel() + self.w2.numel()) * self.w2.element_size()
+        if self.has_shared:
+            n += (self.ws13.numel() + self.ws2.numel()) * self.ws2.element_size()
+        return n
+
+    def expert_bytes(self) -> int:
+        """Bytes of one routed expert's matrices."""
+        return (self.w13[0].numel() + self.w2[0].numel()) * self.w2.element_size()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        E, k = self.num_experts, self.top_k
+        idx, wts, gate = kernels.router_topk(x, self.w_router, E, k, self.norm_topk_prob)
+        plan = kernels.moe_plan(idx, E)
+        act = kernels.moe_gemm1(x, self.w13, plan, k)
+        y = kernels.moe_gemm2(act, self.w2, plan)
+        shared = None
+        if self.has_shared:
+            shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
+        return kernels.moe_combine(y, plan, wts, shared, gate, x.dtype)

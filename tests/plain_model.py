@@ -1,0 +1,225 @@
+"""A plain, slow implementation of Qwen2-MoE for whole sequences: the tests' oracle.
+
+It rests on the reference's formulas, not on its code run: the reference's model code is
+HIP for gfx906 with rocBLAS (src/models/model.hip, src/ops/*.hip) and cannot be compiled
+or imported on a machine without ROCm, so nothing here was compared with its output.
+Each function cites the lines whose arithmetic it restates.  Where Qwen2-MoE needs what
+the reference lacks (q/k/v bias, ``norm_topk_prob=false``, the shared expert with its
+sigmoid gate, ``decoder_sparse_step`` / ``mlp_only_layers``, the sliding window), the
+function says so.
+
+No cache, no batching, no paging: one request, all its tokens at once, one function per
+part.  It shares no code with the package under test: it reads config.json as a plain
+dictionary and the weights through the `safetensors` package.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+
+# ---- reading a model folder -------------------------------------------------------------
+
+def read_model_folder(model_dir: str, dtype: torch.dtype = torch.float32):
+    from safetensors import safe_open
+    with open(os.path.join(model_dir, "config.json")) as fh:
+        cfg = json.load(fh)
+    weights: Dict[str, torch.Tensor] = {}
+    with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            weights[name] = f.get_tensor(name).to(dtype)
+    return cfg, weights
+
+
+# ---- parts ----------------------------------------------------------------------------
+
+def plain_embedding(embed: torch.Tensor, tokens: List[int]) -> torch.Tensor:
+    """h0[t] = embed[token[t]], no scaling (src/ops/kernels.hip:150-159)."""
+    return embed[torch.tensor(tokens, dtype=torch.long)]
+
+
+def plain_rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """inv = rsqrt(mean(x^2) + eps); y = x * inv * w; the weight multiplies directly
+    (src/ops/kernels.hip:22-39)."""
+    inv = torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+    return x * inv * w
+
+
+def plain_inv_freq(head_dim: int, theta: float) -> torch.Tensor:
+    """inv_freq[i] = pow(theta, -2 i / D) in single precision
+    (src/models/model.hip:636-639)."""
+    out = []
+    for i in range(head_dim // 2):
+        expo = np.float32(np.float32(-2.0) * np.float32(i) / np.float32(head_dim))
+        out.append(np.float32(math.pow(float(np.float32(theta)), float(expo))))
+    return torch.tensor(np.array(out, dtype=np.float32))
+
+
+def plain_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """Half-split rotation of [T, heads, D] (src/ops/kernels.hip:85-92):
+    angle = float(pos) * inv_freq[i]; x'[i] = x[i] cos - x[i+D/2] sin;
+    x'[i+D/2] = x[i] sin + x[i+D/2] cos.  The angle is formed in float32 as there."""
+    half = x.shape[-1] // 2
+    angle = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(x.dtype)  # [T, D/2]
+    c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+    a, b = x[..., :half], x[..., half:]
+    return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+
+
+def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                    window: Optional[int] = None) -> torch.Tensor:
+    """q [T, Hq, D], k, v [T, Hkv, D] -> [T, Hq*D].  Query head h reads kv head
+    h // (Hq/Hkv) (src/ops/attention.hip:27-28, 157-158); score = q.k / sqrt(D)
+    (src/models/model.hip:285); key j visible to row t iff j <= t (attention.hip:216);
+    softmax over the visible keys; o = sum p_j v_j (attention.hip:260-266).
+    With a window w (not in the reference): visible iff t - w < j <= t."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    rep = Hq // Hkv
+    out = torch.zeros(T, Hq, D, dtype=q.dtype)
+    idx = torch.arange(T)
+    mask = idx[None, :] <= idx[:, None]
+    if window:
+        mask &= idx[None, :] > idx[:, None] - window
+    for h in range(Hq):
+        kh, vh = k[:, h // rep], v[:, h // rep]
+        s = (q[:, h] @ kh.T) / math.sqrt(D)
+        s = s.masked_fill(~mask, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        out[:, h] = p @ vh
+    return out.reshape(T, Hq * D)
+
+
+def plain_silu(z: torch.Tensor) -> torch.Tensor:
+    """silu(z) = z / (1 + exp(-z)) (src/ops/kernels.hip:136-138)."""
+    return z / (1.0 + torch.exp(-z))
+
+
+def plain_swiglu_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                     w_down: torch.Tensor) -> torch.Tensor:
+    """down(silu(gate x) * up x), no biases (src/models/model.hip:334-336)."""
+    return (plain_silu(x @ w_gate.T) * (x @ w_up.T)) @ w_down.T
+
+
+def plain_router(x: torch.Tensor, w_router: torch.Tensor, k: int, norm_topk: bool):
+    """Logits, softmax over all experts with the maximum subtracted, the k largest in
+    descending order (src/ops/moe.hip:63-76; ties to the lower index here), weights
+    p_e / sum(selected) when norm_topk (moe.hip:77-82, the only form the reference has)
+    or p_e unchanged (Qwen2-MoE's norm_topk_prob=false)."""
+    logits = x @ w_router.T
+    p = torch.softmax(logits, dim=-1)
+    T, E = p.shape
+    idx = torch.zeros(T, k, dtype=torch.long)
+    wts = torch.zeros(T, k, dtype=x.dtype)
+    for t in range(T):
+        order = sorted(range(E), key=lambda e: (-float(p[t, e]), e))[:k]
+        idx[t] = torch.tensor(order)
+        wts[t] = p[t, order]
+    if norm_topk:
+        wts = wts / wts.sum(dim=-1, keepdim=True)
+    return idx, wts
+
+
+def plain_sparse_ffn(x: torch.Tensor, weights: Dict[str, torch.Tensor], prefix: str, cfg: dict
+                     ) -> torch.Tensor:
+    """Routed experts summed in selection order with their routing weights
+    (src/models/model.hip:355-433), plus the shared expert scaled by the sigmoid of its
+    gate logit (Qwen2-MoE; absent from the reference)."""
+    E, k = cfg["num_experts"], cfg["num_experts_per_tok"]
+    idx, wts = plain_router(x, weights[prefix + "gate.weight"], k, bool(cfg.get("norm_topk_prob", False)))
+    out = torch.zeros_like(x)
+    for t in range(x.shape[0]):
+        for j in range(k):
+            e = int(idx[t, j])
+            q = f"{prefix}experts.{e}."
+            y = plain_swiglu_mlp(x[t:t + 1], weights[q + "gate_proj.weight"],
+                                 weights[q + "up_proj.weight"], weights[q + "down_proj.weight"])
+            out[t] += wts[t, j] * y[0]
+    if cfg.get("shared_expert_intermediate_size", 0):
+        q = prefix + "shared_expert."
+        sh = plain_swiglu_mlp(x, weights[q + "gate_proj.weight"], weights[q + "up_proj.weight"],
+                              weights[q + "down_proj.weight"])
+        gamma = 1.0 / (1.0 + torch.exp(-(x @ weights[prefix + "shared_expert_gate.weight"].T)))
+        out = out + gamma * sh
+    return out
+
+
+def layer_is_sparse(cfg: dict, l: int) -> bool:
+    """Qwen2-MoE's rule; the reference treats every layer of an MoE model as sparse
+    (src/models/model.hip:570)."""
+    return (l not in (cfg.get("mlp_only_layers") or []) and cfg.get("num_experts", 0) > 0
+            and (l + 1) % cfg.get("decoder_sparse_step", 1) == 0)
+
+
+def layer_window(cfg: dict, l: int) -> Optional[int]:
+    if cfg.get("use_sliding_window") and l >= cfg["max_window_layers"]:
+        return int(cfg["sliding_window"])
+    return None
+
+
+# ---- the whole model ------------------------------------------------------------------
+
+def plain_forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int],
+                  dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Logits [T, vocab] of one request's whole token list.
+
+    Layer order as src/models/model.hip:206-444: x1 = norm(h); qkv (+ bias, Qwen2-MoE);
+    rotate q, k; attention; h += o_proj(attn); x2 = norm(h); ffn; h += ffn.  The
+    reference adds the attention output to h a second time on its MoE branch
+    (model.hip:311 and 440-444); that is a defect and is not restated.  Final norm and
+    the head (tied to the embedding when tie_word_embeddings, model.hip:497-499,
+    727-755)."""
+    W = {n: t.to(dtype) for n, t in weights.items()}
+    H = cfg["hidden_size"]
+    Hq = cfg["num_attention_heads"]
+    Hkv = cfg.get("num_key_value_heads", Hq)
+    D = cfg.get("head_dim") or H // Hq
+    eps = cfg.get("rms_norm_eps", 1e-6)
+    inv_freq = plain_inv_freq(D, cfg.get("rope_theta", 1e6))
+    T = len(tokens)
+    pos = torch.arange(T)
+    h = plain_embedding(W["model.embed_tokens.weight"], tokens)
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        x1 = plain_rms_norm(h, W[p + "input_layernorm.weight"], eps)
+        q = x1 @ W[p + "self_attn.q_proj.weight"].T
+        k = x1 @ W[p + "self_attn.k_proj.weight"].T
+        v = x1 @ W[p + "self_attn.v_proj.weight"].T
+        if p + "self_attn.q_proj.bias" in W:
+            q = q + W[p + "self_attn.q_proj.bias"]
+            k = k + W[p + "self_attn.k_proj.bias"]
+            v = v + W[p + "self_attn.v_proj.bias"]
+        q = plain_rope(q.reshape(T, Hq, D), pos, inv_freq)
+        k = plain_rope(k.reshape(T, Hkv, D), pos, inv_freq)
+        a = plain_attention(q, k, v.reshape(T, Hkv, D), layer_window(cfg, l))
+        h = h + a @ W[p + "self_attn.o_proj.weight"].T
+        x2 = plain_rms_norm(h, W[p + "post_attention_layernorm.weight"], eps)
+        if layer_is_sparse(cfg, l):
+            f = plain_sparse_ffn(x2, W, p + "mlp.", cfg)
+        else:
+            f = plain_swiglu_mlp(x2, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
+                                 W[p + "mlp.down_proj.weight"])
+        h = h + f
+    n = plain_rms_norm(h, W["model.norm.weight"], eps)
+    head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else W["lm_head.weight"]
+    return n @ head.T
+
+
+def plain_greedy(cfg: dict, weights: Dict[str, torch.Tensor], prompt: List[int], steps: int,
+                 dtype: torch.dtype = torch.float32) -> List[int]:
+    """Greedy generation by re-running the whole sequence each step: argmax, first maximum
+    (src/runtime/engine.cpp:31-34)."""
+    ids = list(prompt)
+    out = []
+    for _ in range(steps):
+        logits = plain_forward(cfg, weights, ids, dtype)
+        nxt = int(torch.argmax(logits[-1]))
+        out.append(nxt)
+        ids.append(nxt)
+    return out
