@@ -1,0 +1,241 @@
+"""Each CUDA kernel alone against its plain PyTorch twin, at sizes other than the engine's:
+widths that are no power of two, head sizes in steps of 16, odd row counts."""
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_kernels as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return dict(rtol=2e-5, atol=2e-5 * scale) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2 * scale)
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ninfer_amd_mi50_b200 import kernels
+    kernels.load()
+    return kernels
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,T", [(777, 200, 13), (2003, 96, 1)])
+def test_embed_rows(K, dtype, V, H, T):
+    table = rnd((V, H), dtype, 1)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32).cuda()
+    out = torch.empty((T, H), dtype=torch.float32, device="cuda")
+    K.embed_rows(table, ids, out)
+    ref = torch.empty_like(out)
+    P.embed_rows(table, ids, ref)
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H", [(5, 200), (33, 1000), (1, 7168)])
+def test_add_rmsnorm(K, dtype, T, H):
+    h = rnd((T, H), torch.float32, 2)
+    delta = rnd((T, H), dtype, 3)
+    w = 1 + 0.05 * rnd((H,), torch.float32, 4)
+    out = torch.empty((T, H), dtype=dtype, device="cuda")
+    h2, ref = h.clone(), torch.empty_like(out)
+    K.add_rmsnorm(h, delta, w, 1e-5, out)
+    P.add_rmsnorm(h2, delta, w, 1e-5, ref)
+    torch.testing.assert_close(h, h2, rtol=0, atol=0)
+    torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+    # without a delta, and the gathered form that leaves h alone
+    out0, ref0 = torch.empty_like(out), torch.empty_like(out)
+    K.add_rmsnorm(h, None, w, 1e-5, out0)
+    P.add_rmsnorm(h2, None, w, 1e-5, ref0)
+    torch.testing.assert_close(out0.float(), ref0.float(), **tol(dtype))
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32).cuda()
+    outr = torch.empty((3, H), dtype=dtype, device="cuda")
+    refr = torch.empty_like(outr)
+    before = h.clone()
+    K.add_rmsnorm_rows(h, delta, rows, w, 1e-5, outr)
+    P.add_rmsnorm_rows(h2, delta, rows, w, 1e-5, refr)
+    assert torch.equal(h, before)
+    torch.testing.assert_close(outr.float(), refr.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K_", [(1, 200, 200), (37, 300, 72), (130, 65, 1000), (3, 2003, 96)])
+def test_linear(K, dtype, M, N, K_):
+    x, w = rnd((M, K_), dtype, 5), rnd((N, K_), dtype, 6, 0.05)
+    for od in (None, torch.float32):
+        out = K.linear(x, w, out_dtype=od)
+        ref = P.linear(x, w, out_dtype=od)
+        torch.testing.assert_close(out.float(), ref.float(), **tol(out.dtype, 0.5))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,I,K_", [(1, 72, 200), (37, 100, 96), (70, 33, 300)])
+def test_linear_swiglu_and_silu_mul(K, dtype, M, I, K_):
+    x, w = rnd((M, K_), dtype, 7), rnd((2 * I, K_), dtype, 8, 0.1)
+    torch.testing.assert_close(K.linear_swiglu(x, w).float(), P.linear_swiglu(x, w).float(), **tol(dtype))
+    gu = rnd((M, 2 * I), dtype, 9)
+    torch.testing.assert_close(K.silu_mul(gu).float(), P.silu_mul(gu).float(), **tol(dtype))
+
+
+def make_cache_case(dtype, Hq, Hkv, D, page, seg_lens, pos0s, n_pages, seed):
+    """A batch of segments with scattered pages; returns everything the attention ops need."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(seg_lens)
+    width = max((p + n + page - 1) // page for p, n in zip(pos0s, seg_lens))
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    for s, (p0, n) in enumerate(zip(pos0s, seg_lens)):
+        for lp in range((p0 + n + page - 1) // page):
+            bt[s, lp] = perm.pop()
+    pages = (torch.randn((n_pages, 2, Hkv, page, D), generator=g)).to(dtype).cuda()
+    positions, row_seg = [], []
+    for s, (p0, n) in enumerate(zip(pos0s, seg_lens)):
+        positions += list(range(p0, p0 + n))
+        row_seg += [s] * n
+    T = len(positions)
+    ctx = SimpleNamespace(positions=torch.tensor(positions, dtype=torch.int32).cuda(),
+                          row_seg=torch.tensor(row_seg, dtype=torch.int32).cuda())
+    qkv = (torch.randn((T, (Hq + 2 * Hkv) * D), generator=g)).to(dtype).cuda()
+    return pages, bt.cuda(), ctx, qkv
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,page,rot", [(6, 2, 48, 16, 48), (4, 1, 128, 64, 128), (5, 5, 80, 32, 32)])
+def test_rope_append(K, dtype, Hq, Hkv, D, page, rot):
+    pages, bt, ctx, qkv = make_cache_case(dtype, Hq, Hkv, D, page, [5, 1, 19], [0, 77, 30], 12, 11)
+    bias = 0.1 * rnd(((Hq + 2 * Hkv) * D,), torch.float32, 12)
+    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32).cuda()
+    q1, p1 = qkv.clone(), pages.clone()
+    q2, p2 = qkv.clone(), pages.clone()
+    K.rope_append(q1, bias, ctx.positions, ctx.row_seg, inv_freq, rot, Hq, Hkv, D, p1, bt, page, True)
+    P.rope_append(q2, bias, ctx.positions, ctx.row_seg, inv_freq, rot, Hq, Hkv, D, p2, bt, page, True)
+    torch.testing.assert_close(q1[:, :Hq * D].float(), q2[:, :Hq * D].float(), **tol(dtype, 3))
+    torch.testing.assert_close(p1.float(), p2.float(), **tol(dtype, 3))
+    # without appending the cache stays as it was; without a table nothing rotates
+    q3, p3 = qkv.clone(), pages.clone()
+    K.rope_append(q3, None, ctx.positions, ctx.row_seg, None, 0, Hq, Hkv, D, p3, bt, page, False)
+    assert torch.equal(p3, pages) and torch.equal(q3, qkv)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [(6, 2, 48, 16, 0), (4, 1, 128, 64, 0), (4, 4, 64, 16, 21),
+                                                  (8, 2, 256, 32, 0), (3, 1, 16, 16, 40)])
+def test_paged_attention(K, dtype, Hq, Hkv, D, page, window):
+    pages, bt, ctx, qkv = make_cache_case(dtype, Hq, Hkv, D, page, [37, 1, 2, 1], [0, 130, 61, 0], 24, 13)
+    scale = 1 / math.sqrt(D)
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    ref = P.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+
+
+def test_attention_finds_one_far_key(K):
+    """One key among hundreds is made to dominate; the output must be its value row."""
+    Hq, Hkv, D, page = 2, 1, 64, 16
+    for dtype in DTYPES:
+        pages, bt, ctx, qkv = make_cache_case(dtype, Hq, Hkv, D, page, [1], [700], 48, 17)
+        far = 3          # a key in the very first page, 697 positions back
+        qkv[0, :Hq * D] = 0
+        qkv[0, 5] = 8.0
+        qkv[0, D + 5] = 8.0
+        pg = int(bt[0, far // page])
+        pages[:, 0, :, :, 5] = 0
+        pages[pg, 0, 0, far % page, 5] = 40.0
+        out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, 0, 1 / math.sqrt(D))
+        want = pages[pg, 1, 0, far % page].float()
+        for h in range(Hq):
+            torch.testing.assert_close(out[0, h * D:(h + 1) * D].float(), want, rtol=1e-2, atol=1e-2)
+
+
+def test_attention_window_edge(K):
+    """The key just outside the window is made huge: it must not be seen; the one just
+    inside must."""
+    Hq, Hkv, D, page, window = 1, 1, 32, 16, 24
+    pages, bt, ctx, qkv = make_cache_case(torch.float32, Hq, Hkv, D, page, [1], [100], 16, 19)
+    qkv[0, :D] = 0
+    qkv[0, 0] = 10.0
+    pages[:, 0, :, :, 0] = 0
+    outside, inside = 100 - window, 100 - window + 1
+    pages[int(bt[0, outside // page]), 0, 0, outside % page, 0] = 50.0
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, 1.0)
+    ref = P.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, 1.0)
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+    pages[int(bt[0, inside // page]), 0, 0, inside % page, 0] = 50.0
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, 1.0)
+    torch.testing.assert_close(out[0], pages[int(bt[0, inside // page]), 1, 0, inside % page], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,E,k,norm,extra", [(9, 200, 6, 3, True, 1), (64, 96, 60, 4, False, 1),
+                                                (1, 512, 16, 4, True, 0), (5, 1000, 130, 8, False, 1)])
+def test_router_topk(K, dtype, T, H, E, k, norm, extra):
+    x = rnd((T, H), dtype, 21)
+    w = rnd((E + extra, H), torch.float32, 22, 0.1)
+    idx, wts, ext = K.router_topk(x, w, E, k, norm)
+    ridx, rwts, rext = P.router_topk(x, w, E, k, norm)
+    assert torch.equal(idx, ridx)
+    torch.testing.assert_close(wts, rwts, rtol=1e-4, atol=1e-6)
+    if extra:
+        torch.testing.assert_close(ext, rext, rtol=1e-4, atol=1e-5)
+    else:
+        assert ext is None
+
+
+def test_router_ties_go_to_lower_index(K):
+    x = torch.ones((2, 64), dtype=torch.float32, device="cuda")
+    w = torch.zeros((8, 64), dtype=torch.float32, device="cuda")
+    w[5] = 0.01
+    idx, wts, _ = K.router_topk(x, w, 8, 3, False)
+    assert idx.tolist() == [[5, 0, 1], [5, 0, 1]]
+
+
+@pytest.mark.parametrize("T,k,E", [(1, 2, 8), (37, 4, 60), (700, 3, 6), (2048, 4, 60)])
+def test_moe_plan(K, T, k, E):
+    g = torch.Generator().manual_seed(23)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    plan = K.moe_plan(idx, E)
+    ref = P.moe_plan(idx, E)
+    assert torch.equal(plan.offsets, ref.offsets)
+    assert torch.equal(plan.order, ref.order)
+    assert torch.equal(plan.inv, ref.inv)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 200, 72, 6, 3), (50, 96, 100, 16, 4), (130, 256, 33, 8, 2)])
+def test_moe_gemms_and_combine(K, dtype, T, H, I, E, k):
+    g = torch.Generator().manual_seed(29)
+    x = rnd((T, H), dtype, 31)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 32, 0.1), rnd((E, H, I), dtype, 33, 0.1)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    wts = torch.rand((T, k), generator=g).cuda()
+    plan = K.moe_plan(idx, E)
+    act = K.moe_gemm1(x, w13, plan, k)
+    ract = P.moe_gemm1(x, w13, plan, k)
+    torch.testing.assert_close(act.float(), ract.float(), **tol(dtype))
+    y = K.moe_gemm2(ract, w2, plan)
+    ry = P.moe_gemm2(ract, w2, plan)
+    torch.testing.assert_close(y.float(), ry.float(), **tol(dtype))
+    shared, gate = rnd((T, H), dtype, 34), rnd((T, 1), torch.float32, 35)
+    out = K.moe_combine(ry, plan, wts, shared, gate, dtype)
+    rout = P.moe_combine(ry, plan, wts, shared, gate, dtype)
+    torch.testing.assert_close(out.float(), rout.float(), **tol(dtype, 2))
+    out = K.moe_combine(ry, plan, wts, None, None, dtype)
+    rout = P.moe_combine(ry, plan, wts, None, None, dtype)
+    torch.testing.assert_close(out.float(), rout.float(), **tol(dtype, 2))
+
+
+def test_refusals_are_clear(K):
+    with pytest.raises(ValueError, match="head_dim"):
+        K.check_head_dim(40)
+    with pytest.raises(Exception, match="CUDA tensor"):
+        K.linear(torch.zeros(2, 4), torch.zeros(3, 4))

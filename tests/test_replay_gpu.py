@@ -1,0 +1,117 @@
+"""The engine on the GPU, in 32-bit and in bfloat16, under every way of cutting the work,
+against the plain whole-sequence model; then the same through ``bin/trace_run``."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import schedules
+from tiny_configs import CONFIGS, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LENGTHS = [33, 150, 7, 97, 70, 201]
+
+# float32: the engine and the plain model differ by summation order only: 1e-4 of the
+# largest logit (measured: about 1e-6).
+# bfloat16: activations between kernels are rounded to 8 bits of mantissa (unit roundoff
+# 2^-9).  Two kinds of difference from the 32-bit plain model follow.  Rounding proper: a
+# random walk over some twenty roundings, measured at 0.4 % of the largest logit for the
+# worst element of a typical row; bound 1.5 %.  And routing: a rounding of 1e-3 in the router's
+# input swaps the k-th and (k+1)-th expert wherever their probabilities are closer than
+# that, which with 6 to 16 experts happens on about one row in fifty; such a row then carries
+# another expert's output, a few per cent of the largest logit.  So at most one row in ten
+# may pass the rounding bound, and none may pass 10 %: a wrong page, position or mask moves
+# a row by the whole scale and is caught by either limit, as it is at 1e-4 in float32.
+def check(got, want, dtype, what):
+    scale = want.abs().max().item()
+    row_err = (got - want).abs().max(dim=1).values
+    if dtype == "float32":
+        assert row_err.max().item() <= 1e-4 * scale, \
+            f"{what}: max error {row_err.max().item():.3e}, scale {scale:.3f}"
+    else:
+        over = (row_err > 1.5e-2 * scale).sum().item()
+        assert over <= max(1, len(row_err) // 10), \
+            f"{what}: {over} of {len(row_err)} rows beyond 1.5 % of scale {scale:.3f}"
+        assert row_err.max().item() <= 0.1 * scale, \
+            f"{what}: max error {row_err.max().item():.3e}, scale {scale:.3f}"
+    return row_err.median().item() / scale
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def folder(request, tmp_path_factory):
+    from ninfer_amd_mi50_b200.weights import write_random_model
+    cfg, seed = CONFIGS[request.param]
+    d = str(tmp_path_factory.mktemp("model") / request.param)
+    write_random_model(cfg, seed, d)
+    pcfg, weights = plain_model.read_model_folder(d)
+    reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 40 + i) for i, n in enumerate(LENGTHS)}
+    want = {r: plain_model.plain_forward(pcfg, weights, t) for r, t in reqs.items()}
+    return d, cfg, reqs, want
+
+
+def make_runner(d, dtype, tokens):
+    from ninfer_amd_mi50_b200.config import EngineOptions
+    from ninfer_amd_mi50_b200.engine import load_runner
+    return load_runner(d, options=EngineOptions(dtype=dtype, page_size=64, num_sequences=4,
+                                                 max_context=tokens, cache_tokens=tokens, use_graph=False))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("how", ["whole", "tail_decoded", "portions", "mixed"])
+def test_schedule_matches_plain(folder, dtype, how):
+    d, cfg, reqs, want = folder
+    if how == "mixed":
+        steps = schedules.mixed(reqs, page=64, pool_tokens=448)
+        runner = make_runner(d, dtype, 448)
+    else:
+        steps = getattr(schedules, how)(reqs)
+        runner = make_runner(d, dtype, 256)
+    got = schedules.run_schedule(runner, steps)
+    assert runner.cache.pages_free() == [g.pool.num_pages for g in runner.cache.groups]
+    worst = max(check(got[r], want[r], dtype, f"{how} {r}") for r in reqs)
+    print(f"\n[{dtype} {how}] worst error / scale = {worst:.2e}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuts_agree_with_each_other(folder, dtype):
+    """Whole prompts against portions and decoded tails: in 32-bit the same kernels see the
+    same rows, so the logits agree to rounding of the last bits."""
+    d, cfg, reqs, want = folder
+    a = schedules.run_schedule(make_runner(d, dtype, 256), schedules.whole(reqs))
+    b = schedules.run_schedule(make_runner(d, dtype, 256), schedules.portions(reqs))
+    c = schedules.run_schedule(make_runner(d, dtype, 256), schedules.tail_decoded(reqs))
+    for r in reqs:
+        check(b[r], a[r], dtype, f"portions vs whole {r}")
+        check(c[r], a[r], dtype, f"tail vs whole {r}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folder, dtype, tmp_path):
+    d, cfg, reqs, want = folder
+    steps = schedules.mixed(reqs, page=64, pool_tokens=448)
+    out = tmp_path / "out"
+    lines = "".join(json.dumps({"step": i, **st}) + "\n" for i, st in enumerate(steps))
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", "448"], input=lines, capture_output=True,
+                       text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.split() == [x for i in range(len(steps)) for x in ("done", str(i))]
+    V = cfg["vocab_size"]
+    got = {}
+    for i, st in enumerate(steps):
+        n = sum(len(e["want"]) for e in st["entries"])
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(n, V)
+        r = 0
+        for e in st["entries"]:
+            got.setdefault(e["id"], []).append(torch.from_numpy(arr[r:r + len(e["want"])].copy()))
+            r += len(e["want"])
+    for r in reqs:
+        check(torch.cat(got[r]), want[r], dtype, f"trace_run {r}")
