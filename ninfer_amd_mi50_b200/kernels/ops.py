@@ -265,3 +265,44 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optio
               c_int(gate.shape[1] if gate is not None else 0), _p(out), c_int(T), c_int(H), c_int(k),
               c_int(_dt(y)), _stream())
     return out
+
+
+# ---------------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------------
+
+SAMPLE_MAX_TOP_K = 1024
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """First maximum of each row of float32 logits [R, V] -> int32 [R]."""
+    _chk(logits, "logits", torch.float32)
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _lib.call("nf_argmax_rows", _p(logits), c_int(R), c_int(V), _p(out), _stream())
+    return out
+
+
+def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, counts: torch.Tensor,
+                       row_of: torch.Tensor, penalty: torch.Tensor) -> None:
+    """In place: for pair i, logits[row_of[i], ids[i]] is divided (if positive) or multiplied
+    (if not) by penalty[row] `counts[i]` times."""
+    _chk(logits, "logits", torch.float32); _chk(ids, "ids", torch.int32)
+    _chk(counts, "counts", torch.int32); _chk(row_of, "row_of", torch.int32)
+    _chk(penalty, "penalty", torch.float32)
+    _lib.call("nf_repetition_penalty", _p(logits), c_int(logits.shape[1]), _p(ids), _p(counts),
+              _p(row_of), _p(penalty), c_int(ids.numel()), _stream())
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+                top_p: torch.Tensor, draw: torch.Tensor) -> torch.Tensor:
+    """One token per row from softmax(logits / temperature) limited by top-k and top-p,
+    using the uniform draws `draw` in [0, 1).  The caller has checked the parameters."""
+    _chk(logits, "logits", torch.float32); _chk(temperature, "temperature", torch.float32)
+    _chk(top_k, "top_k", torch.int32); _chk(top_p, "top_p", torch.float32)
+    _chk(draw, "draw", torch.float32)
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _lib.call("nf_sample_rows", _p(logits), c_int(R), c_int(V), _p(temperature), _p(top_k),
+              _p(top_p), _p(draw), _p(out), _stream())
+    return out

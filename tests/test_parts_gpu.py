@@ -1,0 +1,143 @@
+"""Each part alone on the GPU against the plain function of the same part, and a toy mixer
+with state of its own that is registered, built and stepped without touching the package."""
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_model as PM
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+def fetcher(tensors, dtype):
+    from ninfer_amd_mi50_b200.weights import held_dtype
+
+    def fetch_for(specs):
+        roles = {s.name: s.role for s in specs}
+        return lambda name: tensors[name].to(device="cuda", dtype=held_dtype(roles[name], dtype))
+    return fetch_for
+
+
+def random_tensors(specs, seed):
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for s in specs:
+        t = torch.randn(s.shape, generator=g)
+        out[s.name] = (1 + 0.05 * t if s.init == "norm" else 0.05 * t).to(torch.bfloat16).float()
+    return out
+
+
+def simple_ctx(dtype, seg_lens, page=16):
+    """Fresh requests (position 0 onwards), pages handed out in reverse order."""
+    T = sum(seg_lens)
+    positions, row_seg = [], []
+    for s, n in enumerate(seg_lens):
+        positions += list(range(n))
+        row_seg += [s] * n
+    width = max((n + page - 1) // page for n in seg_lens)
+    n_pages = sum((n + page - 1) // page for n in seg_lens)
+    bt = torch.full((len(seg_lens), width), -1, dtype=torch.int32)
+    nxt = n_pages - 1
+    for s, n in enumerate(seg_lens):
+        for lp in range((n + page - 1) // page):
+            bt[s, lp] = nxt
+            nxt -= 1
+    from ninfer_amd_mi50_b200.parts.base import StepContext
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    row0 = [0]
+    for n in seg_lens:
+        row0.append(row0[-1] + n)
+    ctx = StepContext(dtype=dtype, device=torch.device("cuda"), T=T, S=len(seg_lens),
+                      token_ids=mk([0] * T), positions=mk(positions), row_seg=mk(row_seg),
+                      seg_row0=mk(row0), seg_pos0=mk([0] * len(seg_lens)),
+                      seg_slot=mk(list(range(len(seg_lens)))), logit_rows=mk([]),
+                      seg_len_host=list(seg_lens), seg_pos0_host=[0] * len(seg_lens),
+                      max_rows_per_seg=max(seg_lens), max_context=max(seg_lens))
+    return ctx, bt.cuda(), n_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rms_norm_part(dtype):
+    from ninfer_amd_mi50_b200.parts.norm import RmsNorm
+    n = RmsNorm(size=200, eps=3e-6, prefix="n.")
+    t = random_tensors(n.tensor_specs(), 1)
+    n.load(fetcher(t, dtype)(n.tensor_specs()))
+    h = torch.randn(9, 200, device="cuda")
+    delta = torch.randn(9, 200, device="cuda").to(dtype)
+    want_h = h + delta.float()
+    out = n.add_norm(h, delta, dtype)
+    torch.testing.assert_close(h, want_h)
+    torch.testing.assert_close(out.float(), PM.plain_rms_norm(want_h.cpu(), t["n.weight"], 3e-6).cuda(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,window,bias", [(6, 2, 48, None, True), (4, 1, 128, 21, False)])
+def test_attention_part(dtype, Hq, Hkv, D, window, bias):
+    from ninfer_amd_mi50_b200.config import PartSpec
+    from ninfer_amd_mi50_b200.parts.attention import PagedGqaAttention
+    from ninfer_amd_mi50_b200.parts.base import CacheView
+    H, theta, page = 200, 50000.0, 16
+    att = PagedGqaAttention(hidden_size=H, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, qkv_bias=bias,
+                            position=PartSpec.make("rotary_half_split", head_dim=D, theta=theta),
+                            prefix="a.", window=window)
+    t = random_tensors(att.tensor_specs(), 2)
+    att.load(fetcher(t, dtype)(att.tensor_specs()))
+    seg_lens = [37, 5]
+    ctx, bt, n_pages = simple_ctx(dtype, seg_lens, page)
+    pages = torch.zeros((n_pages + 1, 2, Hkv, page, D), dtype=dtype, device="cuda")
+    x = torch.randn(sum(seg_lens), H).to(torch.bfloat16).float()
+    out = att.forward(x.cuda().to(dtype), ctx, CacheView(att.cache_spec(), pages, bt, page, True), None)
+    inv = PM.plain_inv_freq(D, theta)
+    r0 = 0
+    for n in seg_lens:
+        xs = x[r0:r0 + n]
+        q, k, v = (xs @ t[f"a.{p}_proj.weight"].T + (t[f"a.{p}_proj.bias"] if bias else 0) for p in "qkv")
+        pos = torch.arange(n)
+        q = PM.plain_rope(q.view(n, Hq, D), pos, inv)
+        k = PM.plain_rope(k.view(n, Hkv, D), pos, inv)
+        want = PM.plain_attention(q, k, v.view(n, Hkv, D), window) @ t["a.o_proj.weight"].T
+        torch.testing.assert_close(out[r0:r0 + n].float().cpu(), want, **tol(dtype))
+        r0 += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_dense_and_sparse_feed_forward_parts(dtype):
+    from ninfer_amd_mi50_b200.parts.feedforward import DenseSwiglu, SparseMoeSwiglu
+    H = 200
+    x = torch.randn(23, H).to(torch.bfloat16).float()
+    ctx = SimpleNamespace()
+    dense = DenseSwiglu(hidden_size=H, intermediate_size=232, prefix="m.")
+    t = random_tensors(dense.tensor_specs(), 3)
+    dense.load(fetcher(t, dtype)(dense.tensor_specs()))
+    want = PM.plain_swiglu_mlp(x, t["m.gate_proj.weight"], t["m.up_proj.weight"], t["m.down_proj.weight"])
+    torch.testing.assert_close(dense.forward(x.cuda().to(dtype), ctx).float().cpu(), want, **tol(dtype))
+    for norm_topk, shared in ((True, 104), (False, 0)):
+        moe = SparseMoeSwiglu(hidden_size=H, num_experts=6, top_k=3, norm_topk_prob=norm_topk,
+                              moe_intermediate_size=72, shared_intermediate_size=shared, prefix="m.")
+        t = random_tensors(moe.tensor_specs(), 4)
+        moe.load(fetcher(t, dtype)(moe.tensor_specs()))
+        cfg = {"num_experts": 6, "num_experts_per_tok": 3, "norm_topk_prob": norm_topk,
+               "shared_expert_intermediate_size": shared}
+        want = PM.plain_sparse_ffn(x, t, "m.", cfg)
+        got = moe.forward(x.cuda().to(dtype), ctx).float().cpu()
+        if dtype == torch.float32:
+            torch.testing.assert_close(got, want, **tol(dtype))
+        else:
+            # a row whose k-th and (k+1)-th experts are within rounding may take the other one
+            bad = ((got - want).abs().max(dim=1).values > 3e-2).sum().item()
+            assert bad <= 2
+
+
+def test_rotary_table_follows_single_precision_pow():
+    from ninfer_amd_mi50_b200.parts.position import rotary_inverse_frequencies
+    for D, theta in ((64, 10000.0), (128, 1e6), (48, 50000.0)):
+        assert torch.equal(rotary_inverse_frequencies(D, theta), PM.plain_inv_freq(D, theta))

@@ -1,0 +1,149 @@
+"""Generality of the parts: a toy architecture defined here - a mixer with per-request state
+of its own, a layer that reads another layer's cache, a layer named twice in the order - is
+registered, written as a random model folder, loaded and stepped under every way of
+cutting the work, without a change to the package's files.  It is no model of anyone's."""
+
+import json
+import math
+import os
+
+import pytest
+import torch
+
+import plain_model as PM
+import schedules
+from tiny_configs import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+TOY = {"architectures": ["ToyStateForCausalLM"], "vocab_size": 301, "hidden_size": 96, "state_size": 40,
+       "num_heads": 3, "num_kv_heads": 1, "head_dim": 32, "intermediate_size": 136, "eps": 2e-6,
+       "theta": 7000.0}
+
+
+@pytest.fixture(scope="module")
+def toy_registered():
+    from ninfer_amd_mi50_b200 import kernels
+    from ninfer_amd_mi50_b200.config import LayerCall, LayerSpec, ModelPlan, PartSpec
+    from ninfer_amd_mi50_b200.parts.base import Mixer, StateSpec, TensorSpec
+    from ninfer_amd_mi50_b200.registry import (register_architecture, register_part,
+                                               unregister_architecture, unregister_part)
+
+    @register_part("mixer", "toy_running_state")
+    class ToyRunningState(Mixer):
+        """s_t = sigmoid(decay) * s_{t-1} + W_in x_t ;  y_t = W_out s_t.  The state lives in the
+        request's slot and is carried from one portion of a prompt to the next."""
+
+        def __init__(self, hidden_size, state_size, prefix):
+            self.H, self.S, self.prefix = hidden_size, state_size, prefix
+
+        def tensor_specs(self):
+            p = self.prefix
+            return [TensorSpec(p + "in_proj.weight", (self.S, self.H)),
+                    TensorSpec(p + "out_proj.weight", (self.H, self.S)),
+                    TensorSpec(p + "decay", (self.S,), role="vector")]
+
+        def load(self, fetch):
+            p = self.prefix
+            self.w_in, self.w_out = fetch(p + "in_proj.weight"), fetch(p + "out_proj.weight")
+            self.decay = fetch(p + "decay")
+
+        def state_spec(self):
+            return StateSpec((self.S,), torch.float32)
+
+        def forward(self, x, ctx, cache, state):
+            assert cache is None and state is not None
+            u = kernels.linear(x, self.w_in, out_dtype=torch.float32)
+            a = torch.sigmoid(self.decay)
+            out = torch.empty_like(u)
+            row = 0
+            for slot, n in zip(ctx.seg_slot.tolist(), ctx.seg_len_host):
+                s = state[slot]
+                for i in range(row, row + n):
+                    s = a * s + u[i]
+                    out[i] = s
+                state[slot] = s
+                row += n
+            return kernels.linear(out.to(x.dtype), self.w_out)
+
+    def build_plan(c):
+        norm = PartSpec.make("rms_norm", size=c["hidden_size"], eps=c["eps"])
+        ffn = PartSpec.make("dense_swiglu", hidden_size=c["hidden_size"], intermediate_size=c["intermediate_size"])
+        att = PartSpec.make("paged_gqa_attention", hidden_size=c["hidden_size"], num_heads=c["num_heads"],
+                            num_kv_heads=c["num_kv_heads"], head_dim=c["head_dim"], qkv_bias=False,
+                            position=PartSpec.make("rotary_half_split", head_dim=c["head_dim"], theta=c["theta"]))
+        toy = PartSpec.make("toy_running_state", hidden_size=c["hidden_size"], state_size=c["state_size"])
+        names = (("norm1", "ln1"), ("mixer", "mix"), ("norm2", "ln2"), ("feed_forward", "ff"))
+        layers = tuple(LayerSpec("pre_norm", norm, m, ffn, prefix=f"toy.l{i}.", names=names)
+                       for i, m in enumerate((toy, att, att)))
+        # layer 2 reads layer 1's cache; layer 1 runs a second time, reading what it wrote
+        order = (LayerCall(0, 0), LayerCall(1, 1, True), LayerCall(2, 1, False), LayerCall(1, 1, False))
+        return ModelPlan(c["vocab_size"], c["hidden_size"], layers, order, norm, True,
+                         embedding_name="toy.embed.weight", final_norm_name="toy.norm.", head_name="toy.head.weight")
+
+    register_architecture("ToyStateForCausalLM", lambda d: d, build_plan)
+    yield
+    unregister_architecture("ToyStateForCausalLM")
+    unregister_part("mixer", "toy_running_state")
+
+
+def toy_plain(cfg, W, tokens):
+    """Whole-sequence restatement of the toy model with the plain model's part functions."""
+    H, Hq, Hkv, D = cfg["hidden_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    T = len(tokens)
+    inv = PM.plain_inv_freq(D, cfg["theta"])
+    pos = torch.arange(T)
+    h = PM.plain_embedding(W["toy.embed.weight"], tokens)
+
+    def ffn(i, x):
+        p = f"toy.l{i}.ff."
+        return PM.plain_swiglu_mlp(x, W[p + "gate_proj.weight"], W[p + "up_proj.weight"], W[p + "down_proj.weight"])
+
+    def attn(i, x, kv=None):
+        p = f"toy.l{i}.mix."
+        q = PM.plain_rope((x @ W[p + "q_proj.weight"].T).view(T, Hq, D), pos, inv)
+        if kv is None:
+            k = PM.plain_rope((x @ W[p + "k_proj.weight"].T).view(T, Hkv, D), pos, inv)
+            kv = (k, (x @ W[p + "v_proj.weight"].T).view(T, Hkv, D))
+        return PM.plain_attention(q, kv[0], kv[1]) @ W[p + "o_proj.weight"].T, kv
+
+    # layer 0: the running state
+    x = PM.plain_rms_norm(h, W["toy.l0.ln1.weight"], cfg["eps"])
+    u = x @ W["toy.l0.mix.in_proj.weight"].T
+    a = torch.sigmoid(W["toy.l0.mix.decay"])
+    s = torch.zeros(cfg["state_size"])
+    ys = []
+    for t in range(T):
+        s = a * s + u[t]
+        ys.append(s)
+    h = h + torch.stack(ys) @ W["toy.l0.mix.out_proj.weight"].T
+    h = h + ffn(0, PM.plain_rms_norm(h, W["toy.l0.ln2.weight"], cfg["eps"]))
+    # layer 1 (writes the cache), layer 2 (reads it), layer 1 again (reads it)
+    kv = None
+    for i in (1, 2, 1):
+        o, kv_new = attn(i, PM.plain_rms_norm(h, W[f"toy.l{i}.ln1.weight"], cfg["eps"]), kv)
+        kv = kv or kv_new
+        h = h + o
+        h = h + ffn(i, PM.plain_rms_norm(h, W[f"toy.l{i}.ln2.weight"], cfg["eps"]))
+    return PM.plain_rms_norm(h, W["toy.norm.weight"], cfg["eps"]) @ W["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_steps_under_every_cut(toy_registered, tmp_path, dtype):
+    from ninfer_amd_mi50_b200.config import EngineOptions
+    from ninfer_amd_mi50_b200.engine import load_runner
+    from ninfer_amd_mi50_b200.weights import write_random_model
+    from test_replay_gpu import check
+    d = str(tmp_path / "toy")
+    write_random_model(TOY, 4, d)
+    cfg, W = PM.read_model_folder(d)
+    reqs = {f"r{i}": random_tokens(n, TOY["vocab_size"], 60 + i) for i, n in enumerate([40, 9, 77, 23, 58])}
+    want = {r: toy_plain(cfg, W, t) for r, t in reqs.items()}
+    for make in (schedules.whole, schedules.portions, lambda r: schedules.mixed(r, page=16, pool_tokens=192)):
+        runner = load_runner(d, options=EngineOptions(dtype=dtype, page_size=16, num_sequences=4,
+                                                       max_context=192, cache_tokens=192, use_graph=False))
+        assert [s is not None for s in runner.model.state_specs()] == [True, False, False]
+        assert len(runner.cache.groups) == 1 and runner.cache.groups[0].slots == [1, 2]
+        got = schedules.run_schedule(runner, make(reqs))
+        for r in reqs:
+            check(got[r], want[r], dtype, f"toy {r}")
