@@ -89,6 +89,7 @@ def pack_step(entries: Sequence[StepEntry], cache: CacheManager, dtype: torch.dt
     for _, _, f in tables:
         flat_all += f
     buf = torch.tensor(flat_all, dtype=torch.int32)
+    host_bytes = buf.numel() * 4
     if device.type == "cuda":
         buf = buf.pin_memory().to(device, non_blocking=True)
     parts = list(torch.split(buf, sizes))
@@ -99,6 +100,7 @@ def pack_step(entries: Sequence[StepEntry], cache: CacheManager, dtype: torch.dt
         seg_len_host=seg_len, seg_pos0_host=seg_pos0,
         max_rows_per_seg=max(seg_len) if seg_len else 0,
         max_context=max((p + n for p, n in zip(seg_pos0, seg_len)), default=0))
+    ctx.scratch["h2d_bytes"] = host_bytes
     for (gi, width, _), t in zip(tables, parts[7:]):
         ctx.block_tables[gi] = t.view(S, width)
     return ctx

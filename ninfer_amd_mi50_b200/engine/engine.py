@@ -32,6 +32,7 @@ class Engine:
         self._ids = itertools.count()
         self._fresh_seed = itertools.count(0x5EED)
         self.requests: Dict[Hashable, Request] = {}
+        self.d2h_bytes = 0
 
     # ---- requests ---------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -71,6 +72,7 @@ class Engine:
                 recent=[s.request.tokens for s in sampling],
                 counters=[len(s.request.generated) for s in sampling])
             tokens = picked.cpu().tolist()
+            self.d2h_bytes += picked.numel() * 4
         return list(done) + self.scheduler.update(batch, tokens)
 
     def run_until_idle(self, max_steps: Optional[int] = None) -> int:
@@ -89,6 +91,11 @@ class Engine:
         ids = [self.submit(p, sp, stop_ids) for p, sp in zip(prompts, params)]
         self.run_until_idle()
         return [list(self.requests[i].generated) for i in ids]
+
+    def io_bytes(self):
+        """(host-to-device, device-to-host) bytes moved by the steps so far: the packed step
+        inputs in, the sampled token ids out."""
+        return self.runner.h2d_bytes, self.d2h_bytes
 
     def stats(self) -> Dict[str, Any]:
         st = self.scheduler.stats

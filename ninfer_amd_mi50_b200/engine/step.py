@@ -25,6 +25,7 @@ class ModelRunner:
         self.model, self.cache, self.dtype = model, cache, dtype
         self.device = torch.device(device)
         self.steps_run = 0
+        self.h2d_bytes = 0
         self.tokens_run = 0
 
     # ---- requests -------------------------------------------------------------------
@@ -64,6 +65,7 @@ class ModelRunner:
         for e in entries:
             self.cache.commit(e.req, self.cache.length(e.req) + len(e.tokens))
         self.steps_run += 1
+        self.h2d_bytes += ctx.scratch.get("h2d_bytes", 0)
         self.tokens_run += ctx.T
         return logits
 

@@ -39,8 +39,24 @@ def load() -> ctypes.CDLL:
     return _lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches made through this library so far (one per successful call)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    """Account for launches made outside `call` (a replayed CUDA graph's kernels)."""
+    global _launches
+    _launches += n
+
+
 def call(name: str, *args) -> None:
+    global _launches
     lib = load()
+    _launches += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.nf_last_error().decode(errors='replace')}")

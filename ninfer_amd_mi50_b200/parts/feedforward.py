@@ -53,6 +53,9 @@ class DenseSwiglu(FeedForward):
 
 @register_part("feed_forward", "sparse_moe_swiglu")
 class SparseMoeSwiglu(FeedForward):
+    # set to a list to collect each call's selected experts (measurement only)
+    record_routing = None
+
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, norm_topk_prob: bool,
                  moe_intermediate_size: int, shared_intermediate_size: int, prefix: str):
         if not 1 <= top_k <= num_experts:
@@ -120,6 +123,8 @@ class SparseMoeSwiglu(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         E, k = self.num_experts, self.top_k
         idx, wts, gate = kernels.router_topk(x, self.w_router, E, k, self.norm_topk_prob)
+        if SparseMoeSwiglu.record_routing is not None:
+            SparseMoeSwiglu.record_routing.append(idx.clone())
         plan = kernels.moe_plan(idx, E)
         act = kernels.moe_gemm1(x, self.w13, plan, k)
         y = kernels.moe_gemm2(act, self.w2, plan)

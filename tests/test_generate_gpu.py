@@ -104,19 +104,24 @@ def test_greedy_generation_through_the_entry_point(folders, name):
 
 
 def test_temperature_generation_is_seeded_and_independent_of_batching(folders):
+    """Same seed, same tokens: whatever the batch, the portions, or a pool so small that a
+    request is preempted and recomputed."""
     from ninfer_amd_mi50_b200.api import Ninfer
     d, cfg, _, _ = folders["B"]
-    prompts = [random_tokens(n, cfg["vocab_size"], 80 + n) for n in (1, 5, 40, 97)]
+    prompts = [random_tokens(n, cfg["vocab_size"], 80 + n) for n in (14, 15, 30, 31)]
     runs = []
-    for nseq, chunk, pool in ((4, 16, None), (2, 64, None), (4, 16, 256)):
-        eng = Ninfer(d, max_context=128, prefill_chunk=chunk, num_sequences=nseq, dtype="float32",
-                     cache_tokens=pool)
+    for nseq, chunk, page, pool in ((4, 16, 64, None), (2, 64, 64, None), (4, 16, 16, 96)):
+        eng = Ninfer(d, max_context=64, prefill_chunk=chunk, num_sequences=nseq, dtype="float32",
+                     page_size=page, cache_tokens=pool)
         runs.append(eng.generate(prompts, max_new_tokens=12, temperature=0.8, seed=99))
         if pool:
-            assert eng.stats()["preemptions"] >= 1
+            assert eng.stats()["preemptions"] >= 1 and eng.stats()["out_of_cache"] == 0
         eng.close()
     assert runs[0] == runs[1] == runs[2]
     assert all(len(r) == 12 for r in runs[0])
+    eng = Ninfer(d, max_context=64, num_sequences=4, dtype="float32")
+    assert eng.generate(prompts, max_new_tokens=12, temperature=0.8, seed=100) != runs[0]
+    eng.close()
 
 
 def test_sessions_prefill_decode_and_decode_batch(folders):
