@@ -177,8 +177,10 @@ def main() -> int:
         from ninfer_amd_mi50_b200.parts.feedforward import SparseMoeSwiglu
         ids = open_synthetic(batch, PROMPT)
         SparseMoeSwiglu.record_routing = []
+        graphs, runner.graphs = runner.graphs, None      # routing is recorded by the host-driven step
         runner.step([StepEntry(r, [int(torch.randint(0, V, (1,), generator=g))], [0]) for r in ids])
         torch.cuda.synchronize()
+        runner.graphs = graphs
         routed = SparseMoeSwiglu.record_routing
         SparseMoeSwiglu.record_routing = None
         total = model.head.numel() * model.head.element_size() + batch * model.hidden_size * 2  # head, embedding rows

@@ -89,9 +89,14 @@ class CacheManager:
         if allocate:
             for layer, sp in enumerate(self.state_specs):
                 if sp is not None:
-                    self.state[layer] = torch.zeros((self.max_requests, *sp.shape), dtype=sp.dtype,
+                    # one slot more than requests: padding rows of a replayed graph use the last
+                    self.state[layer] = torch.zeros((self.max_requests + 1, *sp.shape), dtype=sp.dtype,
                                                     device=self.device)
         self.requests: Dict[Hashable, RequestEntry] = {}
+
+    @property
+    def null_slot(self) -> int:
+        return self.max_requests
 
     # ---- sizes ---------------------------------------------------------------------
     def bytes_per_token(self) -> int:

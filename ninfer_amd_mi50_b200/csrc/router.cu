@@ -130,10 +130,12 @@ extern "C" int nf_router_topk(const void* x, const float* wr, int T, int hidden,
   const size_t smem = (size_t)(hidden + E + extra) * sizeof(float);
   NF_REQUIRE(smem <= 200 * 1024, "router: hidden=%d with %d experts needs %zu bytes of shared memory (limit 200 KiB)", hidden, E, smem);
   if (dtype == kF32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t allowed = 48 * 1024;      // raised once per size, outside any stream capture
+    if (smem > allowed) { cudaFuncSetAttribute(router_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
     router_topk_kernel<float><<<T, 128, smem, stream>>>((const float*)x, wr, hidden, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(router_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) { cudaFuncSetAttribute(router_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
     router_topk_kernel<__nv_bfloat16><<<T, 128, smem, stream>>>((const __nv_bfloat16*)x, wr, hidden, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
   }
   return check_launch("router_topk");

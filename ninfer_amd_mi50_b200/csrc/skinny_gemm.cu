@@ -1,0 +1,204 @@
+// Y = X W^T for few rows of X (decode batches): a weight-streaming kernel whose time is the
+// time to read W once.
+//
+// Reference counterparts: ``gemv_kernel_vec8`` (one block per output row, 16-byte loads,
+// float32 accumulation, src/ops/gemv.hip:52-93), ``gemv_fused_kernel<SWIGLU>`` (gate and up
+// rows with the activation in the epilogue, gemv.hip:103-166) and the per-expert GEMV loop of
+// the MoE branch (src/models/model.hip:355-427).  Those serve one row; a batch of decode
+// tokens would read the weights once per row.  Here the weights are the M operand of
+// ``mma.sync.m16n8k16`` (16 output features a tile) and up to 64 rows of X are the N operand,
+// so every weight is read once for the whole batch, and one launch serves all experts.
+//
+// Fragment trick: a lane loads 16 contiguous bytes (8 bf16) of a weight row and 16 bytes of
+// an X row at the same k offset and feeds them to two MMAs as if they were the scattered
+// k columns the instruction expects.  A dot product does not care in which order k is
+// summed as long as both operands agree, so no shuffle or shared-memory staging is needed.
+//
+// Work split: a CTA owns 16 features (8 gate + 8 up with the SwiGLU epilogue) of one
+// group; its 8 warps take interleaved 32-wide chunks of k and their partial sums are added
+// in warp order in shared memory.  The order of summation depends on K only, so a row's
+// result does not depend on the batch it is in.
+#include "common.cuh"
+
+namespace nf {
+
+constexpr int kWarps = 8;
+constexpr int kUnroll = 4;      // chunks of k in flight per warp
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NT: number of 8-row tiles of X a CTA covers (rows <= 8 * NT).
+template <int NT, bool SWIGLU, typename TC>
+__global__ void __launch_bounds__(kWarps * 32)
+skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
+                   size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
+                   const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div) {
+  // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
+  __shared__ float partial[kWarps][NT * 4 * 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = blockIdx.z;
+  int row_begin = 0, row_end = M;
+  if (offsets) { row_begin = offsets[group]; row_end = offsets[group + 1]; }
+  const int m0 = row_begin + blockIdx.y * (8 * NT);
+  if (m0 >= row_end) return;
+  const int rows = min(8 * NT, row_end - m0);
+  const int ntiles = (rows + 7) >> 3;
+  constexpr int FEAT = SWIGLU ? 8 : 16;
+  const int n0 = blockIdx.x * FEAT;
+  const __nv_bfloat16* Wg = W + (size_t)group * w_group_stride;
+
+  // weight rows of this lane: tile row g and tile row g + 8
+  int wr0, wr1;
+  if (SWIGLU) {
+    const int f = min(n0 + g, N - 1);
+    wr0 = f;            // gate
+    wr1 = N + f;        // up
+  } else {
+    wr0 = min(n0 + g, N - 1);
+    wr1 = min(n0 + g + 8, N - 1);
+  }
+  const __nv_bfloat16* w0 = Wg + (size_t)wr0 * K + 8 * t;
+  const __nv_bfloat16* w1 = Wg + (size_t)wr1 * K + 8 * t;
+
+  // X rows of this lane: row g of every 8-row tile
+  const __nv_bfloat16* xp[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int r = m0 + nt * 8 + g;
+    long src = -1;
+    if (r < row_end) src = x_rows ? (long)(x_rows[r] / x_div) : (long)r;
+    xp[nt] = src >= 0 ? X + src * (long)ldx + 8 * t : nullptr;
+  }
+
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+
+  const int nchunks = (K + 31) >> 5;
+  for (int c0 = warp; c0 < nchunks; c0 += kWarps * kUnroll) {
+    uint4 a[kUnroll], b[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = (c0 + u * kWarps) * 32;
+      if (k + 8 * t + 8 <= K && c0 + u * kWarps < nchunks) {
+        a[u] = ld_stream(w0 + k);
+        b[u] = ld_stream(w1 + k);
+      } else {
+        a[u] = make_uint4(0, 0, 0, 0);
+        b[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = (c0 + u * kWarps) * 32;
+      const bool in = k + 8 * t + 8 <= K && c0 + u * kWarps < nchunks;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        if (nt < ntiles) {
+          uint4 x = make_uint4(0, 0, 0, 0);
+          if (in && xp[nt]) x = ld_cached(xp[nt] + k);
+          mma_bf16(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
+          mma_bf16(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+        }
+      }
+    }
+  }
+
+  // add the warps' partial sums in warp order
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) partial[warp][(nt * 4 + i) * 32 + lane] = acc[nt][i];
+  __syncthreads();
+  for (int e = threadIdx.x; e < ntiles * 2 * 32; e += blockDim.x) {
+    // e -> (tile nt, column half h of the fragment, lane l); this thread owns fragment
+    // entries (c[h], c[h + 2]) = (row g, row g + 8) of token column 2 t + h
+    const int l = e & 31, h = (e >> 5) & 1, nt = e >> 6;
+    float lo = 0.f, hi = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      lo += partial[w][(nt * 4 + h) * 32 + l];
+      hi += partial[w][(nt * 4 + h + 2) * 32 + l];
+    }
+    const int gg = l >> 2, tt = l & 3;
+    const int row = m0 + nt * 8 + 2 * tt + h;          // token (sorted position) of this column
+    if (row >= row_end) continue;
+    if (SWIGLU) {
+      const int f = n0 + gg;
+      if (f < N) Y[(size_t)row * ldy + f] = from_float<TC>(lo / (1.f + expf(-lo)) * hi);
+    } else {
+      const int f0 = n0 + gg, f1 = n0 + gg + 8;
+      if (f0 < N) Y[(size_t)row * ldy + f0] = from_float<TC>(lo);
+      if (f1 < N) Y[(size_t)row * ldy + f1] = from_float<TC>(hi);
+    }
+  }
+}
+
+template <int NT, bool SWIGLU, typename TC>
+static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M, int N,
+                     int K, int groups, int max_rows, const int* offsets, const int* x_rows, int x_div,
+                     cudaStream_t stream) {
+  const int feat = SWIGLU ? 8 : 16;
+  dim3 grid((N + feat - 1) / feat, (max_rows + 8 * NT - 1) / (8 * NT), groups);
+  NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many row tiles or groups");
+  skinny_gemm_kernel<NT, SWIGLU, TC><<<grid, kWarps * 32, 0, stream>>>(
+      (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows, x_div);
+  return check_launch("skinny_gemm");
+}
+
+template <bool SWIGLU, typename TC>
+static int launch_sw(int nt, const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M,
+                     int N, int K, int groups, int max_rows, const int* offsets, const int* x_rows,
+                     int x_div, cudaStream_t stream) {
+  switch (nt) {
+    case 1: return launch_nt<1, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    case 2: return launch_nt<2, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    case 4: return launch_nt<4, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    default: return launch_nt<8, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  }
+}
+
+}  // namespace nf
+
+using namespace nf;
+
+// Y[M, N] = epilogue(X[M, K] W[g]^T), bfloat16 inputs, float32 accumulation.
+// out_dtype: 1 bfloat16, 0 float32.  max_rows: bound on the rows of any one group.
+// Needs K % 8 == 0 and 16-byte aligned rows (ldx % 8 == 0, bases aligned).
+extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w_group_stride, void* Y,
+                              int ldy, int M, int N, int K, int groups, int max_rows,
+                              const int* offsets, const int* x_rows, int x_div, int swiglu,
+                              int out_dtype, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && x_div > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+  NF_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "skinny_gemm: K=%d and the row stride %d must be multiples of 8", K, ldx);
+  NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && (w_group_stride % 8 == 0),
+             "skinny_gemm: operands must be 16-byte aligned");
+  NF_REQUIRE(groups == 1 || offsets, "skinny_gemm: grouped product needs row offsets");
+  const int nt = max_rows <= 8 ? 1 : max_rows <= 16 ? 2 : max_rows <= 32 ? 4 : 8;
+  const size_t wgs = (size_t)w_group_stride;
+  if (swiglu) {
+    NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");
+    return launch_sw<true, __nv_bfloat16>(nt, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  }
+  if (out_dtype == kBF16)
+    return launch_sw<false, __nv_bfloat16>(nt, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  return launch_sw<false, float>(nt, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+}

@@ -51,7 +51,7 @@ def load_runner(model_dir: Optional[str] = None, *, config: Optional[Dict[str, A
     cache = CacheManager(model.cache_specs(), model.state_specs(), page_size=options.page_size,
                          num_pages=options.num_pages, max_requests=options.num_sequences,
                          max_context=options.max_context, dtype=dtype, device=device)
-    runner = ModelRunner(model, cache, dtype, device)
+    runner = ModelRunner(model, cache, dtype, device, use_graph=options.use_graph)
     runner.config = typed
     runner.options = options
     log.info(f"ready: weights {model.weight_bytes() / 2**20:.1f} MiB, cache "

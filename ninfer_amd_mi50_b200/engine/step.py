@@ -21,9 +21,14 @@ from .batch import BatchError, StepEntry, pack_step, validate_entries
 
 
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, dtype: torch.dtype, device):
+    def __init__(self, model: DecoderModel, cache: CacheManager, dtype: torch.dtype, device,
+                 use_graph: bool = False):
         self.model, self.cache, self.dtype = model, cache, dtype
         self.device = torch.device(device)
+        self.graphs = None
+        if use_graph and self.device.type == "cuda" and model.graph_safe:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self, cache.max_requests)
         self.steps_run = 0
         self.h2d_bytes = 0
         self.tokens_run = 0
@@ -56,8 +61,11 @@ class ModelRunner:
         validate_entries(entries, self.cache, self.model.vocab_size)
         self.reserve(entries)
         try:
-            ctx = pack_step(entries, self.cache, self.dtype, self.device)
-            logits = self.run(ctx)
+            if self.graphs is not None and self.graphs.eligible(entries):
+                logits, moved = self._step_from_graph(entries)
+            else:
+                ctx = pack_step(entries, self.cache, self.dtype, self.device)
+                logits, moved = self.run(ctx), ctx.scratch.get("h2d_bytes", 0)
         except Exception:
             for e in entries:
                 self.cache.truncate(e.req)
@@ -65,9 +73,21 @@ class ModelRunner:
         for e in entries:
             self.cache.commit(e.req, self.cache.length(e.req) + len(e.tokens))
         self.steps_run += 1
-        self.h2d_bytes += ctx.scratch.get("h2d_bytes", 0)
-        self.tokens_run += ctx.T
+        self.h2d_bytes += moved
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
+
+    def _step_from_graph(self, entries: Sequence[StepEntry]):
+        """A decode-only step: replay the captured graph for this many rows."""
+        g = self.graphs.get(entries)
+        logits = g.run(entries)
+        n = len(entries)
+        if all(len(e.want) == 1 for e in entries):
+            return logits[:n], g.h2d_bytes
+        rows = [i for i, e in enumerate(entries) for _ in e.want]
+        if not rows:
+            return logits[:0], g.h2d_bytes
+        return logits.index_select(0, torch.tensor(rows, device=self.device)), g.h2d_bytes
 
     def run(self, ctx) -> torch.Tensor:
         cache = self.cache

@@ -20,6 +20,11 @@ c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_vo
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
+# Library products of the bfloat16 path must add up in float32: no split-k partial sums
+# rounded to bfloat16, and never TF32 for float32 operands.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+torch.backends.cuda.matmul.allow_tf32 = False
+
 # Tunables that tests may override to force a particular kernel.
 TUNING = {
     "bf16_linear": "auto",        # "simt" | "auto"
@@ -29,6 +34,8 @@ TUNING = {
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
+DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)   # head sizes of the split-key decode kernel
+DECODE_SPLIT = 128                          # keys per block of that kernel
 MAX_EXPERTS = 8192
 
 
@@ -123,6 +130,22 @@ def _gemm_simt(a, lda, b, b_group_stride, c, M, N, K, groups, max_rows, offsets,
               c_int(_dt(c)), _stream())
 
 
+def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu) -> None:
+    _lib.call("nf_skinny_gemm", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
+              c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
+              _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
+              _stream())
+
+
+def _bf16_path(rows: int, K: int, key: str) -> str:
+    """Which bfloat16 product serves `rows` rows: decided by the row count and K only."""
+    if TUNING[key] == "simt":
+        return "simt"
+    if rows <= TUNING["skinny_max_rows"] and K % 8 == 0:
+        return "skinny"
+    return "large"
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x [M, K] times w [N, K] transposed -> [M, N]; float32 accumulation."""
     _chk(x, "x"); _chk(w, "w", x.dtype)
@@ -130,10 +153,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if w.shape[1] != K:
         raise ValueError(f"linear: x has {K} columns, w has {w.shape[1]}")
-    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    out_dtype = out_dtype or x.dtype
     if M == 0:
-        return out
-    _gemm_simt(x, K, w, 0, out, M, N, K, 1, M, None, None, 1, False)
+        return torch.empty((M, N), dtype=out_dtype, device=x.device)
+    path = "simt" if x.dtype == torch.float32 else _bf16_path(M, K, "bf16_linear")
+    if path == "large":
+        # a plain library product, as the reference uses rocBLAS for M > 1 (src/ops/linear.hip)
+        if out_dtype == torch.bfloat16:
+            return torch.mm(x, w.t())
+        try:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            path = "simt"
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if path == "skinny":
+        _skinny(x, K, w, 0, out, M, N, K, 1, M, None, None, 1, False)
+    else:
+        _gemm_simt(x, K, w, 0, out, M, N, K, 1, M, None, None, 1, False)
     return out
 
 
@@ -142,10 +178,16 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     _chk(x, "x"); _chk(w_gate_up, "w_gate_up", x.dtype)
     M, K = x.shape
     inner = w_gate_up.shape[0] // 2
-    out = torch.empty((M, inner), dtype=x.dtype, device=x.device)
     if M == 0:
-        return out
-    _gemm_simt(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True)
+        return torch.empty((M, inner), dtype=x.dtype, device=x.device)
+    path = "simt" if x.dtype == torch.float32 else _bf16_path(M, K, "bf16_linear")
+    if path == "large":
+        return silu_mul(torch.mm(x, w_gate_up.t()))
+    out = torch.empty((M, inner), dtype=x.dtype, device=x.device)
+    if path == "skinny":
+        _skinny(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True)
+    else:
+        _gemm_simt(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True)
     return out
 
 
@@ -176,10 +218,25 @@ def rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torc
 def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.Tensor,
                     block_table: torch.Tensor, page_size: int, ctx, window: int, scale: float
                     ) -> torch.Tensor:
-    """Causal attention of the rows' (rotated) queries in `qkv` over the cache -> [T, Hq*D]."""
+    """Causal attention of the rows' (rotated) queries in `qkv` over the cache -> [T, Hq*D].
+
+    bfloat16 steps in which every request brings one row use the split-key decode kernel;
+    everything else uses the kernel that takes any mix of rows."""
     _chk(qkv, "qkv"); _chk(pages, "pages", qkv.dtype)
     T = qkv.shape[0]
     out = torch.empty((T, Hq * D), dtype=qkv.dtype, device=qkv.device)
+    if T == 0:
+        return out
+    if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
+            and getattr(ctx, "all_single", False) and D in DECODE_HEAD_DIMS):
+        nsplit = max(1, (int(ctx.max_context) + DECODE_SPLIT - 1) // DECODE_SPLIT)
+        ws_acc = torch.empty((T, Hq, nsplit, D), dtype=torch.float32, device=qkv.device)
+        ws_ml = torch.empty((T, Hq, nsplit, 2), dtype=torch.float32, device=qkv.device)
+        _lib.call("nf_decode_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+                  c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
+                  _p(ws_acc), _p(ws_ml), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                  c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
+        return out
     _lib.call("nf_paged_attention_generic", _p(qkv), c_int(qkv.shape[1]), _p(pages),
               _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg),
               _p(out), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
@@ -238,7 +295,11 @@ def moe_gemm1(x: torch.Tensor, w13: torch.Tensor, plan: MoePlan, k: int) -> torc
     act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
     if T == 0:
         return act
-    _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
+    path = "simt" if x.dtype == torch.float32 else _bf16_path(T, H, "bf16_moe")
+    if path == "skinny":
+        _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
+    else:
+        _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
     return act
 
 
@@ -250,7 +311,11 @@ def moe_gemm2(act: torch.Tensor, w2: torch.Tensor, plan: MoePlan) -> torch.Tenso
     y = torch.empty((n, H), dtype=act.dtype, device=act.device)
     if n == 0:
         return y
-    _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
+    path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
+    if path == "skinny":
+        _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
+    else:
+        _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
     return y
 
 

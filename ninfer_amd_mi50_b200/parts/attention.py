@@ -25,6 +25,8 @@ from .base import CacheSpec, CacheView, Fetch, Mixer, StepContext, TensorSpec
 
 @register_part("mixer", "paged_gqa_attention")
 class PagedGqaAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, prefix: str,
                  window: Optional[int] = None):

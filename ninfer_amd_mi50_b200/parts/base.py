@@ -149,6 +149,10 @@ class StepContext:
 class Part:
     """Common to all parts: which tensors it needs and how it takes them."""
 
+    # True if `forward` only launches work on the current stream from device-side data
+    # (no host reads of the step's contents), so that a step may be captured in a CUDA graph.
+    graph_safe = False
+
     def tensor_specs(self) -> List[TensorSpec]:
         return []
 

@@ -25,6 +25,10 @@ class PreNormBlock(Block):
     def parts(self):
         return (self.norm1, self.mixer, self.norm2, self.feed_forward)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.parts())
+
     def tensor_specs(self) -> List[TensorSpec]:
         return [s for p in self.parts() for s in p.tensor_specs()]
 

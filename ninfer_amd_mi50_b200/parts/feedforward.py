@@ -27,6 +27,8 @@ from .base import FeedForward, Fetch, StepContext, TensorSpec
 
 @register_part("feed_forward", "dense_swiglu")
 class DenseSwiglu(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.prefix = prefix
@@ -53,6 +55,8 @@ class DenseSwiglu(FeedForward):
 
 @register_part("feed_forward", "sparse_moe_swiglu")
 class SparseMoeSwiglu(FeedForward):
+    graph_safe = True
+
     # set to a list to collect each call's selected experts (measurement only)
     record_routing = None
 

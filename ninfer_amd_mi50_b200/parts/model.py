@@ -64,6 +64,10 @@ class DecoderModel:
     def state_specs(self) -> List[Optional[StateSpec]]:
         return [b.mixer.state_spec() for b in self.blocks]
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
     def weight_bytes(self) -> int:
         n = sum(b.weight_bytes() for b in self.blocks) + self.final_norm.weight_bytes()
         return n + self.head.numel() * self.head.element_size()

@@ -20,6 +20,8 @@ from .base import Fetch, Norm, TensorSpec
 
 @register_part("norm", "rms_norm")
 class RmsNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float, prefix: str):
         self.size, self.eps, self.prefix = int(size), float(eps), prefix
         self.weight: Optional[torch.Tensor] = None

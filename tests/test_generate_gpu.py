@@ -168,3 +168,31 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     got = schedules.run_schedule(runner, schedules.tail_decoded({"r": toks}, tail=330))["r"]
     check(got, want, dtype, "long decode")
     check(got[:3], want[:3], dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_host_driven_steps(folders, dtype):
+    """Decode-only steps are replayed from CUDA graphs, with padding rows when the number of
+    live requests is not one a graph was built for; the logits must be those of the same
+    step driven from the host."""
+    from ninfer_amd_mi50_b200.api import Ninfer
+    d, cfg, _, _ = folders["A"]
+    outs = []
+    for use_graph in (False, True):
+        eng = Ninfer(d, max_context=256, prefill_chunk=32, num_sequences=12, dtype=dtype, use_graph=use_graph)
+        assert (eng._runner.graphs is not None) == use_graph
+        sessions = [eng.session() for _ in range(11)]
+        for i, s in enumerate(sessions):
+            s.prefill(random_tokens(3 + 7 * i, 1024, 90 + i))
+        logs = []
+        for step in range(5):
+            live = sessions[:11 - 2 * step]            # 11, 9, 7, 5, 3 rows: padded and exact graphs
+            logs.append(torch.from_numpy(eng.decode_batch(live, [(5 * step + j) % 1024 for j in range(len(live))])))
+        outs.append(logs)
+        if use_graph:
+            assert sorted(k[0] for k in eng._runner.graphs.graphs) == [3, 5, 7, 16]
+        for s in sessions:
+            s.close()
+        eng.close()
+    for a, b in zip(*outs):
+        torch.testing.assert_close(a, b, rtol=0, atol=0)
