@@ -17,10 +17,43 @@
 namespace nf {
 
 constexpr int kSplit = 128;        // keys per CTA
-constexpr int kHeadChunk = 4;      // query heads of a group handled per pass over the keys
-constexpr int kU = 4;              // key rows in flight per lane
 
-// Workspace layout per (row, q head, split): D floats of acc, then (m, l) in a separate array.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Workspace per (row, q head, split): D floats of unnormalised output, and (m, l) apart.
+// The CTA first asks for all of its keys and values (asynchronous copies into shared
+// memory, so that all 2 * 128 * D * 2 bytes are in flight at once).  Scores and the
+// weighted sum of values are tensor-core products with the keys (values) as the 16-row
+// operand and up to 8 query heads of the group as the 8-column operand; softmax stays in
+// float32 in between.  Warp w owns keys [32 w, 32 w + 32) of the block.
 template <int D>
 __global__ void __launch_bounds__(128)
 decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
@@ -29,16 +62,22 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
                               const int* __restrict__ positions, const int* __restrict__ row_seg,
                               float* __restrict__ ws_acc, float* __restrict__ ws_ml, int Hq, int Hkv,
                               int page_size, int num_pages, int window, float scale, int nsplit) {
-  constexpr int LPR = D / 8;            // lanes that cover one key row with 16-byte loads
-  constexpr int RPL = 32 / LPR;         // key rows per warp-wide load
-  extern __shared__ float smem[];
+  constexpr int LPR = D / 8;            // 16-byte pieces of one key row
+  constexpr int RPL = 32 / LPR;         // key rows a warp copies at once
+  constexpr int DS = D + 8;             // shared-memory row stride: 16 bytes of padding keep
+                                        // ldmatrix free of bank conflicts
+  constexpr int HC = 8;                 // query heads per tensor-core pass
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   const int G = Hq / Hkv;
-  float* qs = smem;                     // [G][D]
-  float* sc = qs + G * D;               // [G][kSplit]
-  float* red = sc + G * kSplit;         // [4 warps][kHeadChunk][D] partial outputs
-  float* ml = red + 4 * kHeadChunk * D; // [G][2]
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [kSplit][DS]
+  __nv_bfloat16* Vs = Ks + kSplit * DS;                             // [kSplit][DS]
+  float* sc = reinterpret_cast<float*>(Vs + kSplit * DS);           // [G][kSplit] scores, then p
+  const int RH = min(G, HC);                                        // heads kept per pass
+  float* red = sc + G * kSplit;                                     // [4 warps][RH][D]
+  float* ml = red + 4 * RH * D;                                     // [G][2]
   const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
   const int pos = positions[t];
   int lo = 0;
   if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
@@ -50,56 +89,82 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int* bt = block_table + (size_t)seg * bt_width;
   const size_t head_stride = (size_t)page_size * D;
   const size_t page_stride = (size_t)2 * Hkv * head_stride;
-
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int h = i / D, d = i - h * D;
-    qs[i] = __bfloat162float(qkv[(size_t)t * q_row_stride + (size_t)(kvh * G + h) * D + d]);
-  }
-  __syncthreads();
-
+  const int n0 = k_begin - k_base, n1 = k_end - k_base;
   const int sub = lane / LPR, li = lane % LPR;
 
-  // ---- scores -------------------------------------------------------------------------
-  for (int h0 = 0; h0 < G; h0 += kHeadChunk) {
-    const int nh = min(kHeadChunk, G - h0);
-    for (int j0 = k_begin + warp * RPL; j0 < k_end; j0 += 4 * RPL * kU) {
-      float kk[kU][8];
+  // ---- ask for keys, then values; rows outside the key range become zeros --------------------
+  // Lane l looks up the page of row 32 w + l once; the copy loop fetches each row's address
+  // from the lane that knows it.
+  {
+    const int myrow = warp * 32 + lane;
+    const __nv_bfloat16* my_src = nullptr;
+    if (myrow >= n0 && myrow < n1) {
+      const int j = k_base + myrow;
+      const int lp = j / page_size;
+      const int page = lp < bt_width ? bt[lp] : -1;
+      if (page >= 0 && page < num_pages)
+        my_src = pages + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(j - lp * page_size) * D;
+    }
+    const size_t v_off = (size_t)Hkv * head_stride;
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int j = j0 + u * 4 * RPL + sub;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kk[u][e] = 0.f;
-        if (j < k_end) {
-          const int lp = j / page_size;
-          const int page = lp < bt_width ? bt[lp] : -1;
-          if (page >= 0 && page < num_pages)
-            load8(pages + (size_t)page * page_stride + (size_t)kvh * head_stride +
-                  (size_t)(j % page_size) * D + li * 8, kk[u]);
+    for (int kv = 0; kv < 2; ++kv) {
+      __nv_bfloat16* dst = kv ? Vs : Ks;
+#pragma unroll 4
+      for (int it = 0; it < 32 / RPL; ++it) {
+        const int rl = it * RPL + sub;
+        const unsigned long long src = __shfl_sync(0xffffffffu, (unsigned long long)my_src, rl);
+        const int r = warp * 32 + rl;
+        if (rl < 32) {
+          if (src) cp_async16(dst + r * DS + li * 8, reinterpret_cast<const __nv_bfloat16*>(src) + (kv ? v_off : 0) + li * 8);
+          else *reinterpret_cast<uint4*>(dst + r * DS + li * 8) = make_uint4(0, 0, 0, 0);
         }
       }
+      cp_async_commit();
+    }
+  }
+  for (int i = threadIdx.x; i < G * kSplit; i += blockDim.x) sc[i] = 0.f;
+  cp_async_wait<1>();          // keys have landed (values may still be on their way)
+  __syncthreads();
+
+  const __nv_bfloat16* qrow = qkv + (size_t)t * q_row_stride + (size_t)kvh * G * D;
+
+  // ---- scores = K q^T: [32 keys of the warp] x [8 heads] per pass ---------------------------
+  for (int h0 = 0; h0 < G; h0 += HC) {
+    float c[2][4];
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int j = j0 + u * 4 * RPL + sub;
-        const bool valid = j < k_end;
+    for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int hh = 0; hh < kHeadChunk; ++hh) {
-          if (hh < nh) {
-            const float* qh = qs + (h0 + hh) * D + li * 8;
-            float dot = 0.f;
+      for (int i = 0; i < 4; ++i) c[m][i] = 0.f;
+    const bool head_ok = h0 + g < G;
+    const __nv_bfloat16* qh = qrow + (size_t)(h0 + g) * D;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) dot = fmaf(qh[e], kk[u][e], dot);
+    for (int k0 = 0; k0 < D; k0 += 16) {
+      unsigned b0 = 0, b1 = 0;
+      if (head_ok) {
+        b0 = *reinterpret_cast<const unsigned*>(qh + k0 + 2 * tq);
+        b1 = *reinterpret_cast<const unsigned*>(qh + k0 + 2 * tq + 8);
+      }
 #pragma unroll
-            for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            if (valid && li == 0) sc[(h0 + hh) * kSplit + (j - k_base)] = dot * scale;
-          }
-        }
+      for (int m = 0; m < 2; ++m) {
+        unsigned a0, a1, a2, a3;
+        const int row = warp * 32 + m * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(a0, a1, a2, a3, Ks + row * DS + k0 + (lane >> 4) * 8);
+        mma16816(c[m], a0, a1, a2, a3, b0, b1);
       }
     }
+    // c[m] = {(key g, head 2tq), (key g, head 2tq+1), (key g+8, head 2tq), (key g+8, head 2tq+1)}
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = warp * 32 + m * 16 + g + (i >> 1) * 8;
+        const int h = h0 + 2 * tq + (i & 1);
+        if (h < G && r >= n0 && r < n1) sc[h * kSplit + r] = c[m][i] * scale;
+      }
   }
   __syncthreads();
 
   // ---- per head: maximum, exponentials, sum (one warp per head) ----------------------------
-  const int n0 = k_begin - k_base, n1 = k_end - k_base;
   for (int h = warp; h < G; h += 4) {
     float m = -INFINITY;
     for (int i = n0 + lane; i < n1; i += 32) m = fmaxf(m, sc[h * kSplit + i]);
@@ -113,67 +178,49 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
     l = warp_sum(l);
     if (lane == 0) { ml[2 * h] = m; ml[2 * h + 1] = l; }
   }
+  cp_async_wait<0>();          // values have landed
   __syncthreads();
 
-  // ---- acc = sum_j p_j v_j ------------------------------------------------------------------
-  for (int h0 = 0; h0 < G; h0 += kHeadChunk) {
-    const int nh = min(kHeadChunk, G - h0);
-    float acc[kHeadChunk][8];
+  // ---- acc^T = V^T p^T: [D dims] x [8 heads], summed over the warp's 32 keys ------------------
+  for (int h0 = 0; h0 < G; h0 += HC) {
+    // p of head h0 + g for this lane's key columns, as bfloat16 pairs
+    unsigned pb[2][2];
 #pragma unroll
-    for (int hh = 0; hh < kHeadChunk; ++hh)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[hh][e] = 0.f;
-    for (int j0 = k_begin + warp * RPL; j0 < k_end; j0 += 4 * RPL * kU) {
-      float vv[kU][8];
-      bool have[kU];
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int j = j0 + u * 4 * RPL + sub;
-        have[u] = false;
-        if (j < k_end) {
-          const int lp = j / page_size;
-          const int page = lp < bt_width ? bt[lp] : -1;
-          if (page >= 0 && page < num_pages) {
-            load8(pages + (size_t)page * page_stride + (size_t)(Hkv + kvh) * head_stride +
-                  (size_t)(j % page_size) * D + li * 8, vv[u]);
-            have[u] = true;
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        if (have[u]) {
-          const int j = j0 + u * 4 * RPL + sub;
-#pragma unroll
-          for (int hh = 0; hh < kHeadChunk; ++hh) {
-            if (hh < nh) {
-              const float p = sc[(h0 + hh) * kSplit + (j - k_base)];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) acc[hh][e] = fmaf(p, vv[u][e], acc[hh][e]);
-            }
-          }
-        }
+    for (int ks = 0; ks < 2; ++ks) {
+      const int j0 = warp * 32 + ks * 16;
+      if (h0 + g < G) {
+        const float* pr = sc + (h0 + g) * kSplit + j0;
+        pb[ks][0] = pack_bf16(pr[2 * tq], pr[2 * tq + 1]);
+        pb[ks][1] = pack_bf16(pr[2 * tq + 8], pr[2 * tq + 9]);
+      } else {
+        pb[ks][0] = pb[ks][1] = 0u;
       }
     }
-    // lanes with the same `li` hold different key rows: add them, then add the warps in order
 #pragma unroll
-    for (int hh = 0; hh < kHeadChunk; ++hh)
+    for (int d0 = 0; d0 < D; d0 += 16) {
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
+      for (int ks = 0; ks < 2; ++ks) {
+        unsigned a0, a1, a2, a3;
+        const int mi = lane >> 3;
+        const int row = warp * 32 + ks * 16 + (lane & 7) + (mi >> 1) * 8;
+        ldmatrix_x4_trans(a0, a1, a2, a3, Vs + row * DS + d0 + (mi & 1) * 8);
+        mma16816(c, a0, a1, a2, a3, pb[ks][0], pb[ks][1]);
+      }
+      // c = {(dim g, head 2tq), (dim g, head 2tq+1), (dim g+8, head 2tq), (dim g+8, head 2tq+1)}
 #pragma unroll
-        for (int o = LPR; o < 32; o <<= 1) acc[hh][e] += __shfl_xor_sync(0xffffffffu, acc[hh][e], o);
-    if (sub == 0) {
-#pragma unroll
-      for (int hh = 0; hh < kHeadChunk; ++hh)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) red[(warp * kHeadChunk + hh) * D + li * 8 + e] = acc[hh][e];
+      for (int i = 0; i < 4; ++i) {
+        const int hh = 2 * tq + (i & 1);
+        if (hh < RH) red[(warp * RH + hh) * D + d0 + g + (i >> 1) * 8] = c[i];
+      }
     }
     __syncthreads();
+    const int nh = min(HC, G - h0);
     for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
       const int hh = i / D, d = i - hh * D;
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) s += red[(w * kHeadChunk + hh) * D + d];
+      for (int w = 0; w < 4; ++w) s += red[(w * RH + hh) * D + d];
       const int hq = kvh * G + h0 + hh;
       ws_acc[(((size_t)t * Hq + hq) * nsplit + split) * D + d] = s;
     }
@@ -218,8 +265,9 @@ static int launch_split(const void* qkv, int q_row_stride, const void* pages, co
                         float* ws_ml, int T, int Hq, int Hkv, int page_size, int num_pages, int window,
                         float scale, int nsplit, cudaStream_t stream) {
   const int G = Hq / Hkv;
-  const size_t smem = ((size_t)G * D + (size_t)G * kSplit + 4 * kHeadChunk * D + 2 * G) * sizeof(float);
-  NF_REQUIRE(smem <= 160 * 1024, "decode attention: %d query heads per kv head need too much shared memory", G);
+  const size_t smem = (size_t)2 * kSplit * (D + 8) * sizeof(__nv_bfloat16) +
+                      ((size_t)G * kSplit + 4 * (G < 8 ? G : 8) * D + 2 * G) * sizeof(float);
+  NF_REQUIRE(smem <= 200 * 1024, "decode attention: %d query heads per kv head need too much shared memory", G);
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
     cudaFuncSetAttribute(decode_attention_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

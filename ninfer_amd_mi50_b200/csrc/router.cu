@@ -12,33 +12,62 @@
 
 namespace nf {
 
-// One block per token.  wr holds `E + extra` rows of `hidden` float32: E router rows and
-// `extra` further rows whose logits are returned raw (the shared expert's gate).
-template <typename T>
-__global__ void __launch_bounds__(128)
-router_topk_kernel(const T* __restrict__ x, const float* __restrict__ wr, int hidden, int E,
-                   int extra, int k, int norm_topk, int* __restrict__ topk_idx,
-                   float* __restrict__ topk_w, float* __restrict__ extra_out) {
-  extern __shared__ float smem[];      // [hidden] x, [E + extra] logits -> probabilities
-  float* xs = smem;
-  float* lg = smem + hidden;
-  const int t = blockIdx.x;
+// Router logits: out[t, e] = x[t] . wr[e] in float32, for the E router rows and `extra`
+// further rows (the shared expert's gate).  A block takes TT tokens and 8 rows of wr, one
+// warp per row; a lane sums its strided share of the hidden dimension and the warp adds the
+// 32 shares in a fixed tree, so the value for (t, e) is the same whatever TT is and
+// whatever else is in the batch.
+template <typename T, int TT>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n_tokens, int hidden,
+                     int rows, float* __restrict__ out) {
+  extern __shared__ float xs[];        // [TT][hidden]
+  const int t0 = blockIdx.y * TT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const T* xr = x + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_float(xr[i]);
-  __syncthreads();
-  for (int e = warp; e < E + extra; e += 4) {
-    const float* w = wr + (size_t)e * hidden;
-    float dot = 0.f;
-    for (int i = lane; i < hidden; i += 32) dot = fmaf(xs[i], w[i], dot);
-    dot = warp_sum(dot);
-    if (lane == 0) lg[e] = dot;
+  const int nt = min(TT, n_tokens - t0);
+  for (int i = threadIdx.x; i < nt * hidden; i += blockDim.x) {
+    const int tt = i / hidden, c = i - tt * hidden;
+    xs[tt * hidden + c] = to_float(x[(size_t)(t0 + tt) * hidden + c]);
   }
   __syncthreads();
-  if (warp != 0) return;
-  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = lg[E + g];
+  const int e = blockIdx.x * 8 + warp;
+  if (e >= rows) return;
+  const float* w = wr + (size_t)e * hidden;
+  float acc[TT];
+#pragma unroll
+  for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
+  for (int i = lane; i < hidden; i += 32) {
+    const float wv = w[i];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt)
+      if (tt < nt) acc[tt] = fmaf(xs[tt * hidden + i], wv, acc[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < TT; ++tt) {
+    const float v = warp_sum(acc[tt]);
+    if (lane == 0 && tt < nt) out[(size_t)(t0 + tt) * rows + e] = v;
+  }
+}
+
+// One warp per token: softmax over the E router logits, the k largest (ties to the lower
+// index), weights p_e or p_e / sum(selected).
+__global__ void __launch_bounds__(128)
+router_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int extra, int k,
+                     int norm_topk, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                     float* __restrict__ extra_out) {
+  extern __shared__ float smem[];      // [4 warps][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  float* lg = smem + warp * E;
+  const float* row = logits + (size_t)t * (E + extra);
+  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = row[E + g];
   float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+  for (int e = lane; e < E; e += 32) {
+    const float v = row[e];
+    lg[e] = v;
+    mx = fmaxf(mx, v);
+  }
   mx = warp_max(mx);
   float sum = 0.f;
   for (int e = lane; e < E; e += 32) {
@@ -122,23 +151,43 @@ moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict_
 
 using namespace nf;
 
+template <typename T, int TT>
+static int launch_logits(const void* x, const float* wr, int T_, int hidden, int rows, float* logits,
+                         cudaStream_t stream) {
+  const size_t smem = (size_t)TT * hidden * sizeof(float);
+  static size_t allowed = 48 * 1024;      // raised once per size, outside any stream capture
+  if (smem > allowed) {
+    cudaFuncSetAttribute(router_logits_kernel<T, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    allowed = smem;
+  }
+  dim3 grid((rows + 7) / 8, (T_ + TT - 1) / TT);
+  NF_REQUIRE(grid.y <= 65535, "router: too many tokens in one call (%d)", T_);
+  router_logits_kernel<T, TT><<<grid, 256, smem, stream>>>((const T*)x, wr, T_, hidden, rows, logits);
+  return check_launch("router_logits");
+}
+
+template <typename T>
+static int launch_logits_t(const void* x, const float* wr, int T_, int hidden, int rows, float* logits,
+                           cudaStream_t stream) {
+  // tokens per block: as many as fit shared memory, to read the router matrix fewer times
+  if (T_ > 128 && (size_t)8 * hidden * 4 <= 160 * 1024) return launch_logits<T, 8>(x, wr, T_, hidden, rows, logits, stream);
+  if (T_ > 8 && (size_t)2 * hidden * 4 <= 160 * 1024) return launch_logits<T, 2>(x, wr, T_, hidden, rows, logits, stream);
+  return launch_logits<T, 1>(x, wr, T_, hidden, rows, logits, stream);
+}
+
+// logits: float32 scratch [T, E + extra], also an output (the raw router logits).
 extern "C" int nf_router_topk(const void* x, const float* wr, int T, int hidden, int E, int extra,
-                              int k, int norm_topk, int* topk_idx, float* topk_w,
+                              int k, int norm_topk, float* logits, int* topk_idx, float* topk_w,
                               float* extra_out, int dtype, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && hidden > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d hidden=%d E=%d k=%d", T, hidden, E, k);
-  const size_t smem = (size_t)(hidden + E + extra) * sizeof(float);
-  NF_REQUIRE(smem <= 200 * 1024, "router: hidden=%d with %d experts needs %zu bytes of shared memory (limit 200 KiB)", hidden, E, smem);
-  if (dtype == kF32) {
-    static size_t allowed = 48 * 1024;      // raised once per size, outside any stream capture
-    if (smem > allowed) { cudaFuncSetAttribute(router_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
-    router_topk_kernel<float><<<T, 128, smem, stream>>>((const float*)x, wr, hidden, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
-  } else {
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) { cudaFuncSetAttribute(router_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed = smem; }
-    router_topk_kernel<__nv_bfloat16><<<T, 128, smem, stream>>>((const __nv_bfloat16*)x, wr, hidden, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
-  }
-  return check_launch("router_topk");
+  NF_REQUIRE((size_t)hidden * 4 <= 200 * 1024, "router: hidden=%d needs more shared memory than a block has", hidden);
+  NF_REQUIRE((size_t)4 * E * 4 <= 48 * 1024, "router: %d experts are more than the selection kernel holds (3072)", E);
+  int rc = dtype == kF32 ? launch_logits_t<float>(x, wr, T, hidden, E + extra, logits, stream)
+                         : launch_logits_t<__nv_bfloat16>(x, wr, T, hidden, E + extra, logits, stream);
+  if (rc) return rc;
+  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
+  return check_launch("router_select");
 }
 
 extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int* order, int* inv,

@@ -51,15 +51,15 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   __shared__ float partial[kWarps][NT * 4 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int group = blockIdx.z;
+  const int group = blockIdx.z;   // row tiles vary fastest, so CTAs that share weight rows run together
   int row_begin = 0, row_end = M;
   if (offsets) { row_begin = offsets[group]; row_end = offsets[group + 1]; }
-  const int m0 = row_begin + blockIdx.y * (8 * NT);
+  const int m0 = row_begin + blockIdx.x * (8 * NT);
   if (m0 >= row_end) return;
   const int rows = min(8 * NT, row_end - m0);
   const int ntiles = (rows + 7) >> 3;
   constexpr int FEAT = SWIGLU ? 8 : 16;
-  const int n0 = blockIdx.x * FEAT;
+  const int n0 = blockIdx.y * FEAT;
   const __nv_bfloat16* Wg = W + (size_t)group * w_group_stride;
 
   // weight rows of this lane: tile row g and tile row g + 8
@@ -156,8 +156,8 @@ static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y,
                      int K, int groups, int max_rows, const int* offsets, const int* x_rows, int x_div,
                      cudaStream_t stream) {
   const int feat = SWIGLU ? 8 : 16;
-  dim3 grid((N + feat - 1) / feat, (max_rows + 8 * NT - 1) / (8 * NT), groups);
-  NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many row tiles or groups");
+  dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, groups);
+  NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
   skinny_gemm_kernel<NT, SWIGLU, TC><<<grid, kWarps * 32, 0, stream>>>(
       (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows, x_div);
   return check_launch("skinny_gemm");
@@ -169,9 +169,7 @@ static int launch_sw(int nt, const void* X, int ldx, const void* W, size_t wgs, 
                      int x_div, cudaStream_t stream) {
   switch (nt) {
     case 1: return launch_nt<1, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-    case 2: return launch_nt<2, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-    case 4: return launch_nt<4, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-    default: return launch_nt<8, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    default: return launch_nt<2, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
   }
 }
 
@@ -192,7 +190,9 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && (w_group_stride % 8 == 0),
              "skinny_gemm: operands must be 16-byte aligned");
   NF_REQUIRE(groups == 1 || offsets, "skinny_gemm: grouped product needs row offsets");
-  const int nt = max_rows <= 8 ? 1 : max_rows <= 16 ? 2 : max_rows <= 32 ? 4 : 8;
+  // at most 16 rows a CTA: more rows are further CTAs over the same weight rows, launched
+  // next to each other so that the second reading comes from L2
+  const int nt = max_rows <= 8 ? 1 : 2;
   const size_t wgs = (size_t)w_group_stride;
   if (swiglu) {
     NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");

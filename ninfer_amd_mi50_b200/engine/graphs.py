@@ -34,10 +34,9 @@ def row_bucket(n: int) -> int:
 
 
 def context_bucket(n: int, limit: int) -> int:
-    b = 1024
-    while b < n:
-        b <<= 1
-    return min(b, max(limit, 1))
+    """Context bound a graph is built for: the next multiple of 512 (the decode attention
+    launches one block of CTAs per 128 keys of this bound, so a tight bound saves idle CTAs)."""
+    return min((n + 511) // 512 * 512, max(limit, 1))
 
 
 class DecodeGraph:

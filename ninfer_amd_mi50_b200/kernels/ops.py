@@ -30,13 +30,14 @@ TUNING = {
     "bf16_linear": "auto",        # "simt" | "auto"
     "bf16_attention": "auto",     # "generic" | "auto"
     "bf16_moe": "auto",           # "simt" | "auto"
-    "skinny_max_rows": 64,
+    "skinny_max_rows": 16,        # dense products with more rows go to the library
+    "skinny_moe_max_tokens": 128, # routed experts: tokens up to which the streaming kernel serves
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)   # head sizes of the split-key decode kernel
 DECODE_SPLIT = 128                          # keys per block of that kernel
-MAX_EXPERTS = 8192
+MAX_EXPERTS = 3072
 
 
 def check_head_dim(head_dim: int) -> None:
@@ -141,7 +142,8 @@ def _bf16_path(rows: int, K: int, key: str) -> str:
     """Which bfloat16 product serves `rows` rows: decided by the row count and K only."""
     if TUNING[key] == "simt":
         return "simt"
-    if rows <= TUNING["skinny_max_rows"] and K % 8 == 0:
+    limit = TUNING["skinny_max_rows"] if key == "bf16_linear" else TUNING["skinny_moe_max_tokens"]
+    if rows <= limit and K % 8 == 0:
         return "skinny"
     return "large"
 
@@ -268,9 +270,10 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_to
     idx = torch.empty((T, k), dtype=torch.int32, device=x.device)
     wts = torch.empty((T, k), dtype=torch.float32, device=x.device)
     ext = torch.empty((T, extra), dtype=torch.float32, device=x.device) if extra > 0 else None
+    logits = torch.empty((T, E + extra), dtype=torch.float32, device=x.device)
     _lib.call("nf_router_topk", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra),
-              c_int(k), c_int(1 if norm_topk else 0), _p(idx), _p(wts), _p(ext), c_int(_dt(x)),
-              _stream())
+              c_int(k), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext),
+              c_int(_dt(x)), _stream())
     return idx, wts, ext
 
 
