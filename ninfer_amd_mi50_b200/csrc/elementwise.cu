@@ -86,6 +86,15 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
   out[(size_t)t * hidden + i] = from_float<T>(acc);
 }
 
+// out[p] = x[rows[p] / div]: rows of 16-byte pieces
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows, int div,
+                                   uint4* __restrict__ out, int pieces) {
+  const int p = blockIdx.x;
+  const uint4* src = x + (size_t)(rows[p] / div) * pieces;
+  uint4* dst = out + (size_t)p * pieces;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
+}
+
 static inline int row_threads(int n) {
   int t = 32;
   while (t < n && t < 256) t <<= 1;
@@ -144,4 +153,14 @@ extern "C" int nf_moe_combine(const void* y, const int* inv, const float* wts, c
   else
     moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
   return check_launch("moe_combine");
+}
+
+// out[p, :] = x[rows[p] / div, :] for n rows of `row_bytes` bytes (a multiple of 16).
+extern "C" int nf_gather_rows(const void* x, const int* rows, int div, void* out, int n, int row_bytes,
+                              cudaStream_t stream) {
+  if (n == 0) return 0;
+  NF_REQUIRE(n > 0 && div > 0 && row_bytes > 0 && row_bytes % 16 == 0, "gather_rows: rows of %d bytes are not whole 16-byte pieces", row_bytes);
+  NF_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0), "gather_rows: operands must be 16-byte aligned");
+  gather_rows_kernel<<<n, row_threads(row_bytes / 16), 0, stream>>>((const uint4*)x, rows, div, (uint4*)out, row_bytes / 16);
+  return check_launch("gather_rows");
 }

@@ -1,0 +1,344 @@
+// Routed experts at prefill: a grouped GEMM on the 5th-generation tensor cores.
+//
+//   act[p, :] = silu(x[p] Wgate_e^T) * (x[p] Wup_e^T)      (first product, SwiGLU epilogue)
+//   y[p, :]   = act[p] Wdown_e^T                           (second product)
+// for every sorted (token, expert) pair p of expert e, rows [offsets[e], offsets[e+1]).
+//
+// Reference: a host loop over experts with one rocBLAS GEMM each plus gather, activation and
+// scale kernels (src/models/model.hip:355-427).  Here one launch covers all experts.
+//
+// Shape of the work.  With ~137 rows per expert (2,048 tokens, 60 experts, top-4) the
+// product does ~137 FLOP per weight byte, below the machine's ridge: the bound is reading
+// each expert's weights once from HBM.  So the weights are the 128-row M operand
+// (`tcgen05.mma.cta_group::1.kind::f16`, M = 128 features), the expert's tokens are the N
+// operand (N = the expert's row count rounded up to 16, at most 256 per pass), and a CTA owns
+// (expert, 128 features): it streams its slice of the weight matrix exactly once while the
+// expert's rows come from L2.  Ragged row counts cost at most 15 padded columns, not a
+// half-empty 128-row tile.
+//
+// Machinery: operands arrive by TMA (`cp.async.bulk.tensor.2d`, 128-byte swizzle) into a
+// ring of shared-memory stages guarded by mbarriers; one elected thread issues the MMAs,
+// whose float32 accumulators live in tensor memory (gate in columns [0, 256), up in
+// [256, 512)); `tcgen05.commit` hands stages back to the producer and the finished
+// accumulator to four epilogue warps, which read it with `tcgen05.ld`, apply the epilogue
+// and store bfloat16.  No TMA multicast, no clusters.
+//
+// Every wait on an mbarrier is bounded: after a fixed number of polls the kernel records a
+// code in `g_tc_error`, tells its other warps to stop, waits (again bounded) for its own
+// copies in flight, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace nf {
+
+constexpr int kBM = 128;          // features per CTA (MMA M)
+constexpr int kBK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kBNMax = 256;       // tokens per pass (MMA N, columns of one accumulator)
+constexpr int kTmemCols = 512;
+constexpr unsigned kPollLimit = 1u << 24;
+
+__device__ int g_tc_error = 0;
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(void* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if this wait ran out of polls or another role gave up.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, volatile int* stop, int code) {
+  for (unsigned i = 0; i < kPollLimit; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *stop) return false;
+  }
+  *stop = 1;
+  atomicCAS(&g_tc_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row
+// groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_desc(const void* p) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_u32(p) & 0x3FFFFu) >> 4);       // start address
+  d |= (unsigned long long)1 << 16;                                // leading byte offset (unused here)
+  d |= (unsigned long long)(1024 >> 4) << 32;                      // stride byte offset
+  d |= (unsigned long long)1 << 46;                                // descriptor version
+  d |= (unsigned long long)2 << 61;                                // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ unsigned instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(kBM >> 4) << 24);
+}
+
+struct __align__(8) Barriers {
+  unsigned long long full[4], empty[4], acc_full, acc_empty;
+  unsigned tmem_base;
+  int stop;
+};
+
+// grid (feature tiles, groups); 192 threads: warp 0 producer, warp 1 MMA + tensor memory,
+// warps 2..5 epilogue.
+template <bool SWIGLU, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int ldo,
+                       int n_features, int K, int w_rows_per_group) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = kBM * kBK * 2, B_BYTES = kBNMax * kBK * 2;
+  constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * A_BYTES + B_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  volatile int* stop = &bars->stop;
+
+  const int group = blockIdx.y;
+  const int row_begin = offsets[group], row_end = offsets[group + 1];
+  if (row_begin >= row_end) return;                       // the whole CTA leaves before any barrier exists
+  const int f0 = blockIdx.x * kBM;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_rows = row_end - row_begin;
+  const int n_passes = (n_rows + kBNMax - 1) / kBNMax;
+  const int k_steps = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->acc_empty, 4);
+    bars->stop = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---- producer ---------------------------------------------------------------------------
+    if (lane == 0) {
+      const int w_row_gate = group * w_rows_per_group + f0;
+      const int w_row_up = w_row_gate + n_features;         // SwiGLU: the up rows follow the gate rows
+      int it = 0, issued = 0;
+      bool ok = true;
+      for (int pass = 0; pass < n_passes && ok; ++pass) {
+        const int x_row = row_begin + pass * kBNMax;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&bars->empty[s], ((it / STAGES) & 1) ^ 1, stop, 1)) { ok = false; break; }
+          unsigned char* st = smem + s * STAGE_BYTES;
+          mbar_expect_tx(&bars->full[s], STAGE_BYTES);
+          tma_load_2d(st, &map_w, ks * kBK, w_row_gate, &bars->full[s]);
+          if (SWIGLU) tma_load_2d(st + A_BYTES, &map_w, ks * kBK, w_row_up, &bars->full[s]);
+          tma_load_2d(st + (SWIGLU ? 2 : 1) * A_BYTES, &map_x, ks * kBK, x_row, &bars->full[s]);
+          issued = it + 1;
+        }
+      }
+      if (!ok) {
+        // copies already asked for still land in this CTA's shared memory: wait for them
+        for (int j = max(0, issued - STAGES); j < issued; ++j) {
+          const int s = j % STAGES;
+          for (unsigned i = 0; i < (1u << 20); ++i)
+            if (mbar_try(&bars->full[s], (j / STAGES) & 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int pass = 0; pass < n_passes && ok; ++pass) {
+        if (!mbar_wait(&bars->acc_empty, (pass & 1) ^ 1, stop, 2)) break;
+        tc_fence_after();
+        const int n = min(kBNMax, (n_rows - pass * kBNMax + 15) & ~15);
+        const unsigned idesc = instr_desc(n);
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&bars->full[s], (it / STAGES) & 1, stop, 3)) { ok = false; break; }
+          tc_fence_after();
+          unsigned char* st = smem + s * STAGE_BYTES;
+          const unsigned long long a0 = smem_desc(st);
+          const unsigned long long a1 = smem_desc(st + A_BYTES);
+          const unsigned long long b = smem_desc(st + (SWIGLU ? 2 : 1) * A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            // 16 k = 32 bytes further along the swizzled row: +2 in the address field
+            const unsigned acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            tc_mma(tmem, a0 + 2 * kk, b + 2 * kk, idesc, acc);
+            if (SWIGLU) tc_mma(tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
+          }
+          tc_commit(&bars->empty[s]);          // the stage is free once these MMAs have read it
+        }
+        if (ok) tc_commit(&bars->acc_full);    // the accumulator is complete once they have all run
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31 ---------------------
+    const int quad = warp & 3;
+    const int f = f0 + quad * 32 + lane;
+    for (int pass = 0; pass < n_passes; ++pass) {
+      if (!mbar_wait(&bars->acc_full, pass & 1, stop, 4)) break;
+      tc_fence_after();
+      const int p0 = row_begin + pass * kBNMax;
+      const int valid = min(kBNMax, n_rows - pass * kBNMax);
+      const unsigned lane_addr = tmem + ((unsigned)(quad * 32) << 16);
+      for (int c0 = 0; c0 < valid; c0 += 32) {
+        unsigned g[32], u[32];
+        tc_ld32(lane_addr + c0, g);
+        if (SWIGLU) tc_ld32(lane_addr + kBNMax + c0, u);
+        tc_wait_ld();
+        if (f < n_features) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (c0 + c < valid) {
+              float v = __uint_as_float(g[c]);
+              if (SWIGLU) v = v / (1.f + expf(-v)) * __uint_as_float(u[c]);
+              out[(size_t)(p0 + c0 + c) * ldo + f] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host ---------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A row-major bf16 matrix [rows, cols] as a 2-D tensor map with boxes of [box_rows, 64].
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  NF_REQUIRE(fn, "grouped_gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NF_REQUIRE(r == CUDA_SUCCESS, "grouped_gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+template <bool SWIGLU, int STAGES>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const int* offsets, void* out, int ldo,
+                     int n_features, int K, int w_rows_per_group, int groups, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * kBM * kBK * 2 + kBNMax * kBK * 2;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<SWIGLU, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    NF_REQUIRE(e == cudaSuccess, "grouped_gemm_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    set = true;
+  }
+  dim3 grid((n_features + kBM - 1) / kBM, groups);
+  grouped_gemm_tc_kernel<SWIGLU, STAGES><<<grid, 192, smem, stream>>>(mw, mx, offsets, (__nv_bfloat16*)out, ldo,
+                                                                     n_features, K, w_rows_per_group);
+  return check_launch("grouped_gemm_tc");
+}
+
+}  // namespace nf
+
+using namespace nf;
+
+// out[p, :n_features] for sorted rows p of every group; X holds the rows in sorted order
+// ([total_rows, K], already gathered), W is [groups, w_rows, K] with w_rows = 2 * n_features
+// (gate rows then up rows) for the SwiGLU form, else n_features.
+// Needs K % 8 == 0 and 16-byte aligned bases (TMA).
+extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const void* W, int groups,
+                                  int n_features, int K, const int* offsets, void* out, int ldo,
+                                  int swiglu, cudaStream_t stream) {
+  if (total_rows == 0) return 0;
+  NF_REQUIRE(total_rows > 0 && groups > 0 && n_features > 0 && K > 0, "grouped_gemm_tc: bad sizes");
+  NF_REQUIRE(K % 8 == 0, "grouped_gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+  NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "grouped_gemm_tc: operands must be 16-byte aligned");
+  NF_REQUIRE(groups <= 65535, "grouped_gemm_tc: too many groups");
+  const int w_rows = swiglu ? 2 * n_features : n_features;
+  CUtensorMap mw, mx;
+  if (int rc = make_map(&mw, W, (long long)groups * w_rows, K, kBM)) return rc;
+  if (int rc = make_map(&mx, X, total_rows, K, kBNMax)) return rc;
+  if (swiglu) return launch_tc<true, 3>(mw, mx, offsets, out, ldo, n_features, K, w_rows, groups, stream);
+  return launch_tc<false, 4>(mw, mx, offsets, out, ldo, n_features, K, w_rows, groups, stream);
+}
+
+// 0 if no tensor-core kernel has given up on a wait since the last call; else the code of the
+// first wait that did (1 producer, 2 accumulator hand-back, 3 operands, 4 epilogue).  Synchronises.
+extern "C" int nf_grouped_gemm_tc_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+  return v;
+}

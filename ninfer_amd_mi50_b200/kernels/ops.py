@@ -145,7 +145,15 @@ def _bf16_path(rows: int, K: int, key: str) -> str:
     limit = TUNING["skinny_max_rows"] if key == "bf16_linear" else TUNING["skinny_moe_max_tokens"]
     if rows <= limit and K % 8 == 0:
         return "skinny"
+    if key == "bf16_moe" and K % 8:
+        return "simt"          # the tensor-core kernel's TMA copies need 16-byte rows
     return "large"
+
+
+def tensor_core_status() -> int:
+    """0, or the code of the first bounded wait that a tensor-core kernel gave up on since the
+    last call (synchronises the device)."""
+    return int(_lib.load().nf_grouped_gemm_tc_status())
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -301,6 +309,13 @@ def moe_gemm1(x: torch.Tensor, w13: torch.Tensor, plan: MoePlan, k: int) -> torc
     path = "simt" if x.dtype == torch.float32 else _bf16_path(T, H, "bf16_moe")
     if path == "skinny":
         _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
+    elif path == "large":
+        # rows in sorted order, then one tensor-core launch over all experts
+        xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
+        _lib.call("nf_gather_rows", _p(x), _p(plan.order), c_int(k), _p(xp), c_int(T * k),
+                  c_int(H * 2), _stream())
+        _lib.call("nf_grouped_gemm_tc", _p(xp), c_longlong(T * k), _p(w13), c_int(E), c_int(inner),
+                  c_int(H), _p(plan.offsets), _p(act), c_int(inner), c_int(1), _stream())
     else:
         _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
     return act
@@ -317,6 +332,9 @@ def moe_gemm2(act: torch.Tensor, w2: torch.Tensor, plan: MoePlan) -> torch.Tenso
     path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
     if path == "skinny":
         _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
+    elif path == "large":
+        _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2), c_int(E), c_int(H),
+                  c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())
     else:
         _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
     return y

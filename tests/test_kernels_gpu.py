@@ -284,3 +284,40 @@ def test_refusals_are_clear(K):
         K.check_head_dim(40)
     with pytest.raises(Exception, match="CUDA tensor"):
         K.linear(torch.zeros(2, 4), torch.zeros(3, 4))
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(64, 256, 128, 4, 2), (300, 200, 136, 6, 3), (700, 512, 264, 3, 2),
+                                       (2048, 2048, 1408, 60, 4)])
+def test_grouped_gemm_on_tensor_cores(K, T, H, I, E, k):
+    """The tcgen05 / TMEM / TMA grouped product that serves routed experts at prefill: ragged
+    groups (empty, one row, more than one pass of 256 rows), feature counts and k that are not
+    multiples of the tile, against the plain twin; and no bounded wait may have given up."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(T + I)
+    x = rnd((T, H), dtype, 51)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 52, 0.1), rnd((E, H, I), dtype, 53, 0.1)
+    # skewed routing: expert 0 gets nearly every token, the last expert none
+    idx = torch.stack([torch.cat([torch.zeros(1, dtype=torch.long),
+                                  1 + torch.randperm(max(E - 2, 1), generator=g)[:k - 1]]) if t % 7 else
+                       torch.randperm(E - 1, generator=g)[:k] for t in range(T)]).to(torch.int32).cuda()
+    plan = K.moe_plan(idx, E)
+    old = dict(K.TUNING)
+    K.TUNING.update(skinny_moe_max_tokens=0)
+    try:
+        act = K.moe_gemm1(x, w13, plan, k)
+        ract = P.moe_gemm1(x, w13, plan, k) if T <= 700 else None
+        if ract is None:
+            K.TUNING.update(bf16_moe="simt")
+            ract = K.moe_gemm1(x, w13, plan, k)
+            K.TUNING.update(bf16_moe="auto")
+        close(act, ract, dtype)
+        y = K.moe_gemm2(ract, w2, plan)
+        if T <= 700:
+            ry = P.moe_gemm2(ract, w2, plan)
+        else:
+            K.TUNING.update(bf16_moe="simt")
+            ry = K.moe_gemm2(ract, w2, plan)
+        close(y, ry, dtype)
+    finally:
+        K.TUNING.update(old)
+    assert K.tensor_core_status() == 0
