@@ -37,6 +37,8 @@ TUNING = {
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)   # head sizes of the split-key decode kernel
 DECODE_SPLIT = 128                          # keys per block of that kernel
+PREFILL_HEAD_DIMS = tuple(range(16, 129, 16))   # head sizes of the flash prefill kernel
+PREFILL_TILE_ROWS = 64                      # query rows per CTA of that kernel
 MAX_EXPERTS = 3072
 
 
@@ -246,6 +248,15 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
                   c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
                   _p(ws_acc), _p(ws_ml), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
                   c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
+        return out
+    if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
+            and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
+            and qkv.shape[1] % 8 == 0):
+        tiles, n_tiles = ctx.query_tiles(PREFILL_TILE_ROWS)
+        _lib.call("nf_prefill_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+                  c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles),
+                  c_int(n_tiles), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                  c_int(pages.shape[0]), c_int(window), c_float(scale), _stream())
         return out
     _lib.call("nf_paged_attention_generic", _p(qkv), c_int(qkv.shape[1]), _p(pages),
               _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg),

@@ -181,6 +181,34 @@ def test_decode_attention_split_kernel(K, Hq, Hkv, D, page, window):
     torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [(4, 1, 128, 64, 0), (6, 2, 48, 16, 0), (4, 4, 64, 32, 37),
+                                                  (2, 2, 16, 16, 0), (8, 2, 112, 64, 200)])
+def test_prefill_attention_flash_kernel(K, Hq, Hkv, D, page, window):
+    """Mixed segments in bfloat16 take the flash kernel: a long portion continuing an earlier
+    one, a fresh prompt, single rows, a portion that ends exactly on a tile edge."""
+    from ninfer_amd_mi50_b200.parts.base import StepContext
+    dtype = torch.bfloat16
+    seg_lens, pos0s = [150, 1, 64, 3, 1], [70, 333, 0, 127, 0]
+    pages, bt, c, qkv = make_cache_case(dtype, Hq, Hkv, D, page, seg_lens, pos0s, 96, 43)
+    row0 = [0]
+    for n in seg_lens:
+        row0.append(row0[-1] + n)
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    ctx = StepContext(dtype=dtype, device=torch.device("cuda"), T=row0[-1], S=len(seg_lens), token_ids=mk([0]),
+                      positions=c.positions, row_seg=c.row_seg, seg_row0=mk(row0), seg_pos0=mk(pos0s),
+                      seg_slot=mk([0] * 5), logit_rows=mk([]), seg_len_host=seg_lens, seg_pos0_host=pos0s,
+                      max_rows_per_seg=150, max_context=334)
+    scale = 1 / math.sqrt(D)
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    ref = P.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    torch.testing.assert_close(out.float(), ref.float(), **tol(dtype))
+    old = K.TUNING["bf16_attention"]
+    K.TUNING["bf16_attention"] = "generic"
+    gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    K.TUNING["bf16_attention"] = old
+    torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
+
+
 def test_attention_finds_one_far_key(K):
     """One key among hundreds is made to dominate; the output must be its value row."""
     Hq, Hkv, D, page = 2, 1, 64, 16
