@@ -314,3 +314,54 @@ extern "C" int nf_decode_attention(const void* qkv, int q_row_stride, const void
   decode_attention_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(ws_acc, ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit);
   return check_launch("decode_attention_merge");
 }
+
+// ---- the entry point that allocates nothing ---------------------------------------------------
+//
+// Some callers cannot call cudaMalloc (see ninfer_ops.h: plug-ins inside a host that owns the
+// device's memory, loops that cannot afford an allocation's synchronisation, sandboxes that
+// forbid allocations after start-up).  For them the split kernel's scratch lives in this
+// fixed array.  In host code the name `g_decode_scratch` is only a stand-in for the symbol,
+// not a device address: the address is asked for once per device with cudaGetSymbolAddress
+// and then handed to the kernels like any other pointer.
+
+namespace nf {
+constexpr long long kStaticScratchBytes = 8ll << 20;     // 8 MiB on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace nf
+
+extern "C" long long nf_decode_attention_static_scratch_bytes() { return nf::kStaticScratchBytes; }
+
+// Decode attention with the library's own scratch.  Same arguments as nf_decode_attention
+// without the two workspace pointers.  The first call on a device performs the address
+// look-up (make it before any stream capture, with that device current).  Calls share the
+// scratch: kernels of two calls must not overlap on the GPU.  Nothing is allocated.
+extern "C" int nf_decode_attention_static(const void* qkv, int q_row_stride, const void* pages,
+                                          const int* block_table, int bt_width, const int* positions,
+                                          const int* row_seg, void* out, int T, int Hq, int Hkv, int D,
+                                          int page_size, int num_pages, int window, float scale,
+                                          int nsplit, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && Hq > 0 && nsplit > 0 && D > 0, "decode attention (static scratch): bad sizes T=%d Hq=%d nsplit=%d D=%d", T, Hq, nsplit, D);
+  const long long acc_bytes = (long long)T * Hq * nsplit * D * (long long)sizeof(float);
+  const long long ml_bytes = (long long)T * Hq * nsplit * 2 * (long long)sizeof(float);
+  const long long acc_padded = (acc_bytes + 255) / 256 * 256;
+  NF_REQUIRE(acc_padded + ml_bytes <= kStaticScratchBytes,
+             "decode attention (static scratch): T=%d rows x %d heads x %d key blocks x head_dim %d needs %lld bytes "
+             "of scratch, the fixed array holds %lld; use nf_decode_attention with your own workspace",
+             T, Hq, nsplit, D, acc_padded + ml_bytes, kStaticScratchBytes);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  NF_REQUIRE(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, "decode attention (static scratch): cannot tell the current device (%s)", cudaGetErrorString(e));
+  if (!g_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    NF_REQUIRE(e == cudaSuccess && p, "decode attention (static scratch): cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+    g_scratch_addr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_scratch_addr[dev]);
+  return nf_decode_attention(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, out,
+                             reinterpret_cast<float*>(base), reinterpret_cast<float*>(base + acc_padded), T, Hq,
+                             Hkv, D, page_size, num_pages, window, scale, nsplit, stream);
+}
