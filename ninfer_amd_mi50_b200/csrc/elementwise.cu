@@ -95,6 +95,53 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __res
   for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
 }
 
+// 8 bfloat16 at a time: act = silu(gate) * up
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
+                                       int inner) {
+  const int m = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= inner) return;
+  float g[8], u[8];
+  load8(gu + (size_t)m * 2 * inner + i, g);
+  load8(gu + (size_t)m * 2 * inner + inner + i, u);
+  __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(g[e] / (1.f + expf(-g[e])) * u[e]);
+  *reinterpret_cast<uint4*>(act + (size_t)m * inner + i) = *reinterpret_cast<const uint4*>(o);
+}
+
+__global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv,
+                                          const float* __restrict__ wts,
+                                          const __nv_bfloat16* __restrict__ shared,
+                                          const float* __restrict__ gate, int gate_stride,
+                                          __nv_bfloat16* __restrict__ out, int hidden, int k) {
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= hidden) return;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const int p = inv[t * k + j];
+    const float w = wts[t * k + j];
+    float v[8];
+    load8(y + (size_t)p * hidden + i, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += w * v[e];
+  }
+  if (shared) {
+    float v[8];
+    load8(shared + (size_t)t * hidden + i, v);
+    const float gsc = gate ? 1.f / (1.f + expf(-gate[(size_t)t * gate_stride])) : 1.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += v[e] * gsc;
+  }
+  __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
+  *reinterpret_cast<uint4*>(out + (size_t)t * hidden + i) = *reinterpret_cast<const uint4*>(o);
+}
+
 static inline int row_threads(int n) {
   int t = 32;
   while (t < n && t < 256) t <<= 1;
@@ -136,6 +183,11 @@ extern "C" int nf_silu_mul(const void* gu, void* act, int M, int inner, int dtyp
                            cudaStream_t stream) {
   if (M == 0) return 0;
   NF_REQUIRE(M > 0 && inner > 0, "silu_mul: bad sizes M=%d inner=%d", M, inner);
+  if (dtype == kBF16 && inner % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)act % 16 == 0) {
+    dim3 g8(M, (inner / 8 + 127) / 128);
+    silu_mul_bf16x8_kernel<<<g8, 128, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inner);
+    return check_launch("silu_mul");
+  }
   dim3 grid(M, (inner + 255) / 256);
   if (dtype == kF32) silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)act, inner);
   else silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inner);
@@ -147,6 +199,12 @@ extern "C" int nf_moe_combine(const void* y, const int* inv, const float* wts, c
                               int k, int dtype, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && hidden > 0 && k > 0, "moe_combine: bad sizes T=%d hidden=%d k=%d", T, hidden, k);
+  if (dtype == kBF16 && hidden % 8 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+      (!shared || (uintptr_t)shared % 16 == 0)) {
+    dim3 g8(T, (hidden / 8 + 127) / 128);
+    moe_combine_bf16x8_kernel<<<g8, 128, 0, stream>>>((const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
+    return check_launch("moe_combine");
+  }
   dim3 grid(T, (hidden + 255) / 256);
   if (dtype == kF32)
     moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)y, inv, wts, (const float*)shared, gate, gate_stride, (float*)out, hidden, k);

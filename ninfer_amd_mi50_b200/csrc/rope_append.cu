@@ -13,52 +13,67 @@
 
 namespace nf {
 
+// One block per row.  A thread owns pairs of elements: the rotated pair (i, i + rot/2) of a
+// q or k head, or two neighbouring elements that are only biased and copied (dims beyond
+// `rot`, and every dim of a v head).  Owning both elements of a pair, it can write q back in
+// place without a barrier.
 template <typename T>
-__global__ void rope_append_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
-                                   const int* __restrict__ positions,
-                                   const int* __restrict__ row_seg,
-                                   const float* __restrict__ inv_freq, int rot, int Hq, int Hkv,
-                                   int D, T* __restrict__ pages, const int* __restrict__ block_table,
-                                   int bt_width, int page_size, int num_pages) {
+__global__ void __launch_bounds__(256)
+rope_append_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+                   const int* __restrict__ positions, const int* __restrict__ row_seg,
+                   const float* __restrict__ inv_freq, int rot, int Hq, int Hkv, int D,
+                   T* __restrict__ pages, const int* __restrict__ block_table, int bt_width,
+                   int page_size, int num_pages, int append) {
+  extern __shared__ float cs[];            // [rot/2] cos, [rot/2] sin
   const int t = blockIdx.x;
-  const int head = blockIdx.y;           // [0,Hq) q, [Hq,Hq+Hkv) k, [Hq+Hkv, Hq+2Hkv) v
-  const int W = (Hq + 2 * Hkv) * D;
-  T* x = qkv + (size_t)t * W + (size_t)head * D;
-  const float* b = bias ? bias + (size_t)head * D : nullptr;
+  const int half = rot / 2;
   const int pos = positions[t];
-  const bool is_q = head < Hq;
-  const bool is_v = head >= Hq + Hkv;
-
-  T* dst = nullptr;                       // where the k / v head goes in the cache
-  if (!is_q) {
+  const float fpos = (float)pos;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = fpos * inv_freq[i];
+    cs[i] = cosf(angle);
+    cs[half + i] = sinf(angle);
+  }
+  __syncthreads();
+  const int W = (Hq + 2 * Hkv) * D;
+  T* x = qkv + (size_t)t * W;
+  // where this row's keys and values go
+  T* kdst = nullptr;
+  if (append) {
     const int seg = row_seg[t];
     const int lp = pos / page_size;
-    int page = (lp >= 0 && lp < bt_width) ? block_table[(size_t)seg * bt_width + lp] : -1;
-    if (page < 0 || page >= num_pages) return;   // no page reserved: never write out of bounds
-    const int kvh = is_v ? head - Hq - Hkv : head - Hq;
-    dst = pages + ((((size_t)page * 2 + (is_v ? 1 : 0)) * Hkv + kvh) * page_size + pos % page_size) * D;
+    const int page = (lp >= 0 && lp < bt_width) ? block_table[(size_t)seg * bt_width + lp] : -1;
+    if (page >= 0 && page < num_pages)       // no page reserved: never write out of bounds
+      kdst = pages + ((size_t)page * 2 * Hkv * page_size + (size_t)(pos - lp * page_size)) * D;
   }
-  const int half = rot / 2;
-  const float fpos = (float)pos;
-  // blockDim.x >= D: one sweep covers the head, so the barrier below is uniform
-  const int i = threadIdx.x;
-  float v = 0.f;
-  if (i < D) {
-    v = to_float(x[i]) + (b ? b[i] : 0.f);
-    if (!is_v && i < rot) {
-      const int j = i < half ? i : i - half;
-      const int partner = i < half ? i + half : i - half;
-      const float other = to_float(x[partner]) + (b ? b[partner] : 0.f);
-      const float angle = fpos * inv_freq[j];
-      const float c = cosf(angle), s = sinf(angle);
-      v = i < half ? v * c - other * s : other * s + v * c;
+  const size_t kv_head_stride = (size_t)page_size * D;
+  const int slots = D / 2;
+  const int heads = append ? Hq + 2 * Hkv : Hq;
+  for (int idx = threadIdx.x; idx < heads * slots; idx += blockDim.x) {
+    const int head = idx / slots, s = idx - head * slots;
+    const bool is_q = head < Hq, is_v = head >= Hq + Hkv;
+    int i0, i1;
+    bool rotate = false;
+    if (!is_v && s < half) { i0 = s; i1 = s + half; rotate = true; }
+    else if (!is_v) { i0 = rot + 2 * (s - half); i1 = i0 + 1; }
+    else { i0 = 2 * s; i1 = i0 + 1; }
+    const size_t base = (size_t)head * D;
+    float a = to_float(x[base + i0]), b = to_float(x[base + i1]);
+    if (bias) { a += bias[base + i0]; b += bias[base + i1]; }
+    if (rotate) {
+      const float c = cs[s], sn = cs[half + s];
+      const float ra = a * c - b * sn, rb = a * sn + b * c;
+      a = ra; b = rb;
     }
-  }
-  // every thread has read what it needs from x before anyone overwrites it
-  __syncthreads();
-  if (i < D) {
-    if (is_q) x[i] = from_float<T>(v);
-    else dst[i] = from_float<T>(v);
+    if (is_q) {
+      x[base + i0] = from_float<T>(a);
+      x[base + i1] = from_float<T>(b);
+    } else if (kdst) {
+      const int kvh = is_v ? head - Hq - Hkv : head - Hq;
+      T* dst = kdst + ((size_t)(is_v ? Hkv : 0) + kvh) * kv_head_stride;
+      dst[i0] = from_float<T>(a);
+      dst[i1] = from_float<T>(b);
+    }
   }
 }
 
@@ -75,14 +90,12 @@ extern "C" int nf_rope_append(void* qkv, const float* bias, const int* positions
   NF_REQUIRE(rot >= 0 && rot <= D && rot % 2 == 0, "rope_append: rotary width %d must be even and <= head_dim %d", rot, D);
   NF_REQUIRE(rot == 0 || inv_freq, "rope_append: rotation asked without a frequency table");
   NF_REQUIRE(Hq + 2 * Hkv <= 65535, "rope_append: too many heads");
-  // one block covers a whole head in a single sweep
-  int threads = 32;
-  while (threads < D) threads <<= 1;
-  NF_REQUIRE(threads <= 1024, "rope_append: head_dim %d too large", D);
-  dim3 grid(T, append ? Hq + 2 * Hkv : Hq);
+  NF_REQUIRE(D % 2 == 0, "rope_append: head_dim %d must be even", D);
+  const size_t smem = (size_t)rot * sizeof(float);
+  NF_REQUIRE(smem <= 48 * 1024, "rope_append: rotary width %d too large", rot);
   if (dtype == kF32)
-    rope_append_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, bias, positions, row_seg, inv_freq, rot, Hq, Hkv, D, (float*)pages, block_table, bt_width, page_size, num_pages);
+    rope_append_kernel<float><<<T, 256, smem, stream>>>((float*)qkv, bias, positions, row_seg, inv_freq, rot, Hq, Hkv, D, (float*)pages, block_table, bt_width, page_size, num_pages, append);
   else
-    rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, bias, positions, row_seg, inv_freq, rot, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages);
+    rope_append_kernel<__nv_bfloat16><<<T, 256, smem, stream>>>((__nv_bfloat16*)qkv, bias, positions, row_seg, inv_freq, rot, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, append);
   return check_launch("rope_append");
 }

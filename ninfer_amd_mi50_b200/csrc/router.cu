@@ -109,16 +109,24 @@ router_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int 
 //   order[p] = pair (t*k + j) at sorted position p;   inv[pair] = p
 // One block; warp w ranks the pairs of experts w, w + nwarps, ... with ballots, which keeps
 // token order inside an expert.
+// STAGED: the pairs' experts are first copied into shared memory (as 16-bit values), so that
+// the E passes over them do not go to global memory.
+template <bool STAGED>
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict__ offsets,
                 int* __restrict__ order, int* __restrict__ inv) {
-  extern __shared__ int counts[];      // [E + 1]
+  extern __shared__ int counts[];      // [E + 1], then (STAGED) n experts and n ranks as 16-bit
+  unsigned short* ex = reinterpret_cast<unsigned short*>(counts + E + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  if (STAGED) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ex[i] = (unsigned short)topk_idx[i];
+    __syncthreads();
+  }
   for (int e = warp; e < E; e += nwarp) {
     int running = 0;
     for (int base = 0; base < n; base += 32) {
       const int i = base + lane;
-      const bool mine = i < n && topk_idx[i] == e;
+      const bool mine = i < n && (STAGED ? (int)ex[i] : topk_idx[i]) == e;
       const unsigned b = __ballot_sync(0xffffffffu, mine);
       if (mine) inv[i] = running + __popc(b & ((1u << lane) - 1u));   // rank inside the expert
       running += __popc(b);
@@ -190,9 +198,29 @@ extern "C" int nf_router_topk(const void* x, const float* wr, int T, int hidden,
   return check_launch("router_select");
 }
 
+// Selection alone, from float32 logits [T, E + extra] that something else has produced.
+extern "C" int nf_router_select(const float* logits, int T, int E, int extra, int k, int norm_topk,
+                                int* topk_idx, float* topk_w, float* extra_out, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d E=%d k=%d", T, E, k);
+  NF_REQUIRE((size_t)4 * E * 4 <= 48 * 1024, "router: %d experts are more than the selection kernel holds (3072)", E);
+  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
+  return check_launch("router_select");
+}
+
 extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int* order, int* inv,
                            cudaStream_t stream) {
   NF_REQUIRE(n >= 0 && E > 0 && E <= 8192, "moe_plan: bad sizes n=%d E=%d", n, E);
-  moe_plan_kernel<<<1, 1024, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, offsets, order, inv);
+  const size_t staged = (size_t)(E + 1) * sizeof(int) + (size_t)n * sizeof(unsigned short);
+  if (E < 65536 && staged <= 160 * 1024) {
+    static size_t allowed = 48 * 1024;
+    if (staged > allowed) {
+      cudaFuncSetAttribute(moe_plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);
+      allowed = staged;
+    }
+    moe_plan_kernel<true><<<1, 1024, staged, stream>>>(topk_idx, n, E, offsets, order, inv);
+  } else {
+    moe_plan_kernel<false><<<1, 1024, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, offsets, order, inv);
+  }
   return check_launch("moe_plan");
 }

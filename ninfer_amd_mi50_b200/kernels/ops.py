@@ -32,6 +32,7 @@ TUNING = {
     "bf16_moe": "auto",           # "simt" | "auto"
     "skinny_max_rows": 16,        # dense products with more rows go to the library
     "skinny_moe_max_tokens": 128, # routed experts: tokens up to which the streaming kernel serves
+    "router_library_min_rows": 128,  # router logits of more rows than this are library products
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -279,16 +280,43 @@ class MoePlan:
     top_k: int
 
 
-def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool
+def split_router(w_router: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """A float32 routing matrix as bfloat16 `hi` plus bfloat16 `lo` with hi + lo = w to 16 bits
+    of mantissa; `lo` is None when the matrix is exactly bfloat16 (the usual checkpoint).
+    With them, router logits of many rows are tensor-core products whose every partial
+    product is exact and whose sums are float32."""
+    hi = w_router.to(torch.bfloat16)
+    rest = w_router - hi.to(torch.float32)
+    lo = rest.to(torch.bfloat16) if bool((rest != 0).any()) else None
+    return hi, lo
+
+
+def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool,
+                split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """Router logits (float32), softmax, top-k.  Rows of `w_router` beyond E give raw
-    logits back (`extra`, [T, rows - E]).  Returns (idx int32 [T, k], weights float32 [T, k], extra)."""
+    logits back (`extra`, [T, rows - E]).  Returns (idx int32 [T, k], weights float32 [T, k], extra).
+
+    With many bfloat16 rows and a `split` of the matrix (see `split_router`) the logits come
+    from library products with float32 output; otherwise from the float32 CUDA-core kernel."""
     _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
     T, H = x.shape
     extra = w_router.shape[0] - E
     idx = torch.empty((T, k), dtype=torch.int32, device=x.device)
     wts = torch.empty((T, k), dtype=torch.float32, device=x.device)
     ext = torch.empty((T, extra), dtype=torch.float32, device=x.device) if extra > 0 else None
+    if (split is not None and x.dtype == torch.bfloat16 and T > TUNING["router_library_min_rows"]
+            and TUNING["bf16_linear"] != "simt"):
+        try:
+            logits = torch.mm(x, split[0].t(), out_dtype=torch.float32)
+            if split[1] is not None:
+                logits += torch.mm(x, split[1].t(), out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            logits = None
+        if logits is not None:
+            _lib.call("nf_router_select", _p(logits), c_int(T), c_int(E), c_int(extra), c_int(k),
+                      c_int(1 if norm_topk else 0), _p(idx), _p(wts), _p(ext), _stream())
+            return idx, wts, ext
     logits = torch.empty((T, E + extra), dtype=torch.float32, device=x.device)
     _lib.call("nf_router_topk", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra),
               c_int(k), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext),

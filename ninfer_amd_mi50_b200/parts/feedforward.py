@@ -71,6 +71,7 @@ class SparseMoeSwiglu(FeedForward):
         self.shared_intermediate_size = int(shared_intermediate_size)
         self.prefix = prefix
         self.w_router = self.w13 = self.w2 = self.ws13 = self.ws2 = None
+        self.w_router_split = None
 
     @property
     def has_shared(self) -> bool:
@@ -99,6 +100,7 @@ class SparseMoeSwiglu(FeedForward):
             # one matrix yields the router logits and the shared expert's gate logit
             router = torch.cat([router, fetch(p + "shared_expert_gate.weight")], dim=0)
         self.w_router = router.contiguous()
+        self.w_router_split = kernels.split_router(self.w_router) if self.w_router.is_cuda else None
         first = fetch(f"{p}experts.0.gate_proj.weight")
         self.w13 = torch.empty((E, 2 * I, H), dtype=first.dtype, device=first.device)
         self.w2 = torch.empty((E, H, I), dtype=first.dtype, device=first.device)
@@ -126,7 +128,8 @@ class SparseMoeSwiglu(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         E, k = self.num_experts, self.top_k
-        idx, wts, gate = kernels.router_topk(x, self.w_router, E, k, self.norm_topk_prob)
+        idx, wts, gate = kernels.router_topk(x, self.w_router, E, k, self.norm_topk_prob,
+                                             split=self.w_router_split)
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
         plan = kernels.moe_plan(idx, E)

@@ -110,7 +110,11 @@ class MoePlan:
         self.num_experts, self.num_tokens, self.top_k = num_experts, num_tokens, top_k
 
 
-def router_topk(x, w_router, E, k, norm_topk):
+def split_router(w_router):
+    return None
+
+
+def router_topk(x, w_router, E, k, norm_topk, split=None):
     logits = _f(x) @ w_router.T
     extra = logits[:, E:].contiguous() if w_router.shape[0] > E else None
     p = torch.softmax(logits[:, :E], dim=-1)
@@ -198,7 +202,7 @@ def check_router_sizes(num_experts, top_k):
     pass
 
 
-NAMES = ["embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
+NAMES = ["split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
          "rope_append", "paged_attention", "router_topk", "moe_plan", "moe_gemm1", "moe_gemm2",
          "moe_combine", "argmax_rows"]
 

@@ -349,3 +349,22 @@ def test_grouped_gemm_on_tensor_cores(K, T, H, I, E, k):
     finally:
         K.TUNING.update(old)
     assert K.tensor_core_status() == 0
+
+
+@pytest.mark.parametrize("exact_bf16", [True, False])
+def test_router_many_rows_through_split_matrix(K, exact_bf16):
+    """More than 128 bfloat16 rows: the logits come from library products over the routing
+    matrix split into two bfloat16 halves (one half when the matrix is bfloat16 already)."""
+    T, H, E, k = 700, 512, 60, 4
+    x = rnd((T, H), torch.bfloat16, 61)
+    w = rnd((E + 1, H), torch.float32, 62, 0.1)
+    if exact_bf16:
+        w = w.to(torch.bfloat16).float()
+    split = K.split_router(w)
+    assert (split[1] is None) == exact_bf16
+    idx, wts, ext = K.router_topk(x, w, E, k, True, split=split)
+    ridx, rwts, rext = P.router_topk(x, w, E, k, True)
+    same = (idx == ridx).all(dim=1)
+    assert same.float().mean() > 0.995          # a tie within 2^-17 may fall the other way
+    torch.testing.assert_close(wts[same], rwts[same], rtol=2e-4, atol=1e-6)
+    torch.testing.assert_close(ext, rext, rtol=2e-4, atol=2e-5)
