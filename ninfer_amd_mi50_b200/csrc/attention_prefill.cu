@@ -56,7 +56,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [64][DS]
   __nv_bfloat16* KVs = Qs + kBQ * DS;                                     // [2 stages][K, V][64][DS]
-  const int seg = tiles[2 * blockIdx.x], row0 = tiles[2 * blockIdx.x + 1];
+  // tiles late in a long prompt have the most keys: start them first
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int seg = tiles[2 * tile], row0 = tiles[2 * tile + 1];
   const int h = blockIdx.y;
   const int kvh = h / (Hq / Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -155,6 +155,58 @@ moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict_
   }
 }
 
+// The same plan for many pairs, spread over the device.  Block e ranks the pairs of expert e
+// (in pair order, so token order is kept) and counts them; the second kernel turns counts into
+// offsets and scatters.
+__global__ void __launch_bounds__(256)
+moe_rank_kernel(const int* __restrict__ topk_idx, int n, int* __restrict__ counts, int* __restrict__ inv) {
+  __shared__ int warp_tot[8];
+  __shared__ int running_s;
+  const int e = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) running_s = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 256) {
+    const int i = base + threadIdx.x;
+    const bool mine = i < n && topk_idx[i] == e;
+    const unsigned b = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) warp_tot[warp] = __popc(b);
+    __syncthreads();
+    int before = running_s;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (mine) inv[i] = before + __popc(b & ((1u << lane) - 1u));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int t = 0;
+      for (int w = 0; w < 8; ++w) t += warp_tot[w];
+      running_s += t;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[e] = running_s;
+}
+
+__global__ void __launch_bounds__(256)
+moe_scatter_kernel(const int* __restrict__ topk_idx, int n, int E, const int* __restrict__ counts,
+                   int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv) {
+  extern __shared__ int off[];        // [E + 1]
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) { off[e] = run; run += counts[e]; }
+    off[E] = run;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int e = topk_idx[i];
+  if (e < 0 || e >= E) return;
+  const int p = off[e] + inv[i];
+  inv[i] = p;
+  order[p] = i;
+}
+
 }  // namespace nf
 
 using namespace nf;
@@ -208,9 +260,16 @@ extern "C" int nf_router_select(const float* logits, int T, int E, int extra, in
   return check_launch("router_select");
 }
 
+// counts: int32 scratch [E] (may be null: then one block does everything).
 extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int* order, int* inv,
-                           cudaStream_t stream) {
+                           int* counts, cudaStream_t stream) {
   NF_REQUIRE(n >= 0 && E > 0 && E <= 8192, "moe_plan: bad sizes n=%d E=%d", n, E);
+  if (n > 2048 && counts) {
+    moe_rank_kernel<<<E, 256, 0, stream>>>(topk_idx, n, counts, inv);
+    if (int rc = check_launch("moe_rank")) return rc;
+    moe_scatter_kernel<<<(n + 255) / 256, 256, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, counts, offsets, order, inv);
+    return check_launch("moe_scatter");
+  }
   const size_t staged = (size_t)(E + 1) * sizeof(int) + (size_t)n * sizeof(unsigned short);
   if (E < 65536 && staged <= 160 * 1024) {
     static size_t allowed = 48 * 1024;

@@ -331,8 +331,9 @@ def moe_plan(topk_idx: torch.Tensor, E: int) -> MoePlan:
     offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
     order = torch.empty((T * k,), dtype=torch.int32, device=dev)
     inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    counts = torch.empty((E,), dtype=torch.int32, device=dev)
     _lib.call("nf_moe_plan", _p(topk_idx), c_int(T * k), c_int(E), _p(offsets), _p(order), _p(inv),
-              _stream())
+              _p(counts), _stream())
     return MoePlan(offsets, order, inv, E, T, k)
 
 

@@ -25,6 +25,17 @@ from ..registry import register_part
 from .base import FeedForward, Fetch, StepContext, TensorSpec
 
 
+_FORK_MAX_ROWS = 64
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    key = str(device)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
 @register_part("feed_forward", "dense_swiglu")
 class DenseSwiglu(FeedForward):
     graph_safe = True
@@ -128,6 +139,16 @@ class SparseMoeSwiglu(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         E, k = self.num_experts, self.top_k
+        # The shared expert needs nothing from the router, so on small steps (where kernels are
+        # too short to fill the device) it runs beside the routed path on a second stream;
+        # inside a captured graph that becomes a parallel branch.
+        fork = self.has_shared and x.is_cuda and x.shape[0] <= _FORK_MAX_ROWS
+        shared = None
+        if fork:
+            main, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         idx, wts, gate = kernels.router_topk(x, self.w_router, E, k, self.norm_topk_prob,
                                              split=self.w_router_split)
         if SparseMoeSwiglu.record_routing is not None:
@@ -135,7 +156,8 @@ class SparseMoeSwiglu(FeedForward):
         plan = kernels.moe_plan(idx, E)
         act = kernels.moe_gemm1(x, self.w13, plan, k)
         y = kernels.moe_gemm2(act, self.w2, plan)
-        shared = None
-        if self.has_shared:
+        if fork:
+            main.wait_stream(side)
+        elif self.has_shared:
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         return kernels.moe_combine(y, plan, wts, shared, gate, x.dtype)
