@@ -4,11 +4,13 @@
 // Reference: ``prefill_attention_kernel<D>`` (src/ops/attention.hip:136-268): tiles of 16
 // queries x 32 keys, a software double buffer, causal mask on absolute positions so that a
 // later portion sees the keys of earlier ones, online softmax, never a T x T score matrix.
-// Same structure here with tensor cores: a CTA takes up to 64 consecutive rows of one
-// segment and one query head; its 4 warps own 16 rows each; keys and values come in blocks
+// Same structure here with tensor cores: a CTA takes up to 128 consecutive rows of one
+// segment and one query head; its 8 warps own 16 rows each; keys and values come in blocks
 // of 64 through ``cp.async`` into a two-stage shared-memory ring (rows padded by 16 bytes so
 // that ``ldmatrix`` is free of bank conflicts); S = Q K^T and O += P V are
-// ``mma.sync.m16n8k16`` with float32 accumulators; max, exp and sums are float32.
+// ``mma.sync.m16n8k16`` with float32 accumulators; max, exp and sums are float32 (the
+// exponential is ``ex2.approx`` on scores pre-multiplied by log2 e: 2^-22 relative, far below
+// the bfloat16 rounding of P that follows).
 // Key j is visible to a row at position p iff max(0, p - window + 1) <= j <= p.
 // Key blocks are aligned to multiples of 64 keys, so the order of a row's sums depends on
 // its own position only, not on how the prompt was cut.
@@ -16,7 +18,9 @@
 
 namespace nf {
 
-constexpr int kBQ = 64, kBKeys = 64;
+constexpr int kBQ = 128, kBKeys = 64;     // rows per CTA (8 warps x 16), keys per block
+constexpr int kThreads = 256;
+constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ void pf_cp_async16(void* smem_dst, const void* gmem_src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -45,7 +49,7 @@ __device__ __forceinline__ unsigned pf_pack(float lo, float hi) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kThreads)
 prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                          const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table,
                          int bt_width, const int* __restrict__ positions, const int* __restrict__ seg_row0,
@@ -54,7 +58,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   constexpr int DS = D + 8;             // padded row stride in elements
   constexpr int LPR = D / 8;            // 16-byte pieces per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [64][DS]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [128][DS]
   __nv_bfloat16* KVs = Qs + kBQ * DS;                                     // [2 stages][K, V][64][DS]
   // tiles late in a long prompt have the most keys: start them first
   const int tile = gridDim.x - 1 - blockIdx.x;
@@ -129,6 +133,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
     const __nv_bfloat16* Vs = Ks + kBKeys * DS;
     const int kb = kb_first + blk * kBKeys;
 
+    // a warp whose 16 rows lie beyond the tile's rows, or wholly before this block's keys,
+    // only helps with the copies
+    const bool warp_active = warp * 16 < n_rows && kb <= pos_first + warp * 16 + 15;
+    if (warp_active) {
     // ---- S = Q K^T for this warp's 16 rows x 64 keys -------------------------------------------
     float s[kBKeys / 8][4];
 #pragma unroll
@@ -148,21 +156,35 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
         pf_mma(s[n0 / 8 + 1], a0, a1, a2, a3, b2, b3);
       }
     }
-    // ---- scale, mask, online softmax -------------------------------------------------------------
+    // ---- scale (to base-2 exponent units), mask, online softmax ------------------------------------
     float mx[2] = {-INFINITY, -INFINITY};
+    const float sc2 = scale * kLog2e;
+    // every key of the block visible to every row of the warp: no mask to apply
+    const bool all_visible = warp * 16 + 15 < n_rows && kb + kBKeys - 1 <= pos_first + warp * 16 &&
+                             (window <= 0 || kb >= pos_first + warp * 16 + 15 - window + 1);
+    if (all_visible) {
 #pragma unroll
-    for (int n = 0; n < kBKeys / 8; ++n)
+      for (int n = 0; n < kBKeys / 8; ++n)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int j = kb + n * 8 + 2 * tq + (i & 1);
-        const bool hi_row = i >= 2;
-        const int p = hi_row ? p_hi : p_lo;
-        const int w = hi_row ? w_hi : w_lo;
-        const bool row_ok = (hi_row ? r_hi : r_lo) < n_rows;
-        const float v = (row_ok && j <= p && j >= w) ? s[n][i] * scale : -INFINITY;
-        s[n][i] = v;
-        mx[i >> 1] = fmaxf(mx[i >> 1], v);
-      }
+        for (int i = 0; i < 4; ++i) {
+          s[n][i] *= sc2;
+          mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
+        }
+    } else {
+#pragma unroll
+      for (int n = 0; n < kBKeys / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int j = kb + n * 8 + 2 * tq + (i & 1);
+          const bool hi_row = i >= 2;
+          const int p = hi_row ? p_hi : p_lo;
+          const int w = hi_row ? w_hi : w_lo;
+          const bool row_ok = (hi_row ? r_hi : r_lo) < n_rows;
+          const float v = (row_ok && j <= p && j >= w) ? s[n][i] * sc2 : -INFINITY;
+          s[n][i] = v;
+          mx[i >> 1] = fmaxf(mx[i >> 1], v);
+        }
+    }
     float alpha[2], m_use[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -170,7 +192,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float m_new = fmaxf(m_run[r], mx[r]);
       m_use[r] = m_new == -INFINITY ? 0.f : m_new;       // a row with nothing visible yet
-      alpha[r] = expf(m_run[r] - m_use[r]);
+      alpha[r] = exp2f(m_run[r] - m_use[r]);
       m_run[r] = m_new;
     }
     float sum[2] = {0.f, 0.f};
@@ -178,7 +200,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
     for (int n = 0; n < kBKeys / 8; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float p = expf(s[n][i] - m_use[i >> 1]);
+        const float p = exp2f(s[n][i] - m_use[i >> 1]);
         s[n][i] = p;
         sum[i >> 1] += p;
       }
@@ -209,6 +231,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
         pf_mma(o[d0 / 8 + 1], a0, a1, a2, a3, b2, b3);
       }
     }
+    }  // warp_active
     __syncthreads();      // everyone is done with this stage before the next prefetch overwrites it
   }
 
@@ -239,7 +262,7 @@ static int launch_prefill(const void* qkv, int q_row_stride, const void* pages, 
     set = true;
   }
   dim3 grid(n_tiles, Hq);
-  prefill_attention_kernel<D><<<grid, 128, smem, stream>>>(
+  prefill_attention_kernel<D><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions,
       seg_row0, tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size, num_pages, window, scale);
   return check_launch("prefill_attention");
@@ -252,7 +275,7 @@ using namespace nf;
 extern "C" int nf_prefill_attention_tile_rows() { return kBQ; }
 
 // bfloat16; head_dim a multiple of 16 up to 128.  `tiles` is int32 [n_tiles, 2] of (segment,
-// first row): at most 64 consecutive rows of one segment each.
+// first row): at most 128 consecutive rows of one segment each.
 extern "C" int nf_prefill_attention(const void* qkv, int q_row_stride, const void* pages,
                                     const int* block_table, int bt_width, const int* positions,
                                     const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,

@@ -16,8 +16,14 @@
 // expert's rows come from L2.  Ragged row counts cost at most 15 padded columns, not a
 // half-empty 128-row tile.
 //
-// Machinery: operands arrive by TMA (`cp.async.bulk.tensor.2d`, 128-byte swizzle) into a
-// ring of shared-memory stages guarded by mbarriers; one elected thread issues the MMAs,
+// Weights are held *packed* (see kernels/ops.py `pack_weights`): tiles of 128 rows x 64 k,
+// stored contiguously in the order a CTA reads them and already in the 128-byte-swizzled
+// image the tensor core expects, so a stage's weights are one contiguous `cp.async.bulk`
+// copy (32 KB for gate + up) - a stream of whole DRAM pages instead of 128-byte pieces 4 KB
+// apart.  The expert's token rows arrive by TMA tensor copies (`cp.async.bulk.tensor.2d`,
+// 128-byte swizzle, boxes of 64 rows, as many as the pass has rows).  Both land in a ring of
+// shared-memory stages guarded by mbarriers, as deep as shared memory allows for this
+// expert's row count; one elected thread issues the MMAs,
 // whose float32 accumulators live in tensor memory (gate in columns [0, 256), up in
 // [256, 512)); `tcgen05.commit` hands stages back to the producer and the finished
 // accumulator to four epilogue warps, which read it with `tcgen05.ld`, apply the epilogue
@@ -37,6 +43,9 @@ constexpr int kBK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle
 constexpr int kBNMax = 256;       // tokens per pass (MMA N, columns of one accumulator)
 constexpr int kTmemCols = 512;
 constexpr unsigned kPollLimit = 1u << 24;
+constexpr int kXBox = 64;         // token rows per TMA box
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 226 * 1024;   // + 1 KB of alignment slack = the 227 KB a CTA may have
 
 __device__ int g_tc_error = 0;
 
@@ -74,6 +83,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, void* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -115,24 +129,22 @@ __device__ __forceinline__ unsigned instr_desc(int n) {
 }
 
 struct __align__(8) Barriers {
-  unsigned long long full[4], empty[4], acc_full, acc_empty;
+  unsigned long long full[kMaxStages], empty[kMaxStages], acc_full, acc_empty;
   unsigned tmem_base;
   int stop;
 };
 
 // grid (feature tiles, groups); 192 threads: warp 0 producer, warp 1 MMA + tensor memory,
-// warps 2..5 epilogue.
-template <bool SWIGLU, int STAGES>
+// warps 2..5 epilogue.  Wp: packed weights [groups][feature tiles][k tiles][A_ROWS][64].
+template <bool SWIGLU>
 __global__ void __launch_bounds__(192, 1)
-grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_constant__ CUtensorMap map_x,
                        const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int ldo,
-                       int n_features, int K, int w_rows_per_group) {
+                       int n_features, int K) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = kBM * kBK * 2, B_BYTES = kBNMax * kBK * 2;
-  constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * A_BYTES + B_BYTES;
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
-  volatile int* stop = &bars->stop;
+  constexpr int A_BYTES = (SWIGLU ? 2 : 1) * kBM * kBK * 2;     // gate (+ up) tile
+  constexpr int BOX_BYTES = kXBox * kBK * 2;
 
   const int group = blockIdx.y;
   const int row_begin = offsets[group], row_end = offsets[group + 1];
@@ -142,9 +154,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const int n_rows = row_end - row_begin;
   const int n_passes = (n_rows + kBNMax - 1) / kBNMax;
   const int k_steps = (K + kBK - 1) / kBK;
+  const int n_ftiles = gridDim.x;
+  // stage geometry for this expert: weights + as many 64-row boxes as its largest pass needs
+  const int max_boxes = (min(n_rows, kBNMax) + kXBox - 1) / kXBox;
+  const int stage_bytes = A_BYTES + max_boxes * BOX_BYTES;
+  const int stages = min(kMaxStages, (kSmemBudget - (int)sizeof(Barriers)) / stage_bytes);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + (size_t)stages * stage_bytes);
+  volatile int* stop = &bars->stop;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->acc_empty, 4);
     bars->stop = 0;
@@ -162,29 +181,30 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------
     if (lane == 0) {
-      const int w_row_gate = group * w_rows_per_group + f0;
-      const int w_row_up = w_row_gate + n_features;         // SwiGLU: the up rows follow the gate rows
+      const unsigned char* w_tile = reinterpret_cast<const unsigned char*>(Wp) +
+                                    ((size_t)group * n_ftiles + blockIdx.x) * k_steps * A_BYTES;
       int it = 0, issued = 0;
       bool ok = true;
       for (int pass = 0; pass < n_passes && ok; ++pass) {
         const int x_row = row_begin + pass * kBNMax;
+        const int boxes = (min(kBNMax, n_rows - pass * kBNMax) + kXBox - 1) / kXBox;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(&bars->empty[s], ((it / STAGES) & 1) ^ 1, stop, 1)) { ok = false; break; }
-          unsigned char* st = smem + s * STAGE_BYTES;
-          mbar_expect_tx(&bars->full[s], STAGE_BYTES);
-          tma_load_2d(st, &map_w, ks * kBK, w_row_gate, &bars->full[s]);
-          if (SWIGLU) tma_load_2d(st + A_BYTES, &map_w, ks * kBK, w_row_up, &bars->full[s]);
-          tma_load_2d(st + (SWIGLU ? 2 : 1) * A_BYTES, &map_x, ks * kBK, x_row, &bars->full[s]);
+          const int s = it % stages;
+          if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1)) { ok = false; break; }
+          unsigned char* st = smem + (size_t)s * stage_bytes;
+          mbar_expect_tx(&bars->full[s], A_BYTES + boxes * BOX_BYTES);
+          bulk_load(st, w_tile + (size_t)ks * A_BYTES, A_BYTES, &bars->full[s]);
+          for (int b = 0; b < boxes; ++b)
+            tma_load_2d(st + A_BYTES + b * BOX_BYTES, &map_x, ks * kBK, x_row + b * kXBox, &bars->full[s]);
           issued = it + 1;
         }
       }
       if (!ok) {
         // copies already asked for still land in this CTA's shared memory: wait for them
-        for (int j = max(0, issued - STAGES); j < issued; ++j) {
-          const int s = j % STAGES;
+        for (int j = max(0, issued - stages); j < issued; ++j) {
+          const int s = j % stages;
           for (unsigned i = 0; i < (1u << 20); ++i)
-            if (mbar_try(&bars->full[s], (j / STAGES) & 1)) break;
+            if (mbar_try(&bars->full[s], (j / stages) & 1)) break;
         }
       }
     }
@@ -199,13 +219,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         const int n = min(kBNMax, (n_rows - pass * kBNMax + 15) & ~15);
         const unsigned idesc = instr_desc(n);
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(&bars->full[s], (it / STAGES) & 1, stop, 3)) { ok = false; break; }
+          const int s = it % stages;
+          if (!mbar_wait(&bars->full[s], (it / stages) & 1, stop, 3)) { ok = false; break; }
           tc_fence_after();
-          unsigned char* st = smem + s * STAGE_BYTES;
+          unsigned char* st = smem + (size_t)s * stage_bytes;
           const unsigned long long a0 = smem_desc(st);
-          const unsigned long long a1 = smem_desc(st + A_BYTES);
-          const unsigned long long b = smem_desc(st + (SWIGLU ? 2 : 1) * A_BYTES);
+          const unsigned long long a1 = smem_desc(st + kBM * kBK * 2);
+          const unsigned long long b = smem_desc(st + A_BYTES);
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) {
             // 16 k = 32 bytes further along the swizzled row: +2 in the address field
@@ -292,21 +312,20 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
-template <bool SWIGLU, int STAGES>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const int* offsets, void* out, int ldo,
-                     int n_features, int K, int w_rows_per_group, int groups, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * kBM * kBK * 2 + kBNMax * kBK * 2;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+template <bool SWIGLU>
+static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, void* out, int ldo,
+                     int n_features, int K, int groups, cudaStream_t stream) {
+  const size_t smem = (size_t)kSmemBudget + 1024;
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<SWIGLU, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<SWIGLU>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     NF_REQUIRE(e == cudaSuccess, "grouped_gemm_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     set = true;
   }
   dim3 grid((n_features + kBM - 1) / kBM, groups);
-  grouped_gemm_tc_kernel<SWIGLU, STAGES><<<grid, 192, smem, stream>>>(mw, mx, offsets, (__nv_bfloat16*)out, ldo,
-                                                                     n_features, K, w_rows_per_group);
+  grouped_gemm_tc_kernel<SWIGLU><<<grid, 192, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
+                                                             (__nv_bfloat16*)out, ldo, n_features, K);
   return check_launch("grouped_gemm_tc");
 }
 
@@ -314,24 +333,23 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const int* of
 
 using namespace nf;
 
-// out[p, :n_features] for sorted rows p of every group; X holds the rows in sorted order
-// ([total_rows, K], already gathered), W is [groups, w_rows, K] with w_rows = 2 * n_features
-// (gate rows then up rows) for the SwiGLU form, else n_features.
-// Needs K % 8 == 0 and 16-byte aligned bases (TMA).
-extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const void* W, int groups,
+// out[p, :n_features] for sorted rows p of every group.  X holds the rows in sorted order
+// ([total_rows, K], already gathered).  Wp holds the groups' weights packed as
+// [groups][ceil(n_features / 128)][ceil(K / 64)][128 or 256 rows][64], each tile in the
+// 128-byte-swizzled image (SwiGLU: 128 gate rows then the 128 matching up rows per tile),
+// zero-padded.  Needs K % 8 == 0 and a 16-byte aligned X (TMA).
+extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const void* Wp, int groups,
                                   int n_features, int K, const int* offsets, void* out, int ldo,
                                   int swiglu, cudaStream_t stream) {
   if (total_rows == 0) return 0;
   NF_REQUIRE(total_rows > 0 && groups > 0 && n_features > 0 && K > 0, "grouped_gemm_tc: bad sizes");
   NF_REQUIRE(K % 8 == 0, "grouped_gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
-  NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "grouped_gemm_tc: operands must be 16-byte aligned");
+  NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)Wp % 16 == 0), "grouped_gemm_tc: operands must be 16-byte aligned");
   NF_REQUIRE(groups <= 65535, "grouped_gemm_tc: too many groups");
-  const int w_rows = swiglu ? 2 * n_features : n_features;
-  CUtensorMap mw, mx;
-  if (int rc = make_map(&mw, W, (long long)groups * w_rows, K, kBM)) return rc;
-  if (int rc = make_map(&mx, X, total_rows, K, kBNMax)) return rc;
-  if (swiglu) return launch_tc<true, 3>(mw, mx, offsets, out, ldo, n_features, K, w_rows, groups, stream);
-  return launch_tc<false, 4>(mw, mx, offsets, out, ldo, n_features, K, w_rows, groups, stream);
+  CUtensorMap mx;
+  if (int rc = make_map(&mx, X, total_rows, K, kXBox)) return rc;
+  if (swiglu) return launch_tc<true>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
+  return launch_tc<false>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
 }
 
 // 0 if no tensor-core kernel has given up on a wait since the last call; else the code of the

@@ -42,7 +42,11 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
 }
 
 // NT: number of 8-row tiles of X a CTA covers (rows <= 8 * NT).
-template <int NT, bool SWIGLU, typename TC>
+// PACKED: W is held as tiles of 128 (SwiGLU: 128 gate + 128 up) rows x 64 k, contiguous per
+// (feature tile, k tile) and 128-byte swizzled (16-byte piece j of row r sits at j ^ (r & 7)),
+// zero-padded: the layout the tensor-core kernel streams.  A CTA's 16 rows of one k tile are
+// then 2 KB of contiguous memory instead of 16 pieces 2 K bytes apart.
+template <int NT, bool SWIGLU, bool PACKED, typename TC>
 __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
@@ -74,6 +78,17 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   }
   const __nv_bfloat16* w0 = Wg + (size_t)wr0 * K + 8 * t;
   const __nv_bfloat16* w1 = Wg + (size_t)wr1 * K + 8 * t;
+  // packed form: tile row of each of the lane's two rows, and the tile strides
+  constexpr int TROWS = SWIGLU ? 256 : 128;
+  const int ktiles = (K + 63) >> 6;
+  int pr0 = 0, pr1 = 0;
+  size_t ptile = 0;
+  if (PACKED) {
+    const int f = n0 + g;                      // < padded N by construction of the grid
+    ptile = (size_t)(f >> 7) * ktiles * (TROWS * 64);
+    if (SWIGLU) { pr0 = f & 127; pr1 = 128 + (f & 127); }
+    else { pr0 = f & 127; pr1 = (f + 8) & 127; }   // f + 8 stays inside the tile: n0 is a multiple of 16
+  }
 
   // X rows of this lane: row g of every 8-row tile
   const __nv_bfloat16* xp[NT];
@@ -97,7 +112,13 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int k = (c0 + u * kWarps) * 32;
-      if (k + 8 * t + 8 <= K && c0 + u * kWarps < nchunks) {
+      if (PACKED && c0 + u * kWarps < nchunks) {
+        const int kk = k + 8 * t;                   // < padded K: the padding holds zeros
+        const __nv_bfloat16* tile = Wg + ptile + (size_t)(kk >> 6) * (TROWS * 64);
+        const int j = (kk >> 3) & 7;
+        a[u] = ld_stream(tile + pr0 * 64 + ((j ^ (pr0 & 7)) << 3));
+        b[u] = ld_stream(tile + pr1 * 64 + ((j ^ (pr1 & 7)) << 3));
+      } else if (!PACKED && k + 8 * t + 8 <= K && c0 + u * kWarps < nchunks) {
         a[u] = ld_stream(w0 + k);
         b[u] = ld_stream(w1 + k);
       } else {
@@ -151,26 +172,28 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   }
 }
 
-template <int NT, bool SWIGLU, typename TC>
+template <int NT, bool SWIGLU, bool PACKED, typename TC>
 static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M, int N,
                      int K, int groups, int max_rows, const int* offsets, const int* x_rows, int x_div,
                      cudaStream_t stream) {
   const int feat = SWIGLU ? 8 : 16;
   dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, groups);
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
-  skinny_gemm_kernel<NT, SWIGLU, TC><<<grid, kWarps * 32, 0, stream>>>(
+  skinny_gemm_kernel<NT, SWIGLU, PACKED, TC><<<grid, kWarps * 32, 0, stream>>>(
       (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows, x_div);
   return check_launch("skinny_gemm");
 }
 
 template <bool SWIGLU, typename TC>
-static int launch_sw(int nt, const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M,
+static int launch_sw(int nt, bool packed, const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M,
                      int N, int K, int groups, int max_rows, const int* offsets, const int* x_rows,
                      int x_div, cudaStream_t stream) {
-  switch (nt) {
-    case 1: return launch_nt<1, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-    default: return launch_nt<2, SWIGLU, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  if (packed) {
+    if (nt == 1) return launch_nt<1, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    return launch_nt<2, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
   }
+  if (nt == 1) return launch_nt<1, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  return launch_nt<2, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
 }
 
 }  // namespace nf
@@ -180,10 +203,11 @@ using namespace nf;
 // Y[M, N] = epilogue(X[M, K] W[g]^T), bfloat16 inputs, float32 accumulation.
 // out_dtype: 1 bfloat16, 0 float32.  max_rows: bound on the rows of any one group.
 // Needs K % 8 == 0 and 16-byte aligned rows (ldx % 8 == 0, bases aligned).
+// packed != 0: W is in the packed tile layout (w_group_stride then counts packed elements).
 extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w_group_stride, void* Y,
                               int ldy, int M, int N, int K, int groups, int max_rows,
                               const int* offsets, const int* x_rows, int x_div, int swiglu,
-                              int out_dtype, cudaStream_t stream) {
+                              int out_dtype, int packed, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && x_div > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   NF_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "skinny_gemm: K=%d and the row stride %d must be multiples of 8", K, ldx);
@@ -196,9 +220,9 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   const size_t wgs = (size_t)w_group_stride;
   if (swiglu) {
     NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");
-    return launch_sw<true, __nv_bfloat16>(nt, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
   }
   if (out_dtype == kBF16)
-    return launch_sw<false, __nv_bfloat16>(nt, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-  return launch_sw<false, float>(nt, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    return launch_sw<false, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
 }

@@ -39,7 +39,7 @@ SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)   # head sizes of the split-key decode kernel
 DECODE_SPLIT = 128                          # keys per block of that kernel
 PREFILL_HEAD_DIMS = tuple(range(16, 129, 16))   # head sizes of the flash prefill kernel
-PREFILL_TILE_ROWS = 64                      # query rows per CTA of that kernel
+PREFILL_TILE_ROWS = 128                     # query rows per CTA of that kernel
 MAX_EXPERTS = 3072
 
 
@@ -134,11 +134,65 @@ def _gemm_simt(a, lda, b, b_group_stride, c, M, N, K, groups, max_rows, offsets,
               c_int(_dt(c)), _stream())
 
 
-def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu) -> None:
+def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu,
+            packed=False) -> None:
     _lib.call("nf_skinny_gemm", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
               c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
               _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
-              _stream())
+              c_int(1 if packed else 0), _stream())
+
+
+class PackedWeights:
+    """Grouped bfloat16 weights [G, rows, K] in the tile layout the streaming kernels read.
+
+    Tiles of 128 rows x 64 k (SwiGLU: 128 gate rows followed by the 128 matching up rows),
+    stored contiguously as [group][feature tile][k tile][tile rows][64], each tile in the
+    128-byte-swizzled image (the 16-byte piece j of tile row r is stored at piece j ^ (r & 7)),
+    zero-padded to whole tiles.  A CTA that owns 128 features reads one contiguous slab."""
+
+    def __init__(self, data: torch.Tensor, groups: int, n_features: int, K: int, swiglu: bool):
+        self.data, self.groups, self.n_features, self.K, self.swiglu = data, groups, n_features, K, swiglu
+        self.dtype, self.device = data.dtype, data.device
+
+    @property
+    def group_stride(self) -> int:
+        return self.data[0].numel()
+
+    def nbytes(self) -> int:
+        return self.data.numel() * self.data.element_size()
+
+    def group_nbytes(self) -> int:
+        return self.group_stride * self.data.element_size()
+
+
+def can_pack(n_features: int, K: int) -> bool:
+    return K % 8 == 0
+
+
+def pack_weights(w: torch.Tensor, swiglu: bool, chunk: int = 4) -> PackedWeights:
+    """[G, rows, K] bfloat16 (rows = 2 * features with gate rows first when `swiglu`) -> packed."""
+    _chk(w, "w", torch.bfloat16)
+    G, R, K = w.shape
+    N = R // 2 if swiglu else R
+    NT, KT = (N + 127) // 128, (K + 63) // 64
+    rows = 256 if swiglu else 128
+    out = torch.empty((G, NT, KT, rows, 64), dtype=w.dtype, device=w.device)
+    r = torch.arange(rows, device=w.device)
+    src_piece = (torch.arange(8, device=w.device)[None, :] ^ (r[:, None] & 7))       # [rows, 8]
+    for g0 in range(0, G, chunk):
+        blk = w[g0:g0 + chunk]
+        n = blk.shape[0]
+        halves = [blk[:, :N], blk[:, N:]] if swiglu else [blk]
+        tiles = []
+        for h in halves:
+            p = torch.zeros((n, NT * 128, KT * 64), dtype=w.dtype, device=w.device)
+            p[:, :N, :K] = h
+            tiles.append(p.view(n, NT, 128, KT, 64).permute(0, 1, 3, 2, 4))             # [n, NT, KT, 128, 64]
+        t = torch.cat(tiles, dim=3) if swiglu else tiles[0]                            # [n, NT, KT, rows, 64]
+        t = t.reshape(n, NT, KT, rows, 8, 8)
+        idx = src_piece.view(1, 1, 1, rows, 8, 1).expand(n, NT, KT, rows, 8, 8)
+        out[g0:g0 + n] = torch.gather(t, 4, idx).reshape(n, NT, KT, rows, 64)
+    return PackedWeights(out, G, N, K, swiglu)
 
 
 def _bf16_path(rows: int, K: int, key: str) -> str:
@@ -148,8 +202,8 @@ def _bf16_path(rows: int, K: int, key: str) -> str:
     limit = TUNING["skinny_max_rows"] if key == "bf16_linear" else TUNING["skinny_moe_max_tokens"]
     if rows <= limit and K % 8 == 0:
         return "skinny"
-    if key == "bf16_moe" and K % 8:
-        return "simt"          # the tensor-core kernel's TMA copies need 16-byte rows
+    if key == "bf16_moe":
+        return "simt"          # unpacked expert weights and many tokens: the CUDA-core product
     return "large"
 
 
@@ -337,44 +391,70 @@ def moe_plan(topk_idx: torch.Tensor, E: int) -> MoePlan:
     return MoePlan(offsets, order, inv, E, T, k)
 
 
-def moe_gemm1(x: torch.Tensor, w13: torch.Tensor, plan: MoePlan, k: int) -> torch.Tensor:
-    """Sorted pair p (token order[p] // k, expert e) -> silu(x Wgate_e^T) * (x Wup_e^T)  [T*k, I]."""
-    _chk(x, "x"); _chk(w13, "w13", x.dtype)
+def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
+    """Sorted pair p (token order[p] // k, expert e) -> silu(x Wgate_e^T) * (x Wup_e^T)  [T*k, I].
+
+    `w13` is [E, 2I, H] (gate rows first), or `PackedWeights` of it for the bfloat16 kernels."""
+    _chk(x, "x")
     T, H = x.shape
-    E, two_i, _ = w13.shape
-    inner = two_i // 2
+    packed = isinstance(w13, PackedWeights)
+    if packed:
+        E, inner = w13.groups, w13.n_features
+        if x.dtype != torch.bfloat16 or w13.K != H or not w13.swiglu:
+            raise ValueError("moe_gemm1: packed weights do not fit the activations")
+    else:
+        _chk(w13, "w13", x.dtype)
+        E, two_i, _ = w13.shape
+        inner = two_i // 2
     act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
     if T == 0:
+        return act
+    if packed:
+        if T <= TUNING["skinny_moe_max_tokens"]:
+            _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
+                    k, True, packed=True)
+        else:
+            # rows in sorted order, then one tensor-core launch over all experts
+            xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
+            _lib.call("nf_gather_rows", _p(x), _p(plan.order), c_int(k), _p(xp), c_int(T * k),
+                      c_int(H * 2), _stream())
+            _lib.call("nf_grouped_gemm_tc", _p(xp), c_longlong(T * k), _p(w13.data), c_int(E),
+                      c_int(inner), c_int(H), _p(plan.offsets), _p(act), c_int(inner), c_int(1), _stream())
         return act
     path = "simt" if x.dtype == torch.float32 else _bf16_path(T, H, "bf16_moe")
     if path == "skinny":
         _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
-    elif path == "large":
-        # rows in sorted order, then one tensor-core launch over all experts
-        xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
-        _lib.call("nf_gather_rows", _p(x), _p(plan.order), c_int(k), _p(xp), c_int(T * k),
-                  c_int(H * 2), _stream())
-        _lib.call("nf_grouped_gemm_tc", _p(xp), c_longlong(T * k), _p(w13), c_int(E), c_int(inner),
-                  c_int(H), _p(plan.offsets), _p(act), c_int(inner), c_int(1), _stream())
     else:
         _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
     return act
 
 
-def moe_gemm2(act: torch.Tensor, w2: torch.Tensor, plan: MoePlan) -> torch.Tensor:
-    """Sorted pair p of expert e -> act[p] Wdown_e^T  [T*k, H]."""
-    _chk(act, "act"); _chk(w2, "w2", act.dtype)
+def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan) -> torch.Tensor:
+    """Sorted pair p of expert e -> act[p] Wdown_e^T  [T*k, H].  `w2` is [E, H, I] or packed."""
+    _chk(act, "act")
     n, inner = act.shape
-    E, H, _ = w2.shape
+    packed = isinstance(w2, PackedWeights)
+    if packed:
+        E, H = w2.groups, w2.n_features
+        if act.dtype != torch.bfloat16 or w2.K != inner or w2.swiglu:
+            raise ValueError("moe_gemm2: packed weights do not fit the activations")
+    else:
+        _chk(w2, "w2", act.dtype)
+        E, H, _ = w2.shape
     y = torch.empty((n, H), dtype=act.dtype, device=act.device)
     if n == 0:
+        return y
+    if packed:
+        if plan.num_tokens <= TUNING["skinny_moe_max_tokens"]:
+            _skinny(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens, plan.offsets,
+                    None, 1, False, packed=True)
+        else:
+            _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2.data), c_int(E), c_int(H),
+                      c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())
         return y
     path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
     if path == "skinny":
         _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
-    elif path == "large":
-        _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2), c_int(E), c_int(H),
-                  c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())
     else:
         _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
     return y

@@ -121,6 +121,11 @@ class SparseMoeSwiglu(FeedForward):
             self.w13[e, I:].copy_(fetch(q + "up_proj.weight"))
             self.w2[e].copy_(fetch(q + "down_proj.weight"))
         del first
+        if (self.w13.is_cuda and self.w13.dtype == torch.bfloat16 and kernels.can_pack(I, H)
+                and kernels.can_pack(H, I)):
+            # the bfloat16 kernels stream the experts from a tile layout; the row-major form goes
+            self.w13 = kernels.pack_weights(self.w13, swiglu=True)
+            self.w2 = kernels.pack_weights(self.w2, swiglu=False)
         if self.has_shared:
             q = p + "shared_expert."
             self.ws13 = torch.cat([fetch(q + "gate_proj.weight"), fetch(q + "up_proj.weight")],
@@ -128,14 +133,19 @@ class SparseMoeSwiglu(FeedForward):
             self.ws2 = fetch(q + "down_proj.weight")
 
     def weight_bytes(self) -> int:
-        n = self.w_router.numel() * 4 + (self.w13.numel() + self.w2.numel()) * self.w2.element_size()
+        n = self.w_router.numel() * 4 + self._expert_total_bytes()
         if self.has_shared:
             n += (self.ws13.numel() + self.ws2.numel()) * self.ws2.element_size()
         return n
 
+    def _expert_total_bytes(self) -> int:
+        if isinstance(self.w13, kernels.PackedWeights):
+            return self.w13.nbytes() + self.w2.nbytes()
+        return (self.w13.numel() + self.w2.numel()) * self.w2.element_size()
+
     def expert_bytes(self) -> int:
         """Bytes of one routed expert's matrices."""
-        return (self.w13[0].numel() + self.w2[0].numel()) * self.w2.element_size()
+        return self._expert_total_bytes() // self.num_experts
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         E, k = self.num_experts, self.top_k

@@ -194,6 +194,14 @@ def argmax_rows(logits):
     return torch.argmax(logits, dim=-1).to(torch.int32)
 
 
+def can_pack(n_features, K):
+    return False
+
+
+class PackedWeights:
+    pass
+
+
 def check_head_dim(head_dim):
     pass
 
@@ -202,7 +210,7 @@ def check_router_sizes(num_experts, top_k):
     pass
 
 
-NAMES = ["split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
+NAMES = ["can_pack", "PackedWeights", "split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
          "rope_append", "paged_attention", "router_topk", "moe_plan", "moe_gemm1", "moe_gemm2",
          "moe_combine", "argmax_rows"]
 
