@@ -4,8 +4,9 @@
 // Reference: ``prefill_attention_kernel<D>`` (src/ops/attention.hip:136-268): tiles of 16
 // queries x 32 keys, a software double buffer, causal mask on absolute positions so that a
 // later portion sees the keys of earlier ones, online softmax, never a T x T score matrix.
-// Same structure here with tensor cores: a CTA takes up to 128 consecutive rows of one
-// segment and one query head; its 8 warps own 16 rows each; keys and values come in blocks
+// Same structure here with tensor cores: a tile is up to 64 consecutive rows of one segment
+// and one query head, 16 rows per warp; a CTA runs two tiles one after the other, a heavy one
+// (late in a long prompt, many keys) and a light one, so that CTAs are about equally long; keys and values come in blocks
 // of 64 through ``cp.async`` into a two-stage shared-memory ring (rows padded by 16 bytes so
 // that ``ldmatrix`` is free of bank conflicts); S = Q K^T and O += P V are
 // ``mma.sync.m16n8k16`` with float32 accumulators; max, exp and sums are float32 (the
@@ -18,8 +19,8 @@
 
 namespace nf {
 
-constexpr int kBQ = 128, kBKeys = 64;     // rows per CTA (8 warps x 16), keys per block
-constexpr int kThreads = 256;
+constexpr int kBQ = 64, kBKeys = 64;      // rows per tile (4 warps x 16), keys per block
+constexpr int kThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ void pf_cp_async16(void* smem_dst, const void* gmem_src) {
@@ -58,12 +59,12 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
   constexpr int DS = D + 8;             // padded row stride in elements
   constexpr int LPR = D / 8;            // 16-byte pieces per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [128][DS]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [64][DS]
   __nv_bfloat16* KVs = Qs + kBQ * DS;                                     // [2 stages][K, V][64][DS]
-  // tiles late in a long prompt have the most keys: start them first
-  const int tile = gridDim.x - 1 - blockIdx.x;
-  const int seg = tiles[2 * tile], row0 = tiles[2 * tile + 1];
   const int h = blockIdx.y;
+  for (int which = 0; which < 2; ++which) {
+  const int seg = tiles[4 * blockIdx.x + 2 * which], row0 = tiles[4 * blockIdx.x + 2 * which + 1];
+  if (seg < 0) break;
   const int kvh = h / (Hq / Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -248,6 +249,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride
       *reinterpret_cast<unsigned*>(dst + n * 8 + 2 * tq) = v;
     }
   }
+  __syncthreads();      // the next tile reuses the shared memory
+  }  // which
 }
 
 template <int D>
@@ -274,8 +277,9 @@ using namespace nf;
 
 extern "C" int nf_prefill_attention_tile_rows() { return kBQ; }
 
-// bfloat16; head_dim a multiple of 16 up to 128.  `tiles` is int32 [n_tiles, 2] of (segment,
-// first row): at most 128 consecutive rows of one segment each.
+// bfloat16; head_dim a multiple of 16 up to 128.  `tiles` is int32 [n_ctas, 2, 2]: for every CTA two
+// tiles as (segment, first row), each at most 64 consecutive rows of one segment; the second may
+// be (-1, -1).
 extern "C" int nf_prefill_attention(const void* qkv, int q_row_stride, const void* pages,
                                     const int* block_table, int bt_width, const int* positions,
                                     const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,

@@ -54,6 +54,71 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
   }
 }
 
+// Four elements a thread per step (float4 of h, 4 values of delta / out); same sums in the
+// same order per thread as the scalar kernel would give with a stride of 4 * blockDim.
+__device__ __forceinline__ void load4(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T, bool GATHER>
+__global__ void add_rmsnorm_x4_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                      const int* __restrict__ rows, const float* __restrict__ w,
+                                      float eps, T* __restrict__ out, int hidden) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int src = GATHER ? rows[r] : r;
+  float* hr = h + (size_t)src * hidden;
+  const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  T* o = out + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float v[4];
+    load4(hr + i, v);
+    if (dr) {
+      float d[4];
+      load4(dr + i, d);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] += d[e];
+      if (!GATHER) store4(hr + i, v);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float v[4], wv[4];
+    load4(hr + i, v);
+    if (GATHER && dr) {
+      float d[4];
+      load4(dr + i, d);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] += d[e];
+    }
+    load4(w + i, wv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * wv[e];
+    store4(o + i, v);
+  }
+}
+
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, int inner) {
   const int m = blockIdx.x;
@@ -168,6 +233,18 @@ extern "C" int nf_add_rmsnorm(float* h, const void* delta, const int* rows, cons
                               cudaStream_t stream) {
   if (R == 0) return 0;
   NF_REQUIRE(R > 0 && hidden > 0, "add_rmsnorm: bad sizes R=%d hidden=%d", R, hidden);
+  if (hidden % 4 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+      (!delta || (uintptr_t)delta % 16 == 0)) {
+    const int t4 = row_threads(hidden / 4);
+    if (dtype == kF32) {
+      if (rows) add_rmsnorm_x4_kernel<float, true><<<R, t4, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);
+      else add_rmsnorm_x4_kernel<float, false><<<R, t4, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);
+    } else {
+      if (rows) add_rmsnorm_x4_kernel<__nv_bfloat16, true><<<R, t4, 0, stream>>>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
+      else add_rmsnorm_x4_kernel<__nv_bfloat16, false><<<R, t4, 0, stream>>>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
+    }
+    return check_launch("add_rmsnorm");
+  }
   const int th = row_threads(hidden);
   if (dtype == kF32) {
     if (rows) add_rmsnorm_kernel<float, true><<<R, th, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);

@@ -77,6 +77,71 @@ rope_append_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
   }
 }
 
+// bfloat16, rotation over the whole head (rot == D, D % 16 == 0): a thread owns 8 consecutive
+// dims of the low half and the 8 matching dims of the high half of one head, 16 bytes each way.
+__global__ void __launch_bounds__(256)
+rope_append_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
+                          const int* __restrict__ positions, const int* __restrict__ row_seg,
+                          const float* __restrict__ inv_freq, int Hq, int Hkv, int D,
+                          __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table,
+                          int bt_width, int page_size, int num_pages, int append) {
+  extern __shared__ float cs[];            // [D/2] cos, [D/2] sin
+  const int t = blockIdx.x;
+  const int half = D / 2;
+  const int pos = positions[t];
+  const float fpos = (float)pos;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = fpos * inv_freq[i];
+    cs[i] = cosf(angle);
+    cs[half + i] = sinf(angle);
+  }
+  __syncthreads();
+  const int W = (Hq + 2 * Hkv) * D;
+  __nv_bfloat16* x = qkv + (size_t)t * W;
+  __nv_bfloat16* kdst = nullptr;
+  if (append) {
+    const int seg = row_seg[t];
+    const int lp = pos / page_size;
+    const int page = (lp >= 0 && lp < bt_width) ? block_table[(size_t)seg * bt_width + lp] : -1;
+    if (page >= 0 && page < num_pages)
+      kdst = pages + ((size_t)page * 2 * Hkv * page_size + (size_t)(pos - lp * page_size)) * D;
+  }
+  const size_t kv_head_stride = (size_t)page_size * D;
+  const int groups = half / 8;             // 8-dim groups per half head
+  const int heads = append ? Hq + 2 * Hkv : Hq;
+  for (int idx = threadIdx.x; idx < heads * groups; idx += blockDim.x) {
+    const int head = idx / groups, gi = idx - head * groups;
+    const bool is_q = head < Hq, is_v = head >= Hq + Hkv;
+    const size_t base = (size_t)head * D;
+    const int i0 = gi * 8, i1 = half + gi * 8;
+    float a[8], b[8];
+    load8(x + base + i0, a);
+    load8(x + base + i1, b);
+    if (bias) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { a[e] += bias[base + i0 + e]; b[e] += bias[base + i1 + e]; }
+    }
+    if (!is_v) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cs[i0 + e], sn = cs[half + i0 + e];
+        const float ra = a[e] * c - b[e] * sn, rb = a[e] * sn + b[e] * c;
+        a[e] = ra; b[e] = rb;
+      }
+    }
+    __align__(16) __nv_bfloat16 oa[8], ob[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { oa[e] = __float2bfloat16_rn(a[e]); ob[e] = __float2bfloat16_rn(b[e]); }
+    __nv_bfloat16* dst = nullptr;
+    if (is_q) dst = x + base;
+    else if (kdst) dst = kdst + ((size_t)(is_v ? Hkv : 0) + (is_v ? head - Hq - Hkv : head - Hq)) * kv_head_stride;
+    if (dst) {
+      *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(oa);
+      *reinterpret_cast<uint4*>(dst + i1) = *reinterpret_cast<const uint4*>(ob);
+    }
+  }
+}
+
 }  // namespace nf
 
 using namespace nf;
@@ -93,6 +158,10 @@ extern "C" int nf_rope_append(void* qkv, const float* bias, const int* positions
   NF_REQUIRE(D % 2 == 0, "rope_append: head_dim %d must be even", D);
   const size_t smem = (size_t)rot * sizeof(float);
   NF_REQUIRE(smem <= 48 * 1024, "rope_append: rotary width %d too large", rot);
+  if (dtype == kBF16 && rot == D && D % 16 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)pages % 16 == 0) {
+    rope_append_bf16x8_kernel<<<T, 256, smem, stream>>>((__nv_bfloat16*)qkv, bias, positions, row_seg, inv_freq, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, append);
+    return check_launch("rope_append");
+  }
   if (dtype == kF32)
     rope_append_kernel<float><<<T, 256, smem, stream>>>((float*)qkv, bias, positions, row_seg, inv_freq, rot, Hq, Hkv, D, (float*)pages, block_table, bt_width, page_size, num_pages, append);
   else

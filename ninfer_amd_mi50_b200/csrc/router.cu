@@ -52,19 +52,20 @@ router_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr, int 
 // One warp per token: softmax over the E router logits, the k largest (ties to the lower
 // index), weights p_e or p_e / sum(selected).
 __global__ void __launch_bounds__(128)
-router_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int extra, int k,
-                     int norm_topk, int* __restrict__ topk_idx, float* __restrict__ topk_w,
-                     float* __restrict__ extra_out) {
+router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp_stride, int n_tokens,
+                     int E, int extra, int k, int norm_topk, int* __restrict__ topk_idx,
+                     float* __restrict__ topk_w, float* __restrict__ extra_out) {
   extern __shared__ float smem[];      // [4 warps][E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= n_tokens) return;
   float* lg = smem + warp * E;
-  const float* row = logits + (size_t)t * (E + extra);
-  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = row[E + g];
+  // logits[t, e] sits at t * tok_stride + e * exp_stride (either may be the unit stride)
+  const float* row = logits + (size_t)t * tok_stride;
+  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = row[(size_t)(E + g) * exp_stride];
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
-    const float v = row[e];
+    const float v = row[(size_t)e * exp_stride];
     lg[e] = v;
     mx = fmaxf(mx, v);
   }
@@ -158,32 +159,31 @@ moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict_
 // The same plan for many pairs, spread over the device.  Block e ranks the pairs of expert e
 // (in pair order, so token order is kept) and counts them; the second kernel turns counts into
 // offsets and scatters.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_rank_kernel(const int* __restrict__ topk_idx, int n, int* __restrict__ counts, int* __restrict__ inv) {
-  __shared__ int warp_tot[8];
-  __shared__ int running_s;
+  // warp w takes the contiguous chunk w of the pairs: count, prefix over warps, then rank
+  __shared__ int warp_tot[32];
   const int e = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) running_s = 0;
-  __syncthreads();
-  for (int base = 0; base < n; base += 256) {
-    const int i = base + threadIdx.x;
-    const bool mine = i < n && topk_idx[i] == e;
-    const unsigned b = __ballot_sync(0xffffffffu, mine);
-    if (lane == 0) warp_tot[warp] = __popc(b);
-    __syncthreads();
-    int before = running_s;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    if (mine) inv[i] = before + __popc(b & ((1u << lane) - 1u));
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int t = 0;
-      for (int w = 0; w < 8; ++w) t += warp_tot[w];
-      running_s += t;
-    }
-    __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const int chunk = ((n + nwarp - 1) / nwarp + 31) & ~31;
+  const int lo = warp * chunk, hi = min(n, lo + chunk);
+  int cnt = 0;
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    cnt += __popc(__ballot_sync(0xffffffffu, i < hi && topk_idx[i] == e));
   }
-  if (threadIdx.x == 0) counts[e] = running_s;
+  if (lane == 0) warp_tot[warp] = cnt;
+  __syncthreads();
+  int running = 0;
+  for (int w = 0; w < warp; ++w) running += warp_tot[w];
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const bool mine = i < hi && topk_idx[i] == e;
+    const unsigned b = __ballot_sync(0xffffffffu, mine);
+    if (mine) inv[i] = running + __popc(b & ((1u << lane) - 1u));
+    running += __popc(b);
+  }
+  if (threadIdx.x == blockDim.x - 1) counts[e] = running;
 }
 
 __global__ void __launch_bounds__(256)
@@ -246,17 +246,20 @@ extern "C" int nf_router_topk(const void* x, const float* wr, int T, int hidden,
   int rc = dtype == kF32 ? launch_logits_t<float>(x, wr, T, hidden, E + extra, logits, stream)
                          : launch_logits_t<__nv_bfloat16>(x, wr, T, hidden, E + extra, logits, stream);
   if (rc) return rc;
-  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
+  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, E + extra, 1, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
   return check_launch("router_select");
 }
 
-// Selection alone, from float32 logits [T, E + extra] that something else has produced.
-extern "C" int nf_router_select(const float* logits, int T, int E, int extra, int k, int norm_topk,
-                                int* topk_idx, float* topk_w, float* extra_out, cudaStream_t stream) {
+// Selection alone, from float32 logits that something else has produced: logits[t, e] at
+// t * tok_stride + e * exp_stride ([T, E + extra] row-major: strides (E + extra, 1); transposed:
+// (1, T)).
+extern "C" int nf_router_select(const float* logits, long long tok_stride, long long exp_stride, int T,
+                                int E, int extra, int k, int norm_topk, int* topk_idx, float* topk_w,
+                                float* extra_out, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d E=%d k=%d", T, E, k);
   NF_REQUIRE((size_t)4 * E * 4 <= 48 * 1024, "router: %d experts are more than the selection kernel holds (3072)", E);
-  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
+  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, (long)tok_stride, (long)exp_stride, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
   return check_launch("router_select");
 }
 
@@ -265,7 +268,7 @@ extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int*
                            int* counts, cudaStream_t stream) {
   NF_REQUIRE(n >= 0 && E > 0 && E <= 8192, "moe_plan: bad sizes n=%d E=%d", n, E);
   if (n > 2048 && counts) {
-    moe_rank_kernel<<<E, 256, 0, stream>>>(topk_idx, n, counts, inv);
+    moe_rank_kernel<<<E, 1024, 0, stream>>>(topk_idx, n, counts, inv);
     if (int rc = check_launch("moe_rank")) return rc;
     moe_scatter_kernel<<<(n + 255) / 256, 256, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, counts, offsets, order, inv);
     return check_launch("moe_scatter");

@@ -32,14 +32,15 @@ TUNING = {
     "bf16_moe": "auto",           # "simt" | "auto"
     "skinny_max_rows": 16,        # dense products with more rows go to the library
     "skinny_moe_max_tokens": 128, # routed experts: tokens up to which the streaming kernel serves
-    "router_library_min_rows": 128,  # router logits of more rows than this are library products
+    "router_tensor_min_rows": 128,   # router logits of more rows than this use tensor cores
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
 DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)   # head sizes of the split-key decode kernel
 DECODE_SPLIT = 128                          # keys per block of that kernel
 PREFILL_HEAD_DIMS = tuple(range(16, 129, 16))   # head sizes of the flash prefill kernel
-PREFILL_TILE_ROWS = 128                     # query rows per CTA of that kernel
+PREFILL_TILE_ROWS = 64                      # query rows per tile of that kernel
+PREFILL_KEY_BLOCK = 64                      # keys per block of that kernel
 MAX_EXPERTS = 3072
 
 
@@ -307,7 +308,7 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
     if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
             and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
             and qkv.shape[1] % 8 == 0):
-        tiles, n_tiles = ctx.query_tiles(PREFILL_TILE_ROWS)
+        tiles, n_tiles = ctx.paired_query_tiles(PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK)
         _lib.call("nf_prefill_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
                   c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles),
                   c_int(n_tiles), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
@@ -352,25 +353,28 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_to
     logits back (`extra`, [T, rows - E]).  Returns (idx int32 [T, k], weights float32 [T, k], extra).
 
     With many bfloat16 rows and a `split` of the matrix (see `split_router`) the logits come
-    from library products with float32 output; otherwise from the float32 CUDA-core kernel."""
+    from tensor-core products with float32 sums; otherwise from the float32 CUDA-core kernel."""
     _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
     T, H = x.shape
     extra = w_router.shape[0] - E
     idx = torch.empty((T, k), dtype=torch.int32, device=x.device)
     wts = torch.empty((T, k), dtype=torch.float32, device=x.device)
     ext = torch.empty((T, extra), dtype=torch.float32, device=x.device) if extra > 0 else None
-    if (split is not None and x.dtype == torch.bfloat16 and T > TUNING["router_library_min_rows"]
-            and TUNING["bf16_linear"] != "simt"):
-        try:
-            logits = torch.mm(x, split[0].t(), out_dtype=torch.float32)
-            if split[1] is not None:
-                logits += torch.mm(x, split[1].t(), out_dtype=torch.float32)
-        except (TypeError, RuntimeError):
-            logits = None
-        if logits is not None:
-            _lib.call("nf_router_select", _p(logits), c_int(T), c_int(E), c_int(extra), c_int(k),
-                      c_int(1 if norm_topk else 0), _p(idx), _p(wts), _p(ext), _stream())
-            return idx, wts, ext
+    if (split is not None and x.dtype == torch.bfloat16 and T > TUNING["router_tensor_min_rows"]
+            and TUNING["bf16_linear"] != "simt" and H % 8 == 0):
+        # logits^T [E + extra, T] = W_r x^T with the streaming tensor-core kernel: the routing
+        # matrix (at most a few dozen rows) plays the part of the batch, the tokens that of the
+        # weights.  Products of bfloat16 values are exact, sums are float32.
+        rows = E + extra
+        logits_t = torch.empty((rows, T), dtype=torch.float32, device=x.device)
+        _skinny(split[0], H, x, 0, logits_t, rows, T, H, 1, rows, None, None, 1, False)
+        if split[1] is not None:
+            low = torch.empty_like(logits_t)
+            _skinny(split[1], H, x, 0, low, rows, T, H, 1, rows, None, None, 1, False)
+            logits_t += low
+        _lib.call("nf_router_select", _p(logits_t), c_longlong(1), c_longlong(T), c_int(T), c_int(E),
+                  c_int(extra), c_int(k), c_int(1 if norm_topk else 0), _p(idx), _p(wts), _p(ext), _stream())
+        return idx, wts, ext
     logits = torch.empty((T, E + extra), dtype=torch.float32, device=x.device)
     _lib.call("nf_router_topk", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra),
               c_int(k), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext),

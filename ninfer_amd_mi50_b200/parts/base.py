@@ -113,7 +113,7 @@ class StepContext:
     max_context: int = 0           # bound on pos0 + rows over the segments of this step
     graph_mode: bool = False
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
-    _tiles: Dict[int, Tuple[torch.Tensor, int]] = field(default_factory=dict)
+    _tiles: Dict[object, Tuple[torch.Tensor, int]] = field(default_factory=dict)
 
     @property
     def all_single(self) -> bool:
@@ -140,6 +140,42 @@ class StepContext:
         t = torch.tensor(flat, dtype=torch.int32).reshape(n_tiles, 2).to(self.device)
         self._tiles[rows_per_tile] = (t, n_tiles)
         return t, n_tiles
+
+
+    def paired_query_tiles(self, rows_per_tile: int, window: int, keys_per_block: int
+                           ) -> Tuple[torch.Tensor, int]:
+        """Query tiles two to a CTA, a heavy one with a light one.
+
+        A tile late in a long prompt reads many more keys than an early one; giving each CTA
+        the i-th heaviest and the i-th lightest tile makes CTAs about equally long.  Returns
+        (int32 [n_pairs, 2, 2] of (segment, first row), second entry (-1, -1) if there is
+        none; n_pairs)."""
+        key = ("pairs", rows_per_tile, window, keys_per_block)
+        if key in self._tiles:
+            return self._tiles[key]
+        if self.seg_len_host is None or self.seg_pos0_host is None:
+            raise RuntimeError("paired_query_tiles needs host segment lengths (not in graph mode)")
+        tiles = []
+        row = 0
+        for s, (n, pos0) in enumerate(zip(self.seg_len_host, self.seg_pos0_host)):
+            for r in range(0, n, rows_per_tile):
+                first = pos0 + r
+                last = pos0 + min(r + rows_per_tile, n) - 1
+                lo = max(0, first - window + 1) if window > 0 else 0
+                work = last // keys_per_block - lo // keys_per_block + 1
+                tiles.append((work, s, row + r))
+            row += n
+        tiles.sort(key=lambda t: -t[0])
+        flat: List[int] = []
+        i, j = 0, len(tiles) - 1
+        while i <= j:
+            flat += [tiles[i][1], tiles[i][2]]
+            flat += [tiles[j][1], tiles[j][2]] if j > i else [-1, -1]
+            i, j = i + 1, j - 1
+        n_pairs = len(flat) // 4
+        t = torch.tensor(flat, dtype=torch.int32).reshape(n_pairs, 2, 2).to(self.device)
+        self._tiles[key] = (t, n_pairs)
+        return t, n_pairs
 
 
 # --------------------------------------------------------------------------------------
