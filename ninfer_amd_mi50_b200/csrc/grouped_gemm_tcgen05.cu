@@ -45,7 +45,8 @@ constexpr int kTmemCols = 512;
 constexpr unsigned kPollLimit = 1u << 24;
 constexpr int kXBox = 64;         // token rows per TMA box
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 226 * 1024;   // + 1 KB of alignment slack = the 227 KB a CTA may have
+constexpr int kMaxGroupsTc = 1024;   // groups one launch may have (their pass counts live in shared memory)
+constexpr int kSmemBudget = 225 * 1024;   // + 1 KB of alignment slack + a few static bytes <= the 227 KB a CTA may have
 
 __device__ int g_tc_error = 0;
 
@@ -134,33 +135,56 @@ struct __align__(8) Barriers {
   int stop;
 };
 
-// grid (feature tiles, groups); 192 threads: warp 0 producer, warp 1 MMA + tensor memory,
-// warps 2..5 epilogue.  Wp: packed weights [groups][feature tiles][k tiles][A_ROWS][64].
+// Persistent: one CTA per SM walks the work items (group, pass of 256 rows, feature tile)
+// cta, cta + grid, ... with feature tiles varying fastest, so CTAs that run together share an
+// expert's token rows in L2, and the passes of a heavily loaded expert - which re-read its
+// weights - run next to each other and find them in L2.  Items cost about the same, so the
+// static assignment stays balanced however unevenly the router loads the experts.  192 threads: warp 0 producer, warp 1 MMA + tensor memory, warps 2..5 epilogue.  The
+// producer is not held back by the epilogue: while the epilogue warps drain an item's
+// accumulator, the stages fill with the next item's first k tiles, so the memory pipe never
+// goes idle between items.  Wp: packed weights [groups][feature tiles][k tiles][A_ROWS][64].
 template <bool SWIGLU>
 __global__ void __launch_bounds__(192, 1)
 grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_constant__ CUtensorMap map_x,
                        const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int ldo,
-                       int n_features, int K) {
+                       int n_features, int K, int groups) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int A_BYTES = (SWIGLU ? 2 : 1) * kBM * kBK * 2;     // gate (+ up) tile
   constexpr int BOX_BYTES = kXBox * kBK * 2;
+  __shared__ int s_max_rows;
 
-  const int group = blockIdx.y;
-  const int row_begin = offsets[group], row_end = offsets[group + 1];
-  if (row_begin >= row_end) return;                       // the whole CTA leaves before any barrier exists
-  const int f0 = blockIdx.x * kBM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_rows = row_end - row_begin;
-  const int n_passes = (n_rows + kBNMax - 1) / kBNMax;
   const int k_steps = (K + kBK - 1) / kBK;
-  const int n_ftiles = gridDim.x;
-  // stage geometry for this expert: weights + as many 64-row boxes as its largest pass needs
-  const int max_boxes = (min(n_rows, kBNMax) + kXBox - 1) / kXBox;
+  const int n_ftiles = (n_features + kBM - 1) / kBM;
+
+  // stage geometry, the same for every item: weights + as many 64-row boxes as the largest
+  // pass of any group needs
+  if (threadIdx.x == 0) s_max_rows = 0;
+  __syncthreads();
+  {
+    int mx = 0;
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) mx = max(mx, offsets[g + 1] - offsets[g]);
+    if (mx) atomicMax(&s_max_rows, mx);
+  }
+  __syncthreads();
+  const int max_boxes = (min(max(s_max_rows, 1), kBNMax) + kXBox - 1) / kXBox;
   const int stage_bytes = A_BYTES + max_boxes * BOX_BYTES;
-  const int stages = min(kMaxStages, (kSmemBudget - (int)sizeof(Barriers)) / stage_bytes);
+  const int tail_bytes = (int)sizeof(Barriers) + (groups + 1) * (int)sizeof(int);
+  const int stages = min(kMaxStages, (kSmemBudget - tail_bytes) / stage_bytes);
   Barriers* bars = reinterpret_cast<Barriers*>(smem + (size_t)stages * stage_bytes);
+  int* s_pass_start = reinterpret_cast<int*>(bars + 1);     // [groups + 1] first pass index of every group
   volatile int* stop = &bars->stop;
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int g = 0; g < groups; ++g) {
+      s_pass_start[g] = run;
+      run += (offsets[g + 1] - offsets[g] + kBNMax - 1) / kBNMax;
+    }
+    s_pass_start[groups] = run;
+  }
+  __syncthreads();
+  const int n_items = s_pass_start[groups] * n_ftiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -181,22 +205,29 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------
     if (lane == 0) {
-      const unsigned char* w_tile = reinterpret_cast<const unsigned char*>(Wp) +
-                                    ((size_t)group * n_ftiles + blockIdx.x) * k_steps * A_BYTES;
       int it = 0, issued = 0;
       bool ok = true;
-      for (int pass = 0; pass < n_passes && ok; ++pass) {
-        const int x_row = row_begin + pass * kBNMax;
-        const int boxes = (min(kBNMax, n_rows - pass * kBNMax) + kXBox - 1) / kXBox;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % stages;
-          if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1)) { ok = false; break; }
-          unsigned char* st = smem + (size_t)s * stage_bytes;
-          mbar_expect_tx(&bars->full[s], A_BYTES + boxes * BOX_BYTES);
-          bulk_load(st, w_tile + (size_t)ks * A_BYTES, A_BYTES, &bars->full[s]);
-          for (int b = 0; b < boxes; ++b)
-            tma_load_2d(st + A_BYTES + b * BOX_BYTES, &map_x, ks * kBK, x_row + b * kXBox, &bars->full[s]);
-          issued = it + 1;
+      int group = 0;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int gp = item / n_ftiles, ft = item - gp * n_ftiles;      // global pass index, feature tile
+        while (s_pass_start[group + 1] <= gp) ++group;
+        const int pass = gp - s_pass_start[group];
+        const int row_begin = offsets[group], n_rows = offsets[group + 1] - row_begin;
+        const unsigned char* w_tile = reinterpret_cast<const unsigned char*>(Wp) +
+                                      ((size_t)group * n_ftiles + ft) * k_steps * A_BYTES;
+        {
+          const int x_row = row_begin + pass * kBNMax;
+          const int boxes = (min(kBNMax, n_rows - pass * kBNMax) + kXBox - 1) / kXBox;
+          for (int ks = 0; ks < k_steps; ++ks, ++it) {
+            const int s = it % stages;
+            if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1)) { ok = false; break; }
+            unsigned char* st = smem + (size_t)s * stage_bytes;
+            mbar_expect_tx(&bars->full[s], A_BYTES + boxes * BOX_BYTES);
+            bulk_load(st, w_tile + (size_t)ks * A_BYTES, A_BYTES, &bars->full[s]);
+            for (int b = 0; b < boxes; ++b)
+              tma_load_2d(st + A_BYTES + b * BOX_BYTES, &map_x, ks * kBK, x_row + b * kXBox, &bars->full[s]);
+            issued = it + 1;
+          }
         }
       }
       if (!ok) {
@@ -211,62 +242,79 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
   } else if (warp == 1) {
     // ---- MMA issuer -----------------------------------------------------------------------------
     if (lane == 0) {
-      int it = 0;
+      int it = 0, pass_ctr = 0;
       bool ok = true;
-      for (int pass = 0; pass < n_passes && ok; ++pass) {
-        if (!mbar_wait(&bars->acc_empty, (pass & 1) ^ 1, stop, 2)) break;
-        tc_fence_after();
-        const int n = min(kBNMax, (n_rows - pass * kBNMax + 15) & ~15);
-        const unsigned idesc = instr_desc(n);
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % stages;
-          if (!mbar_wait(&bars->full[s], (it / stages) & 1, stop, 3)) { ok = false; break; }
+      int group = 0;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++pass_ctr) {
+        const int gp = item / n_ftiles;
+        while (s_pass_start[group + 1] <= gp) ++group;
+        const int pass = gp - s_pass_start[group];
+        const int n_rows = offsets[group + 1] - offsets[group];
+        {
+          if (!mbar_wait(&bars->acc_empty, (pass_ctr & 1) ^ 1, stop, 2)) { ok = false; break; }
           tc_fence_after();
-          unsigned char* st = smem + (size_t)s * stage_bytes;
-          const unsigned long long a0 = smem_desc(st);
-          const unsigned long long a1 = smem_desc(st + kBM * kBK * 2);
-          const unsigned long long b = smem_desc(st + A_BYTES);
+          const int n = min(kBNMax, (n_rows - pass * kBNMax + 15) & ~15);
+          const unsigned idesc = instr_desc(n);
+          for (int ks = 0; ks < k_steps; ++ks, ++it) {
+            const int s = it % stages;
+            if (!mbar_wait(&bars->full[s], (it / stages) & 1, stop, 3)) { ok = false; break; }
+            tc_fence_after();
+            unsigned char* st = smem + (size_t)s * stage_bytes;
+            const unsigned long long a0 = smem_desc(st);
+            const unsigned long long a1 = smem_desc(st + kBM * kBK * 2);
+            const unsigned long long b = smem_desc(st + A_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk) {
-            // 16 k = 32 bytes further along the swizzled row: +2 in the address field
-            const unsigned acc = (ks > 0 || kk > 0) ? 1u : 0u;
-            tc_mma(tmem, a0 + 2 * kk, b + 2 * kk, idesc, acc);
-            if (SWIGLU) tc_mma(tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
+            for (int kk = 0; kk < kBK / 16; ++kk) {
+              // 16 k = 32 bytes further along the swizzled row: +2 in the address field
+              const unsigned acc = (ks > 0 || kk > 0) ? 1u : 0u;
+              tc_mma(tmem, a0 + 2 * kk, b + 2 * kk, idesc, acc);
+              if (SWIGLU) tc_mma(tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
+            }
+            tc_commit(&bars->empty[s]);          // the stage is free once these MMAs have read it
           }
-          tc_commit(&bars->empty[s]);          // the stage is free once these MMAs have read it
+          if (ok) tc_commit(&bars->acc_full);    // the accumulator is complete once they have all run
         }
-        if (ok) tc_commit(&bars->acc_full);    // the accumulator is complete once they have all run
       }
     }
   } else {
     // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31 ---------------------
     const int quad = warp & 3;
-    const int f = f0 + quad * 32 + lane;
-    for (int pass = 0; pass < n_passes; ++pass) {
-      if (!mbar_wait(&bars->acc_full, pass & 1, stop, 4)) break;
-      tc_fence_after();
-      const int p0 = row_begin + pass * kBNMax;
-      const int valid = min(kBNMax, n_rows - pass * kBNMax);
-      const unsigned lane_addr = tmem + ((unsigned)(quad * 32) << 16);
-      for (int c0 = 0; c0 < valid; c0 += 32) {
-        unsigned g[32], u[32];
-        tc_ld32(lane_addr + c0, g);
-        if (SWIGLU) tc_ld32(lane_addr + kBNMax + c0, u);
-        tc_wait_ld();
-        if (f < n_features) {
+    int pass_ctr = 0;
+    bool ok = true;
+    int group = 0;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++pass_ctr) {
+      const int gp = item / n_ftiles, ft = item - gp * n_ftiles;
+      while (s_pass_start[group + 1] <= gp) ++group;
+      const int pass = gp - s_pass_start[group];
+      const int row_begin = offsets[group], n_rows = offsets[group + 1] - row_begin;
+      const int f = ft * kBM + quad * 32 + lane;
+      {
+        if (!mbar_wait(&bars->acc_full, pass_ctr & 1, stop, 4)) { ok = false; break; }
+        tc_fence_after();
+        const int p0 = row_begin + pass * kBNMax;
+        const int valid = min(kBNMax, n_rows - pass * kBNMax);
+        const unsigned lane_addr = tmem + ((unsigned)(quad * 32) << 16);
+        for (int c0 = 0; c0 < valid; c0 += 32) {
+          unsigned g[32], u[32];
+          tc_ld32(lane_addr + c0, g);
+          if (SWIGLU) tc_ld32(lane_addr + kBNMax + c0, u);
+          tc_wait_ld();
+          if (f < n_features) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (c0 + c < valid) {
-              float v = __uint_as_float(g[c]);
-              if (SWIGLU) v = v / (1.f + expf(-v)) * __uint_as_float(u[c]);
-              out[(size_t)(p0 + c0 + c) * ldo + f] = __float2bfloat16_rn(v);
+            for (int c = 0; c < 32; ++c) {
+              if (c0 + c < valid) {
+                float v = __uint_as_float(g[c]);
+                // the result is rounded to bfloat16 (2^-9): the fast exponential's 2^-21 is far below
+                if (SWIGLU) v = v / (1.f + __expf(-v)) * __uint_as_float(u[c]);
+                out[(size_t)(p0 + c0 + c) * ldo + f] = __float2bfloat16_rn(v);
+              }
             }
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->acc_empty);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty);
     }
   }
 
@@ -323,9 +371,17 @@ static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, 
     NF_REQUIRE(e == cudaSuccess, "grouped_gemm_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     set = true;
   }
-  dim3 grid((n_features + kBM - 1) / kBM, groups);
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm <= 0) n_sm = 1;
+  }
+  // at least one pass per non-empty group; the kernel itself counts the exact number of items
+  const int grid = n_sm;
   grouped_gemm_tc_kernel<SWIGLU><<<grid, 192, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
-                                                             (__nv_bfloat16*)out, ldo, n_features, K);
+                                                             (__nv_bfloat16*)out, ldo, n_features, K, groups);
   return check_launch("grouped_gemm_tc");
 }
 
@@ -345,7 +401,7 @@ extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const voi
   NF_REQUIRE(total_rows > 0 && groups > 0 && n_features > 0 && K > 0, "grouped_gemm_tc: bad sizes");
   NF_REQUIRE(K % 8 == 0, "grouped_gemm_tc: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
   NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)Wp % 16 == 0), "grouped_gemm_tc: operands must be 16-byte aligned");
-  NF_REQUIRE(groups <= 65535, "grouped_gemm_tc: too many groups");
+  NF_REQUIRE(groups <= kMaxGroupsTc, "grouped_gemm_tc: %d groups, at most %d", groups, kMaxGroupsTc);
   CUtensorMap mx;
   if (int rc = make_map(&mx, X, total_rows, K, kXBox)) return rc;
   if (swiglu) return launch_tc<true>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);

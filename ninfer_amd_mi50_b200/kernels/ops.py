@@ -307,7 +307,7 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
         return out
     if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
             and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
-            and qkv.shape[1] % 8 == 0):
+            and getattr(ctx, "seg_pos0_host", None) is not None and qkv.shape[1] % 8 == 0):
         tiles, n_tiles = ctx.paired_query_tiles(PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK)
         _lib.call("nf_prefill_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
                   c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles),
