@@ -61,7 +61,8 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
                               const int* __restrict__ block_table, int bt_width,
                               const int* __restrict__ positions, const int* __restrict__ row_seg,
                               float* __restrict__ ws_acc, float* __restrict__ ws_ml, int Hq, int Hkv,
-                              int page_size, int num_pages, int window, float scale, int nsplit) {
+                              int page_size, int num_pages, int window, float scale, int nsplit,
+                              int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
   constexpr int LPR = D / 8;            // 16-byte pieces of one key row
   constexpr int RPL = 32 / LPR;         // key rows a warp copies at once
   constexpr int DS = D + 8;             // shared-memory row stride: 16 bytes of padding keep
@@ -232,6 +233,37 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
     o[0] = ml[2 * h];
     o[1] = ml[2 * h + 1];
   }
+  if (!counters) return;
+  // ---- the CTA that finishes last for this (row, kv head) merges the key blocks -----------------
+  // Which CTA that is does not matter: it reads every block's partial result and adds them in
+  // ascending block order.  The counter is left at zero for the next launch.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  const int s0 = lo / kSplit, s1 = min(pos / kSplit, nsplit - 1);
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&counters[t * Hkv + kvh], 1);
+    s_last = prev == s1 - s0;
+    if (s_last) counters[t * Hkv + kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int h = 0; h < G; ++h) {
+    const int hq = kvh * G + h;
+    const float* mlp = ws_ml + ((size_t)t * Hq + hq) * nsplit * 2;
+    const float* accp = ws_acc + ((size_t)t * Hq + hq) * nsplit * D;
+    float m = -INFINITY;
+    for (int s = s0; s <= s1; ++s) m = fmaxf(m, __ldcg(mlp + 2 * s));
+    float l = 0.f;
+    for (int s = s0; s <= s1; ++s) l += __ldcg(mlp + 2 * s + 1) * expf(__ldcg(mlp + 2 * s) - m);
+    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float o = 0.f;
+      for (int s = s0; s <= s1; ++s) o += __ldcg(accp + (size_t)s * D + d) * expf(__ldcg(mlp + 2 * s) - m);
+      out[((size_t)t * Hq + hq) * D + d] = __float2bfloat16_rn(o * inv_l);
+    }
+  }
 }
 
 // One block per (row, q head): merge the splits of the row's key range in ascending order.
@@ -263,7 +295,7 @@ template <int D>
 static int launch_split(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                         int bt_width, const int* positions, const int* row_seg, float* ws_acc,
                         float* ws_ml, int T, int Hq, int Hkv, int page_size, int num_pages, int window,
-                        float scale, int nsplit, cudaStream_t stream) {
+                        float scale, int nsplit, int* counters, void* out, cudaStream_t stream) {
   const int G = Hq / Hkv;
   const size_t smem = (size_t)2 * kSplit * (D + 8) * sizeof(__nv_bfloat16) +
                       ((size_t)G * kSplit + 4 * (G < 8 ? G : 8) * D + 2 * G) * sizeof(float);
@@ -276,7 +308,8 @@ static int launch_split(const void* qkv, int q_row_stride, const void* pages, co
   dim3 grid(T, Hkv, nsplit);
   decode_attention_split_kernel<D><<<grid, 128, smem, stream>>>(
       (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions,
-      row_seg, ws_acc, ws_ml, Hq, Hkv, page_size, num_pages, window, scale, nsplit);
+      row_seg, ws_acc, ws_ml, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters,
+      (__nv_bfloat16*)out);
   return check_launch("decode_attention_split");
 }
 
@@ -288,31 +321,53 @@ extern "C" int nf_decode_attention_split_size() { return kSplit; }
 
 // bfloat16 only; head_dim in {16, 32, 64, 128, 256}.  `nsplit` >= ceil(max context / 128) of
 // the rows in this call.  Workspace: ws_acc float32 [T, Hq, nsplit, D], ws_ml [T, Hq, nsplit, 2].
-extern "C" int nf_decode_attention(const void* qkv, int q_row_stride, const void* pages,
-                                   const int* block_table, int bt_width, const int* positions,
-                                   const int* row_seg, void* out, float* ws_acc, float* ws_ml, int T,
-                                   int Hq, int Hkv, int D, int page_size, int num_pages, int window,
-                                   float scale, int nsplit, cudaStream_t stream) {
+static int decode_attention_impl(const void* qkv, int q_row_stride, const void* pages,
+                                 const int* block_table, int bt_width, const int* positions,
+                                 const int* row_seg, void* out, float* ws_acc, float* ws_ml, int T,
+                                 int Hq, int Hkv, int D, int page_size, int num_pages, int window,
+                                 float scale, int nsplit, int* counters, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && nsplit > 0, "decode attention: bad sizes T=%d Hq=%d Hkv=%d nsplit=%d", T, Hq, Hkv, nsplit);
   NF_REQUIRE(Hkv <= 65535 && nsplit <= 65535, "decode attention: too many kv heads or key blocks");
   int rc;
   switch (D) {
-    case 16: rc = launch_split<16>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream); break;
-    case 32: rc = launch_split<32>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream); break;
-    case 64: rc = launch_split<64>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream); break;
-    case 128: rc = launch_split<128>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream); break;
-    case 256: rc = launch_split<256>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream); break;
+    case 16: rc = launch_split<16>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
+    case 32: rc = launch_split<32>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
+    case 64: rc = launch_split<64>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
+    case 128: rc = launch_split<128>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
+    case 256: rc = launch_split<256>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
     default:
       set_error("decode attention: head_dim %d is not one of 16, 32, 64, 128, 256", D);
       return 1;
   }
-  if (rc) return rc;
+  if (rc || counters) return rc;      // with counters the split kernel's last CTAs have merged
   dim3 grid(T, Hq);
   int threads = 32;
   while (threads < D && threads < 256) threads <<= 1;
   decode_attention_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(ws_acc, ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit);
   return check_launch("decode_attention_merge");
+}
+
+extern "C" int nf_decode_attention(const void* qkv, int q_row_stride, const void* pages,
+                                   const int* block_table, int bt_width, const int* positions,
+                                   const int* row_seg, void* out, float* ws_acc, float* ws_ml, int T,
+                                   int Hq, int Hkv, int D, int page_size, int num_pages, int window,
+                                   float scale, int nsplit, cudaStream_t stream) {
+  return decode_attention_impl(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, out, ws_acc,
+                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, nullptr, stream);
+}
+
+// The same in one launch: `counters` are T * Hkv ints that are zero before the call and are left
+// zero after it; the CTA that finishes a (row, kv head) last merges its key blocks.
+extern "C" int nf_decode_attention_fused(const void* qkv, int q_row_stride, const void* pages,
+                                         const int* block_table, int bt_width, const int* positions,
+                                         const int* row_seg, void* out, float* ws_acc, float* ws_ml,
+                                         int* counters, int T, int Hq, int Hkv, int D, int page_size,
+                                         int num_pages, int window, float scale, int nsplit,
+                                         cudaStream_t stream) {
+  NF_REQUIRE(counters, "decode attention: the one-launch form needs its counters");
+  return decode_attention_impl(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, out, ws_acc,
+                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, counters, stream);
 }
 
 // ---- the entry point that allocates nothing ---------------------------------------------------

@@ -12,6 +12,26 @@
 
 namespace nf {
 
+// A lane's share of a dot product: elements lane, lane + 32, ... in four interleaved partial
+// sums (so that the loads overlap), added as (s0 + s1) + (s2 + s3).  Every router kernel
+// uses this, so a logit's value does not depend on which of them computed it.
+__device__ __forceinline__ float lane_dot(const float* __restrict__ xs, const float* __restrict__ w,
+                                          int hidden, int lane) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int i = lane;
+  for (; i + 96 < hidden; i += 128) {
+    const float w0 = w[i], w1 = w[i + 32], w2 = w[i + 64], w3 = w[i + 96];
+    s0 = fmaf(xs[i], w0, s0);
+    s1 = fmaf(xs[i + 32], w1, s1);
+    s2 = fmaf(xs[i + 64], w2, s2);
+    s3 = fmaf(xs[i + 96], w3, s3);
+  }
+  if (i < hidden) s0 = fmaf(xs[i], w[i], s0);
+  if (i + 32 < hidden) s1 = fmaf(xs[i + 32], w[i + 32], s1);
+  if (i + 64 < hidden) s2 = fmaf(xs[i + 64], w[i + 64], s2);
+  return (s0 + s1) + (s2 + s3);
+}
+
 // Router logits: out[t, e] = x[t] . wr[e] in float32, for the E router rows and `extra`
 // further rows (the shared expert's gate).  A block takes TT tokens and 8 rows of wr, one
 // warp per row; a lane sums its strided share of the hidden dimension and the warp adds the
@@ -35,13 +55,7 @@ router_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr, int 
   const float* w = wr + (size_t)e * hidden;
   float acc[TT];
 #pragma unroll
-  for (int tt = 0; tt < TT; ++tt) acc[tt] = 0.f;
-  for (int i = lane; i < hidden; i += 32) {
-    const float wv = w[i];
-#pragma unroll
-    for (int tt = 0; tt < TT; ++tt)
-      if (tt < nt) acc[tt] = fmaf(xs[tt * hidden + i], wv, acc[tt]);
-  }
+  for (int tt = 0; tt < TT; ++tt) acc[tt] = lane_dot(xs + tt * hidden, w, hidden, lane);
 #pragma unroll
   for (int tt = 0; tt < TT; ++tt) {
     const float v = warp_sum(acc[tt]);
@@ -49,23 +63,17 @@ router_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr, int 
   }
 }
 
-// One warp per token: softmax over the E router logits, the k largest (ties to the lower
-// index), weights p_e or p_e / sum(selected).
-__global__ void __launch_bounds__(128)
-router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp_stride, int n_tokens,
-                     int E, int extra, int k, int norm_topk, int* __restrict__ topk_idx,
-                     float* __restrict__ topk_w, float* __restrict__ extra_out) {
-  extern __shared__ float smem[];      // [4 warps][E]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= n_tokens) return;
-  float* lg = smem + warp * E;
-  // logits[t, e] sits at t * tok_stride + e * exp_stride (either may be the unit stride)
-  const float* row = logits + (size_t)t * tok_stride;
-  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = row[(size_t)(E + g) * exp_stride];
+// One warp, one token: softmax over the E router logits, the k largest (ties to the lower
+// index), weights p_e or p_e / sum(selected).  `lg` is E floats of the warp's shared memory;
+// logits[t, e] sits at row[e * exp_stride].
+__device__ __forceinline__ void select_token(const float* row, long exp_stride, float* lg, int t, int E,
+                                             int extra, int k, int norm_topk, int* __restrict__ topk_idx,
+                                             float* __restrict__ topk_w, float* __restrict__ extra_out,
+                                             int lane) {
+  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = __ldcg(row + (size_t)(E + g) * exp_stride);
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
-    const float v = row[(size_t)e * exp_stride];
+    const float v = __ldcg(row + (size_t)e * exp_stride);
     lg[e] = v;
     mx = fmaxf(mx, v);
   }
@@ -103,24 +111,32 @@ router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp
   if (norm_topk) {
     for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] /= sel_sum;
   }
+  __syncwarp();
 }
 
-// Plan: stable counting sort of the n = T*k pairs by expert.
-//   offsets[e] .. offsets[e+1]  rows of expert e in sorted order
-//   order[p] = pair (t*k + j) at sorted position p;   inv[pair] = p
-// One block; warp w ranks the pairs of experts w, w + nwarps, ... with ballots, which keeps
-// token order inside an expert.
-// STAGED: the pairs' experts are first copied into shared memory (as 16-bit values), so that
-// the E passes over them do not go to global memory.
+__global__ void __launch_bounds__(128)
+router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp_stride, int n_tokens,
+                     int E, int extra, int k, int norm_topk, int* __restrict__ topk_idx,
+                     float* __restrict__ topk_w, float* __restrict__ extra_out) {
+  extern __shared__ float smem[];      // [4 warps][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  // logits[t, e] sits at t * tok_stride + e * exp_stride (either may be the unit stride)
+  select_token(logits + (size_t)t * tok_stride, exp_stride, smem + warp * E, t, E, extra, k, norm_topk,
+               topk_idx, topk_w, extra_out, lane);
+}
+
+// Plan by one block: stable counting sort of the n pairs by expert.  `counts` is E + 1 ints
+// of shared memory; with STAGED, `ex` holds n 16-bit expert ids so that the E passes over the
+// pairs do not go to global memory.
 template <bool STAGED>
-__global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict__ offsets,
-                int* __restrict__ order, int* __restrict__ inv) {
-  extern __shared__ int counts[];      // [E + 1], then (STAGED) n experts and n ranks as 16-bit
-  unsigned short* ex = reinterpret_cast<unsigned short*>(counts + E + 1);
+__device__ __forceinline__ void plan_block(const int* __restrict__ topk_idx, int n, int E,
+                                           int* __restrict__ offsets, int* __restrict__ order,
+                                           int* __restrict__ inv, int* counts, unsigned short* ex) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   if (STAGED) {
-    for (int i = threadIdx.x; i < n; i += blockDim.x) ex[i] = (unsigned short)topk_idx[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ex[i] = (unsigned short)__ldcg(topk_idx + i);
     __syncthreads();
   }
   for (int e = warp; e < E; e += nwarp) {
@@ -148,12 +164,63 @@ moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict_
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int e = topk_idx[i];
+    const int e = STAGED ? (int)ex[i] : topk_idx[i];
     if (e < 0 || e >= E) continue;
     const int p = counts[e] + inv[i];
     inv[i] = p;
     order[p] = i;
   }
+}
+
+template <bool STAGED>
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict__ offsets,
+                int* __restrict__ order, int* __restrict__ inv) {
+  extern __shared__ int counts[];      // [E + 1], then (STAGED) n experts as 16-bit
+  plan_block<STAGED>(topk_idx, n, E, offsets, order, inv, counts,
+                     reinterpret_cast<unsigned short*>(counts + E + 1));
+}
+
+// Few tokens (decode steps): logits, selection and plan in one launch.  Blocks (8 router rows,
+// 1 token) compute logits as `router_logits_kernel` does; the block that finishes last - which
+// one does not matter, it reads what all have written - selects for every token and builds the
+// plan.  `ticket` is an int that is zero before the launch and is left zero after it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n_tokens, int hidden,
+                    int E, int extra, int k, int norm_topk, float* __restrict__ logits,
+                    int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ extra_out,
+                    int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv,
+                    int* __restrict__ ticket) {
+  extern __shared__ float xs[];        // [hidden]; the last block reuses it
+  __shared__ int s_last;
+  const int rows = E + extra;
+  const int t = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_float(x[(size_t)t * hidden + i]);
+  __syncthreads();
+  const int e = blockIdx.x * 8 + warp;
+  if (e < rows) {
+    const float v = warp_sum(lane_dot(xs, wr + (size_t)e * hidden, hidden, lane));
+    if (lane == 0) logits[(size_t)t * rows + e] = v;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1) == (int)(gridDim.x * gridDim.y) - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // ---- the last block: selection for every token, then the plan ------------------------------
+  float* lg = xs;                                   // [8 warps][E]
+  for (int tt = warp; tt < n_tokens; tt += 8)
+    select_token(logits + (size_t)tt * rows, 1, lg + warp * E, tt, E, extra, k, norm_topk, topk_idx, topk_w,
+                 extra_out, lane);
+  __threadfence_block();
+  __syncthreads();
+  int* counts = reinterpret_cast<int*>(xs);         // [E + 1], then the pairs' experts
+  plan_block<true>(topk_idx, n_tokens * k, E, offsets, order, inv, counts,
+                   reinterpret_cast<unsigned short*>(counts + E + 1));
+  if (threadIdx.x == 0) *ticket = 0;
 }
 
 // The same plan for many pairs, spread over the device.  Block e ranks the pairs of expert e
@@ -248,6 +315,31 @@ extern "C" int nf_router_topk(const void* x, const float* wr, int T, int hidden,
   if (rc) return rc;
   router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, E + extra, 1, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
   return check_launch("router_select");
+}
+
+// Few tokens: logits + selection + plan in one launch.  Needs max(hidden, 8 * E, E + 1 + T * k / 2 + 1)
+// floats of shared memory; `ticket` is a zeroed int that the kernel leaves zeroed.
+extern "C" int nf_router_fused(const void* x, const float* wr, int T, int hidden, int E, int extra, int k,
+                               int norm_topk, float* logits, int* topk_idx, float* topk_w,
+                               float* extra_out, int* offsets, int* order, int* inv, int* ticket,
+                               int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && T <= 65535 && hidden > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d hidden=%d E=%d k=%d", T, hidden, E, k);
+  size_t words = (size_t)hidden;
+  if ((size_t)8 * E > words) words = (size_t)8 * E;
+  if ((size_t)E + 2 + (size_t)T * k / 2 > words) words = (size_t)E + 2 + (size_t)T * k / 2;
+  const size_t smem = words * sizeof(float);
+  NF_REQUIRE(smem <= 160 * 1024 && E < 65536, "router: sizes too large for the fused kernel");
+  static size_t allowed_f = 48 * 1024, allowed_b = 48 * 1024;
+  dim3 grid((E + extra + 7) / 8, T);
+  if (dtype == kF32) {
+    if (smem > allowed_f) { cudaFuncSetAttribute(router_fused_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_f = smem; }
+    router_fused_kernel<float><<<grid, 256, smem, stream>>>((const float*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, ticket);
+  } else {
+    if (smem > allowed_b) { cudaFuncSetAttribute(router_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_b = smem; }
+    router_fused_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, ticket);
+  }
+  return check_launch("router_fused");
 }
 
 // Selection alone, from float32 logits that something else has produced: logits[t, e] at

@@ -33,6 +33,10 @@ TUNING = {
     "skinny_max_rows": 16,        # dense products with more rows go to the library
     "skinny_moe_max_tokens": 128, # routed experts: tokens up to which the streaming kernel serves
     "router_tensor_min_rows": 128,   # router logits of more rows than this use tensor cores
+    "router_fused_max_rows": 64,     # up to this many rows, routing is a single launch
+    # decode attention can merge its key blocks in the same launch (the last CTA of a row does
+    # it); measured slower than the separate merge kernel at every batch size, so it is off
+    "decode_merge_fused_max_rows": 0,
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -283,6 +287,20 @@ def rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torc
               _stream())
 
 
+_COUNTERS = {}
+
+
+def _zeroed_counters(device, n: int) -> torch.Tensor:
+    """Ints that kernels find zero and leave zero (completion counters of one-launch
+    reductions).  Kept for the life of the process, so that captured graphs may refer to them."""
+    key = str(device)
+    bufs = _COUNTERS.setdefault(key, [])
+    if not bufs or bufs[-1].numel() < n:
+        # earlier, smaller buffers stay alive: a captured graph may still point at them
+        bufs.append(torch.zeros((max(n, 4096),), dtype=torch.int32, device=device))
+    return bufs[-1]
+
+
 def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.Tensor,
                     block_table: torch.Tensor, page_size: int, ctx, window: int, scale: float
                     ) -> torch.Tensor:
@@ -300,10 +318,18 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
         nsplit = max(1, (int(ctx.max_context) + DECODE_SPLIT - 1) // DECODE_SPLIT)
         ws_acc = torch.empty((T, Hq, nsplit, D), dtype=torch.float32, device=qkv.device)
         ws_ml = torch.empty((T, Hq, nsplit, 2), dtype=torch.float32, device=qkv.device)
-        _lib.call("nf_decode_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+        if T > TUNING["decode_merge_fused_max_rows"]:
+            _lib.call("nf_decode_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+                      c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
+                      _p(ws_acc), _p(ws_ml), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                      c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
+            return out
+        counters = _zeroed_counters(qkv.device, T * Hkv)
+        _lib.call("nf_decode_attention_fused", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
                   c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
-                  _p(ws_acc), _p(ws_ml), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
-                  c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
+                  _p(ws_acc), _p(ws_ml), _p(counters), c_int(T), c_int(Hq), c_int(Hkv), c_int(D),
+                  c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit),
+                  _stream())
         return out
     if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
             and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
@@ -393,6 +419,38 @@ def moe_plan(topk_idx: torch.Tensor, E: int) -> MoePlan:
     _lib.call("nf_moe_plan", _p(topk_idx), c_int(T * k), c_int(E), _p(offsets), _p(order), _p(inv),
               _p(counts), _stream())
     return MoePlan(offsets, order, inv, E, T, k)
+
+
+_TICKETS = {}
+
+
+def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool,
+          split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None):
+    """Routing of a step: `router_topk` and `moe_plan` together -> (idx, weights, extra, plan).
+
+    Up to `TUNING["router_fused_max_rows"]` rows this is one launch: blocks compute the
+    logits, and the block that finishes last selects for every row and builds the plan."""
+    _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
+    T, H = x.shape
+    if T == 0 or T > TUNING["router_fused_max_rows"]:
+        idx, wts, ext = router_topk(x, w_router, E, k, norm_topk, split=split)
+        return idx, wts, ext, moe_plan(idx, E)
+    dev = x.device
+    extra = w_router.shape[0] - E
+    key = str(dev)
+    if key not in _TICKETS:
+        _TICKETS[key] = torch.zeros((1,), dtype=torch.int32, device=dev)
+    idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+    ext = torch.empty((T, extra), dtype=torch.float32, device=dev) if extra > 0 else None
+    logits = torch.empty((T, E + extra), dtype=torch.float32, device=dev)
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    order = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    _lib.call("nf_router_fused", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra), c_int(k),
+              c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
+              _p(inv), _p(_TICKETS[key]), c_int(_dt(x)), _stream())
+    return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k)
 
 
 def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:

@@ -159,11 +159,10 @@ class SparseMoeSwiglu(FeedForward):
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
-        idx, wts, gate = kernels.router_topk(x, self.w_router, E, k, self.norm_topk_prob,
+        idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
                                              split=self.w_router_split)
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
-        plan = kernels.moe_plan(idx, E)
         act = kernels.moe_gemm1(x, self.w13, plan, k)
         y = kernels.moe_gemm2(act, self.w2, plan)
         if fork:

@@ -149,6 +149,11 @@ def moe_plan(topk_idx, E):
     return MoePlan(mk(offsets), mk(order), mk(inv), E, T, k)
 
 
+def route(x, w_router, E, k, norm_topk, split=None):
+    idx, wts, ext = router_topk(x, w_router, E, k, norm_topk)
+    return idx, wts, ext, moe_plan(idx, E)
+
+
 def moe_gemm1(x, w13, plan, k):
     T, H = x.shape
     E, two_i, _ = w13.shape
@@ -211,7 +216,7 @@ def check_router_sizes(num_experts, top_k):
 
 
 NAMES = ["can_pack", "PackedWeights", "split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
-         "rope_append", "paged_attention", "router_topk", "moe_plan", "moe_gemm1", "moe_gemm2",
+         "rope_append", "paged_attention", "router_topk", "route", "moe_plan", "moe_gemm1", "moe_gemm2",
          "moe_combine", "argmax_rows"]
 
 

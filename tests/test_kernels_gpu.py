@@ -179,6 +179,16 @@ def test_decode_attention_split_kernel(K, Hq, Hkv, D, page, window):
     ctx.all_single = False
     gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
     torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
+    # the one-launch form (last CTA of a row merges), twice: its counters must come back to zero
+    ctx.all_single = True
+    old = K.TUNING["decode_merge_fused_max_rows"]
+    K.TUNING["decode_merge_fused_max_rows"] = 64
+    try:
+        for _ in range(2):
+            one = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+            assert torch.equal(one, out)
+    finally:
+        K.TUNING["decode_merge_fused_max_rows"] = old
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,page,window", [(4, 1, 128, 64, 0), (6, 2, 48, 16, 0), (4, 4, 64, 32, 37),
@@ -261,6 +271,26 @@ def test_router_topk(K, dtype, T, H, E, k, norm, extra):
         torch.testing.assert_close(ext, rext, rtol=1e-4, atol=1e-5)
     else:
         assert ext is None
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,E,k,norm,extra", [(1, 200, 6, 3, True, 1), (8, 2048, 60, 4, False, 1),
+                                                (64, 96, 16, 4, True, 0), (33, 1000, 130, 8, False, 1)])
+def test_route_in_one_launch(K, dtype, T, H, E, k, norm, extra):
+    """Few rows: logits, selection and plan come from one launch; twice in a row, since the
+    kernel must leave its ticket counter as it found it."""
+    x = rnd((T, H), dtype, 71)
+    w = rnd((E + extra, H), torch.float32, 72, 0.1)
+    ridx, rwts, rext = P.router_topk(x, w, E, k, norm)
+    rplan = P.moe_plan(ridx, E)
+    for _ in range(2):
+        idx, wts, ext, plan = K.route(x, w, E, k, norm)
+        assert torch.equal(idx, ridx)
+        torch.testing.assert_close(wts, rwts, rtol=1e-4, atol=1e-6)
+        if extra:
+            torch.testing.assert_close(ext, rext, rtol=1e-4, atol=1e-5)
+        assert torch.equal(plan.offsets, rplan.offsets) and torch.equal(plan.order, rplan.order)
+        assert torch.equal(plan.inv, rplan.inv)
 
 
 def test_router_ties_go_to_lower_index(K):
