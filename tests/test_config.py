@@ -96,3 +96,22 @@ def test_engine_options():
         EngineOptions(dtype="int4")
     with pytest.raises(ValueError):
         EngineOptions(page_size=24)
+
+
+def test_shared_keys_agree_with_the_reference_parser():
+    """The reference's own config parser, compiled from its sources, read the same three
+    configurations (tests/golden/reference_config.json, made by
+    tests/golden/make_reference_config_golden.sh)."""
+    import os
+    from tiny_configs import CONFIGS
+    golden = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_config.json")))
+    for name, (cfg, _) in CONFIGS.items():
+        ours, ref = Qwen2MoeConfig.from_dict(cfg), golden[name]
+        assert ours.architecture == ref["arch"] and ours.model_type == ref["model_type"]
+        for key in ("vocab_size", "hidden_size", "num_hidden_layers", "num_attention_heads",
+                    "num_key_value_heads", "intermediate_size", "head_dim", "num_experts",
+                    "num_experts_per_tok", "moe_intermediate_size", "tie_word_embeddings"):
+            assert getattr(ours, key) == ref[key], (name, key)
+        assert abs(ours.rms_norm_eps - ref["rms_norm_eps"]) <= 1e-7 * ours.rms_norm_eps * 10
+        assert abs(ours.rope_theta - ref["rope_theta"]) <= 1e-6 * ours.rope_theta
+        assert ref["is_moe"] is True and ref["ffn_inner"] == ours.moe_intermediate_size
