@@ -13,7 +13,7 @@ from ninfer_amd_mi50_b200.engine import StepEntry, load_runner
 from ninfer_amd_mi50_b200.weights import write_random_model
 
 
-@pytest.fixture(params=["A", "B", "C"])
+@pytest.fixture(params=["A", "B", "C", "D"])
 def tiny(request, tmp_path, monkeypatch):
     cfg, seed = CONFIGS[request.param]
     d = str(tmp_path / request.param)

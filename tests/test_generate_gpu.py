@@ -84,7 +84,7 @@ def test_sampler_refuses_what_it_cannot_do():
     check_params(SamplingParams(0.0, 5000, 0.9), 151936)     # greedy ignores both
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_greedy_generation_through_the_entry_point(folders, name):
     from ninfer_amd_mi50_b200.api import Ninfer
     d, cfg, pcfg, weights = folders[name]

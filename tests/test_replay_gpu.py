@@ -45,7 +45,7 @@ def check(got, want, dtype, what):
     return row_err.median().item() / scale
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def folder(request, tmp_path_factory):
     from ninfer_amd_mi50_b200.weights import write_random_model
     cfg, seed = CONFIGS[request.param]

@@ -41,7 +41,21 @@ TINY_C = {
     "hidden_act": "silu", "qkv_bias": True,
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# Awkward on purpose: a width and inner sizes that are not multiples of 8 (so the 16-byte-row
+# kernels must step aside for the general ones), a single kv head for five query heads, one
+# expert per token, a dense first layer, a tiny vocabulary, no `head_dim` key (derived), no bias.
+TINY_D = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 76,
+    "num_experts": 4, "num_experts_per_tok": 1, "moe_intermediate_size": 36,
+    "shared_expert_intermediate_size": 52, "norm_topk_prob": False,
+    "decoder_sparse_step": 1, "mlp_only_layers": [0], "vocab_size": 131,
+    "rope_theta": 777.0, "rms_norm_eps": 1e-4, "tie_word_embeddings": True,
+    "use_sliding_window": False, "qkv_bias": False, "hidden_act": "silu",
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def random_tokens(n: int, vocab: int, seed: int):
