@@ -267,27 +267,53 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
 }
 
 // One block per (row, q head): merge the splits of the row's key range in ascending order.
+// The blocks' (m, l) go to shared memory in one parallel read; then every thread owns a few
+// output dims and adds the blocks' partial outputs with weights exp(m_s - m) / l.
+constexpr int kMaxMergeSplits = 1024;
 template <typename T>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
                                               const float* __restrict__ ws_ml,
                                               const int* __restrict__ positions, T* __restrict__ out,
                                               int Hq, int D, int window, int nsplit) {
+  __shared__ float wgt[kMaxMergeSplits];
+  __shared__ float s_m, s_inv;
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   int lo = 0;
   if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
-  const int s0 = lo / kSplit, s1 = pos / kSplit;      // first and last split with keys
-  const float* ml = ws_ml + ((size_t)t * Hq + h) * nsplit * 2;
-  const float* acc = ws_acc + ((size_t)t * Hq + h) * nsplit * D;
-  float m = -INFINITY;
-  for (int s = s0; s <= s1 && s < nsplit; ++s) m = fmaxf(m, ml[2 * s]);
-  float l = 0.f;
-  for (int s = s0; s <= s1 && s < nsplit; ++s) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
-  const float inv_l = l > 0.f ? 1.f / l : 0.f;
+  const int s0 = lo / kSplit, s1 = min(pos / kSplit, nsplit - 1);      // first and last split with keys
+  const int n = s1 - s0 + 1;
+  const float* ml = ws_ml + (((size_t)t * Hq + h) * nsplit + s0) * 2;
+  const float* acc = ws_acc + (((size_t)t * Hq + h) * nsplit + s0) * D;
+  for (int s = threadIdx.x; s < n; s += blockDim.x) wgt[s] = ml[2 * s];          // m_s for now
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = -INFINITY;
+    for (int s = 0; s < n; ++s) m = fmaxf(m, wgt[s]);
+    s_m = m;
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < n; s += blockDim.x) wgt[s] = expf(wgt[s] - s_m);  // now exp(m_s - m)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float l = 0.f;
+    for (int s = 0; s < n; ++s) l += ml[2 * s + 1] * wgt[s];                      // ascending order
+    s_inv = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float o = 0.f;
-    for (int s = s0; s <= s1 && s < nsplit; ++s) o += acc[(size_t)s * D + d] * expf(ml[2 * s] - m);
-    out[((size_t)t * Hq + h) * D + d] = from_float<T>(o * inv_l);
+    int s = 0;
+    for (; s + 4 <= n; s += 4) {
+      const float a0 = acc[(size_t)s * D + d], a1 = acc[(size_t)(s + 1) * D + d];
+      const float a2 = acc[(size_t)(s + 2) * D + d], a3 = acc[(size_t)(s + 3) * D + d];
+      o += a0 * wgt[s];
+      o += a1 * wgt[s + 1];
+      o += a2 * wgt[s + 2];
+      o += a3 * wgt[s + 3];
+    }
+    for (; s < n; ++s) o += acc[(size_t)s * D + d] * wgt[s];
+    out[((size_t)t * Hq + h) * D + d] = from_float<T>(o * s_inv);
   }
 }
 
@@ -328,7 +354,7 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
                                  float scale, int nsplit, int* counters, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && nsplit > 0, "decode attention: bad sizes T=%d Hq=%d Hkv=%d nsplit=%d", T, Hq, Hkv, nsplit);
-  NF_REQUIRE(Hkv <= 65535 && nsplit <= 65535, "decode attention: too many kv heads or key blocks");
+  NF_REQUIRE(Hkv <= 65535 && nsplit <= kMaxMergeSplits, "decode attention: too many kv heads or key blocks (context beyond %d keys)", kMaxMergeSplits * kSplit);
   int rc;
   switch (D) {
     case 16: rc = launch_split<16>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;

@@ -108,35 +108,40 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 
   const int nchunks = (K + 31) >> 5;
   for (int c0 = warp; c0 < nchunks; c0 += kWarps * kUnroll) {
-    uint4 a[kUnroll], b[kUnroll];
+    // a round: ask for the weights and the matching pieces of X of kUnroll chunks at once, so
+    // that the (L2) latency of X hides behind the (DRAM) latency of W
+    uint4 a[kUnroll], b[kUnroll], xv[kUnroll][NT];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int k = (c0 + u * kWarps) * 32;
-      if (PACKED && c0 + u * kWarps < nchunks) {
+      const bool live = c0 + u * kWarps < nchunks;
+      if (PACKED && live) {
         const int kk = k + 8 * t;                   // < padded K: the padding holds zeros
         const __nv_bfloat16* tile = Wg + ptile + (size_t)(kk >> 6) * (TROWS * 64);
         const int j = (kk >> 3) & 7;
         a[u] = ld_stream(tile + pr0 * 64 + ((j ^ (pr0 & 7)) << 3));
         b[u] = ld_stream(tile + pr1 * 64 + ((j ^ (pr1 & 7)) << 3));
-      } else if (!PACKED && k + 8 * t + 8 <= K && c0 + u * kWarps < nchunks) {
+      } else if (!PACKED && live && k + 8 * t + 8 <= K) {
         a[u] = ld_stream(w0 + k);
         b[u] = ld_stream(w1 + k);
       } else {
         a[u] = make_uint4(0, 0, 0, 0);
         b[u] = make_uint4(0, 0, 0, 0);
       }
+      const bool in = live && k + 8 * t + 8 <= K;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        xv[u][nt] = make_uint4(0, 0, 0, 0);
+        if (in && nt < ntiles && xp[nt]) xv[u][nt] = ld_cached(xp[nt] + k);
+      }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int k = (c0 + u * kWarps) * 32;
-      const bool in = k + 8 * t + 8 <= K && c0 + u * kWarps < nchunks;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         if (nt < ntiles) {
-          uint4 x = make_uint4(0, 0, 0, 0);
-          if (in && xp[nt]) x = ld_cached(xp[nt] + k);
-          mma_bf16(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
-          mma_bf16(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+          mma_bf16(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, xv[u][nt].x, xv[u][nt].y);
+          mma_bf16(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, xv[u][nt].z, xv[u][nt].w);
         }
       }
     }
