@@ -12,12 +12,27 @@
 
 namespace nf {
 
-// A lane's share of a dot product: elements lane, lane + 32, ... in four interleaved partial
-// sums (so that the loads overlap), added as (s0 + s1) + (s2 + s3).  Every router kernel
+// A lane's share of a dot product in four partial sums, added as (s0 + s1) + (s2 + s3): with a
+// width that is a multiple of 4, elements 4 lane .. 4 lane + 3 of every 128; else elements lane,
+// lane + 32, ...  Every router kernel
 // uses this, so a logit's value does not depend on which of them computed it.
 __device__ __forceinline__ float lane_dot(const float* __restrict__ xs, const float* __restrict__ w,
                                           int hidden, int lane) {
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if ((hidden & 3) == 0 && ((uintptr_t)w & 15) == 0) {
+    // 16 bytes a lane a step; eight steps asked for before the first is used, so that the
+    // whole row is two round trips to memory, not sixteen
+#pragma unroll 8
+    for (int i = lane * 4; i < hidden; i += 128) {
+      const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      const float4 xv = *reinterpret_cast<const float4*>(xs + i);
+      s0 = fmaf(xv.x, wv.x, s0);
+      s1 = fmaf(xv.y, wv.y, s1);
+      s2 = fmaf(xv.z, wv.z, s2);
+      s3 = fmaf(xv.w, wv.w, s3);
+    }
+    return (s0 + s1) + (s2 + s3);
+  }
   int i = lane;
   for (; i + 96 < hidden; i += 128) {
     const float w0 = w[i], w1 = w[i + 32], w2 = w[i + 64], w3 = w[i + 96];
@@ -127,13 +142,15 @@ router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp
                topk_idx, topk_w, extra_out, lane);
 }
 
-// Plan by one block: stable counting sort of the n pairs by expert.  `counts` is E + 1 ints
+// Plan by one block: stable counting sort of the n pairs by expert, and (if `active` is
+// given) the list of experts that have pairs, ascending, padded with -1 to n_active_max.  `counts` is E + 1 ints
 // of shared memory; with STAGED, `ex` holds n 16-bit expert ids so that the E passes over the
 // pairs do not go to global memory.
 template <bool STAGED>
 __device__ __forceinline__ void plan_block(const int* __restrict__ topk_idx, int n, int E,
                                            int* __restrict__ offsets, int* __restrict__ order,
-                                           int* __restrict__ inv, int* counts, unsigned short* ex) {
+                                           int* __restrict__ inv, int* counts, unsigned short* ex,
+                                           int* __restrict__ active, int n_active_max) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   if (STAGED) {
     for (int i = threadIdx.x; i < n; i += blockDim.x) ex[i] = (unsigned short)__ldcg(topk_idx + i);
@@ -152,15 +169,18 @@ __device__ __forceinline__ void plan_block(const int* __restrict__ topk_idx, int
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int run = 0;
+    int run = 0, na = 0;
     for (int e = 0; e < E; ++e) {
       const int c = counts[e];
+      if (c > 0 && active && na < n_active_max) active[na++] = e;
       counts[e] = run;
       offsets[e] = run;
       run += c;
     }
     counts[E] = run;
     offsets[E] = run;
+    if (active)
+      for (; na < n_active_max; ++na) active[na] = -1;
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -175,10 +195,11 @@ __device__ __forceinline__ void plan_block(const int* __restrict__ topk_idx, int
 template <bool STAGED>
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict__ offsets,
-                int* __restrict__ order, int* __restrict__ inv) {
+                int* __restrict__ order, int* __restrict__ inv, int* __restrict__ active,
+                int n_active_max) {
   extern __shared__ int counts[];      // [E + 1], then (STAGED) n experts as 16-bit
   plan_block<STAGED>(topk_idx, n, E, offsets, order, inv, counts,
-                     reinterpret_cast<unsigned short*>(counts + E + 1));
+                     reinterpret_cast<unsigned short*>(counts + E + 1), active, n_active_max);
 }
 
 // Few tokens (decode steps): logits, selection and plan in one launch.  Blocks (8 router rows,
@@ -191,7 +212,7 @@ router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n
                     int E, int extra, int k, int norm_topk, float* __restrict__ logits,
                     int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ extra_out,
                     int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv,
-                    int* __restrict__ ticket) {
+                    int* __restrict__ active, int n_active_max, int* __restrict__ ticket) {
   extern __shared__ float xs[];        // [hidden]; the last block reuses it
   __shared__ int s_last;
   const int rows = E + extra;
@@ -219,7 +240,7 @@ router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n
   __syncthreads();
   int* counts = reinterpret_cast<int*>(xs);         // [E + 1], then the pairs' experts
   plan_block<true>(topk_idx, n_tokens * k, E, offsets, order, inv, counts,
-                   reinterpret_cast<unsigned short*>(counts + E + 1));
+                   reinterpret_cast<unsigned short*>(counts + E + 1), active, n_active_max);
   if (threadIdx.x == 0) *ticket = 0;
 }
 
@@ -255,12 +276,20 @@ moe_rank_kernel(const int* __restrict__ topk_idx, int n, int* __restrict__ count
 
 __global__ void __launch_bounds__(256)
 moe_scatter_kernel(const int* __restrict__ topk_idx, int n, int E, const int* __restrict__ counts,
-                   int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv) {
+                   int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv,
+                   int* __restrict__ active, int n_active_max) {
   extern __shared__ int off[];        // [E + 1]
   if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) { off[e] = run; run += counts[e]; }
+    int run = 0, na = 0;
+    const bool list = active && blockIdx.x == 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = run;
+      if (list && counts[e] > 0 && na < n_active_max) active[na++] = e;
+      run += counts[e];
+    }
     off[E] = run;
+    if (list)
+      for (; na < n_active_max; ++na) active[na] = -1;
   }
   __syncthreads();
   if (blockIdx.x == 0)
@@ -321,8 +350,8 @@ extern "C" int nf_router_topk(const void* x, const float* wr, int T, int hidden,
 // floats of shared memory; `ticket` is a zeroed int that the kernel leaves zeroed.
 extern "C" int nf_router_fused(const void* x, const float* wr, int T, int hidden, int E, int extra, int k,
                                int norm_topk, float* logits, int* topk_idx, float* topk_w,
-                               float* extra_out, int* offsets, int* order, int* inv, int* ticket,
-                               int dtype, cudaStream_t stream) {
+                               float* extra_out, int* offsets, int* order, int* inv, int* active,
+                               int n_active_max, int* ticket, int dtype, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && T <= 65535 && hidden > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d hidden=%d E=%d k=%d", T, hidden, E, k);
   size_t words = (size_t)hidden;
@@ -334,10 +363,10 @@ extern "C" int nf_router_fused(const void* x, const float* wr, int T, int hidden
   dim3 grid((E + extra + 7) / 8, T);
   if (dtype == kF32) {
     if (smem > allowed_f) { cudaFuncSetAttribute(router_fused_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_f = smem; }
-    router_fused_kernel<float><<<grid, 256, smem, stream>>>((const float*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, ticket);
+    router_fused_kernel<float><<<grid, 256, smem, stream>>>((const float*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
   } else {
     if (smem > allowed_b) { cudaFuncSetAttribute(router_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_b = smem; }
-    router_fused_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, ticket);
+    router_fused_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
   }
   return check_launch("router_fused");
 }
@@ -356,13 +385,14 @@ extern "C" int nf_router_select(const float* logits, long long tok_stride, long 
 }
 
 // counts: int32 scratch [E] (may be null: then one block does everything).
+// active / n_active_max: optional list of the experts that have pairs (ascending, -1 padded).
 extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int* order, int* inv,
-                           int* counts, cudaStream_t stream) {
+                           int* counts, int* active, int n_active_max, cudaStream_t stream) {
   NF_REQUIRE(n >= 0 && E > 0 && E <= 8192, "moe_plan: bad sizes n=%d E=%d", n, E);
   if (n > 2048 && counts) {
     moe_rank_kernel<<<E, 1024, 0, stream>>>(topk_idx, n, counts, inv);
     if (int rc = check_launch("moe_rank")) return rc;
-    moe_scatter_kernel<<<(n + 255) / 256, 256, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, counts, offsets, order, inv);
+    moe_scatter_kernel<<<(n + 255) / 256, 256, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, counts, offsets, order, inv, active, n_active_max);
     return check_launch("moe_scatter");
   }
   const size_t staged = (size_t)(E + 1) * sizeof(int) + (size_t)n * sizeof(unsigned short);
@@ -372,9 +402,9 @@ extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int*
       cudaFuncSetAttribute(moe_plan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);
       allowed = staged;
     }
-    moe_plan_kernel<true><<<1, 1024, staged, stream>>>(topk_idx, n, E, offsets, order, inv);
+    moe_plan_kernel<true><<<1, 1024, staged, stream>>>(topk_idx, n, E, offsets, order, inv, active, n_active_max);
   } else {
-    moe_plan_kernel<false><<<1, 1024, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, offsets, order, inv);
+    moe_plan_kernel<false><<<1, 1024, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, offsets, order, inv, active, n_active_max);
   }
   return check_launch("moe_plan");
 }

@@ -50,12 +50,16 @@ template <int NT, bool SWIGLU, bool PACKED, typename TC>
 __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
-                   const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div) {
+                   const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div,
+                   const int* __restrict__ group_map) {
   // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
   __shared__ float partial[kWarps][NT * 4 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int group = blockIdx.z;   // row tiles vary fastest, so CTAs that share weight rows run together
+  // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
+  // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
+  const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
+  if (group < 0) return;
   int row_begin = 0, row_end = M;
   if (offsets) { row_begin = offsets[group]; row_end = offsets[group + 1]; }
   const int m0 = row_begin + blockIdx.x * (8 * NT);
@@ -180,25 +184,25 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 template <int NT, bool SWIGLU, bool PACKED, typename TC>
 static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M, int N,
                      int K, int groups, int max_rows, const int* offsets, const int* x_rows, int x_div,
-                     cudaStream_t stream) {
+                     const int* group_map, int n_mapped, cudaStream_t stream) {
   const int feat = SWIGLU ? 8 : 16;
-  dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, groups);
+  dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, group_map ? n_mapped : groups);
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
   skinny_gemm_kernel<NT, SWIGLU, PACKED, TC><<<grid, kWarps * 32, 0, stream>>>(
-      (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows, x_div);
+      (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows, x_div, group_map);
   return check_launch("skinny_gemm");
 }
 
 template <bool SWIGLU, typename TC>
 static int launch_sw(int nt, bool packed, const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M,
                      int N, int K, int groups, int max_rows, const int* offsets, const int* x_rows,
-                     int x_div, cudaStream_t stream) {
+                     int x_div, const int* group_map, int n_mapped, cudaStream_t stream) {
   if (packed) {
-    if (nt == 1) return launch_nt<1, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-    return launch_nt<2, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    if (nt == 1) return launch_nt<1, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+    return launch_nt<2, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
   }
-  if (nt == 1) return launch_nt<1, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-  return launch_nt<2, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+  if (nt == 1) return launch_nt<1, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+  return launch_nt<2, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
 }
 
 }  // namespace nf
@@ -209,10 +213,13 @@ using namespace nf;
 // out_dtype: 1 bfloat16, 0 float32.  max_rows: bound on the rows of any one group.
 // Needs K % 8 == 0 and 16-byte aligned rows (ldx % 8 == 0, bases aligned).
 // packed != 0: W is in the packed tile layout (w_group_stride then counts packed elements).
+// group_map / n_mapped: optional list of the groups to run (-1 entries are skipped); the grid
+// then has n_mapped groups instead of `groups`.
 extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w_group_stride, void* Y,
                               int ldy, int M, int N, int K, int groups, int max_rows,
                               const int* offsets, const int* x_rows, int x_div, int swiglu,
-                              int out_dtype, int packed, cudaStream_t stream) {
+                              int out_dtype, int packed, const int* group_map, int n_mapped,
+                              cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && x_div > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   NF_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "skinny_gemm: K=%d and the row stride %d must be multiples of 8", K, ldx);
@@ -225,9 +232,9 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   const size_t wgs = (size_t)w_group_stride;
   if (swiglu) {
     NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");
-    return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
   }
   if (out_dtype == kBF16)
-    return launch_sw<false, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
-  return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, stream);
+    return launch_sw<false, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+  return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
 }

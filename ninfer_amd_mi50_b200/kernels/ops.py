@@ -142,11 +142,12 @@ def _gemm_simt(a, lda, b, b_group_stride, c, M, N, K, groups, max_rows, offsets,
 
 
 def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu,
-            packed=False) -> None:
+            packed=False, group_map=None) -> None:
     _lib.call("nf_skinny_gemm", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
               c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
               _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
-              c_int(1 if packed else 0), _stream())
+              c_int(1 if packed else 0), _p(group_map),
+              c_int(group_map.numel() if group_map is not None else 0), _stream())
 
 
 class PackedWeights:
@@ -361,6 +362,7 @@ class MoePlan:
     num_experts: int
     num_tokens: int
     top_k: int
+    active: Optional[torch.Tensor] = None   # int32 [min(E, T * k)] experts that have pairs, -1 padded
 
 
 def split_router(w_router: torch.Tensor) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -418,9 +420,10 @@ def moe_plan(topk_idx: torch.Tensor, E: int) -> MoePlan:
     order = torch.empty((T * k,), dtype=torch.int32, device=dev)
     inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
     counts = torch.empty((E,), dtype=torch.int32, device=dev)
+    active = torch.empty((min(E, max(T * k, 1)),), dtype=torch.int32, device=dev)
     _lib.call("nf_moe_plan", _p(topk_idx), c_int(T * k), c_int(E), _p(offsets), _p(order), _p(inv),
-              _p(counts), _stream())
-    return MoePlan(offsets, order, inv, E, T, k)
+              _p(counts), _p(active), c_int(active.numel()), _stream())
+    return MoePlan(offsets, order, inv, E, T, k, active)
 
 
 _TICKETS = {}
@@ -449,10 +452,11 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
     offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
     order = torch.empty((T * k,), dtype=torch.int32, device=dev)
     inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    active = torch.empty((min(E, T * k),), dtype=torch.int32, device=dev)
     _lib.call("nf_router_fused", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), c_int(extra), c_int(k),
               c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
-              _p(inv), _p(_TICKETS[key]), c_int(_dt(x)), _stream())
-    return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k)
+              _p(inv), _p(active), c_int(active.numel()), _p(_TICKETS[key]), c_int(_dt(x)), _stream())
+    return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
 
 
 def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
@@ -476,7 +480,7 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
     if packed:
         if T <= TUNING["skinny_moe_max_tokens"]:
             _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
-                    k, True, packed=True)
+                    k, True, packed=True, group_map=plan.active)
         else:
             # rows in sorted order, then one tensor-core launch over all experts
             xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
@@ -487,7 +491,8 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
         return act
     path = "simt" if x.dtype == torch.float32 else _bf16_path(T, H, "bf16_moe")
     if path == "skinny":
-        _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
+        _skinny(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True,
+                group_map=plan.active)
     else:
         _gemm_simt(x, H, w13, two_i * H, act, T * k, inner, H, E, T, plan.offsets, plan.order, k, True)
     return act
@@ -511,14 +516,15 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan) -> torch.Tensor:
     if packed:
         if plan.num_tokens <= TUNING["skinny_moe_max_tokens"]:
             _skinny(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens, plan.offsets,
-                    None, 1, False, packed=True)
+                    None, 1, False, packed=True, group_map=plan.active)
         else:
             _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2.data), c_int(E), c_int(H),
                       c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())
         return y
     path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
     if path == "skinny":
-        _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
+        _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False,
+                group_map=plan.active)
     else:
         _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
     return y

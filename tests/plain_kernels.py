@@ -105,9 +105,10 @@ def paged_attention(qkv, Hq, Hkv, D, pages, block_table, page_size, ctx, window,
 
 
 class MoePlan:
-    def __init__(self, offsets, order, inv, num_experts, num_tokens, top_k):
+    def __init__(self, offsets, order, inv, num_experts, num_tokens, top_k, active=None):
         self.offsets, self.order, self.inv = offsets, order, inv
         self.num_experts, self.num_tokens, self.top_k = num_experts, num_tokens, top_k
+        self.active = active
 
 
 def split_router(w_router):
@@ -146,7 +147,9 @@ def moe_plan(topk_idx, E):
         offsets.append(offsets[-1] + c)
     dev = topk_idx.device
     mk = lambda l: torch.tensor(l, dtype=torch.int32, device=dev)
-    return MoePlan(mk(offsets), mk(order), mk(inv), E, T, k)
+    n_act = min(E, max(T * k, 1))
+    act = [e for e in range(E) if counts[e] > 0]
+    return MoePlan(mk(offsets), mk(order), mk(inv), E, T, k, mk(act + [-1] * (n_act - len(act))))
 
 
 def route(x, w_router, E, k, norm_topk, split=None):

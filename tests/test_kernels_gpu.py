@@ -290,7 +290,7 @@ def test_route_in_one_launch(K, dtype, T, H, E, k, norm, extra):
         if extra:
             torch.testing.assert_close(ext, rext, rtol=1e-4, atol=1e-5)
         assert torch.equal(plan.offsets, rplan.offsets) and torch.equal(plan.order, rplan.order)
-        assert torch.equal(plan.inv, rplan.inv)
+        assert torch.equal(plan.inv, rplan.inv) and torch.equal(plan.active, rplan.active)
 
 
 def test_router_ties_go_to_lower_index(K):
@@ -310,6 +310,7 @@ def test_moe_plan(K, T, k, E):
     assert torch.equal(plan.offsets, ref.offsets)
     assert torch.equal(plan.order, ref.order)
     assert torch.equal(plan.inv, ref.inv)
+    assert torch.equal(plan.active, ref.active)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
