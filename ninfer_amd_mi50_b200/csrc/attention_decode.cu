@@ -79,6 +79,8 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
+  chain_release();
+  chain_wait();          // queries and this step's keys were written by the kernel before
   const int pos = positions[t];
   int lo = 0;
   if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
@@ -181,6 +183,7 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   }
   cp_async_wait<0>();          // values have landed
   __syncthreads();
+  chain_release_late();
 
   // ---- acc^T = V^T p^T: [D dims] x [8 heads], summed over the warp's 32 keys ------------------
   for (int h0 = 0; h0 < G; h0 += HC) {
@@ -278,6 +281,8 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
   __shared__ float wgt[kMaxMergeSplits];
   __shared__ float s_m, s_inv;
   const int t = blockIdx.x, h = blockIdx.y;
+  chain_release();
+  chain_wait();
   const int pos = positions[t];
   int lo = 0;
   if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
@@ -332,10 +337,10 @@ static int launch_split(const void* qkv, int q_row_stride, const void* pages, co
     allowed = smem;
   }
   dim3 grid(T, Hkv, nsplit);
-  decode_attention_split_kernel<D><<<grid, 128, smem, stream>>>(
-      (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width, positions,
-      row_seg, ws_acc, ws_ml, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters,
-      (__nv_bfloat16*)out);
+  launch_chained(decode_attention_split_kernel<D>, grid, dim3(128), smem, stream,
+                 (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width,
+                 positions, row_seg, ws_acc, ws_ml, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters,
+                 (__nv_bfloat16*)out);
   return check_launch("decode_attention_split");
 }
 
@@ -370,7 +375,8 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
   dim3 grid(T, Hq);
   int threads = 32;
   while (threads < D && threads < 256) threads <<= 1;
-  decode_attention_merge_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(ws_acc, ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit);
+  launch_chained(decode_attention_merge_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const float*)ws_acc,
+                 (const float*)ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit);
   return check_launch("decode_attention_merge");
 }
 

@@ -18,6 +18,44 @@ enum DType : int { kF32 = 0, kBF16 = 1 };
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 
+// Programmatic dependent launch.  A kernel launched through `launch_chained` may begin while
+// the kernel before it in the stream is still draining: its CTAs are scheduled as soon as every
+// CTA of the predecessor has started (each calls `chain_release` first thing), do whatever does
+// not depend on the predecessor (index arithmetic, fetching weights), and then block in
+// `chain_wait` until the predecessor has completed and its writes are visible.  That hides the
+// launch and ramp-up of the many short kernels of a decode step.  Kernels launched the ordinary
+// way are unaffected; for them both calls do nothing.
+extern int g_chained_launch;   // nf_set_chained_launch(): 0 turns the attribute off
+#ifdef NF_CHAIN_EARLY_RELEASE
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;"); }
+#else
+// Measured on B200: releasing at the top of every kernel made decode steps 20-25 % slower (the
+// successors' CTAs sit on the SMs spinning while the predecessor still needs them), so the
+// release is left to the implicit one at kernel exit; the attribute then only lets the next
+// launch be prepared early.
+__device__ __forceinline__ void chain_release() {}
+#endif
+// A release late in a kernel, once its CTA has asked for all it will read: the successor's
+// CTAs then arrive while this one reduces and writes.
+__device__ __forceinline__ void chain_release_late() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = g_chained_launch ? 1 : 0;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch
+}
+
 #define NF_REQUIRE(cond, ...)            \
   do {                                   \
     if (!(cond)) {                       \

@@ -83,6 +83,8 @@ __global__ void add_rmsnorm_x4_kernel(float* __restrict__ h, const T* __restrict
                                       float eps, T* __restrict__ out, int hidden) {
   __shared__ float red[33];
   const int r = blockIdx.x;
+  chain_release();
+  chain_wait();
   const int src = GATHER ? rows[r] : r;
   float* hr = h + (size_t)src * hidden;
   const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
@@ -182,6 +184,8 @@ __global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, c
                                           __nv_bfloat16* __restrict__ out, int hidden, int k) {
   const int t = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  chain_release();
+  chain_wait();
   if (i >= hidden) return;
   float acc[8];
 #pragma unroll
@@ -237,11 +241,11 @@ extern "C" int nf_add_rmsnorm(float* h, const void* delta, const int* rows, cons
       (!delta || (uintptr_t)delta % 16 == 0)) {
     const int t4 = row_threads(hidden / 4);
     if (dtype == kF32) {
-      if (rows) add_rmsnorm_x4_kernel<float, true><<<R, t4, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);
-      else add_rmsnorm_x4_kernel<float, false><<<R, t4, 0, stream>>>(h, (const float*)delta, rows, w, eps, (float*)out, hidden);
+      if (rows) launch_chained(add_rmsnorm_x4_kernel<float, true>, dim3(R), dim3(t4), 0, stream, h, (const float*)delta, rows, w, eps, (float*)out, hidden);
+      else launch_chained(add_rmsnorm_x4_kernel<float, false>, dim3(R), dim3(t4), 0, stream, h, (const float*)delta, rows, w, eps, (float*)out, hidden);
     } else {
-      if (rows) add_rmsnorm_x4_kernel<__nv_bfloat16, true><<<R, t4, 0, stream>>>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
-      else add_rmsnorm_x4_kernel<__nv_bfloat16, false><<<R, t4, 0, stream>>>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
+      if (rows) launch_chained(add_rmsnorm_x4_kernel<__nv_bfloat16, true>, dim3(R), dim3(t4), 0, stream, h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
+      else launch_chained(add_rmsnorm_x4_kernel<__nv_bfloat16, false>, dim3(R), dim3(t4), 0, stream, h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, hidden);
     }
     return check_launch("add_rmsnorm");
   }
@@ -279,7 +283,7 @@ extern "C" int nf_moe_combine(const void* y, const int* inv, const float* wts, c
   if (dtype == kBF16 && hidden % 8 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
       (!shared || (uintptr_t)shared % 16 == 0)) {
     dim3 g8(T, (hidden / 8 + 127) / 128);
-    moe_combine_bf16x8_kernel<<<g8, 128, 0, stream>>>((const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
+    launch_chained(moe_combine_bf16x8_kernel, g8, dim3(128), 0, stream, (const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
     return check_launch("moe_combine");
   }
   dim3 grid(T, (hidden + 255) / 256);

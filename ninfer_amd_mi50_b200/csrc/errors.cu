@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 namespace nf {
+int g_chained_launch = 1;
 static thread_local char g_error[512] = "";
 
 void set_error(const char* fmt, ...) {
@@ -28,3 +29,10 @@ int check_launch(const char* what) {
 extern "C" const char* nf_last_error() { return nf::g_error; }
 
 extern "C" int nf_abi_version() { return 1; }
+
+// 1: kernels of the decode path are launched with programmatic stream serialization (they may
+// begin while their predecessor drains); 0: ordinary launches.
+extern "C" int nf_set_chained_launch(int on) {
+  nf::g_chained_launch = on ? 1 : 0;
+  return 0;
+}

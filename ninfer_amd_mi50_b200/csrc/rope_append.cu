@@ -88,6 +88,8 @@ rope_append_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restri
   extern __shared__ float cs[];            // [D/2] cos, [D/2] sin
   const int t = blockIdx.x;
   const int half = D / 2;
+  chain_release();
+  chain_wait();
   const int pos = positions[t];
   const float fpos = (float)pos;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -159,7 +161,7 @@ extern "C" int nf_rope_append(void* qkv, const float* bias, const int* positions
   const size_t smem = (size_t)rot * sizeof(float);
   NF_REQUIRE(smem <= 48 * 1024, "rope_append: rotary width %d too large", rot);
   if (dtype == kBF16 && rot == D && D % 16 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)pages % 16 == 0) {
-    rope_append_bf16x8_kernel<<<T, 256, smem, stream>>>((__nv_bfloat16*)qkv, bias, positions, row_seg, inv_freq, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, append);
+    launch_chained(rope_append_bf16x8_kernel, dim3(T), dim3(256), smem, stream, (__nv_bfloat16*)qkv, bias, positions, row_seg, inv_freq, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, append);
     return check_launch("rope_append");
   }
   if (dtype == kF32)

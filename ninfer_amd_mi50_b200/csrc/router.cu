@@ -218,6 +218,8 @@ router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n
   const int rows = E + extra;
   const int t = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  chain_release();
+  chain_wait();
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_float(x[(size_t)t * hidden + i]);
   __syncthreads();
   const int e = blockIdx.x * 8 + warp;
@@ -363,10 +365,10 @@ extern "C" int nf_router_fused(const void* x, const float* wr, int T, int hidden
   dim3 grid((E + extra + 7) / 8, T);
   if (dtype == kF32) {
     if (smem > allowed_f) { cudaFuncSetAttribute(router_fused_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_f = smem; }
-    router_fused_kernel<float><<<grid, 256, smem, stream>>>((const float*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
+    launch_chained(router_fused_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
   } else {
     if (smem > allowed_b) { cudaFuncSetAttribute(router_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_b = smem; }
-    router_fused_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
+    launch_chained(router_fused_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
   }
   return check_launch("router_fused");
 }

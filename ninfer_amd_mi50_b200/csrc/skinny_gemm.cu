@@ -56,6 +56,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   __shared__ float partial[kWarps][NT * 4 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  chain_release();
+  chain_wait();          // offsets, row maps and X come from the kernels before this one
   // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
   // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
   const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
@@ -151,6 +153,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     }
   }
 
+  chain_release_late();
   // add the warps' partial sums in warp order
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -188,8 +191,9 @@ static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y,
   const int feat = SWIGLU ? 8 : 16;
   dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, group_map ? n_mapped : groups);
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
-  skinny_gemm_kernel<NT, SWIGLU, PACKED, TC><<<grid, kWarps * 32, 0, stream>>>(
-      (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows, x_div, group_map);
+  launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
+                 (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
+                 x_div, group_map);
   return check_launch("skinny_gemm");
 }
 
