@@ -17,6 +17,7 @@ enum DType : int { kF32 = 0, kBF16 = 1 };
 
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
+void note_launch_error(cudaError_t e);
 
 // Programmatic dependent launch.  A kernel launched through `launch_chained` may begin while
 // the kernel before it in the stream is still draining: its CTAs are scheduled as soon as every
@@ -53,7 +54,9 @@ inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = g_chained_launch ? 1 : 0;
-  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) note_launch_error(e);     // check_launch reports it even if the runtime
+                                                  // did not keep it as its last error
 }
 
 #define NF_REQUIRE(cond, ...)            \

@@ -15,8 +15,14 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static thread_local cudaError_t g_noted = cudaSuccess;
+
+void note_launch_error(cudaError_t e) { g_noted = e; }
+
 int check_launch(const char* what) {
   cudaError_t e = cudaPeekAtLastError();
+  if (e == cudaSuccess) e = g_noted;
+  g_noted = cudaSuccess;
   if (e != cudaSuccess) {
     set_error("%s: %s", what, cudaGetErrorString(e));
     (void)cudaGetLastError();

@@ -57,7 +57,11 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   chain_release();
-  chain_wait();          // offsets, row maps and X come from the kernels before this one
+  // A dense product needs nothing from the kernel before it until it reads X: its first round
+  // of weights is asked for before the wait.  A grouped one reads offsets and row maps at once.
+  const bool dense = !offsets && !x_rows && !group_map;
+  bool waited = !dense;
+  if (!dense) chain_wait();
   // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
   // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
   const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
@@ -134,7 +138,12 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
         a[u] = make_uint4(0, 0, 0, 0);
         b[u] = make_uint4(0, 0, 0, 0);
       }
-      const bool in = live && k + 8 * t + 8 <= K;
+    }
+    if (!waited) { chain_wait(); waited = true; }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = (c0 + u * kWarps) * 32;
+      const bool in = c0 + u * kWarps < nchunks && k + 8 * t + 8 <= K;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         xv[u][nt] = make_uint4(0, 0, 0, 0);
@@ -153,6 +162,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     }
   }
 
+  if (!waited) chain_wait();      // a warp without chunks still must not write before the wait
   chain_release_late();
   // add the warps' partial sums in warp order
 #pragma unroll

@@ -13,6 +13,7 @@ page is the cache's null page.  They cost a little work and touch nothing that i
 
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Sequence, Tuple
 
 import numpy as np
@@ -76,8 +77,18 @@ class DecodeGraph:
         torch.cuda.synchronize(dev)
         before = klib.launch_count()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = runner.run(self.ctx)
+        # No cyclic garbage collection while the stream captures: collecting an older engine's
+        # graphs then would destroy them inside this capture, which the runtime forbids and
+        # answers by invalidating the capture.
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = runner.run(self.ctx)
+        finally:
+            if collecting:
+                gc.enable()
         self.kernels = klib.launch_count() - before
         self.h2d_bytes = total * 4
 

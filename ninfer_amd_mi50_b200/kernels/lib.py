@@ -9,6 +9,7 @@ the first call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Optional
 
@@ -35,6 +36,8 @@ def load() -> ctypes.CDLL:
             except OSError as e:
                 raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from None
             lib.nf_last_error.restype = ctypes.c_char_p
+            if os.environ.get("NINFER_CHAINED_LAUNCH", "1") == "0":
+                lib.nf_set_chained_launch(0)     # plain launches: every kernel waits for the one before
             _lib = lib
     return _lib
 
