@@ -196,3 +196,47 @@ def test_graph_replay_equals_host_driven_steps(folders, dtype):
         eng.close()
     for a, b in zip(*outs):
         torch.testing.assert_close(a, b, rtol=0, atol=0)
+
+
+def test_capture_survives_an_older_engine_waiting_for_the_collector(folders, monkeypatch):
+    """An engine that died inside a reference cycle keeps its CUDA graphs until the cyclic
+    collector runs.  If that happened during a later engine's capture, the graphs would be
+    destroyed inside the capture and invalidate it; the capture therefore holds the collector
+    off.  Here the older engine becomes garbage in the middle of the capture, followed by
+    enough cyclic garbage to set an enabled collector off."""
+    import gc
+    from ninfer_amd_mi50_b200.api import Ninfer
+    from ninfer_amd_mi50_b200.engine.step import ModelRunner
+    d, cfg, _, _ = folders["A"]
+    first = Ninfer(d, max_context=128, prefill_chunk=32, num_sequences=2, dtype="bfloat16", use_graph=True)
+    s = first.session()
+    s.prefill(random_tokens(5, 1024, 7))
+    ref = first.decode_batch([s], [3]).copy()
+    assert first._runner.graphs.graphs                      # a graph was captured
+    s.close()
+    del s
+    held = [first]
+    del first
+    seen = []
+    plain_run = ModelRunner.run
+
+    def run(self, ctx):
+        if torch.cuda.is_current_stream_capturing() and held:
+            ring = [held.pop()]
+            ring.append(ring)
+            del ring
+            for _ in range(5000):                            # far beyond the collector's thresholds
+                c = []
+                c.append(c)
+            seen.append(gc.isenabled())
+        return plain_run(self, ctx)
+
+    monkeypatch.setattr(ModelRunner, "run", run)
+    second = Ninfer(d, max_context=128, prefill_chunk=32, num_sequences=2, dtype="bfloat16", use_graph=True)
+    s = second.session()
+    s.prefill(random_tokens(5, 1024, 7))
+    out = second.decode_batch([s], [3])
+    assert seen == [False] and gc.isenabled()
+    assert (out == ref).all()
+    s.close()
+    second.close()
