@@ -273,11 +273,15 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
 // The blocks' (m, l) go to shared memory in one parallel read; then every thread owns a few
 // output dims and adds the blocks' partial outputs with weights exp(m_s - m) / l.
 constexpr int kMaxMergeSplits = 1024;
+constexpr int kMergeRun = 16;        // blocks one thread adds in a row
+// dthreads: threads that share the D dims (a power of two); blockDim.x is a multiple of it.
+// Dynamic shared memory: ceil(nsplit / kMergeRun) * D floats if nsplit > kMergeRun, else none.
 template <typename T>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
                                               const float* __restrict__ ws_ml,
                                               const int* __restrict__ positions, T* __restrict__ out,
-                                              int Hq, int D, int window, int nsplit) {
+                                              int Hq, int D, int window, int nsplit, int dthreads) {
+  extern __shared__ float runs[];      // [runs of this row][D]
   __shared__ float wgt[kMaxMergeSplits];
   __shared__ float s_m, s_inv;
   const int t = blockIdx.x, h = blockIdx.y;
@@ -306,18 +310,35 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
     s_inv = l > 0.f ? 1.f / l : 0.f;
   }
   __syncthreads();
+  // Runs of kMergeRun blocks are added by different thread groups (a long context has hundreds of
+  // blocks, and one thread walking them all is a chain of memory latencies); the runs' sums are
+  // then added in ascending order.  Which run a block falls in depends on the row's own range
+  // only, so the order of the sum does too.
+  const int nruns = (n + kMergeRun - 1) / kMergeRun;
+  const int groups = blockDim.x / dthreads, group = threadIdx.x / dthreads, dl = threadIdx.x - group * dthreads;
+  for (int r = group; r < nruns; r += groups) {
+    const int sb = r * kMergeRun, se = min(n, sb + kMergeRun);
+    for (int d = dl; d < D; d += dthreads) {
+      float o = 0.f;
+      int s = sb;
+      for (; s + 4 <= se; s += 4) {
+        const float a0 = acc[(size_t)s * D + d], a1 = acc[(size_t)(s + 1) * D + d];
+        const float a2 = acc[(size_t)(s + 2) * D + d], a3 = acc[(size_t)(s + 3) * D + d];
+        o += a0 * wgt[s];
+        o += a1 * wgt[s + 1];
+        o += a2 * wgt[s + 2];
+        o += a3 * wgt[s + 3];
+      }
+      for (; s < se; ++s) o += acc[(size_t)s * D + d] * wgt[s];
+      if (nruns == 1) out[((size_t)t * Hq + h) * D + d] = from_float<T>(o * s_inv);
+      else runs[(size_t)r * D + d] = o;
+    }
+  }
+  if (nruns == 1) return;
+  __syncthreads();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float o = 0.f;
-    int s = 0;
-    for (; s + 4 <= n; s += 4) {
-      const float a0 = acc[(size_t)s * D + d], a1 = acc[(size_t)(s + 1) * D + d];
-      const float a2 = acc[(size_t)(s + 2) * D + d], a3 = acc[(size_t)(s + 3) * D + d];
-      o += a0 * wgt[s];
-      o += a1 * wgt[s + 1];
-      o += a2 * wgt[s + 2];
-      o += a3 * wgt[s + 3];
-    }
-    for (; s < n; ++s) o += acc[(size_t)s * D + d] * wgt[s];
+    for (int r = 0; r < nruns; ++r) o += runs[(size_t)r * D + d];
     out[((size_t)t * Hq + h) * D + d] = from_float<T>(o * s_inv);
   }
 }
@@ -346,9 +367,25 @@ static int launch_split(const void* qkv, int q_row_stride, const void* pages, co
 
 }  // namespace nf
 
+namespace nf {
+// attention_decode_stream.cu: the persistent form of the split kernel (same partial results layout)
+int decode_attention_stream_fits(int T, int Hq, int Hkv, int D, int page_size);
+int decode_attention_stream(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
+                            int bt_width, const int* positions, const int* row_seg, float* ws_acc, float* ws_ml,
+                            int T, int Hq, int Hkv, int D, int page_size, int num_pages, int window, float scale,
+                            int nsplit, cudaStream_t stream);
+int g_decode_stream = 1;
+}  // namespace nf
+
 using namespace nf;
 
 extern "C" int nf_decode_attention_split_size() { return kSplit; }
+
+// 0: one CTA per block of keys; 1 (default): the persistent streaming kernel where it fits.
+extern "C" int nf_set_decode_stream(int on) {
+  g_decode_stream = on ? 1 : 0;
+  return 0;
+}
 
 // bfloat16 only; head_dim in {16, 32, 64, 128, 256}.  `nsplit` >= ceil(max context / 128) of
 // the rows in this call.  Workspace: ws_acc float32 [T, Hq, nsplit, D], ws_ml [T, Hq, nsplit, 2].
@@ -361,6 +398,13 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
   NF_REQUIRE(T > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && nsplit > 0, "decode attention: bad sizes T=%d Hq=%d Hkv=%d nsplit=%d", T, Hq, Hkv, nsplit);
   NF_REQUIRE(Hkv <= 65535 && nsplit <= kMaxMergeSplits, "decode attention: too many kv heads or key blocks (context beyond %d keys)", kMaxMergeSplits * kSplit);
   int rc;
+  // The persistent kernel pays a start-up (every CTA lists the rows' blocks) that only many
+  // blocks repay: measured on B200, it wins from about a thousand blocks on.
+  if (g_decode_stream && !counters && (long long)T * Hkv * nsplit >= 1024 &&
+      decode_attention_stream_fits(T, Hq, Hkv, D, page_size)) {
+    rc = decode_attention_stream(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml,
+                                 T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, stream);
+  } else
   switch (D) {
     case 16: rc = launch_split<16>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
     case 32: rc = launch_split<32>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
@@ -373,10 +417,21 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
   }
   if (rc || counters) return rc;      // with counters the split kernel's last CTAs have merged
   dim3 grid(T, Hq);
-  int threads = 32;
-  while (threads < D && threads < 256) threads <<= 1;
-  launch_chained(decode_attention_merge_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const float*)ws_acc,
-                 (const float*)ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit);
+  int dthreads = 32;
+  while (dthreads < D && dthreads < 256) dthreads <<= 1;
+  const int max_runs = (nsplit + kMergeRun - 1) / kMergeRun;
+  int groups = 1024 / dthreads < max_runs ? 1024 / dthreads : max_runs;
+  const size_t smem = max_runs > 1 ? (size_t)max_runs * D * sizeof(float) : 0;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_merge_kernel<__nv_bfloat16>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    NF_REQUIRE(e == cudaSuccess, "decode attention: the merge cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    allowed = smem;
+  }
+  launch_chained(decode_attention_merge_kernel<__nv_bfloat16>, grid, dim3(dthreads * groups), smem, stream,
+                 (const float*)ws_acc, (const float*)ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit,
+                 dthreads);
   return check_launch("decode_attention_merge");
 }
 

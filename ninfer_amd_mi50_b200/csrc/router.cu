@@ -219,12 +219,42 @@ router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n
   const int t = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   chain_release();
+  // The router's row is a weight: a lane asks for its share (up to 16 pieces of 16 bytes) before
+  // it waits for the kernel that writes x.  The sums below run in lane_dot's order exactly.
+  const int e = blockIdx.x * 8 + warp;
+  const float* w = wr + (size_t)min(e, rows - 1) * hidden;
+  constexpr int kPre = 16;
+  const bool pre = (hidden & 3) == 0 && ((uintptr_t)wr & 15) == 0 && hidden <= kPre * 128;
+  float4 wv[kPre];
+  if (pre) {
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int i = lane * 4 + j * 128;
+      wv[j] = i < hidden ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   chain_wait();
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_float(x[(size_t)t * hidden + i]);
   __syncthreads();
-  const int e = blockIdx.x * 8 + warp;
   if (e < rows) {
-    const float v = warp_sum(lane_dot(xs, wr + (size_t)e * hidden, hidden, lane));
+    float v;
+    if (pre) {
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        const int i = lane * 4 + j * 128;
+        if (i < hidden) {
+          const float4 xv = *reinterpret_cast<const float4*>(xs + i);
+          s0 = fmaf(xv.x, wv[j].x, s0);
+          s1 = fmaf(xv.y, wv[j].y, s1);
+          s2 = fmaf(xv.z, wv[j].z, s2);
+          s3 = fmaf(xv.w, wv[j].w, s3);
+        }
+      }
+      v = warp_sum((s0 + s1) + (s2 + s3));
+    } else {
+      v = warp_sum(lane_dot(xs, w, hidden, lane));
+    }
     if (lane == 0) logits[(size_t)t * rows + e] = v;
   }
   __threadfence();

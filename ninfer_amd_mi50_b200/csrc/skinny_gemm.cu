@@ -41,17 +41,35 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// What the rotate-and-append epilogue needs (see rope_append.cu for the separate kernel): the
+// product is the q/k/v projection of attention, rows of W laid out [q heads | k heads | v heads]
+// x D.  A CTA then owns 8 dims of the low half of one head and the 8 matching dims of the high
+// half, so each accumulator pair (row g, row g + 8) is one rotation pair: bias, rotation by
+// pos * inv_freq (float32), and the result goes to Y (queries) or straight into the cache page
+// of (request, position) (keys, values) - the projection's output never makes a round trip.
+struct RopeEpilogue {
+  const float* bias;          // [(Hq + 2 Hkv) D] or null
+  const int* positions;       // [M]
+  const int* row_seg;         // [M] block-table row of each row of X
+  const float* inv_freq;      // [D / 2]
+  __nv_bfloat16* pages;       // [num_pages, 2, Hkv, page_size, D]
+  const int* block_table;     // [segments, bt_width]
+  int Hq, Hkv, D, bt_width, page_size, num_pages, append;
+};
+
 // NT: number of 8-row tiles of X a CTA covers (rows <= 8 * NT).
 // PACKED: W is held as tiles of 128 (SwiGLU: 128 gate + 128 up) rows x 64 k, contiguous per
 // (feature tile, k tile) and 128-byte swizzled (16-byte piece j of row r sits at j ^ (r & 7)),
 // zero-padded: the layout the tensor-core kernel streams.  A CTA's 16 rows of one k tile are
 // then 2 KB of contiguous memory instead of 16 pieces 2 K bytes apart.
-template <int NT, bool SWIGLU, bool PACKED, typename TC>
+// ROPE: the rotate-and-append epilogue (dense, unpacked, bfloat16 out); blockIdx.y then counts
+// (head, 8-dim group of the low half) instead of 16-feature tiles.
+template <int NT, bool SWIGLU, bool PACKED, typename TC, bool ROPE = false>
 __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
                    const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div,
-                   const int* __restrict__ group_map) {
+                   const int* __restrict__ group_map, RopeEpilogue rope) {
   // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
   __shared__ float partial[kWarps][NT * 4 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -78,7 +96,14 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 
   // weight rows of this lane: tile row g and tile row g + 8
   int wr0, wr1;
-  if (SWIGLU) {
+  int rope_f0 = 0;      // ROPE: first of this CTA's 8 low-half features
+  if (ROPE) {
+    const int groups = rope.D >> 4;                    // 8-dim groups in half a head
+    const int head = blockIdx.y / groups, j = blockIdx.y - head * groups;
+    rope_f0 = head * rope.D + j * 8;
+    wr0 = rope_f0 + g;
+    wr1 = wr0 + (rope.D >> 1);
+  } else if (SWIGLU) {
     const int f = min(n0 + g, N - 1);
     wr0 = f;            // gate
     wr1 = N + f;        // up
@@ -183,7 +208,35 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     const int gg = l >> 2, tt = l & 3;
     const int row = m0 + nt * 8 + 2 * tt + h;          // token (sorted position) of this column
     if (row >= row_end) continue;
-    if (SWIGLU) {
+    if (ROPE) {
+      const int half = rope.D >> 1;
+      const int f0 = rope_f0 + gg, f1 = f0 + half;
+      const int head = f0 / rope.D, d = f0 - head * rope.D;
+      if (rope.bias) { lo += rope.bias[f0]; hi += rope.bias[f1]; }
+      const int pos = rope.positions[row];
+      if (head < rope.Hq + rope.Hkv) {                 // queries and keys turn, values do not
+        const float angle = (float)pos * rope.inv_freq[d];
+        const float c = cosf(angle), sn = sinf(angle);
+        const float ra = lo * c - hi * sn, rb = lo * sn + hi * c;
+        lo = ra;
+        hi = rb;
+      }
+      if (head < rope.Hq) {
+        Y[(size_t)row * ldy + f0] = from_float<TC>(lo);
+        Y[(size_t)row * ldy + f1] = from_float<TC>(hi);
+      } else if (rope.append) {
+        const int lp = pos / rope.page_size;
+        const int page = (lp >= 0 && lp < rope.bt_width) ? rope.block_table[(size_t)rope.row_seg[row] * rope.bt_width + lp] : -1;
+        if (page >= 0 && page < rope.num_pages) {
+          const bool is_v = head >= rope.Hq + rope.Hkv;
+          const int kvh = head - rope.Hq - (is_v ? rope.Hkv : 0);
+          __nv_bfloat16* dst = rope.pages + ((((size_t)page * 2 + (is_v ? 1 : 0)) * rope.Hkv + kvh) * rope.page_size +
+                                             (size_t)(pos - lp * rope.page_size)) * rope.D;
+          dst[d] = __float2bfloat16_rn(lo);
+          dst[d + half] = __float2bfloat16_rn(hi);
+        }
+      }
+    } else if (SWIGLU) {
       const int f = n0 + gg;
       if (f < N) Y[(size_t)row * ldy + f] = from_float<TC>(lo / (1.f + expf(-lo)) * hi);
     } else {
@@ -203,7 +256,7 @@ static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y,
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
   launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
                  (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
-                 x_div, group_map);
+                 x_div, group_map, RopeEpilogue{});
   return check_launch("skinny_gemm");
 }
 
@@ -251,4 +304,35 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   if (out_dtype == kBF16)
     return launch_sw<false, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
   return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+}
+
+// qkv = X Wqkv^T with bias, rotation and the append to the cache in the epilogue (see
+// RopeEpilogue): queries land rotated in Y [M, (Hq + 2 Hkv) D] (its key and value columns are
+// left untouched), keys and values in `pages` at (block_table[row_seg[r]], positions[r]).
+// bfloat16; the rotation covers the whole head; D % 16 == 0; M <= 16 rows.
+extern "C" int nf_skinny_qkv_rope(const void* X, int ldx, const void* W, void* Y, int ldy, int M, int K,
+                                  const float* bias, const int* positions, const int* row_seg,
+                                  const float* inv_freq, int Hq, int Hkv, int D, void* pages,
+                                  const int* block_table, int bt_width, int page_size, int num_pages,
+                                  int append, cudaStream_t stream) {
+  if (M == 0) return 0;
+  NF_REQUIRE(M > 0 && M <= 16 && K > 0 && Hq > 0 && Hkv > 0, "skinny_qkv_rope: bad sizes M=%d K=%d", M, K);
+  NF_REQUIRE(D > 0 && D % 16 == 0, "skinny_qkv_rope: head_dim %d must be a multiple of 16", D);
+  NF_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "skinny_qkv_rope: K=%d and the row stride %d must be multiples of 8", K, ldx);
+  NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "skinny_qkv_rope: operands must be 16-byte aligned");
+  NF_REQUIRE(positions && row_seg && inv_freq && pages && block_table, "skinny_qkv_rope: missing tables");
+  const int N = (Hq + 2 * Hkv) * D;
+  RopeEpilogue r{bias, positions, row_seg, inv_freq, (__nv_bfloat16*)pages, block_table,
+                 Hq, Hkv, D, bt_width, page_size, num_pages, append};
+  dim3 grid(1, N / 16, 1);
+  NF_REQUIRE(grid.y <= 65535, "skinny_qkv_rope: too many heads");
+  if (M <= 8)
+    launch_chained(skinny_gemm_kernel<1, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
+                   (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, r);
+  else
+    launch_chained(skinny_gemm_kernel<2, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
+                   (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, r);
+  return check_launch("skinny_qkv_rope");
 }

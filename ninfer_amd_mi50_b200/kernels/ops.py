@@ -34,6 +34,8 @@ TUNING = {
     # routed experts: up to this many tokens the streaming kernel serves, beyond it the
     # tensor-core kernel (measured: equal at 16 tokens, 25 % faster at 64)
     "skinny_moe_max_tokens": 8,
+    "skinny_staged": False,
+    "qkv_rope_fused": True,       # few bfloat16 rows: rotation and cache append in the projection's epilogue       # streaming kernel with weights staged through shared memory (cp.async)
     "router_tensor_min_rows": 128,   # router logits of more rows than this use tensor cores
     "router_fused_max_rows": 16,     # up to this many rows, routing is a single launch
     # decode attention can merge its key blocks in the same launch (the last CTA of a row does
@@ -148,6 +150,16 @@ def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, 
               _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
               c_int(1 if packed else 0), _p(group_map),
               c_int(group_map.numel() if group_map is not None else 0), _stream())
+
+
+def _skinny_staged(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu,
+                   packed=False, group_map=None, early_index=False) -> None:
+    _lib.call("nf_skinny_staged", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
+              c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
+              _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
+              c_int(1 if packed else 0), _p(group_map),
+              c_int(group_map.numel() if group_map is not None else 0), c_int(1 if early_index else 0),
+              _stream())
 
 
 class PackedWeights:
@@ -288,6 +300,38 @@ def rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torc
               c_int(Hkv), c_int(D), _p(pages), _p(block_table), c_int(block_table.shape[1]),
               c_int(page_size), c_int(pages.shape[0]), c_int(1 if append else 0), c_int(_dt(qkv)),
               _stream())
+
+
+def linear_rope_append(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                       positions: torch.Tensor, row_seg: torch.Tensor, inv_freq: torch.Tensor,
+                       rotary_dim: int, Hq: int, Hkv: int, D: int, pages: torch.Tensor,
+                       block_table: torch.Tensor, page_size: int, append: bool) -> torch.Tensor:
+    """qkv = x w_qkv^T, then `rope_append` on it -> [T, (Hq + 2 Hkv) D] whose query columns hold
+    the rotated queries (the key and value columns are not meant to be read: they went to the
+    cache).  A bfloat16 step of few rows does both in one kernel: the streaming product's
+    epilogue adds the bias, rotates and writes keys and values into their cache page."""
+    T, K = x.shape
+    if (TUNING["qkv_rope_fused"] and x.is_cuda and x.dtype == torch.bfloat16 and 0 < T <= min(16, TUNING["skinny_max_rows"])
+            and TUNING["bf16_linear"] == "auto" and K % 8 == 0 and D % 16 == 0 and rotary_dim == D
+            and inv_freq is not None):
+        _chk(x, "x"); _chk(w_qkv, "w_qkv", x.dtype); _chk(pages, "pages", x.dtype)
+        _chk(block_table, "block_table", torch.int32); _chk(positions, "positions", torch.int32)
+        _chk(row_seg, "row_seg", torch.int32); _chk(inv_freq, "inv_freq", torch.float32)
+        if bias is not None:
+            _chk(bias, "bias", torch.float32)
+        N = (Hq + 2 * Hkv) * D
+        if w_qkv.shape != (N, K):
+            raise ValueError("linear_rope_append: the projection does not match the head counts")
+        qkv = torch.empty((T, N), dtype=x.dtype, device=x.device)
+        _lib.call("nf_skinny_qkv_rope", _p(x), c_int(K), _p(w_qkv), _p(qkv), c_int(N), c_int(T), c_int(K),
+                  _p(bias), _p(positions), _p(row_seg), _p(inv_freq), c_int(Hq), c_int(Hkv), c_int(D),
+                  _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(page_size),
+                  c_int(pages.shape[0]), c_int(1 if append else 0), _stream())
+        return qkv
+    qkv = linear(x, w_qkv)
+    rope_append(qkv, bias, positions, row_seg, inv_freq, rotary_dim, Hq, Hkv, D, pages, block_table,
+                page_size, append)
+    return qkv
 
 
 _COUNTERS = {}
@@ -479,8 +523,12 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
         return act
     if packed:
         if T <= TUNING["skinny_moe_max_tokens"]:
-            _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
-                    k, True, packed=True, group_map=plan.active)
+            if TUNING["skinny_staged"]:
+                _skinny_staged(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets,
+                               plan.order, k, True, packed=True, group_map=plan.active)
+            else:
+                _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
+                        k, True, packed=True, group_map=plan.active)
         else:
             # rows in sorted order, then one tensor-core launch over all experts
             xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
@@ -498,8 +546,12 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
     return act
 
 
-def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan) -> torch.Tensor:
-    """Sorted pair p of expert e -> act[p] Wdown_e^T  [T*k, H].  `w2` is [E, H, I] or packed."""
+def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False) -> torch.Tensor:
+    """Sorted pair p of expert e -> act[p] Wdown_e^T  [T*k, H].  `w2` is [E, H, I] or packed.
+
+    `plan_is_older`: the plan was complete before the kernel that produced `act` was launched
+    (the usual order: router, first product, this).  The streaming kernel then starts fetching
+    weights while that kernel is still finishing."""
     _chk(act, "act")
     n, inner = act.shape
     packed = isinstance(w2, PackedWeights)
@@ -515,8 +567,13 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan) -> torch.Tensor:
         return y
     if packed:
         if plan.num_tokens <= TUNING["skinny_moe_max_tokens"]:
-            _skinny(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens, plan.offsets,
-                    None, 1, False, packed=True, group_map=plan.active)
+            if TUNING["skinny_staged"]:
+                _skinny_staged(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens,
+                               plan.offsets, None, 1, False, packed=True, group_map=plan.active,
+                               early_index=plan_is_older)
+            else:
+                _skinny(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens, plan.offsets,
+                        None, 1, False, packed=True, group_map=plan.active)
         else:
             _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2.data), c_int(E), c_int(H),
                       c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())

@@ -76,22 +76,26 @@ class PagedGqaAttention(Mixer):
                 state: Optional[torch.Tensor]) -> torch.Tensor:
         assert cache is not None, "attention needs a cache slot"
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = kernels.linear(x, self.w_qkv)
         table = self.position.rotary_table(x.device)
         bias = self.b_qkv
         if table is None:
             # an encoding that is not a half-split rotation: bias first, then its own hook
+            qkv = kernels.linear(x, self.w_qkv)
             if bias is not None:
                 qkv.add_(bias.to(qkv.dtype))
                 bias = None
             q = qkv[:, :self.q_width].unflatten(1, (Hq, D))
             k = qkv[:, self.q_width:self.q_width + self.kv_width].unflatten(1, (Hkv, D))
             self.position.apply(q, k, ctx.positions)
-            inv_freq, rot = None, 0
+            kernels.rope_append(qkv, None, ctx.positions, ctx.row_seg, None, 0, Hq, Hkv, D,
+                                cache.pages, cache.block_table, cache.page_size, cache.append)
         else:
+            # projection, bias, rotation and the write of k, v at (request, position): one kernel
+            # on small bfloat16 steps, two otherwise
             inv_freq, rot = table
-        kernels.rope_append(qkv, bias, ctx.positions, ctx.row_seg, inv_freq, rot, Hq, Hkv, D,
-                            cache.pages, cache.block_table, cache.page_size, cache.append)
+            qkv = kernels.linear_rope_append(x, self.w_qkv, bias, ctx.positions, ctx.row_seg, inv_freq, rot,
+                                             Hq, Hkv, D, cache.pages, cache.block_table, cache.page_size,
+                                             cache.append)
         out = kernels.paged_attention(qkv, Hq, Hkv, D, cache.pages, cache.block_table,
                                       cache.page_size, ctx, self.window or 0, self.scale)
         return kernels.linear(out, self.w_o)

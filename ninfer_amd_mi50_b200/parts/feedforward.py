@@ -164,7 +164,7 @@ class SparseMoeSwiglu(FeedForward):
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
         act = kernels.moe_gemm1(x, self.w13, plan, k)
-        y = kernels.moe_gemm2(act, self.w2, plan)
+        y = kernels.moe_gemm2(act, self.w2, plan, plan_is_older=True)
         if fork:
             main.wait_stream(side)
         elif self.has_shared:

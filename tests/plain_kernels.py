@@ -83,6 +83,14 @@ def rope_append(qkv, bias, positions, row_seg, inv_freq, rotary_dim, Hq, Hkv, D,
         pages[page, 1, :, pos % page_size, :] = x[t, Hq + Hkv:].to(pages.dtype)
 
 
+def linear_rope_append(x, w_qkv, bias, positions, row_seg, inv_freq, rotary_dim, Hq, Hkv, D, pages,
+                       block_table, page_size, append):
+    qkv = linear(x, w_qkv)
+    rope_append(qkv, bias, positions, row_seg, inv_freq, rotary_dim, Hq, Hkv, D, pages, block_table,
+                page_size, append)
+    return qkv
+
+
 def paged_attention(qkv, Hq, Hkv, D, pages, block_table, page_size, ctx, window, scale):
     T = qkv.shape[0]
     out = torch.zeros((T, Hq * D), dtype=torch.float32, device=qkv.device)
@@ -173,7 +181,7 @@ def moe_gemm1(x, w13, plan, k):
     return act.to(x.dtype)
 
 
-def moe_gemm2(act, w2, plan):
+def moe_gemm2(act, w2, plan, plan_is_older=False):
     n, inner = act.shape
     E, H, _ = w2.shape
     y = torch.zeros((n, H), dtype=torch.float32, device=act.device)
@@ -219,7 +227,7 @@ def check_router_sizes(num_experts, top_k):
 
 
 NAMES = ["can_pack", "PackedWeights", "split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
-         "rope_append", "paged_attention", "router_topk", "route", "moe_plan", "moe_gemm1", "moe_gemm2",
+         "rope_append", "linear_rope_append", "paged_attention", "router_topk", "route", "moe_plan", "moe_gemm1", "moe_gemm2",
          "moe_combine", "argmax_rows"]
 
 

@@ -152,6 +152,42 @@ def test_rope_append(K, dtype, Hq, Hkv, D, page, rot):
     assert torch.equal(p3, pages) and torch.equal(q3, qkv)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page,H,rows", [(4, 1, 128, 64, 256, 3), (6, 2, 48, 16, 200, 11), (16, 16, 128, 64, 2048, 8),
+                                                  (5, 5, 80, 32, 104, 16), (3, 1, 16, 16, 40, 1)])
+@pytest.mark.parametrize("append,with_bias", [(True, True), (False, False)])
+def test_projection_with_rotate_and_append_epilogue(K, Hq, Hkv, D, page, H, rows, append, with_bias):
+    """Few bfloat16 rows: q/k/v projection, bias, rotation and the write into the cache in one
+    kernel, against projection and rotate-and-append done apart by the plain twins (float32
+    throughout, rounded once) and by the two separate kernels."""
+    dtype = torch.bfloat16
+    lens = [0, 63, 64, 129, 5, 700, 31, 1, 2, 300, 17, 64, 65, 127, 128, 9][:rows]
+    pages, bt, ctx, _ = make_cache_case(dtype, Hq, Hkv, D, page, [1] * rows, lens, 256, 23)
+    N = (Hq + 2 * Hkv) * D
+    x, w = rnd((rows, H), dtype, 24), rnd((N, H), dtype, 25, 0.1)
+    bias = 0.1 * rnd((N,), torch.float32, 26) if with_bias else None
+    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / D) for i in range(D // 2)], dtype=torch.float32).cuda()
+    p1, p2, p3 = pages.clone(), pages.clone(), pages.clone()
+    q1 = K.linear_rope_append(x, w, bias, ctx.positions, ctx.row_seg, inv_freq, D, Hq, Hkv, D, p1, bt, page, append)
+    # plain: the projection kept in float32 until the one rounding at the end
+    y = (x.float() @ w.float().T)
+    q2 = y.clone()
+    pf = p2.float()
+    P.rope_append(q2, bias, ctx.positions, ctx.row_seg, inv_freq, D, Hq, Hkv, D, pf, bt, page, append)
+    torch.testing.assert_close(q1[:, :Hq * D].float(), q2[:, :Hq * D].to(dtype).float(), **tol(dtype, 3))
+    torch.testing.assert_close(p1.float(), pf.to(dtype).float(), **tol(dtype, 3))
+    if not append:
+        assert torch.equal(p1, pages)
+    # the two-kernel path
+    old = dict(K.TUNING)
+    try:
+        K.TUNING.update(qkv_rope_fused=False)
+        q3 = K.linear_rope_append(x, w, bias, ctx.positions, ctx.row_seg, inv_freq, D, Hq, Hkv, D, p3, bt, page, append)
+    finally:
+        K.TUNING.update(old)
+    torch.testing.assert_close(q1[:, :Hq * D].float(), q3[:, :Hq * D].float(), **tol(dtype, 4))
+    torch.testing.assert_close(p1.float(), p3.float(), **tol(dtype, 4))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hkv,D,page,window", [(6, 2, 48, 16, 0), (4, 1, 128, 64, 0), (4, 4, 64, 16, 21),
                                                   (8, 2, 256, 32, 0), (3, 1, 16, 16, 40)])
@@ -179,16 +215,65 @@ def test_decode_attention_split_kernel(K, Hq, Hkv, D, page, window):
     ctx.all_single = False
     gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
     torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
-    # the one-launch form (last CTA of a row merges), twice: its counters must come back to zero
+    # the one-launch form (one CTA per block of keys; the last CTA of a row merges), twice: its
+    # counters must come back to zero.  It rounds differently from the streaming kernel.
     ctx.all_single = True
     old = K.TUNING["decode_merge_fused_max_rows"]
     K.TUNING["decode_merge_fused_max_rows"] = 64
     try:
-        for _ in range(2):
-            one = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
-            assert torch.equal(one, out)
+        ones = [K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale) for _ in range(2)]
     finally:
         K.TUNING["decode_merge_fused_max_rows"] = old
+    assert torch.equal(ones[0], ones[1])
+    torch.testing.assert_close(ones[0].float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [(8, 4, 128, 64, 0), (32, 2, 64, 16, 300), (4, 4, 64, 32, 0),
+                                                  (3, 3, 128, 16, 1000)])
+def test_decode_attention_streaming_kernel(K, Hq, Hkv, D, page, window):
+    """Steps with a thousand and more blocks of keys take the persistent streaming kernel:
+    many rows with contexts from one key to seventeen blocks, with and without a window, up to
+    16 query heads a group.  Against the any-rows kernel (itself checked against the plain
+    twin), against the plain twin on the rows it can afford, and against the one-CTA-per-block
+    kernel it replaces."""
+    from ninfer_amd_mi50_b200.kernels import lib as klib
+    dtype = torch.bfloat16
+    lens = [0, 15, 16, 17, 127, 128, 129, 2100, 700, 383, 5, 1, 64, 1023, 1024, 1025, 2047, 2048, 33, 900,
+            1500, 1777, 250, 255, 256, 257, 511, 512, 513, 1999, 47, 48, 49, 1200, 1300, 1400, 640, 641, 2, 3]
+    n_pages = sum((n + 1 + page - 1) // page for n in lens) + 3
+    pages, bt, ctx, qkv = make_cache_case(dtype, Hq, Hkv, D, page, [1] * len(lens), lens, n_pages, 43)
+    ctx.all_single, ctx.max_context = True, max(lens) + 1
+    assert len(lens) * Hkv * ((ctx.max_context + 127) // 128) >= 1024
+    scale = 1 / math.sqrt(D)
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    lib = klib.load()
+    try:
+        lib.nf_set_decode_stream(0)
+        per_block = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    finally:
+        lib.nf_set_decode_stream(1)
+    assert not torch.equal(out, per_block)          # two kernels ran (they round differently)
+    torch.testing.assert_close(out.float(), per_block.float(), **tol(dtype))
+    ctx.all_single = False
+    gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
+    few = [0, 1, 4, 5, 6, 10, 11, 32, 38, 39]       # short rows: the plain twin walks key by key
+    sub = SimpleNamespace(positions=ctx.positions[few], row_seg=ctx.row_seg[few])
+    ref = P.paged_attention(qkv[few], Hq, Hkv, D, pages, bt, page, sub, window, scale)
+    torch.testing.assert_close(out[few].float(), ref.float(), **tol(dtype))
+    # a far key that matters: make one early key of the longest row dominate one head's scores
+    t_long = lens.index(2100)
+    q = qkv.clone()
+    seg = int(ctx.row_seg[t_long])
+    j = 777 if window == 0 else 2100 - min(window, 2100) + 3
+    kpage, slot = int(bt[seg, j // page]), j % page
+    q[t_long, :D] = 0
+    q[t_long, 0] = 30.0 / scale
+    pages[kpage, 0, 0, slot, :] = 0
+    pages[kpage, 0, 0, slot, 0] = 8.0                # score 240; the others are 30 * N(0, 1)
+    ctx.all_single = True
+    hot = K.paged_attention(q, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    torch.testing.assert_close(hot[t_long, :D].float(), pages[kpage, 1, 0, slot, :].float(), rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,page,window", [(4, 1, 128, 64, 0), (6, 2, 48, 16, 0), (4, 4, 64, 32, 37),
@@ -382,6 +467,38 @@ def test_grouped_gemm_on_tensor_cores(K, T, H, I, E, k):
     finally:
         K.TUNING.update(old)
     assert K.tensor_core_status() == 0
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 256, 128, 4, 2), (5, 200, 136, 6, 3), (8, 2048, 1408, 60, 4),
+                                       (13, 512, 264, 7, 2), (3, 40, 24, 3, 1)])
+def test_staged_streaming_equals_register_streaming(K, T, H, I, E, k):
+    """The streaming kernel that stages weights through shared memory with asynchronous copies
+    does the arithmetic of the one that loads them into registers, in the same order: equal bits,
+    on packed and on plain weights, with and without the early start of the second product; both
+    close to the plain twin."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(T * 31 + H)
+    x = rnd((T, H), dtype, 71)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 72, 0.1), rnd((E, H, I), dtype, 73, 0.1)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    plan = K.moe_plan(idx, E)
+    pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
+    old = dict(K.TUNING)
+    try:
+        K.TUNING.update(skinny_moe_max_tokens=10 ** 9, skinny_staged=False)
+        act0 = K.moe_gemm1(x, pw13, plan, k)
+        y0 = K.moe_gemm2(act0, pw2, plan)
+        K.TUNING.update(skinny_staged=True)
+        act1 = K.moe_gemm1(x, pw13, plan, k)
+        y1 = K.moe_gemm2(act1, pw2, plan)
+        y2 = K.moe_gemm2(act1, pw2, plan, plan_is_older=True)
+    finally:
+        K.TUNING.update(old)
+    assert K.tensor_core_status() == 0
+    assert torch.equal(act0, act1) and torch.equal(y0, y1) and torch.equal(y0, y2)
+    ract = P.moe_gemm1(x, w13, plan, k)
+    close(act1, ract, dtype)
+    close(y1, P.moe_gemm2(ract, w2, plan), dtype)
 
 
 @pytest.mark.parametrize("exact_bf16", [True, False])
