@@ -69,25 +69,33 @@ __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
                    const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div,
-                   const int* __restrict__ group_map, RopeEpilogue rope) {
+                   const int* __restrict__ group_map, int early_index, RopeEpilogue rope) {
   // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
   __shared__ float partial[kWarps][NT * 4 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   chain_release();
   // A dense product needs nothing from the kernel before it until it reads X: its first round
-  // of weights is asked for before the wait.  A grouped one reads offsets and row maps at once.
-  const bool dense = !offsets && !x_rows && !group_map;
+  // of weights is asked for before the wait.  A grouped one reads offsets and row maps at once,
+  // unless the caller vouches (early_index) that those were complete before the kernel that
+  // precedes this launch began - the router's plan, when this is the experts' second product.
+  const bool dense = (!offsets && !x_rows && !group_map) || early_index;
   bool waited = !dense;
   if (!dense) chain_wait();
   // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
   // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
   const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
-  if (group < 0) return;
+  if (group < 0) {
+    if (!waited) chain_wait();
+    return;
+  }
   int row_begin = 0, row_end = M;
   if (offsets) { row_begin = offsets[group]; row_end = offsets[group + 1]; }
   const int m0 = row_begin + blockIdx.x * (8 * NT);
-  if (m0 >= row_end) return;
+  if (m0 >= row_end) {
+    if (!waited) chain_wait();
+    return;
+  }
   const int rows = min(8 * NT, row_end - m0);
   const int ntiles = (rows + 7) >> 3;
   constexpr int FEAT = SWIGLU ? 8 : 16;
@@ -250,26 +258,26 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 template <int NT, bool SWIGLU, bool PACKED, typename TC>
 static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M, int N,
                      int K, int groups, int max_rows, const int* offsets, const int* x_rows, int x_div,
-                     const int* group_map, int n_mapped, cudaStream_t stream) {
+                     const int* group_map, int n_mapped, int early_index, cudaStream_t stream) {
   const int feat = SWIGLU ? 8 : 16;
   dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, group_map ? n_mapped : groups);
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
   launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
                  (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
-                 x_div, group_map, RopeEpilogue{});
+                 x_div, group_map, early_index, RopeEpilogue{});
   return check_launch("skinny_gemm");
 }
 
 template <bool SWIGLU, typename TC>
 static int launch_sw(int nt, bool packed, const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M,
                      int N, int K, int groups, int max_rows, const int* offsets, const int* x_rows,
-                     int x_div, const int* group_map, int n_mapped, cudaStream_t stream) {
+                     int x_div, const int* group_map, int n_mapped, int early_index, cudaStream_t stream) {
   if (packed) {
-    if (nt == 1) return launch_nt<1, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
-    return launch_nt<2, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+    if (nt == 1) return launch_nt<1, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
+    return launch_nt<2, SWIGLU, true, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
   }
-  if (nt == 1) return launch_nt<1, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
-  return launch_nt<2, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+  if (nt == 1) return launch_nt<1, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
+  return launch_nt<2, SWIGLU, false, TC>(X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
 }
 
 }  // namespace nf
@@ -281,12 +289,14 @@ using namespace nf;
 // Needs K % 8 == 0 and 16-byte aligned rows (ldx % 8 == 0, bases aligned).
 // packed != 0: W is in the packed tile layout (w_group_stride then counts packed elements).
 // group_map / n_mapped: optional list of the groups to run (-1 entries are skipped); the grid
-// then has n_mapped groups instead of `groups`.
+// then has n_mapped groups instead of `groups`.  early_index != 0: offsets, x_rows and group_map
+// were complete before the kernel that precedes this launch in the stream began, so they may be
+// read - and the first weights asked for - before that kernel has finished.
 extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w_group_stride, void* Y,
                               int ldy, int M, int N, int K, int groups, int max_rows,
                               const int* offsets, const int* x_rows, int x_div, int swiglu,
                               int out_dtype, int packed, const int* group_map, int n_mapped,
-                              cudaStream_t stream) {
+                              int early_index, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && x_div > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   NF_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "skinny_gemm: K=%d and the row stride %d must be multiples of 8", K, ldx);
@@ -299,11 +309,11 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   const size_t wgs = (size_t)w_group_stride;
   if (swiglu) {
     NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");
-    return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+    return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
   }
   if (out_dtype == kBF16)
-    return launch_sw<false, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
-  return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, stream);
+    return launch_sw<false, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
+  return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
 }
 
 // qkv = X Wqkv^T with bias, rotation and the append to the cache in the epilogue (see
@@ -329,10 +339,10 @@ extern "C" int nf_skinny_qkv_rope(const void* X, int ldx, const void* W, void* Y
   if (M <= 8)
     launch_chained(skinny_gemm_kernel<1, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, r);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, r);
   else
     launch_chained(skinny_gemm_kernel<2, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, r);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, r);
   return check_launch("skinny_qkv_rope");
 }

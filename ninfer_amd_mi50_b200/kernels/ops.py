@@ -34,8 +34,7 @@ TUNING = {
     # routed experts: up to this many tokens the streaming kernel serves, beyond it the
     # tensor-core kernel (measured: equal at 16 tokens, 25 % faster at 64)
     "skinny_moe_max_tokens": 8,
-    "skinny_staged": False,
-    "qkv_rope_fused": True,       # few bfloat16 rows: rotation and cache append in the projection's epilogue       # streaming kernel with weights staged through shared memory (cp.async)
+    "qkv_rope_fused": True,       # few bfloat16 rows: rotation and cache append in the projection's epilogue
     "router_tensor_min_rows": 128,   # router logits of more rows than this use tensor cores
     "router_fused_max_rows": 16,     # up to this many rows, routing is a single launch
     # decode attention can merge its key blocks in the same launch (the last CTA of a row does
@@ -144,17 +143,8 @@ def _gemm_simt(a, lda, b, b_group_stride, c, M, N, K, groups, max_rows, offsets,
 
 
 def _skinny(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu,
-            packed=False, group_map=None) -> None:
+            packed=False, group_map=None, early_index=False) -> None:
     _lib.call("nf_skinny_gemm", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
-              c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
-              _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
-              c_int(1 if packed else 0), _p(group_map),
-              c_int(group_map.numel() if group_map is not None else 0), _stream())
-
-
-def _skinny_staged(x, ldx, w, w_group_stride, out, M, N, K, groups, max_rows, offsets, x_rows, x_div, swiglu,
-                   packed=False, group_map=None, early_index=False) -> None:
-    _lib.call("nf_skinny_staged", _p(x), c_int(ldx), _p(w), c_longlong(w_group_stride), _p(out),
               c_int(out.shape[1]), c_int(M), c_int(N), c_int(K), c_int(groups), c_int(max_rows),
               _p(offsets), _p(x_rows), c_int(x_div), c_int(1 if swiglu else 0), c_int(_dt(out)),
               c_int(1 if packed else 0), _p(group_map),
@@ -523,12 +513,8 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
         return act
     if packed:
         if T <= TUNING["skinny_moe_max_tokens"]:
-            if TUNING["skinny_staged"]:
-                _skinny_staged(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets,
-                               plan.order, k, True, packed=True, group_map=plan.active)
-            else:
-                _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
-                        k, True, packed=True, group_map=plan.active)
+            _skinny(x, H, w13.data, w13.group_stride, act, T * k, inner, H, E, T, plan.offsets, plan.order,
+                    k, True, packed=True, group_map=plan.active)
         else:
             # rows in sorted order, then one tensor-core launch over all experts
             xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
@@ -567,13 +553,8 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
         return y
     if packed:
         if plan.num_tokens <= TUNING["skinny_moe_max_tokens"]:
-            if TUNING["skinny_staged"]:
-                _skinny_staged(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens,
-                               plan.offsets, None, 1, False, packed=True, group_map=plan.active,
-                               early_index=plan_is_older)
-            else:
-                _skinny(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens, plan.offsets,
-                        None, 1, False, packed=True, group_map=plan.active)
+            _skinny(act, inner, w2.data, w2.group_stride, y, n, H, inner, E, plan.num_tokens, plan.offsets,
+                    None, 1, False, packed=True, group_map=plan.active, early_index=plan_is_older)
         else:
             _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2.data), c_int(E), c_int(H),
                       c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), _stream())
@@ -581,7 +562,7 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
     path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
     if path == "skinny":
         _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False,
-                group_map=plan.active)
+                group_map=plan.active, early_index=plan_is_older)
     else:
         _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
     return y
