@@ -81,14 +81,22 @@ router_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr, int 
 // One warp, one token: softmax over the E router logits, the k largest (ties to the lower
 // index), weights p_e or p_e / sum(selected).  `lg` is E floats of the warp's shared memory;
 // logits[t, e] sits at row[e * exp_stride].
+// GLOBAL: the logits are in global memory, written by other blocks of this launch (read past
+// L1); otherwise they are in this block's shared memory.  `chosen`, if given, also receives the
+// k selected experts of the token as 16-bit ids (shared memory, for a plan in the same block).
+template <bool GLOBAL = true>
 __device__ __forceinline__ void select_token(const float* row, long exp_stride, float* lg, int t, int E,
                                              int extra, int k, int norm_topk, int* __restrict__ topk_idx,
                                              float* __restrict__ topk_w, float* __restrict__ extra_out,
-                                             int lane) {
-  for (int g = lane; g < extra; g += 32) extra_out[(size_t)t * extra + g] = __ldcg(row + (size_t)(E + g) * exp_stride);
+                                             int lane, unsigned short* chosen = nullptr) {
+  for (int g = lane; g < extra; g += 32) {
+    const float* p = row + (size_t)(E + g) * exp_stride;
+    extra_out[(size_t)t * extra + g] = GLOBAL ? __ldcg(p) : *p;
+  }
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
-    const float v = __ldcg(row + (size_t)e * exp_stride);
+    const float* p = row + (size_t)e * exp_stride;
+    const float v = GLOBAL ? __ldcg(p) : *p;
     lg[e] = v;
     mx = fmaxf(mx, v);
   }
@@ -118,6 +126,7 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
     if (lane == 0) {
       topk_idx[(size_t)t * k + j] = best_e;
       topk_w[(size_t)t * k + j] = best / sum;
+      if (chosen) chosen[(size_t)t * k + j] = (unsigned short)best_e;
       lg[best_e] = -2.f;                           // taken
     }
     sel_sum += best / sum;
@@ -276,6 +285,181 @@ router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n
   if (threadIdx.x == 0) *ticket = 0;
 }
 
+// Few tokens, second form: the same work by ONE thread-block cluster of 8 CTAs, with the
+// hand-over from "all logits" to "selection and plan" through distributed shared memory and the
+// cluster barrier instead of global memory, a fence and a ticket.  Every warp of the cluster
+// owns router rows e = 8 cta + warp + 64 j: it asks for its first row's weights before the
+// dependency wait, multiplies it with every token of the step (x sits in shared memory as
+// float32, the sums run in `lane_dot`'s order, so a logit has the bits the other kernels give
+// it) and stores the logits into CTA 0's shared memory.  After the barrier CTA 0 selects (one
+// warp per token) and builds the plan without leaving shared memory; the others are done.
+constexpr int kRouterCluster = 8;
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(float* local_ptr, unsigned cta, float v) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(local_ptr);
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(cta));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_cluster_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n_tokens, int hidden,
+                      int E, int extra, int k, int norm_topk, float* __restrict__ logits_out,
+                      int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ extra_out,
+                      int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv,
+                      int* __restrict__ active, int n_active_max) {
+  extern __shared__ __align__(16) float rs[];
+  const int rows = E + extra;
+  const int n = n_tokens * k;
+  float* xs = rs;                                        // [n_tokens][hidden]
+  float* lg_all = xs + (size_t)n_tokens * hidden;        // [n_tokens][rows]   (CTA 0's copy is the one used)
+  float* sel = lg_all + (size_t)n_tokens * rows;         // [8 warps][E]
+  int* counts = reinterpret_cast<int*>(sel + 8 * E);     // [E + 1]
+  int* rank = counts + E + 1;                            // [n]
+  unsigned short* chosen = reinterpret_cast<unsigned short*>(rank + n);   // [n]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned cta = cluster_ctarank();
+  const int e0 = (int)cta * 8 + warp;
+
+  constexpr int kPre = 16;
+  const bool vec = (hidden & 3) == 0 && ((uintptr_t)wr & 15) == 0;
+  const bool pre = vec && hidden <= kPre * 128 && e0 < rows;
+  float4 wv[kPre];
+  if (pre) {
+    const float* w = wr + (size_t)e0 * hidden;
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int i = lane * 4 + j * 128;
+      wv[j] = i < hidden ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  chain_wait();
+  {
+    // x -> float32 in shared memory, 16 bytes of x a thread a step where alignment allows
+    const int total = n_tokens * hidden;
+    constexpr int PER = 16 / (int)sizeof(T);
+    if (((uintptr_t)x & 15) == 0 && total % PER == 0) {
+      constexpr int U = 8;                       // loads in flight a thread: the rows are one trip to L2, not one each
+      const int step = blockDim.x * PER;
+      for (int i0 = threadIdx.x * PER; i0 < total; i0 += step * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * step < total) raw[u] = *reinterpret_cast<const uint4*>(x + i0 + u * step);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * step < total) {
+            const T* v = reinterpret_cast<const T*>(&raw[u]);
+            // 16-byte stores: scalar ones would put the lanes 8 floats apart, 8 to a bank
+#pragma unroll
+            for (int j = 0; j < PER; j += 4)
+              *reinterpret_cast<float4*>(xs + i0 + u * step + j) =
+                  make_float4(to_float(v[j]), to_float(v[j + 1]), to_float(v[j + 2]), to_float(v[j + 3]));
+          }
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < total; i += blockDim.x) xs[i] = to_float(x[i]);
+    }
+  }
+  __syncthreads();
+  for (int e = e0; e < rows; e += 8 * kRouterCluster) {
+    const float* w = wr + (size_t)e * hidden;
+    float mine = 0.f;
+    for (int t = 0; t < n_tokens; ++t) {
+      const float* xt = xs + (size_t)t * hidden;
+      float v;
+      if (pre && e == e0) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kPre; ++j) {
+          const int i = lane * 4 + j * 128;
+          if (i < hidden) {
+            const float4 xv = *reinterpret_cast<const float4*>(xt + i);
+            s0 = fmaf(xv.x, wv[j].x, s0);
+            s1 = fmaf(xv.y, wv[j].y, s1);
+            s2 = fmaf(xv.z, wv[j].z, s2);
+            s3 = fmaf(xv.w, wv[j].w, s3);
+          }
+        }
+        v = warp_sum((s0 + s1) + (s2 + s3));
+      } else {
+        v = warp_sum(lane_dot(xt, w, hidden, lane));
+      }
+      if (lane == t) mine = v;          // lane t keeps token t's logit (n_tokens <= 32)
+    }
+    // one remote store a lane, all in flight together: a store into another CTA's shared
+    // memory takes long, and one after the other they would add up
+    if (lane < n_tokens) {
+      st_cluster_f32(lg_all + (size_t)lane * rows + e, 0, mine);
+      if (logits_out) logits_out[(size_t)lane * rows + e] = mine;
+    }
+  }
+  cluster_sync_all();
+  if (cta != 0) return;
+  // ---- CTA 0: selection for every token, then the plan, all in shared memory --------------------
+  for (int tt = warp; tt < n_tokens; tt += 8)
+    select_token<false>(lg_all + (size_t)tt * rows, 1, sel + warp * E, tt, E, extra, k, norm_topk, topk_idx, topk_w,
+                        extra_out, lane, chosen);
+  __syncthreads();
+  for (int e = warp; e < E; e += 8) {
+    int running = 0;
+    for (int base = 0; base < n; base += 32) {
+      const int i = base + lane;
+      const bool mine = i < n && (int)chosen[i] == e;
+      const unsigned b = __ballot_sync(0xffffffffu, mine);
+      if (mine) rank[i] = running + __popc(b & ((1u << lane) - 1u));   // rank inside the expert
+      running += __popc(b);
+    }
+    if (lane == 0) counts[e] = running;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // one warp, 32 experts a round: exclusive prefix of the counts (-> offsets) and the list of
+    // the experts that have pairs, ascending, then -1
+    int run = 0, na = 0;
+    for (int base = 0; base <= E; base += 32) {
+      const int e = base + lane;
+      const int c = e < E ? counts[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (e <= E) {
+        counts[e] = run + incl - c;
+        offsets[e] = run + incl - c;
+      }
+      run += __shfl_sync(0xffffffffu, incl, 31);
+      const unsigned b = __ballot_sync(0xffffffffu, c > 0);
+      if (active) {
+        const int at = na + __popc(b & ((1u << lane) - 1u));
+        if (c > 0 && at < n_active_max) active[at] = e;
+      }
+      na += __popc(b);
+    }
+    if (active)
+      for (int i = min(na, n_active_max) + lane; i < n_active_max; i += 32) active[i] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int p = counts[chosen[i]] + rank[i];
+    inv[i] = p;
+    order[p] = i;
+  }
+}
+
 // The same plan for many pairs, spread over the device.  Block e ranks the pairs of expert e
 // (in pair order, so token order is kept) and counts them; the second kernel turns counts into
 // offsets and scatters.
@@ -401,6 +585,64 @@ extern "C" int nf_router_fused(const void* x, const float* wr, int T, int hidden
     launch_chained(router_fused_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)x, wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max, ticket);
   }
   return check_launch("router_fused");
+}
+
+// The same by one cluster of 8 CTAs (see router_cluster_kernel); `logits` may be null.  Takes what
+// fits its shared memory: 0 if (T, hidden, E, k) do, so that the caller can fall back.
+extern "C" int nf_router_cluster_fits(int T, int hidden, int E, int extra, int k) {
+  const size_t words = (size_t)T * hidden + (size_t)T * (E + extra) + (size_t)8 * E + (size_t)E + 1 + (size_t)T * k +
+                       ((size_t)T * k + 1) / 2;
+  return T > 0 && T <= 32 && E < 65536 && words * sizeof(float) <= 180 * 1024 ? 1 : 0;
+}
+
+extern "C" int nf_router_cluster(const void* x, const float* wr, int T, int hidden, int E, int extra, int k,
+                                 int norm_topk, float* logits, int* topk_idx, float* topk_w,
+                                 float* extra_out, int* offsets, int* order, int* inv, int* active,
+                                 int n_active_max, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && hidden > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d hidden=%d E=%d k=%d", T, hidden, E, k);
+  NF_REQUIRE(nf_router_cluster_fits(T, hidden, E, extra, k), "router: sizes too large for the cluster kernel");
+  const size_t words = (size_t)T * hidden + (size_t)T * (E + extra) + (size_t)8 * E + (size_t)E + 1 + (size_t)T * k +
+                       ((size_t)T * k + 1) / 2;
+  const size_t smem = words * sizeof(float);
+  static size_t allowed_f = 48 * 1024, allowed_b = 48 * 1024;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kRouterCluster);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  // The routed experts wait for this small kernel while the shared expert's large one, launched
+  // at the same moment on another stream, would fill every SM first: ask for the highest launch
+  // priority, so that these 8 CTAs are placed before that kernel's.
+  static int top_priority = 1;
+  if (top_priority == 1) {
+    int least = 0, greatest = 0;
+    cudaDeviceGetStreamPriorityRange(&least, &greatest);
+    top_priority = greatest;
+  }
+  cudaLaunchAttribute attrs[3];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = kRouterCluster;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributePriority;
+  attrs[1].val.priority = top_priority;
+  attrs[2].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[2].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = g_chained_launch ? 3 : 2;
+  cudaError_t e;
+  if (dtype == kF32) {
+    if (smem > allowed_f) { cudaFuncSetAttribute(router_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_f = smem; }
+    e = cudaLaunchKernelEx(&cfg, router_cluster_kernel<float>, (const float*)x, wr, T, hidden, E, extra, k, norm_topk,
+                           logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max);
+  } else {
+    if (smem > allowed_b) { cudaFuncSetAttribute(router_cluster_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_b = smem; }
+    e = cudaLaunchKernelEx(&cfg, router_cluster_kernel<__nv_bfloat16>, (const __nv_bfloat16*)x, wr, T, hidden, E, extra, k,
+                           norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max);
+  }
+  if (e != cudaSuccess) note_launch_error(e);
+  return check_launch("router_cluster");
 }
 
 // Selection alone, from float32 logits that something else has produced: logits[t, e] at

@@ -360,22 +360,35 @@ def test_router_topk(K, dtype, T, H, E, k, norm, extra):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,H,E,k,norm,extra", [(1, 200, 6, 3, True, 1), (8, 2048, 60, 4, False, 1),
-                                                (64, 96, 16, 4, True, 0), (33, 1000, 130, 8, False, 1)])
+                                                (16, 96, 16, 4, True, 0), (13, 1000, 130, 8, False, 1),
+                                                (64, 96, 16, 4, True, 0), (5, 3000, 70, 2, True, 2)])
 def test_route_in_one_launch(K, dtype, T, H, E, k, norm, extra):
-    """Few rows: logits, selection and plan come from one launch; twice in a row, since the
-    kernel must leave its ticket counter as it found it."""
+    """Few rows: logits, selection and plan come from one launch - by one thread-block cluster,
+    or by a grid whose last block finishes the work; each twice in a row, since the second
+    form must leave its ticket counter as it found it.  Both give the same bits."""
     x = rnd((T, H), dtype, 71)
     w = rnd((E + extra, H), torch.float32, 72, 0.1)
     ridx, rwts, rext = P.router_topk(x, w, E, k, norm)
     rplan = P.moe_plan(ridx, E)
-    for _ in range(2):
-        idx, wts, ext, plan = K.route(x, w, E, k, norm)
-        assert torch.equal(idx, ridx)
-        torch.testing.assert_close(wts, rwts, rtol=1e-4, atol=1e-6)
-        if extra:
-            torch.testing.assert_close(ext, rext, rtol=1e-4, atol=1e-5)
-        assert torch.equal(plan.offsets, rplan.offsets) and torch.equal(plan.order, rplan.order)
-        assert torch.equal(plan.inv, rplan.inv) and torch.equal(plan.active, rplan.active)
+    old = dict(K.TUNING)
+    seen = []
+    try:
+        for cluster in (True, False):
+            K.TUNING.update(router_cluster_max_rows=32 if cluster else 0)
+            for _ in range(2):
+                idx, wts, ext, plan = K.route(x, w, E, k, norm)
+                assert torch.equal(idx, ridx)
+                torch.testing.assert_close(wts, rwts, rtol=1e-4, atol=1e-6)
+                if extra:
+                    torch.testing.assert_close(ext, rext, rtol=1e-4, atol=1e-5)
+                assert torch.equal(plan.offsets, rplan.offsets) and torch.equal(plan.order, rplan.order)
+                assert torch.equal(plan.inv, rplan.inv) and torch.equal(plan.active, rplan.active)
+            seen.append((wts, ext))
+    finally:
+        K.TUNING.update(old)
+    assert torch.equal(seen[0][0], seen[1][0])
+    if extra:
+        assert torch.equal(seen[0][1], seen[1][1])
 
 
 def test_router_ties_go_to_lower_index(K):
