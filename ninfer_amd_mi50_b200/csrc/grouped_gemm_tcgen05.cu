@@ -32,9 +32,7 @@
 // Every wait on an mbarrier is bounded: after a fixed number of polls the kernel records a
 // code in `g_tc_error`, tells its other warps to stop, waits (again bounded) for its own
 // copies in flight, frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace nf {
 
@@ -42,7 +40,6 @@ constexpr int kBM = 128;          // features per CTA (MMA M)
 constexpr int kBK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kBNMax = 256;       // tokens per pass (MMA N, columns of one accumulator)
 constexpr int kTmemCols = 512;
-constexpr unsigned kPollLimit = 1u << 24;
 constexpr int kXBox = 64;         // token rows per TMA box
 constexpr int kMaxStages = 8;
 constexpr int kMaxGroupsTc = 1024;   // groups one launch may have (their pass counts live in shared memory)
@@ -50,80 +47,6 @@ constexpr int kSmemBudget = 225 * 1024;   // + 1 KB of alignment slack + a few s
 
 __device__ int g_tc_error = 0;
 
-// ---- PTX wrappers -----------------------------------------------------------------------------
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(void* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false if this wait ran out of polls or another role gave up.
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, volatile int* stop, int code) {
-  for (unsigned i = 0; i < kPollLimit; ++i) {
-    if (mbar_try(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *stop) return false;
-  }
-  *stop = 1;
-  atomicCAS(&g_tc_error, 0, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, void* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(void* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
-                                       unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row
-// groups 1024 bytes apart.
-__device__ __forceinline__ unsigned long long smem_desc(const void* p) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_u32(p) & 0x3FFFFu) >> 4);       // start address
-  d |= (unsigned long long)1 << 16;                                // leading byte offset (unused here)
-  d |= (unsigned long long)(1024 >> 4) << 32;                      // stride byte offset
-  d |= (unsigned long long)1 << 46;                                // descriptor version
-  d |= (unsigned long long)2 << 61;                                // 128-byte swizzle
-  return d;
-}
 // Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ unsigned instr_desc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(kBM >> 4) << 24);
@@ -220,7 +143,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
           const int boxes = (min(kBNMax, n_rows - pass * kBNMax) + kXBox - 1) / kXBox;
           for (int ks = 0; ks < k_steps; ++ks, ++it) {
             const int s = it % stages;
-            if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1)) { ok = false; break; }
+            if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1, &g_tc_error)) { ok = false; break; }
             unsigned char* st = smem + (size_t)s * stage_bytes;
             mbar_expect_tx(&bars->full[s], A_BYTES + boxes * BOX_BYTES);
             bulk_load(st, w_tile + (size_t)ks * A_BYTES, A_BYTES, &bars->full[s]);
@@ -251,13 +174,13 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
         const int pass = gp - s_pass_start[group];
         const int n_rows = offsets[group + 1] - offsets[group];
         {
-          if (!mbar_wait(&bars->acc_empty, (pass_ctr & 1) ^ 1, stop, 2)) { ok = false; break; }
+          if (!mbar_wait(&bars->acc_empty, (pass_ctr & 1) ^ 1, stop, 2, &g_tc_error)) { ok = false; break; }
           tc_fence_after();
           const int n = min(kBNMax, (n_rows - pass * kBNMax + 15) & ~15);
           const unsigned idesc = instr_desc(n);
           for (int ks = 0; ks < k_steps; ++ks, ++it) {
             const int s = it % stages;
-            if (!mbar_wait(&bars->full[s], (it / stages) & 1, stop, 3)) { ok = false; break; }
+            if (!mbar_wait(&bars->full[s], (it / stages) & 1, stop, 3, &g_tc_error)) { ok = false; break; }
             tc_fence_after();
             unsigned char* st = smem + (size_t)s * stage_bytes;
             const unsigned long long a0 = smem_desc(st);
@@ -289,7 +212,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
       const int row_begin = offsets[group], n_rows = offsets[group + 1] - row_begin;
       const int f = ft * kBM + quad * 32 + lane;
       {
-        if (!mbar_wait(&bars->acc_full, pass_ctr & 1, stop, 4)) { ok = false; break; }
+        if (!mbar_wait(&bars->acc_full, pass_ctr & 1, stop, 4, &g_tc_error)) { ok = false; break; }
         tc_fence_after();
         const int p0 = row_begin + pass * kBNMax;
         const int valid = min(kBNMax, n_rows - pass * kBNMax);
@@ -327,38 +250,6 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
 }
 
 // ---- host ---------------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// A row-major bf16 matrix [rows, cols] as a 2-D tensor map with boxes of [box_rows, 64].
-static int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  NF_REQUIRE(fn, "grouped_gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  NF_REQUIRE(r == CUDA_SUCCESS, "grouped_gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return 0;
-}
 
 template <bool SWIGLU>
 static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, void* out, int ldo,

@@ -34,6 +34,9 @@ TUNING = {
     # routed experts: up to this many tokens the streaming kernel serves, beyond it the
     # tensor-core kernel (measured: equal at 16 tokens, 25 % faster at 64)
     "skinny_moe_max_tokens": 8,
+    # prompt portions: steps with at least this many rows use the tcgen05 attention kernel (head
+    # size 64 or 128), fewer the mma.sync one; a huge number turns the tensor-core kernel off
+    "prefill_attention_tc_min_rows": 128,
     "qkv_rope_fused": True,       # few bfloat16 rows: rotation and cache append in the projection's epilogue
     "router_tensor_min_rows": 128,   # router logits of more rows than this use tensor cores
     "router_fused_max_rows": 16,     # up to this many rows, routing is a single launch
@@ -222,8 +225,10 @@ def _bf16_path(rows: int, K: int, key: str) -> str:
 
 def tensor_core_status() -> int:
     """0, or the code of the first bounded wait that a tensor-core kernel gave up on since the
-    last call (synchronises the device)."""
-    return int(_lib.load().nf_grouped_gemm_tc_status())
+    last call (synchronises the device): 1-4 from the grouped GEMM, 101-110 from attention."""
+    lib = _lib.load()
+    gemm, attn = int(lib.nf_grouped_gemm_tc_status()), int(lib.nf_prefill_attention_tc_status())
+    return gemm if gemm else (100 + attn if attn else 0)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -374,6 +379,16 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
     if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
             and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
             and getattr(ctx, "seg_pos0_host", None) is not None and qkv.shape[1] % 8 == 0):
+        if (T >= TUNING["prefill_attention_tc_min_rows"] and qkv.is_contiguous() and pages.is_contiguous()
+                and _lib.load().nf_prefill_attention_tc_fits(c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                                                            c_longlong(pages.shape[0]))):
+            # tcgen05 / TMEM / TMA: tiles of 128 rows, blocks of 128 keys
+            tiles, n_tiles = ctx.paired_query_tiles(128, window, 128)
+            _lib.call("nf_prefill_attention_tc", _p(qkv), c_longlong(T), c_int(qkv.shape[1]), _p(pages),
+                      _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0),
+                      _p(tiles), c_int(n_tiles), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                      c_int(pages.shape[0]), c_int(window), c_float(scale), _stream())
+            return out
         tiles, n_tiles = ctx.paired_query_tiles(PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK)
         _lib.call("nf_prefill_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
                   c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles),

@@ -304,6 +304,57 @@ def test_prefill_attention_flash_kernel(K, Hq, Hkv, D, page, window):
     torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [(4, 2, 128, 64, 0), (3, 1, 64, 16, 0), (2, 2, 128, 128, 300),
+                                                  (8, 2, 64, 32, 77), (2, 1, 128, 16, 0)])
+def test_prefill_attention_on_tensor_cores(K, Hq, Hkv, D, page, window):
+    """Steps with many rows take the tcgen05 attention kernel: a long portion that continues an
+    earlier one across many blocks of 128 keys, a fresh prompt that ends inside a tile, single
+    rows, a portion of exactly one tile.  Against the mma.sync kernel and the any-rows kernel
+    (both checked against the plain twin elsewhere), against the plain twin on some rows, and
+    with one far key made to dominate; and no bounded wait may have given up."""
+    from ninfer_amd_mi50_b200.parts.base import StepContext
+    dtype = torch.bfloat16
+    seg_lens, pos0s = [700, 1, 300, 128, 1, 5], [450, 333, 0, 128, 0, 1019]
+    n_pages = sum((p + n + page - 1) // page for p, n in zip(pos0s, seg_lens)) + 2
+    pages, bt, c, qkv = make_cache_case(dtype, Hq, Hkv, D, page, seg_lens, pos0s, n_pages, 47)
+    row0 = [0]
+    for n in seg_lens:
+        row0.append(row0[-1] + n)
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+
+    def context():
+        return StepContext(dtype=dtype, device=torch.device("cuda"), T=row0[-1], S=len(seg_lens), token_ids=mk([0]),
+                           positions=c.positions, row_seg=c.row_seg, seg_row0=mk(row0), seg_pos0=mk(pos0s),
+                           seg_slot=mk([0] * len(seg_lens)), logit_rows=mk([]), seg_len_host=seg_lens,
+                           seg_pos0_host=pos0s, max_rows_per_seg=max(seg_lens), max_context=1200)
+    scale = 1 / math.sqrt(D)
+    # a far key that matters: row 650 of the long portion (position 1100) sees key 40 dominate head 0
+    t_hot, j_hot = 650, 40 if window == 0 else 1100 - window + 2
+    qkv[t_hot, :D] = 0
+    qkv[t_hot, 0] = 30.0 / scale
+    kpage, slot = int(bt[0, j_hot // page]), j_hot % page
+    pages[kpage, 0, 0, slot, :] = 0
+    pages[kpage, 0, 0, slot, 0] = 8.0                # score 240; the others are 30 * N(0, 1)
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, context(), window, scale)
+    assert K.tensor_core_status() == 0
+    old = dict(K.TUNING)
+    try:
+        K.TUNING.update(prefill_attention_tc_min_rows=10 ** 9)
+        flash = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, context(), window, scale)
+        K.TUNING.update(bf16_attention="generic")
+        gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, context(), window, scale)
+    finally:
+        K.TUNING.update(old)
+    assert not torch.equal(out, flash)               # two kernels ran (they round differently)
+    torch.testing.assert_close(out.float(), flash.float(), **tol(dtype))
+    torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
+    torch.testing.assert_close(out[t_hot, :D].float(), pages[kpage, 1, 0, slot, :].float(), rtol=2e-2, atol=2e-2)
+    few = [0, 1, 699, 700, 701, 702, 1000, 1001, 1128, 1129, 1130, 1134]
+    sub = SimpleNamespace(positions=c.positions[few], row_seg=c.row_seg[few])
+    ref = P.paged_attention(qkv[few], Hq, Hkv, D, pages, bt, page, sub, window, scale)
+    torch.testing.assert_close(out[few].float(), ref.float(), **tol(dtype))
+
+
 def test_attention_finds_one_far_key(K):
     """One key among hundreds is made to dominate; the output must be its value row."""
     Hq, Hkv, D, page = 2, 1, 64, 16
