@@ -19,11 +19,12 @@
 //              one of two S buffers in tensor memory, and O += P V (M = 128, N = D, P K-major
 //              from shared memory, V as it lies in the cache: MN-major); QK of block b + 1 is
 //              issued before PV of block b, so the tensor core works while the softmax runs
-//   warps 2-5  softmax: thread r owns row r (tensor-memory lane r): reads its 128 scores with
-//              ``tcgen05.ld``, masks, keeps a reference maximum that is only raised when a score
-//              exceeds it by more than 2^8 (then O's row is rescaled in tensor memory), writes
-//              P = 2^(s - m) as bfloat16 into shared memory in the swizzled K-major image, and
-//              at the end of the tile divides O by the row sum and stores it
+//   warps 2-9  softmax: row r is tensor-memory lane r; two threads share a row (warps w and w + 4
+//              may touch the same 32 lanes) and take 64 of its 128 scores each: ``tcgen05.ld``,
+//              mask, a reference maximum that is only raised when a score exceeds it by more than
+//              2^8 (then O's row is rescaled in tensor memory), P = 2^(s - m) as bfloat16 into one
+//              of two shared-memory buffers in the swizzled K-major image; at the end of the tile
+//              O divided by the row sum is stored
 //
 // Everything between the roles goes through mbarriers; every wait is bounded: after a fixed
 // number of polls the kernel records a code in `g_fa_error`, tells its other warps to stop,
@@ -40,7 +41,7 @@ namespace {
 
 constexpr int kQ = 128;          // rows per tile (MMA M)
 constexpr int kKeys = 128;       // keys per block (MMA N of the first product, K of the second)
-constexpr int kFaThreads = 192;
+constexpr int kFaThreads = 320;  // producer, MMA issuer, 8 softmax warps
 constexpr int kAtom = 128 * 128; // bytes of a swizzle atom column: 128 rows x 64 bf16
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRaise = 8.f;    // raise the reference maximum only beyond this many powers of two
@@ -48,8 +49,8 @@ constexpr float kRaise = 8.f;    // raise the reference maximum only beyond this
 __device__ int g_fa_error = 0;
 
 struct __align__(8) FaBarriers {
-  unsigned long long q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full,
-      pv_done, o_final, o_read;
+  unsigned long long q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
+      p_free[2], o_final, o_read;
   unsigned tmem_base;
   int stop;
 };
@@ -112,8 +113,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* Qs = smem;
   unsigned char* KV = Qs + QB;                    // [2 stages][K block, V block]
-  unsigned char* Ps = KV + 4 * QB;                // [2 atoms][128 rows][128 bytes]
-  FaBarriers* bars = reinterpret_cast<FaBarriers*>(Ps + 2 * kAtom);
+  unsigned char* Ps = KV + 4 * QB;                // [2 buffers][2 atoms][128 rows][128 bytes]
+  FaBarriers* bars = reinterpret_cast<FaBarriers*>(Ps + 4 * kAtom);
+  float* s_rowsum = reinterpret_cast<float*>(bars + 1);      // [2 halves][128 rows]: the two threads of a row add up
   volatile int* stop = &bars->stop;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
@@ -131,12 +133,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->v_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->s_empty[s], 4);
+      mbar_init(&bars->s_empty[s], 8);
     }
-    mbar_init(&bars->p_full, 4);
-    mbar_init(&bars->pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->p_full[i], 8);
+      mbar_init(&bars->p_free[i], 1);
+    }
     mbar_init(&bars->o_final, 1);
-    mbar_init(&bars->o_read, 4);
+    mbar_init(&bars->o_read, 8);
     bars->stop = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -231,18 +235,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // O += P V of the block whose keys sit in stage (gp & 1); `first`: the first block of a tile
       auto issue_pv = [&](bool first) -> bool {
         if (!mbar_wait(&bars->v_full[gp & 1], (gp >> 1) & 1, stop, 4, &g_fa_error)) return false;
-        if (!mbar_wait(&bars->p_full, gp & 1, stop, 5, &g_fa_error)) return false;
+        if (!mbar_wait(&bars->p_full[gp & 1], (gp >> 1) & 1, stop, 5, &g_fa_error)) return false;
         if (first && gq > 0 && !mbar_wait(&bars->o_read, (gq - 1) & 1, stop, 6, &g_fa_error)) return false;
         tc_fence_after();
         const unsigned char* vst = KV + (size_t)(gp & 1) * 2 * QB + QB;
 #pragma unroll
         for (int kk = 0; kk < kKeys / 16; ++kk) {
-          const unsigned long long a = smem_desc(Ps + (kk >> 2) * kAtom) + 2 * (kk & 3);
+          const unsigned long long a = smem_desc(Ps + (gp & 1) * 2 * kAtom + (kk >> 2) * kAtom) + 2 * (kk & 3);
           const unsigned long long b = smem_desc_mn(vst + kk * 16 * 128, kAtom);
           tc_mma(tmem_o, a, b, idesc_pv, (!first || kk > 0) ? 1u : 0u);
         }
         tc_commit(&bars->v_empty[gp & 1]);       // the values of this block are free ...
-        tc_commit(&bars->pv_done);               // ... and so are P and O, once these have run
+        tc_commit(&bars->p_free[gp & 1]);        // ... and so is its P buffer, once these have run
         ++gp;
         return true;
       };
@@ -273,53 +277,69 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   } else {
-    // ---- softmax, correction, epilogue: thread r <-> row r <-> tensor-memory lane r ------------------
-    const int quad = warp & 3;                       // the 32 lanes this warp may touch
+    // ---- softmax, correction, epilogue ---------------------------------------------------------------
+    // Eight warps: warp w may touch tensor-memory lanes 32 (w % 4) .. + 31, so warps w and w + 4
+    // share 32 rows and split their columns in halves.  Two warps a scheduler instead of one hide
+    // each other's latencies (tensor-memory loads, the exponential unit, instruction fetch).
+    const int quad = warp & 3;                       // the 32 lanes (rows) this warp may touch
+    const int half = (warp - 2) >> 2;                // which half of the columns
     const int r = quad * 32 + lane;
     const unsigned lane_addr = (unsigned)(quad * 32) << 16;
     const float sc2 = scale * kLog2e;
+    constexpr int HK = kKeys / 2;                    // score columns of this thread
+    constexpr int HD = D / 2;                        // output columns of this thread
     int gs = 0, gp = 0, gq = 0;
     bool ok = true;
+    // the two threads of a row meet at a named barrier of their 64 (ids 1..4)
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
     for (int which = 0; which < 2 && ok; ++which, ++gq) {
       const TileInfo t = tile_info(tiles, which, seg_row0, positions, window);
       if (t.seg < 0) break;
       const bool row_ok = r < t.n_rows;
       const int p_r = t.pos_first + r;
       const int w_r = window > 0 ? max(0, p_r - window + 1) : 0;
-      float m_ref = 0.f, l_run = 0.f;
+      const bool row_sees = row_ok && p_r >= w_r;
+      const unsigned j_span = row_sees ? (unsigned)(p_r - w_r) : 0u;
+      float m_ref = 0.f, l_run = 0.f;      // l_run: this thread's half of the row sum
       bool have = false;                   // the row has seen a visible key
       for (int blk = 0; blk < t.n_blocks && ok; ++blk, ++gs, ++gp) {
         const int s = gs & 1;
         if (!mbar_wait(&bars->s_full[s], (gs >> 1) & 1, stop, 8, &g_fa_error)) { ok = false; break; }
         tc_fence_after();
-        float v[kKeys];
-#pragma unroll
-        for (int c = 0; c < kKeys / 32; ++c) tc_ld32(tmem + lane_addr + s * kKeys + 32 * c, reinterpret_cast<unsigned*>(v + 32 * c));
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->s_empty[s]);           // the scores are in registers
         const int kb = t.kb_first + blk * kKeys;
-        float mx = -INFINITY;
         // every key of the block visible to every row of this warp: no mask to apply
         const bool all_visible = quad * 32 + 31 < t.n_rows && kb + kKeys - 1 <= t.pos_first + quad * 32 &&
                                  (window <= 0 || kb >= t.pos_first + quad * 32 + 31 - window + 1);
-        if (all_visible) {
+        // key j of this block (0..127) is visible to the row iff j - j_lo <= j_span (unsigned)
+        const int j_lo = w_r - kb;
+        const unsigned s_row = tmem + lane_addr + s * kKeys;
+        const unsigned s_addr = s_row + half * HK;
+        // First pass: the row's maximum, by both threads of the row over all 128 scores (cheaper
+        // than meeting to exchange two halves).  The scores stay in tensor memory and are read
+        // again below, 32 columns at a time: the code of one pass over a whole row would not fit
+        // the instruction cache close to the scheduler.
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < kKeys / 32; ++c) {
+          unsigned u[32];
+          tc_ld32(s_row + 32 * c, u);
+          tc_wait_ld();
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains, not one
+          if (all_visible) {
 #pragma unroll
-          for (int c = 0; c < kKeys; ++c) {
-            v[c] *= sc2;
-            mx = fmaxf(mx, v[c]);
-          }
-        } else {
+            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(u[i]));
+          } else {
 #pragma unroll
-          for (int c = 0; c < kKeys; ++c) {
-            const int j = kb + c;
-            v[c] = (row_ok && j <= p_r && j >= w_r) ? v[c] * sc2 : -INFINITY;
-            mx = fmaxf(mx, v[c]);
+            for (int i = 0; i < 32; ++i) {
+              const bool vis = row_sees && (unsigned)(32 * c + i - j_lo) <= j_span;
+              m4[i & 3] = fmaxf(m4[i & 3], vis ? __uint_as_float(u[i]) : -INFINITY);
+            }
           }
+          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
         }
+        mx *= sc2;                                   // sc2 > 0: the maximum of the scaled scores
         // the reference maximum: set by the first block with a visible key, raised only when a
-        // score passes it by 2^8
+        // score passes it by 2^8 (both threads of a row decide alike)
         float alpha = 1.f;
         bool raise = false;
         if (!have) {                       // nothing visible so far (O's row and l are zero)
@@ -330,57 +350,87 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           alpha = exp2f(m_ref - mx);
           m_ref = mx;
         }
-        // P and O are free once the product of the block before has run
-        if (gp > 0 && !mbar_wait(&bars->pv_done, (gp - 1) & 1, stop, 9, &g_fa_error)) { ok = false; break; }
-        if (__any_sync(0xffffffffu, raise)) {                   // the whole warp, each row by its own factor
+        // Two P buffers: this block's is free once the product of two blocks ago has run, so the
+        // softmax of a block does not wait for the product of the block before it - unless some
+        // row's reference maximum is raised: then O must be at rest, i.e. every product issued so
+        // far must have run (they complete in order).
+        const bool any_raise = __any_sync(0xffffffffu, raise);
+        if (gp > 1 && !mbar_wait(&bars->p_free[gp & 1], ((gp - 2) >> 1) & 1, stop, 9, &g_fa_error)) { ok = false; break; }
+        if (any_raise) {                                        // the whole warp, each row by its own factor
+          if (gp > 0 && !mbar_wait(&bars->p_free[(gp - 1) & 1], ((gp - 1) >> 1) & 1, stop, 9, &g_fa_error)) { ok = false; break; }
           tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
             unsigned o[32];
-            tc_ld32(tmem_o + lane_addr + 32 * c, o);
+            tc_ld32(tmem_o + lane_addr + half * HD + 32 * c, o);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tc_st32(tmem_o + lane_addr + 32 * c, o);
+            tc_st32(tmem_o + lane_addr + half * HD + 32 * c, o);
           }
           tc_wait_st();
           l_run *= alpha;
         }
-        // P = 2^(s - m) as bfloat16 in the swizzled K-major image; the sum in float32
+        // Second pass: P = 2^(s * scale * log2 e - m) as bfloat16 in the swizzled K-major image (this
+        // thread's 64 keys are one swizzle atom of its row); the sum in float32
         float sum = 0.f;
-#pragma unroll
-        for (int piece = 0; piece < kKeys / 8; ++piece) {
-          float p[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            p[i] = ex2(v[piece * 8 + i] - m_ref);
-            sum += p[i];
+        unsigned char* prow = Ps + (gp & 1) * 2 * kAtom + half * kAtom + r * 128;
+#pragma unroll 1
+        for (int c = 0; c < HK / 32; ++c) {
+          unsigned u[32];
+          tc_ld32(s_addr + 32 * c, u);
+          tc_wait_ld();
+          if (c == HK / 32 - 1) {                    // the scores are in registers: hand the buffer back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->s_empty[s]);
           }
-          uint4 w;
-          __nv_bfloat162 b0 = __floats2bfloat162_rn(p[0], p[1]), b1 = __floats2bfloat162_rn(p[2], p[3]);
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(p[4], p[5]), b3 = __floats2bfloat162_rn(p[6], p[7]);
-          w.x = *reinterpret_cast<unsigned*>(&b0);
-          w.y = *reinterpret_cast<unsigned*>(&b1);
-          w.z = *reinterpret_cast<unsigned*>(&b2);
-          w.w = *reinterpret_cast<unsigned*>(&b3);
-          *reinterpret_cast<uint4*>(Ps + (piece >> 3) * kAtom + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = w;
+          float p[32];
+          if (all_visible) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p[i] = ex2(fmaf(__uint_as_float(u[i]), sc2, -m_ref));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const bool vis = row_sees && (unsigned)(half * HK + 32 * c + i - j_lo) <= j_span;
+              p[i] = vis ? ex2(fmaf(__uint_as_float(u[i]), sc2, -m_ref)) : 0.f;
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 w;
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(p[8 * q], p[8 * q + 1]), b1 = __floats2bfloat162_rn(p[8 * q + 2], p[8 * q + 3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(p[8 * q + 4], p[8 * q + 5]), b3 = __floats2bfloat162_rn(p[8 * q + 6], p[8 * q + 7]);
+            w.x = *reinterpret_cast<unsigned*>(&b0);
+            w.y = *reinterpret_cast<unsigned*>(&b1);
+            w.z = *reinterpret_cast<unsigned*>(&b2);
+            w.w = *reinterpret_cast<unsigned*>(&b3);
+            const int piece = 4 * c + q;             // 16-byte piece of the atom's row: keys 8 piece .. + 7
+            *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) = w;
+            sum += ((p[8 * q] + p[8 * q + 1]) + (p[8 * q + 2] + p[8 * q + 3])) +
+                   ((p[8 * q + 4] + p[8 * q + 5]) + (p[8 * q + 6] + p[8 * q + 7]));
+          }
         }
         l_run += sum;
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_full);
+        if (lane == 0) mbar_arrive(&bars->p_full[gp & 1]);
       }
       if (!ok) break;
       // ---- the tile's rows: O / l ---------------------------------------------------------------------
+      s_rowsum[half * kQ + r] = l_run;
+      pair_sync();
+      const float l_row = s_rowsum[r] + s_rowsum[kQ + r];        // same order in both threads
+      pair_sync();                                               // both have read: the slots may be reused
       if (!mbar_wait(&bars->o_final, gq & 1, stop, 10, &g_fa_error)) { ok = false; break; }
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = out + (size_t)(t.row0 + r) * Hq * D + (size_t)h * D;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+      __nv_bfloat16* dst = out + (size_t)(t.row0 + r) * Hq * D + (size_t)h * D + half * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
         unsigned o[32];
-        tc_ld32(tmem_o + lane_addr + 32 * c, o);
+        tc_ld32(tmem_o + lane_addr + half * HD + 32 * c, o);
         tc_wait_ld();
         if (row_ok) {
 #pragma unroll
@@ -417,7 +467,7 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const int* 
                       const int* positions, const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,
                       int Hkv, int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
   constexpr int QB = (D / 64) * kAtom;
-  const size_t smem = 1024 + (size_t)5 * QB + 2 * kAtom + sizeof(FaBarriers);
+  const size_t smem = 1024 + (size_t)5 * QB + 4 * kAtom + sizeof(FaBarriers) + 2 * kQ * sizeof(float);
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
