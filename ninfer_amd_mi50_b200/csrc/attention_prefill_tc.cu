@@ -12,9 +12,9 @@
 // `StepContext.paired_query_tiles`).  Keys and values come in blocks of 128 keys, aligned to
 // multiples of 128, so the order of a row's sums depends on its own position only.
 //
-//   warp 0     producer: TMA tensor copies (128-byte swizzle) of the Q tile and, page by page
-//              through the block table, of the K and V blocks into two-stage rings (keys are
-//              released as soon as their scores are done, values after the second product)
+//   warp 0     producer of Q and K, warp 10 producer of V: TMA tensor copies (128-byte swizzle),
+//              page by page through the block table, into two-stage rings (a key stage is free
+//              as soon as its scores are done, a value stage after the second product)
 //   warp 1     MMA issuer: S = Q K^T (M = 128 rows, N = 128 keys, both operands K-major) into
 //              one of two S buffers in tensor memory, and O += P V (M = 128, N = D, P K-major
 //              from shared memory, V as it lies in the cache: MN-major); QK of block b + 1 is
@@ -41,7 +41,7 @@ namespace {
 
 constexpr int kQ = 128;          // rows per tile (MMA M)
 constexpr int kKeys = 128;       // keys per block (MMA N of the first product, K of the second)
-constexpr int kFaThreads = 320;  // producer, MMA issuer, 8 softmax warps
+constexpr int kFaThreads = 352;  // key producer, MMA issuer, 8 softmax warps, value producer
 constexpr int kAtom = 128 * 128; // bytes of a swizzle atom column: 128 rows x 64 bf16
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRaise = 8.f;    // raise the reference maximum only beyond this many powers of two
@@ -49,8 +49,8 @@ constexpr float kRaise = 8.f;    // raise the reference maximum only beyond this
 __device__ int g_fa_error = 0;
 
 struct __align__(8) FaBarriers {
-  unsigned long long q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
-      p_free[2], o_final, o_read;
+  unsigned long long q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full,
+      p_free, o_final, o_read;
   unsigned tmem_base;
   int stop;
 };
@@ -87,8 +87,8 @@ struct TileInfo {
 __device__ __forceinline__ TileInfo tile_info(const int* tiles, int which, const int* seg_row0, const int* positions,
                                               int window) {
   TileInfo t;
-  t.seg = tiles[4 * blockIdx.x + 2 * which];
-  t.row0 = tiles[4 * blockIdx.x + 2 * which + 1];
+  t.seg = tiles[4 * blockIdx.y + 2 * which];
+  t.row0 = tiles[4 * blockIdx.y + 2 * which + 1];
   if (t.seg < 0) return t;
   t.n_rows = min(kQ, seg_row0[t.seg + 1] - t.row0);
   t.pos_first = positions[t.row0];
@@ -113,12 +113,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* Qs = smem;
   unsigned char* KV = Qs + QB;                    // [2 stages][K block, V block]
-  unsigned char* Ps = KV + 4 * QB;                // [2 buffers][2 atoms][128 rows][128 bytes]
-  FaBarriers* bars = reinterpret_cast<FaBarriers*>(Ps + 4 * kAtom);
+  unsigned char* Ps = KV + 4 * QB;                // [2 atoms][128 rows][128 bytes]
+  FaBarriers* bars = reinterpret_cast<FaBarriers*>(Ps + 2 * kAtom);
   float* s_rowsum = reinterpret_cast<float*>(bars + 1);      // [2 halves][128 rows]: the two threads of a row add up
+  float* s_rowmax = s_rowsum + 2 * kQ;                       // [2 block parities][2 halves][128 rows]
   volatile int* stop = &bars->stop;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;        // heads vary fastest: the device starts the heaviest tiles of all heads first
   const int kvh = h / (Hq / Hkv);
 
   // zeros in both stages: a block's second page may not exist, and what the tensor core then
@@ -135,10 +136,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->s_empty[s], 8);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->p_full[i], 8);
-      mbar_init(&bars->p_free[i], 1);
-    }
+    mbar_init(&bars->p_full, 8);
+    mbar_init(&bars->p_free, 1);
     mbar_init(&bars->o_final, 1);
     mbar_init(&bars->o_read, 8);
     bars->stop = 0;
@@ -155,9 +154,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const unsigned tmem = bars->tmem_base;
   const unsigned tmem_o = tmem + 2 * kKeys;       // S buffers at columns 0 and 128, O at 256
 
-  if (warp == 0) {
-    // ---- producer ---------------------------------------------------------------------------------
+  if (warp == 0 || warp == 10) {
+    // ---- producers: warp 0 brings Q and the keys, warp 10 the values --------------------------------
+    // Two threads, because the two rings turn at different times: a key stage is free as soon as
+    // the scores of its block are done (long before that block's softmax), a value stage only after
+    // the second product; one thread serving both in turn would hold the keys back.
     if (lane == 0) {
+      const int kv = warp == 0 ? 0 : 1;
       int gb = 0, issued_stage[2] = {-1, -1};
       bool ok = true, q_pending = false;
       int gq = 0;
@@ -183,31 +186,29 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         };
         int page_now[8], page_next[8];
         lookup(0, page_next);
-        if (!mbar_wait(&bars->q_empty, (gq & 1) ^ 1, stop, 1, &g_fa_error)) { ok = false; break; }
-        mbar_expect_tx(&bars->q_full, QB);
-        for (int a = 0; a < ATOMS; ++a) tma_load_2d(Qs + a * kAtom, &map_q, h * D + 64 * a, t.row0, &bars->q_full);
-        q_pending = true;
+        if (kv == 0) {
+          if (!mbar_wait(&bars->q_empty, (gq & 1) ^ 1, stop, 1, &g_fa_error)) { ok = false; break; }
+          mbar_expect_tx(&bars->q_full, QB);
+          for (int a = 0; a < ATOMS; ++a) tma_load_2d(Qs + a * kAtom, &map_q, h * D + 64 * a, t.row0, &bars->q_full);
+          q_pending = true;
+        }
         for (int blk = 0; blk < t.n_blocks; ++blk, ++gb) {
           const int s = gb & 1;
           int n_ok = 0;
           for (int pi = 0; pi < per; ++pi) { page_now[pi] = page_next[pi]; n_ok += page_now[pi] >= 0; }
           lookup(blk + 1, page_next);
-          unsigned char* st = KV + (size_t)s * 2 * QB;
-          for (int kv = 0; kv < 2; ++kv) {
-            // keys first: their stage is free as soon as the scores of two blocks ago are done
-            void* full = kv ? &bars->v_full[s] : &bars->k_full[s];
-            void* empty = kv ? &bars->v_empty[s] : &bars->k_empty[s];
-            if (!mbar_wait(empty, ((gb >> 1) & 1) ^ 1, stop, 2, &g_fa_error)) { ok = false; break; }
-            mbar_expect_tx(full, (unsigned)n_ok * page_size * D * 2);
-            for (int pi = 0; pi < per; ++pi) {
-              if (page_now[pi] < 0) continue;
-              const int y = ((page_now[pi] * 2 + kv) * Hkv + kvh) * page_size;
-              for (int a = 0; a < ATOMS; ++a)
-                tma_load_2d(st + kv * QB + a * kAtom + pi * page_size * 128, &map_kv, 64 * a, y, full);
-            }
-            issued_stage[s] = 2 * gb + kv;
+          unsigned char* st = KV + (size_t)s * 2 * QB + kv * QB;
+          void* full = kv ? &bars->v_full[s] : &bars->k_full[s];
+          void* empty = kv ? &bars->v_empty[s] : &bars->k_empty[s];
+          if (!mbar_wait(empty, ((gb >> 1) & 1) ^ 1, stop, 2, &g_fa_error)) { ok = false; break; }
+          mbar_expect_tx(full, (unsigned)n_ok * page_size * D * 2);
+          for (int pi = 0; pi < per; ++pi) {
+            if (page_now[pi] < 0) continue;
+            const int y = ((page_now[pi] * 2 + kv) * Hkv + kvh) * page_size;
+            for (int a = 0; a < ATOMS; ++a)
+              tma_load_2d(st + a * kAtom + pi * page_size * 128, &map_kv, 64 * a, y, full);
           }
-          if (!ok) break;
+          issued_stage[s] = gb;
         }
       }
       if (!ok) {
@@ -217,12 +218,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (mbar_try(&bars->q_full, (gq - 1) & 1)) break;
         for (int s = 0; s < 2; ++s) {
           if (issued_stage[s] < 0) continue;
-          const int g = issued_stage[s] >> 1;
+          void* full = kv ? &bars->v_full[s] : &bars->k_full[s];
           for (unsigned i = 0; i < (1u << 20); ++i)
-            if (mbar_try(&bars->k_full[s], (g >> 1) & 1)) break;
-          if (issued_stage[s] & 1)
-            for (unsigned i = 0; i < (1u << 20); ++i)
-              if (mbar_try(&bars->v_full[s], (g >> 1) & 1)) break;
+            if (mbar_try(full, (issued_stage[s] >> 1) & 1)) break;
         }
       }
     }
@@ -235,18 +233,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // O += P V of the block whose keys sit in stage (gp & 1); `first`: the first block of a tile
       auto issue_pv = [&](bool first) -> bool {
         if (!mbar_wait(&bars->v_full[gp & 1], (gp >> 1) & 1, stop, 4, &g_fa_error)) return false;
-        if (!mbar_wait(&bars->p_full[gp & 1], (gp >> 1) & 1, stop, 5, &g_fa_error)) return false;
+        if (!mbar_wait(&bars->p_full, gp & 1, stop, 5, &g_fa_error)) return false;
         if (first && gq > 0 && !mbar_wait(&bars->o_read, (gq - 1) & 1, stop, 6, &g_fa_error)) return false;
         tc_fence_after();
         const unsigned char* vst = KV + (size_t)(gp & 1) * 2 * QB + QB;
 #pragma unroll
         for (int kk = 0; kk < kKeys / 16; ++kk) {
-          const unsigned long long a = smem_desc(Ps + (gp & 1) * 2 * kAtom + (kk >> 2) * kAtom) + 2 * (kk & 3);
+          const unsigned long long a = smem_desc(Ps + (kk >> 2) * kAtom) + 2 * (kk & 3);
           const unsigned long long b = smem_desc_mn(vst + kk * 16 * 128, kAtom);
           tc_mma(tmem_o, a, b, idesc_pv, (!first || kk > 0) ? 1u : 0u);
         }
         tc_commit(&bars->v_empty[gp & 1]);       // the values of this block are free ...
-        tc_commit(&bars->p_free[gp & 1]);        // ... and so is its P buffer, once these have run
+        tc_commit(&bars->p_free);                // ... and so are P and O, once these have run
         ++gp;
         return true;
       };
@@ -312,32 +310,36 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                  (window <= 0 || kb >= t.pos_first + quad * 32 + 31 - window + 1);
         // key j of this block (0..127) is visible to the row iff j - j_lo <= j_span (unsigned)
         const int j_lo = w_r - kb;
-        const unsigned s_row = tmem + lane_addr + s * kKeys;
-        const unsigned s_addr = s_row + half * HK;
-        // First pass: the row's maximum, by both threads of the row over all 128 scores (cheaper
-        // than meeting to exchange two halves).  The scores stay in tensor memory and are read
-        // again below, 32 columns at a time: the code of one pass over a whole row would not fit
-        // the instruction cache close to the scheduler.
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < kKeys / 32; ++c) {
-          unsigned u[32];
-          tc_ld32(s_row + 32 * c, u);
-          tc_wait_ld();
+        // This thread's 64 scores, read once and kept in registers.
+        unsigned u[HK];
+        tc_ld32(tmem + lane_addr + s * kKeys + half * HK, u);
+        tc_ld32(tmem + lane_addr + s * kKeys + half * HK + 32, u + 32);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_empty[s]);           // the buffer may take the scores of block + 2
+        float mx;
+        {
           float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains, not one
           if (all_visible) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(u[i]));
+            for (int i = 0; i < HK; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(u[i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const bool vis = row_sees && (unsigned)(32 * c + i - j_lo) <= j_span;
-              m4[i & 3] = fmaxf(m4[i & 3], vis ? __uint_as_float(u[i]) : -INFINITY);
+            for (int i = 0; i < HK; ++i) {
+              const bool vis = row_sees && (unsigned)(half * HK + i - j_lo) <= j_span;
+              u[i] = vis ? u[i] : 0xff800000u;                   // -inf: stays masked below
+              m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(u[i]));
             }
           }
-          mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
-        mx *= sc2;                                   // sc2 > 0: the maximum of the scaled scores
+        // the row's maximum: the larger of the two halves (slots alternate with the block's parity,
+        // so a fast thread cannot overwrite what its partner has yet to read)
+        float* slot = s_rowmax + (gs & 1) * 2 * kQ;
+        slot[half * kQ + r] = mx;
+        pair_sync();
+        mx = fmaxf(mx, slot[(half ^ 1) * kQ + r]) * sc2;         // sc2 > 0: the maximum of the scaled scores
         // the reference maximum: set by the first block with a visible key, raised only when a
         // score passes it by 2^8 (both threads of a row decide alike)
         float alpha = 1.f;
@@ -350,14 +352,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           alpha = exp2f(m_ref - mx);
           m_ref = mx;
         }
-        // Two P buffers: this block's is free once the product of two blocks ago has run, so the
-        // softmax of a block does not wait for the product of the block before it - unless some
-        // row's reference maximum is raised: then O must be at rest, i.e. every product issued so
-        // far must have run (they complete in order).
-        const bool any_raise = __any_sync(0xffffffffu, raise);
-        if (gp > 1 && !mbar_wait(&bars->p_free[gp & 1], ((gp - 2) >> 1) & 1, stop, 9, &g_fa_error)) { ok = false; break; }
-        if (any_raise) {                                        // the whole warp, each row by its own factor
-          if (gp > 0 && !mbar_wait(&bars->p_free[(gp - 1) & 1], ((gp - 1) >> 1) & 1, stop, 9, &g_fa_error)) { ok = false; break; }
+        // P and O are free once the product of the block before has run
+        if (gp > 0 && !mbar_wait(&bars->p_free, (gp - 1) & 1, stop, 9, &g_fa_error)) { ok = false; break; }
+        if (__any_sync(0xffffffffu, raise)) {                   // the whole warp, each row by its own factor
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < HD / 32; ++c) {
@@ -371,51 +368,31 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tc_wait_st();
           l_run *= alpha;
         }
-        // Second pass: P = 2^(s * scale * log2 e - m) as bfloat16 in the swizzled K-major image (this
-        // thread's 64 keys are one swizzle atom of its row); the sum in float32
+        // P = 2^(s * scale * log2 e - m) as bfloat16 in the swizzled K-major image (this thread's
+        // 64 keys are one swizzle atom of its row); the sum in float32.  A masked score is -inf
+        // and gives 0.
         float sum = 0.f;
-        unsigned char* prow = Ps + (gp & 1) * 2 * kAtom + half * kAtom + r * 128;
-#pragma unroll 1
-        for (int c = 0; c < HK / 32; ++c) {
-          unsigned u[32];
-          tc_ld32(s_addr + 32 * c, u);
-          tc_wait_ld();
-          if (c == HK / 32 - 1) {                    // the scores are in registers: hand the buffer back
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->s_empty[s]);
-          }
-          float p[32];
-          if (all_visible) {
+        unsigned char* prow = Ps + half * kAtom + r * 128;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) p[i] = ex2(fmaf(__uint_as_float(u[i]), sc2, -m_ref));
-          } else {
+        for (int q = 0; q < HK / 8; ++q) {
+          float p[8];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const bool vis = row_sees && (unsigned)(half * HK + 32 * c + i - j_lo) <= j_span;
-              p[i] = vis ? ex2(fmaf(__uint_as_float(u[i]), sc2, -m_ref)) : 0.f;
-            }
-          }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 w;
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(p[8 * q], p[8 * q + 1]), b1 = __floats2bfloat162_rn(p[8 * q + 2], p[8 * q + 3]);
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(p[8 * q + 4], p[8 * q + 5]), b3 = __floats2bfloat162_rn(p[8 * q + 6], p[8 * q + 7]);
-            w.x = *reinterpret_cast<unsigned*>(&b0);
-            w.y = *reinterpret_cast<unsigned*>(&b1);
-            w.z = *reinterpret_cast<unsigned*>(&b2);
-            w.w = *reinterpret_cast<unsigned*>(&b3);
-            const int piece = 4 * c + q;             // 16-byte piece of the atom's row: keys 8 piece .. + 7
-            *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) = w;
-            sum += ((p[8 * q] + p[8 * q + 1]) + (p[8 * q + 2] + p[8 * q + 3])) +
-                   ((p[8 * q + 4] + p[8 * q + 5]) + (p[8 * q + 6] + p[8 * q + 7]));
-          }
+          for (int i = 0; i < 8; ++i) p[i] = ex2(fmaf(__uint_as_float(u[8 * q + i]), sc2, -m_ref));
+          uint4 w;
+          __nv_bfloat162 b0 = __floats2bfloat162_rn(p[0], p[1]), b1 = __floats2bfloat162_rn(p[2], p[3]);
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p[4], p[5]), b3 = __floats2bfloat162_rn(p[6], p[7]);
+          w.x = *reinterpret_cast<unsigned*>(&b0);
+          w.y = *reinterpret_cast<unsigned*>(&b1);
+          w.z = *reinterpret_cast<unsigned*>(&b2);
+          w.w = *reinterpret_cast<unsigned*>(&b3);
+          *reinterpret_cast<uint4*>(prow + ((q ^ (r & 7)) << 4)) = w;   // piece q: keys 8 q .. 8 q + 7 of the atom
+          sum += ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
         }
         l_run += sum;
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_full[gp & 1]);
+        if (lane == 0) mbar_arrive(&bars->p_full);
       }
       if (!ok) break;
       // ---- the tile's rows: O / l ---------------------------------------------------------------------
@@ -467,14 +444,14 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const int* 
                       const int* positions, const int* seg_row0, const int* tiles, int n_tiles, void* out, int Hq,
                       int Hkv, int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
   constexpr int QB = (D / 64) * kAtom;
-  const size_t smem = 1024 + (size_t)5 * QB + 4 * kAtom + sizeof(FaBarriers) + 2 * kQ * sizeof(float);
+  const size_t smem = 1024 + (size_t)5 * QB + 2 * kAtom + sizeof(FaBarriers) + 6 * kQ * sizeof(float);
   static bool set = false;
   if (!set) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     NF_REQUIRE(e == cudaSuccess, "prefill attention: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     set = true;
   }
-  dim3 grid(n_tiles, Hq);
+  dim3 grid(Hq, n_tiles);
   prefill_attention_tc_kernel<D><<<grid, kFaThreads, smem, stream>>>(mq, mkv, block_table, bt_width, positions, seg_row0,
                                                                     tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size,
                                                                     num_pages, window, scale);
@@ -491,7 +468,7 @@ extern "C" int nf_prefill_attention_tc_tile_rows() { return kQ; }
 // 1 if the tensor-core kernel takes these sizes.
 extern "C" int nf_prefill_attention_tc_fits(int Hq, int Hkv, int D, int page_size, long long num_pages) {
   const bool page_ok = page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
-  return (D == 64 || D == 128) && page_ok && Hkv > 0 && Hq % Hkv == 0 && Hq <= 65535 &&
+  return (D == 64 || D == 128) && page_ok && Hkv > 0 && Hq % Hkv == 0 &&
          num_pages * 2 * Hkv * page_size < (1ll << 31);
 }
 
@@ -505,7 +482,7 @@ extern "C" int nf_prefill_attention_tc(const void* qkv, long long T, int q_row_s
                                        int Hkv, int D, int page_size, int num_pages, int window, float scale,
                                        cudaStream_t stream) {
   if (n_tiles == 0) return 0;
-  NF_REQUIRE(n_tiles > 0 && T > 0, "prefill attention: bad sizes tiles=%d T=%lld", n_tiles, T);
+  NF_REQUIRE(n_tiles > 0 && n_tiles <= 65535 && T > 0, "prefill attention: bad sizes tiles=%d T=%lld", n_tiles, T);
   NF_REQUIRE(nf_prefill_attention_tc_fits(Hq, Hkv, D, page_size, num_pages), "prefill attention: sizes the tensor-core kernel does not take (Hq=%d Hkv=%d D=%d page=%d)", Hq, Hkv, D, page_size);
   NF_REQUIRE(q_row_stride % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)pages % 16 == 0, "prefill attention: rows must be 16-byte aligned");
   CUtensorMap mq, mkv;

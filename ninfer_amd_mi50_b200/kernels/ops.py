@@ -383,7 +383,7 @@ def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.T
                 and _lib.load().nf_prefill_attention_tc_fits(c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
                                                             c_longlong(pages.shape[0]))):
             # tcgen05 / TMEM / TMA: tiles of 128 rows, blocks of 128 keys
-            tiles, n_tiles = ctx.paired_query_tiles(128, window, 128)
+            tiles, n_tiles = ctx.paired_query_tiles(128, window, 128, pair=False)
             _lib.call("nf_prefill_attention_tc", _p(qkv), c_longlong(T), c_int(qkv.shape[1]), _p(pages),
                       _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0),
                       _p(tiles), c_int(n_tiles), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),

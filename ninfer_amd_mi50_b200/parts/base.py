@@ -142,15 +142,15 @@ class StepContext:
         return t, n_tiles
 
 
-    def paired_query_tiles(self, rows_per_tile: int, window: int, keys_per_block: int
-                           ) -> Tuple[torch.Tensor, int]:
+    def paired_query_tiles(self, rows_per_tile: int, window: int, keys_per_block: int,
+                           pair: bool = True) -> Tuple[torch.Tensor, int]:
         """Query tiles two to a CTA, a heavy one with a light one.
 
         A tile late in a long prompt reads many more keys than an early one; giving each CTA
         the i-th heaviest and the i-th lightest tile makes CTAs about equally long.  Returns
         (int32 [n_pairs, 2, 2] of (segment, first row), second entry (-1, -1) if there is
-        none; n_pairs)."""
-        key = ("pairs", rows_per_tile, window, keys_per_block)
+        none; n_pairs).  With `pair` false every CTA gets one tile, heaviest first."""
+        key = ("pairs", rows_per_tile, window, keys_per_block, pair)
         if key in self._tiles:
             return self._tiles[key]
         if self.seg_len_host is None or self.seg_pos0_host is None:
@@ -167,7 +167,12 @@ class StepContext:
             row += n
         tiles.sort(key=lambda t: -t[0])
         flat: List[int] = []
-        i, j = 0, len(tiles) - 1
+        if not pair:
+            # one tile a CTA, heaviest first: the device hands CTAs to SMs as they fall free, so
+            # the light tiles fill the end
+            for _, s, r in tiles:
+                flat += [s, r, -1, -1]
+        i, j = (0, len(tiles) - 1) if pair else (1, 0)
         while i <= j:
             flat += [tiles[i][1], tiles[i][2]]
             flat += [tiles[j][1], tiles[j][2]] if j > i else [-1, -1]
