@@ -96,11 +96,13 @@ class Ninfer:
                  prefill_chunk: int = 512, num_sequences: int = 1, *, dtype: str = "bfloat16",
                  page_size: int = 64, cache_tokens: Optional[int] = None,
                  max_batched_tokens: Optional[int] = None, use_graph: bool = True,
+                 run_ahead: bool = True,
                  config: Optional[Dict[str, Any]] = None, random_weights: Optional[int] = None,
                  device: str = "cuda:0"):
         opts = EngineOptions(dtype=dtype, max_context=max_context, prefill_chunk=prefill_chunk,
                              num_sequences=num_sequences, page_size=page_size, cache_tokens=cache_tokens,
-                             max_batched_tokens=max_batched_tokens, use_graph=use_graph, device=device)
+                             max_batched_tokens=max_batched_tokens, use_graph=use_graph, run_ahead=run_ahead,
+                             device=device)
         self._engine = Engine(model_dir, config=config, random_seed=random_weights, options=opts)
         self._runner = self._engine.runner
         self.vocab = self._engine.vocab_size

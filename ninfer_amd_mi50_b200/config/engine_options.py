@@ -25,6 +25,7 @@ class EngineOptions:
     cache_tokens: Optional[int] = None   # pool size in tokens (default: num_sequences * max_context)
     max_batched_tokens: Optional[int] = None  # token budget of one step
     use_graph: bool = True           # replay decode-only steps from CUDA graphs
+    run_ahead: bool = True           # launch the next decode step before reading this one's tokens
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

@@ -12,6 +12,7 @@
 // order of every sum, depends on the row's own position (and window) only.
 //
 // All query heads of a group share the CTA, so keys and values are read once per kv head.
+#define NF_CHAIN_CLASS 8
 #include "common.cuh"
 
 namespace nf {
@@ -80,7 +81,7 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   chain_release();
-  chain_wait();          // queries and this step's keys were written by the kernel before
+  chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by the kernel before
   const int pos = positions[t];
   int lo = 0;
   if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
@@ -286,7 +287,7 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
   __shared__ float s_m, s_inv;
   const int t = blockIdx.x, h = blockIdx.y;
   chain_release();
-  chain_wait();
+  chain_wait(ws_acc, ws_ml, positions);
   const int pos = positions[t];
   int lo = 0;
   if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;

@@ -25,6 +25,7 @@
 // A block's partial result depends on the row's own position and window only (blocks are
 // aligned to absolute key indices, tiles run in ascending order), so a row's output does not
 // depend on what else is in the batch.
+#define NF_CHAIN_CLASS 8
 #include "common.cuh"
 
 namespace nf {
@@ -84,7 +85,7 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int G = Hq / Hkv;
-  chain_wait();          // queries, positions and this step's keys were written by kernels before
+  chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by kernels before
 
   // ---- every CTA lists the rows' blocks: row t has blocks s_first[t] .. of its key range -------
   for (int t = threadIdx.x; t < T; t += blockDim.x) {

@@ -26,7 +26,20 @@ void note_launch_error(cudaError_t e);
 // `chain_wait` until the predecessor has completed and its writes are visible.  That hides the
 // launch and ramp-up of the many short kernels of a decode step.  Kernels launched the ordinary
 // way are unaffected; for them both calls do nothing.
-extern int g_chained_launch;   // nf_set_chained_launch(): 0 turns the attribute off
+// nf_chain_break(): the next launch through `launch_chained` (by this thread) is an ordinary one.
+// For the first kernel after a wait on another stream's event: its dependency is then not the
+// kernel before it in its own stream, and a programmatic edge does not describe it.
+bool take_chain_break();
+// Whether a launch of class `cls` on `stream` gets the attribute: the class is switched on, no
+// break is pending, and the stream is being captured into a graph.  Outside a capture launches
+// are ordinary: a step driven from the host gains nothing (the host is slower than the
+// kernels), and on streams driven that way one decode step in some ten thousand came out
+// different with the attribute on - never with it off, and never in replayed graphs.
+bool chain_this_launch(int cls, cudaStream_t stream);
+extern int g_chained_launch;   // nf_set_chained_launch(): a mask over NF_CHAIN_CLASS bits; 0 turns the attribute off
+#ifndef NF_CHAIN_CLASS
+#define NF_CHAIN_CLASS 0x40     // a source file may name its class before including this header
+#endif
 #ifdef NF_CHAIN_EARLY_RELEASE
 __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;"); }
 #else
@@ -40,6 +53,22 @@ __device__ __forceinline__ void chain_release() {}
 // CTAs then arrive while this one reduces and writes.
 __device__ __forceinline__ void chain_release_late() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The wait, and then every pointer through which the kernel will read what earlier kernels
+// wrote is passed through an empty asm statement.  Loads through `const __restrict__` pointers
+// are "invariant" to the compiler (ld.global.nc), and a compiler may move invariant loads above
+// barriers; a load of the predecessor's output issued before the wait would read it
+// half-written.  A pointer that comes out of an asm statement is a new value to the compiler,
+// and a load cannot be issued before its address exists.  A precaution: no such move was seen.
+template <typename T>
+__device__ __forceinline__ void chain_fresh(T& p) {          // T: a pointer type, qualifiers and all
+  static_assert(sizeof(T) == 8, "chain_fresh takes pointers");
+  asm volatile("" : "+l"(p)::"memory");
+}
+template <typename... P>
+__device__ __forceinline__ void chain_wait(P&... ptrs) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  (chain_fresh(ptrs), ...);
+}
 
 template <typename... KArgs, typename... Args>
 inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -53,7 +82,7 @@ inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = &attr;
-  cfg.numAttrs = g_chained_launch ? 1 : 0;
+  cfg.numAttrs = chain_this_launch(NF_CHAIN_CLASS, stream) ? 1 : 0;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) note_launch_error(e);     // check_launch reports it even if the runtime
                                                   // did not keep it as its last error

@@ -5,7 +5,26 @@
 #include "common.cuh"
 
 namespace nf {
-int g_chained_launch = 1;
+int g_chained_launch = -1;
+static thread_local bool g_chain_break = false;
+bool take_chain_break() {
+  const bool b = g_chain_break;
+  g_chain_break = false;
+  return b;
+}
+void set_chain_break() { g_chain_break = true; }
+int g_chain_outside_capture = 0;      // nf_set_chained_launch_outside_capture(): for experiments
+bool chain_this_launch(int cls, cudaStream_t stream) {
+  const bool pending_break = take_chain_break();          // consumed by this launch either way
+  if (!(g_chained_launch & cls) || pending_break) return false;
+  if (g_chain_outside_capture) return true;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  return st == cudaStreamCaptureStatusActive;
+}
 static thread_local char g_error[512] = "";
 
 void set_error(const char* fmt, ...) {
@@ -38,7 +57,17 @@ extern "C" int nf_abi_version() { return 1; }
 
 // 1: kernels of the decode path are launched with programmatic stream serialization (they may
 // begin while their predecessor drains); 0: ordinary launches.
+extern "C" int nf_set_chained_launch_outside_capture(int on) {
+  nf::g_chain_outside_capture = on ? 1 : 0;
+  return 0;
+}
+
+extern "C" int nf_chain_break() {
+  nf::set_chain_break();
+  return 0;
+}
+
 extern "C" int nf_set_chained_launch(int on) {
-  nf::g_chained_launch = on ? 1 : 0;
+  nf::g_chained_launch = on;
   return 0;
 }

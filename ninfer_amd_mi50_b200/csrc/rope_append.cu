@@ -9,6 +9,7 @@
 //   angle = float(pos) * inv_freq[i];  x'[i] = x[i] cos - x[i+rot/2] sin;
 //   x'[i+rot/2] = x[i] sin + x[i+rot/2] cos          (angle, cos, sin, products in float32)
 // Cache page layout: [2 (k, v)][kv_heads][page_size][head_dim].
+#define NF_CHAIN_CLASS 4
 #include "common.cuh"
 
 namespace nf {
@@ -89,7 +90,7 @@ rope_append_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restri
   const int t = blockIdx.x;
   const int half = D / 2;
   chain_release();
-  chain_wait();
+  chain_wait(qkv, positions, row_seg, block_table);
   const int pos = positions[t];
   const float fpos = (float)pos;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {

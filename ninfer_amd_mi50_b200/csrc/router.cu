@@ -8,6 +8,7 @@
 // for the host.  Ties go to the lower expert index.  With norm_topk the weights are
 // p_e / sum(selected p); without, p_e as they are (the reference always renormalises,
 // moe.hip:77-82).
+#define NF_CHAIN_CLASS 16
 #include "common.cuh"
 
 namespace nf {
@@ -242,7 +243,7 @@ router_fused_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n
       wv[j] = i < hidden ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
-  chain_wait();
+  chain_wait(x);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_float(x[(size_t)t * hidden + i]);
   __syncthreads();
   if (e < rows) {
@@ -330,6 +331,10 @@ router_cluster_kernel(const T* __restrict__ x, const float* __restrict__ wr, int
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned cta = cluster_ctarank();
   const int e0 = (int)cta * 8 + warp;
+  // A CTA's shared memory may only be written from another CTA once that CTA is running: every
+  // thread announces itself here, and waits for all the others right before its first remote
+  // store (the dot products pass in between, so the meeting costs nothing).
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
   constexpr int kPre = 16;
   const bool vec = (hidden & 3) == 0 && ((uintptr_t)wr & 15) == 0;
@@ -343,7 +348,7 @@ router_cluster_kernel(const T* __restrict__ x, const float* __restrict__ wr, int
       wv[j] = i < hidden ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
-  chain_wait();
+  chain_wait(x);
   {
     // x -> float32 in shared memory, 16 bytes of x a thread a step where alignment allows
     const int total = n_tokens * hidden;
@@ -373,6 +378,7 @@ router_cluster_kernel(const T* __restrict__ x, const float* __restrict__ wr, int
     }
   }
   __syncthreads();
+  bool met = false;                      // this thread has seen every CTA of the cluster running
   for (int e = e0; e < rows; e += 8 * kRouterCluster) {
     const float* w = wr + (size_t)e * hidden;
     float mine = 0.f;
@@ -400,11 +406,16 @@ router_cluster_kernel(const T* __restrict__ x, const float* __restrict__ wr, int
     }
     // one remote store a lane, all in flight together: a store into another CTA's shared
     // memory takes long, and one after the other they would add up
+    if (!met) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      met = true;
+    }
     if (lane < n_tokens) {
       st_cluster_f32(lg_all + (size_t)lane * rows + e, 0, mine);
       if (logits_out) logits_out[(size_t)lane * rows + e] = mine;
     }
   }
+  if (!met) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // a warp without rows
   cluster_sync_all();
   if (cta != 0) return;
   // ---- CTA 0: selection for every token, then the plan, all in shared memory --------------------
@@ -630,7 +641,7 @@ extern "C" int nf_router_cluster(const void* x, const float* wr, int T, int hidd
   attrs[2].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attrs[2].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
-  cfg.numAttrs = g_chained_launch ? 3 : 2;
+  cfg.numAttrs = chain_this_launch(NF_CHAIN_CLASS, stream) ? 3 : 2;
   cudaError_t e;
   if (dtype == kF32) {
     if (smem > allowed_f) { cudaFuncSetAttribute(router_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_f = smem; }

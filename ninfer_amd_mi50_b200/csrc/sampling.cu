@@ -51,6 +51,61 @@ argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ ou
   }
 }
 
+// The same over a long row in two steps: the row is cut into `chunks` pieces, a block per piece
+// writes its first maximum (value and index), and a warp per row picks the first maximum among
+// the pieces.  One block per row reads a 600 KB row of a large vocabulary alone for 40 us; cut
+// into pieces the whole device reads it.
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int V, int chunk, float* __restrict__ pv,
+                      int* __restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (size_t)r * V;
+  const int lo = c * chunk, hi = min(V, lo + chunk);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  // ascending indices per thread, so "greater than" keeps the first of equal values
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    pv[(size_t)r * gridDim.x + c] = best;
+    pi[(size_t)r * gridDim.x + c] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int chunks, int* __restrict__ out) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < chunks; c += 32) {
+    const float v = pv[(size_t)r * chunks + c];
+    const int i = pi[(size_t)r * chunks + c];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;   // all NaN: token 0
+}
+
 // logits[row, id] = v > 0 ? v / p^count : v * p^count for (id, count) pairs of each row.
 __global__ void repetition_penalty_kernel(float* __restrict__ logits, int V,
                                           const int* __restrict__ ids, const int* __restrict__ counts,
@@ -256,6 +311,24 @@ extern "C" int nf_argmax_rows(const float* logits, int R, int V, int* out, cudaS
   NF_REQUIRE(R > 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
   argmax_rows_kernel<<<R, 1024, 0, stream>>>(logits, V, out);
   return check_launch("argmax_rows");
+}
+
+// Pieces a row is cut into by the two-step form: 1 means "use nf_argmax_rows".
+extern "C" int nf_argmax_chunks(int R, int V) {
+  if (V < 16384 || R > 4096) return 1;       // short rows, or rows enough to fill the device anyway
+  int c = (V + 4095) / 4096;
+  return c > 64 ? 64 : c;
+}
+
+// scratch_v float32 [R, chunks], scratch_i int32 [R, chunks], chunks = nf_argmax_chunks(R, V) > 1.
+extern "C" int nf_argmax_rows_split(const float* logits, int R, int V, int chunks, float* scratch_v,
+                                    int* scratch_i, int* out, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(R > 0 && V > 0 && chunks > 1 && R <= 65535, "argmax: bad sizes R=%d V=%d chunks=%d", R, V, chunks);
+  const int chunk = (V + chunks - 1) / chunks;
+  argmax_partial_kernel<<<dim3(chunks, R), 256, 0, stream>>>(logits, V, chunk, scratch_v, scratch_i);
+  argmax_final_kernel<<<R, 32, 0, stream>>>(scratch_v, scratch_i, chunks, out);
+  return check_launch("argmax_rows_split");
 }
 
 extern "C" int nf_repetition_penalty(float* logits, int V, const int* ids, const int* counts,

@@ -18,6 +18,7 @@
 // group; its 8 warps take interleaved 32-wide chunks of k and their partial sums are added
 // in warp order in shared memory.  The order of summation depends on K only, so a row's
 // result does not depend on the batch it is in.
+#define NF_CHAIN_CLASS 1
 #include "common.cuh"
 
 namespace nf {
@@ -81,7 +82,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   // precedes this launch began - the router's plan, when this is the experts' second product.
   const bool dense = (!offsets && !x_rows && !group_map) || early_index;
   bool waited = !dense;
-  if (!dense) chain_wait();
+  if (!dense) chain_wait(X, offsets, x_rows, group_map);
   // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
   // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
   const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
@@ -172,7 +173,11 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
         b[u] = make_uint4(0, 0, 0, 0);
       }
     }
-    if (!waited) { chain_wait(); waited = true; }
+    if (!waited) {
+      // the rows of X (and, for the rotary epilogue, the step's tables) are read only from here on
+      chain_wait(rope.positions, rope.row_seg, rope.block_table);
+      waited = true;
+    }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int k = (c0 + u * kWarps) * 32;
@@ -195,7 +200,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     }
   }
 
-  if (!waited) chain_wait();      // a warp without chunks still must not write before the wait
+  if (!waited) chain_wait(rope.positions, rope.row_seg, rope.block_table);   // a warp without chunks: no write, no table read before the wait
   chain_release_late();
   // add the warps' partial sums in warp order
 #pragma unroll

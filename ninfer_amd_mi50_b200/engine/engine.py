@@ -33,6 +33,11 @@ class Engine:
         self._fresh_seed = itertools.count(0x5EED)
         self.requests: Dict[Hashable, Request] = {}
         self.d2h_bytes = 0
+        self._ahead = None      # (batch, drawn tokens on the device) of a step launched ahead of its turn
+        self.ahead_steps = 0    # steps launched that way
+        self._copy_stream = None
+        self._landing = [None, None]     # pinned buffers the drawn tokens land in, used in turn
+        self._landing_turn = 0
 
     # ---- requests ---------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -57,23 +62,97 @@ class Engine:
     # ---- stepping ---------------------------------------------------------------------
     def step(self) -> List[Request]:
         """One scheduler step: build the batch, run it, sample, record.  Returns the requests
-        that finished in this step."""
-        before = len(self.scheduler.finished)
-        batch = self.scheduler.schedule()
-        done = self.scheduler.finished[before:]      # finished without running (out of cache)
-        if not batch:
-            return list(done)
-        logits = self.runner.step(self.scheduler.entries(batch))
-        sampling = [s for s in batch if s.sample]
+        that finished in this step.
+
+        With `run_ahead`, a pure decode step launches its successor before the host reads the
+        tokens it drew (they are handed on inside the device), so the device does not idle
+        while the host schedules; that successor is picked up by the next call."""
+        done: List[Request] = []
+        if self._ahead is not None and not any(s.request.status == "running" for s in self._ahead[0]):
+            self._ahead = None          # every request of that step has stopped meanwhile: nothing to record
+        if self._ahead is not None:
+            batch, picked = self._ahead
+            self._ahead = None
+        else:
+            before = len(self.scheduler.finished)
+            batch = self.scheduler.schedule()
+            done = list(self.scheduler.finished[before:])      # finished without running (out of cache)
+            if not batch:
+                return done
+            logits = self.runner.step(self.scheduler.entries(batch))
+            picked = self._sample(batch, logits, ahead=False)
         tokens: List[int] = []
-        if sampling:
-            picked = self.sampler.sample(
-                logits, [s.request.params for s in sampling],
-                recent=[s.request.tokens for s in sampling],
-                counters=[len(s.request.generated) for s in sampling])
-            tokens = picked.cpu().tolist()
+        if picked is not None:
+            landing = self._start_readback(picked)
+            if self.options.run_ahead:
+                self._ahead = self._launch_ahead(batch, picked)
+            tokens = self._finish_readback(landing)
             self.d2h_bytes += picked.numel() * 4
-        return list(done) + self.scheduler.update(batch, tokens)
+        return done + self.scheduler.update(batch, tokens)
+
+    # The drawn tokens come to the host on a stream of their own, into pinned memory: a copy
+    # on the compute stream would queue behind the step that has just been launched ahead, and
+    # the host would wait for that step too.
+    def _start_readback(self, picked: torch.Tensor):
+        if not picked.is_cuda:
+            return picked, None
+        n = picked.numel()
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=picked.device)
+        slot = self._landing[self._landing_turn % 2]
+        if slot is None or slot.numel() < n:
+            slot = torch.empty((max(n, 64),), dtype=torch.int32).pin_memory()
+            self._landing[self._landing_turn % 2] = slot
+        self._landing_turn += 1
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(picked.device))
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(ready)
+            slot[:n].copy_(picked, non_blocking=True)
+            landed = torch.cuda.Event()
+            landed.record(self._copy_stream)
+        picked.record_stream(self._copy_stream)
+        return slot[:n], landed
+
+    @staticmethod
+    def _finish_readback(landing) -> List[int]:
+        host, landed = landing
+        if landed is not None:
+            landed.synchronize()
+        return host.tolist()
+
+    def _sample(self, batch, logits: torch.Tensor, ahead: bool) -> Optional[torch.Tensor]:
+        sampling = [s for s in batch if s.sample]
+        if not sampling:
+            return None
+        # a step that runs ahead draws the token after the one still on its way to the host
+        extra = 1 if ahead else 0
+        return self.sampler.sample(
+            logits, [s.request.params for s in sampling],
+            recent=[s.request.tokens for s in sampling],
+            counters=[len(s.request.generated) + extra for s in sampling])
+
+    def _launch_ahead(self, batch, picked: torch.Tensor):
+        """Launch the step after `batch` on the tokens in `picked` (still on the device), if the
+        scheduler can say what that step is without knowing them.  Returns (batch, its drawn
+        tokens on the device) or None."""
+        if not self.runner.can_take_device_tokens(len(batch)):
+            return None
+        nxt = self.scheduler.schedule_ahead(batch)
+        if nxt is None:
+            return None
+        tokens = picked
+        if len(nxt) != len(batch):
+            keep = [i for i, s in enumerate(batch) if any(n.request is s.request for n in nxt)]
+            tokens = picked.index_select(0, torch.tensor(keep, dtype=torch.long, device=picked.device))
+        try:
+            logits = self.runner.step(self.scheduler.entries(nxt), device_tokens=tokens)
+        except Exception:
+            for s in nxt:
+                self.cache.truncate(s.request.id)
+            raise
+        self.ahead_steps += 1
+        return nxt, self._sample(nxt, logits, ahead=True)
 
     def run_until_idle(self, max_steps: Optional[int] = None) -> int:
         steps = 0
@@ -101,4 +180,5 @@ class Engine:
         st = self.scheduler.stats
         return {"steps": st.steps, "prompt_tokens": st.prompt_tokens, "decode_tokens": st.decode_tokens,
                 "preemptions": st.preemptions, "finished": st.finished, "out_of_cache": st.out_of_cache,
-                "pages_free": self.cache.pages_free(), "live_requests": len(self.cache.requests)}
+                "pages_free": self.cache.pages_free(), "live_requests": len(self.cache.requests),
+                "ahead_steps": self.ahead_steps}

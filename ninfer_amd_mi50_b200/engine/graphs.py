@@ -14,7 +14,7 @@ page is the cache's null page.  They cost a little work and touch nothing that i
 from __future__ import annotations
 
 import gc
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -112,12 +112,16 @@ class DecodeGraph:
             tbl[n:, 0] = g.null_page
             tbl[n:, 1:] = -1
 
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Pages for the new tokens are reserved already.  Returns logits [S, vocab] that stay
-        valid until the next replay of this graph."""
+        valid until the next replay of this graph.  `device_tokens` (int32 [len(entries)] on the
+        device) replace the entries' token ids: the tokens a step before has just drawn, which
+        the host has not read yet."""
         lengths = [self.runner.cache.length(e.req) for e in entries]
         self._fill(entries, lengths)
         self.dev.copy_(self.host, non_blocking=True)
+        if device_tokens is not None:
+            self.dev[self.offsets[0]:self.offsets[0] + len(entries)].copy_(device_tokens)
         self.graph.replay()
         klib.count_launches(self.kernels)
         return self.logits

@@ -140,6 +140,46 @@ class Scheduler:
             budget -= n
         return batch
 
+    def schedule_ahead(self, batch: Sequence[Scheduled]) -> Optional[List[Scheduled]]:
+        """The batch that follows `batch` if none of its requests stops on the token it is about
+        to receive - decided before that token is known, so that the next step can be launched
+        while the host still waits for this one.  Only when nothing else could be in that
+        batch: every running request decodes in `batch`, nobody waits, no request's sampling
+        looks at earlier tokens (repetition penalty).  Requests that will finish by length or
+        context with the coming token are left out; a request that stops on a stop token after
+        all has run one token for nothing, which `update` is told to ignore.  Holds the pages
+        of the returned batch; returns None (holding nothing) if running ahead is not possible.
+        The entries' token ids are placeholders: the real ones are still on the device."""
+        if self.waiting or not batch or len(batch) != len(self.running):
+            return None
+        nxt: List[Scheduled] = []
+        for s in batch:
+            req = s.request
+            if not s.sample or len(s.tokens) != 1 or req.status != "running" or req.remaining != 1:
+                return None
+            if req.params.repetition_penalty != 1.0:
+                return None
+            after = len(req.generated) + 1                       # generated tokens once this step's is in
+            if after >= req.params.max_new_tokens or len(req.prompt) + after >= self.max_context:
+                continue                                         # finishes with the coming token
+            nxt.append(Scheduled(req, [0], True))
+        if not nxt:
+            return None
+        # this step's token sits at position `computed`, the next one at `computed + 1`
+        if not all(self.cache.can_reserve(s.request.id, s.request.computed + 2) for s in nxt):
+            return None
+        done: List[Scheduled] = []
+        try:
+            for s in nxt:
+                self.cache.reserve(s.request.id, s.request.computed + 2)
+                done.append(s)
+        except Exception:
+            for s in done:
+                self.cache.truncate(s.request.id)
+            return None
+        self.stats.steps += 1
+        return nxt
+
     def _place(self, req: Request, n: int, batch: List[Scheduled]) -> int:
         """Hold pages for `n` more tokens of a running request and put it into the batch.
         If the pool is short, the most recently admitted request gives way - which may be
@@ -205,6 +245,12 @@ class Scheduler:
         it = iter(sampled)
         for s in batch:
             req = s.request
+            if req.status != "running":
+                # a step that ran ahead of the news that this request had stopped: its row was
+                # computed for nothing and its token is dropped
+                if s.sample:
+                    next(it)
+                continue
             if len(s.tokens) == 1 and req.generated and req.computed >= len(req.prompt):
                 self.stats.decode_tokens += 1
             else:

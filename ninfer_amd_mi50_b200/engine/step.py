@@ -53,8 +53,12 @@ class ModelRunner:
                 self.cache.truncate(e.req)
             raise
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """float32 logits [R, vocab] on the device, R = total wanted rows, in entry order."""
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """float32 logits [R, vocab] on the device, R = total wanted rows, in entry order.
+
+        `device_tokens`: for a decode-only step replayed from a graph, the entries' token ids
+        as an int32 tensor on the device, to be used instead of the (placeholder) ids in the
+        entries; `can_take_device_tokens` says whether a step qualifies."""
         entries = list(entries)
         if not entries:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
@@ -62,7 +66,9 @@ class ModelRunner:
         self.reserve(entries)
         try:
             if self.graphs is not None and self.graphs.eligible(entries):
-                logits, moved = self._step_from_graph(entries)
+                logits, moved = self._step_from_graph(entries, device_tokens)
+            elif device_tokens is not None:
+                raise ValueError("token ids on the device can only feed a step that is replayed from a graph")
             else:
                 ctx = pack_step(entries, self.cache, self.dtype, self.device)
                 logits, moved = self.run(ctx), ctx.scratch.get("h2d_bytes", 0)
@@ -77,10 +83,14 @@ class ModelRunner:
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
 
-    def _step_from_graph(self, entries: Sequence[StepEntry]):
+    def can_take_device_tokens(self, n_entries: int) -> bool:
+        """Whether a step of `n_entries` single tokens would be replayed from a graph."""
+        return self.graphs is not None and 0 < n_entries <= self.graphs.max_rows
+
+    def _step_from_graph(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None):
         """A decode-only step: replay the captured graph for this many rows."""
         g = self.graphs.get(entries)
-        logits = g.run(entries)
+        logits = g.run(entries, device_tokens)
         n = len(entries)
         if all(len(e.want) == 1 for e in entries):
             return logits[:n], g.h2d_bytes

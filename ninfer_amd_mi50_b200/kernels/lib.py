@@ -36,8 +36,14 @@ def load() -> ctypes.CDLL:
             except OSError as e:
                 raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from None
             lib.nf_last_error.restype = ctypes.c_char_p
-            if os.environ.get("NINFER_CHAINED_LAUNCH", "1") == "0":
-                lib.nf_set_chained_launch(0)     # plain launches: every kernel waits for the one before
+            mask = os.environ.get("NINFER_CHAINED_LAUNCH")
+            if mask is not None:
+                # 0: plain launches (every kernel waits for the one before); otherwise a mask of the
+                # kernel classes that keep the attribute: 1 streaming products, 2 norm and combine,
+                # 4 rotary, 8 decode attention, 16 router
+                lib.nf_set_chained_launch(int(mask))
+            if os.environ.get("NINFER_CHAINED_OUTSIDE_CAPTURE") == "1":
+                lib.nf_set_chained_launch_outside_capture(1)     # experiments only
             _lib = lib
     return _lib
 

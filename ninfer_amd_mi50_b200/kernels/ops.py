@@ -223,6 +223,13 @@ def _bf16_path(rows: int, K: int, key: str) -> str:
     return "large"
 
 
+def chain_break() -> None:
+    """The next kernel launched (by this thread) waits for everything before it in its stream
+    in the ordinary way.  To be called after making a stream wait for another stream's event:
+    the kernel that follows must not be chained to the kernel before it in its own stream."""
+    _lib.load().nf_chain_break()
+
+
 def tensor_core_status() -> int:
     """0, or the code of the first bounded wait that a tensor-core kernel gave up on since the
     last call (synchronises the device): 1-4 from the grouped GEMM, 101-110 from attention."""
@@ -618,6 +625,14 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     _chk(logits, "logits", torch.float32)
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    chunks = int(_lib.load().nf_argmax_chunks(c_int(R), c_int(V))) if R else 1
+    if chunks > 1:
+        # a long row is cut into pieces so that the whole device reads it
+        sv = torch.empty((R, chunks), dtype=torch.float32, device=logits.device)
+        si = torch.empty((R, chunks), dtype=torch.int32, device=logits.device)
+        _lib.call("nf_argmax_rows_split", _p(logits), c_int(R), c_int(V), c_int(chunks), _p(sv), _p(si),
+                  _p(out), _stream())
+        return out
     _lib.call("nf_argmax_rows", _p(logits), c_int(R), c_int(V), _p(out), _stream())
     return out
 

@@ -158,6 +158,7 @@ class SparseMoeSwiglu(FeedForward):
             main, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
+                kernels.chain_break()       # its input comes from the other stream
                 shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
                                              split=self.w_router_split)
@@ -167,6 +168,7 @@ class SparseMoeSwiglu(FeedForward):
         y = kernels.moe_gemm2(act, self.w2, plan, plan_is_older=True)
         if fork:
             main.wait_stream(side)
+            kernels.chain_break()           # the combine also reads what the other stream produced
         elif self.has_shared:
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         return kernels.moe_combine(y, plan, wts, shared, gate, x.dtype)

@@ -218,6 +218,10 @@ class PackedWeights:
     pass
 
 
+def chain_break():
+    pass
+
+
 def check_head_dim(head_dim):
     pass
 
@@ -226,7 +230,7 @@ def check_router_sizes(num_experts, top_k):
     pass
 
 
-NAMES = ["can_pack", "PackedWeights", "split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
+NAMES = ["chain_break", "can_pack", "PackedWeights", "split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
          "rope_append", "linear_rope_append", "paged_attention", "router_topk", "route", "moe_plan", "moe_gemm1", "moe_gemm2",
          "moe_combine", "argmax_rows"]
 

@@ -29,6 +29,17 @@ def test_argmax_takes_the_first_maximum():
     l[3, 2002] = 60.0
     got = kernels.argmax_rows(l).tolist()
     assert got == torch.argmax(l, dim=-1).tolist() and got[1] == 77 and got[3] == 2002
+    # a long row is cut into pieces: ties across pieces and inside one, the last element, a
+    # length that is no multiple of the piece
+    for V in (16384, 151936, 40001):
+        l = torch.randn(6, V, device="cuda")
+        l[1, 77] = l[1, V - 5] = 50.0
+        l[2, 5000] = l[2, 5001] = 50.0
+        l[3, V - 1] = 60.0
+        l[4] = 1.0                                   # all equal: the first index
+        got = kernels.argmax_rows(l).tolist()
+        assert got == torch.argmax(l, dim=-1).tolist()
+        assert got[1] == 77 and got[2] == 5000 and got[3] == V - 1 and got[4] == 0
 
 
 @pytest.mark.parametrize("V", [515, 2003, 151936])
@@ -240,3 +251,60 @@ def test_capture_survives_an_older_engine_waiting_for_the_collector(folders, mon
     assert (out == ref).all()
     s.close()
     second.close()
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_running_ahead_changes_no_token(folders, temperature):
+    """Decode steps are launched before the host has read the tokens of the step before (they
+    travel inside the device).  Same tokens as without, also when requests stop on a stop token
+    (their row in the step ahead was computed for nothing) or finish by length at different
+    times; and every page comes back."""
+    from ninfer_amd_mi50_b200.api import Ninfer
+    d, cfg, _, _ = folders["A"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 300 + n) for n in (5, 9, 17, 3, 12)]
+    runs, stats = [], []
+    for ahead in (False, True):
+        eng = Ninfer(d, max_context=128, prefill_chunk=32, num_sequences=5, dtype="bfloat16", run_ahead=ahead)
+        free = eng.stats()["pages_free"]
+        base = eng.generate(prompts, max_new_tokens=40, temperature=temperature, seed=5)
+        # stop ids taken from what the requests generate: some stop early, at different steps
+        stops = {base[0][7], base[1][20], base[3][2]}
+        outs = [base, eng.generate(prompts, max_new_tokens=40, temperature=temperature, seed=5, stop_ids=stops)]
+        # lengths that differ per request (finishing by length is known in advance)
+        from ninfer_amd_mi50_b200.sampling import SamplingParams
+        ps = [SamplingParams(temperature, 50, 0.95, 1.0, 5, n) for n in (3, 40, 11, 1, 25)]
+        outs.append(eng._engine.generate(prompts, ps))
+        runs.append(outs)
+        stats.append(eng.stats())
+        assert eng.stats()["pages_free"] == free and eng.stats()["live_requests"] == 0
+        eng.close()
+    assert runs[0] == runs[1]
+    assert stats[0]["ahead_steps"] == 0 and stats[1]["ahead_steps"] > 50
+    assert any(len(o) < 40 for o in runs[1][1])          # some request did stop early
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_a_replayed_step_gives_the_same_bits_every_time(folders, name):
+    """A captured decode step, replayed on unchanged inputs, must give the same logits bit for
+    bit.  With the kernels of the step launched chained (each may begin while its predecessor
+    drains), the first kernel after a wait on another stream - the shared expert's branch, and
+    the combine that joins it - must be an ordinary launch: chained, it began before the other
+    stream's kernel had finished, and every replay of the step differed."""
+    from ninfer_amd_mi50_b200.config import EngineOptions
+    from ninfer_amd_mi50_b200.engine import StepEntry, load_runner
+    d, cfg, _, _ = folders[name]
+    runner = load_runner(d, options=EngineOptions(dtype="bfloat16", page_size=64, num_sequences=4,
+                                                   max_context=256, cache_tokens=1024))
+    for r in range(3):
+        runner.open(r)
+        runner.step([StepEntry(r, random_tokens(70 + 9 * r, cfg["vocab_size"], 500 + r), [])])
+    for s in range(2):
+        runner.step([StepEntry(r, [5 + s + r], [0]) for r in range(3)])
+    torch.cuda.synchronize()
+    (graph,) = runner.graphs.graphs.values()
+    graph.graph.replay()
+    torch.cuda.synchronize()
+    ref = graph.logits.clone()
+    for _ in range(300):
+        graph.graph.replay()
+        assert torch.equal(graph.logits, ref)

@@ -137,3 +137,56 @@ def test_sampling_is_independent_of_preemption():
         outs.append({r.id: r.generated for r in sch.finished})
         assert all(r.finish_reason == "length" for r in sch.finished)
     assert outs[0] == outs[1]
+
+
+def test_running_ahead_is_decided_without_the_coming_token():
+    """`schedule_ahead` names the next decode batch before this one's tokens are known: only
+    when every running request decodes and nobody waits; requests that finish by length with
+    the coming token are left out; a request that stops on a stop token after all is skipped
+    by `update`, and no page is lost either way."""
+    cache, sch = make(pages=16, reqs=4, budget=32, chunk=16)
+    sch.add(req(1, 5, max_new=3))
+    sch.add(req(2, 7, max_new=6, stop=(9,)))
+    b = sch.schedule()                                   # both prompts whole: not a decode step
+    assert sch.schedule_ahead(b) is None
+    for s in b:
+        cache.commit(s.request.id, s.request.computed + len(s.tokens))
+    sch.update(b, [7, 7])
+    b = sch.schedule()                                   # first pure decode step (token 2 of each)
+    assert [len(s.tokens) for s in b] == [1, 1]
+    for s in b:
+        cache.commit(s.request.id, s.request.computed + 1)
+    nxt = sch.schedule_ahead(b)
+    # request 1 has one token and gets its second now; max_new 3 -> it still runs ahead
+    assert [s.request.id for s in nxt] == [1, 2] and all(s.sample and len(s.tokens) == 1 for s in nxt)
+    for s in nxt:
+        cache.commit(s.request.id, s.request.computed + 2)
+    sch.update(b, [7, 9])                                # request 2 stops on its stop token
+    assert [r.id for r in sch.finished] == [2]
+    cache.check()
+    # the step that ran ahead: request 2's row is ignored, request 1 gets its third token and ends
+    done = sch.update(nxt, [7, 123])
+    assert [r.id for r in done] == [1] and sch.finished[-1].generated == [7, 7, 7]
+    assert sch.finished[0].generated == [7, 9]
+    assert sch.idle and cache.pages_free() == [16]
+    cache.check()
+    # a request about to finish by length is left out of the step ahead
+    sch.add(req(3, 4, max_new=2))
+    sch.add(req(4, 4, max_new=5))
+    b = sch.schedule()
+    for s in b:
+        cache.commit(s.request.id, s.request.computed + len(s.tokens))
+    sch.update(b, [7, 7])
+    b = sch.schedule()
+    for s in b:
+        cache.commit(s.request.id, s.request.computed + 1)
+    nxt = sch.schedule_ahead(b)
+    assert [s.request.id for s in nxt] == [4]
+    # somebody waiting: no running ahead
+    sch.add(req(5, 4))
+    for s in nxt:
+        cache.commit(s.request.id, s.request.computed + 2)
+    sch.update(b, [7, 7])
+    sch.update(nxt, [7])
+    b = sch.schedule()
+    assert any(len(s.tokens) > 1 for s in b) and sch.schedule_ahead(b) is None
