@@ -1,7 +1,9 @@
 """Generality of the parts: a toy architecture defined here - a mixer with per-request state
-of its own, a layer that reads another layer's cache, a layer named twice in the order - is
-registered, written as a random model folder, loaded and stepped under every way of
-cutting the work, without a change to the package's files.  It is no model of anyone's."""
+of its own, a feed-forward that routes rows between two matrices, a position encoding of
+another form (adjacent pairs turned, not half-split), a layer that reads another layer's
+cache, a layer named twice in the order - is registered, written as a random model folder,
+loaded and stepped under every way of cutting the work, without a change to the package's
+files.  It is no model of anyone's."""
 
 import json
 import math
@@ -25,7 +27,7 @@ TOY = {"architectures": ["ToyStateForCausalLM"], "vocab_size": 301, "hidden_size
 def toy_registered():
     from ninfer_amd_mi50_b200 import kernels
     from ninfer_amd_mi50_b200.config import LayerCall, LayerSpec, ModelPlan, PartSpec
-    from ninfer_amd_mi50_b200.parts.base import Mixer, StateSpec, TensorSpec
+    from ninfer_amd_mi50_b200.parts.base import FeedForward, Mixer, PositionEncoding, StateSpec, TensorSpec
     from ninfer_amd_mi50_b200.registry import (register_architecture, register_part,
                                                unregister_architecture, unregister_part)
 
@@ -66,6 +68,50 @@ def toy_registered():
                 row += n
             return kernels.linear(out.to(x.dtype), self.w_out)
 
+    @register_part("feed_forward", "toy_sign_router")
+    class ToySignRouter(FeedForward):
+        """A row goes through matrix 1 if its projection on a routing vector is positive, else
+        through matrix 0 (the decision is taken in float32 on the row as the engine holds it)."""
+
+        def __init__(self, hidden_size, prefix):
+            self.H, self.prefix = hidden_size, prefix
+
+        def tensor_specs(self):
+            p = self.prefix
+            return [TensorSpec(p + "route", (self.H,), role="vector"),
+                    TensorSpec(p + "w0.weight", (self.H, self.H)), TensorSpec(p + "w1.weight", (self.H, self.H))]
+
+        def load(self, fetch):
+            p = self.prefix
+            self.route, self.w = fetch(p + "route"), [fetch(p + "w0.weight"), fetch(p + "w1.weight")]
+
+        def forward(self, x, ctx):
+            up = (x.float() @ self.route) > 0
+            out = torch.empty_like(x)
+            for e in (0, 1):
+                rows = torch.nonzero(up == bool(e)).flatten()
+                if rows.numel():
+                    out[rows] = kernels.linear(x[rows].contiguous(), self.w[e])
+            return out
+
+    @register_part("position", "toy_adjacent_pairs")
+    class ToyAdjacentPairs(PositionEncoding):
+        """Dims (2i, 2i + 1) are turned by pos * theta^(-2i/D): not the half-split form, so
+        there is no table for the fused kernel and `apply` does the work."""
+
+        def __init__(self, head_dim, theta):
+            self.D, self.theta = head_dim, theta
+
+        def apply(self, q, k, positions):
+            inv = torch.tensor([self.theta ** (-2.0 * i / self.D) for i in range(self.D // 2)],
+                               dtype=torch.float32, device=q.device)
+            ang = positions.float()[:, None] * inv[None, :]
+            c, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            for t in (q, k):
+                a, b = t[..., 0::2].float().clone(), t[..., 1::2].float().clone()
+                t[..., 0::2] = (a * c - b * sn).to(t.dtype)
+                t[..., 1::2] = (a * sn + b * c).to(t.dtype)
+
     def build_plan(c):
         norm = PartSpec.make("rms_norm", size=c["hidden_size"], eps=c["eps"])
         ffn = PartSpec.make("dense_swiglu", hidden_size=c["hidden_size"], intermediate_size=c["intermediate_size"])
@@ -73,11 +119,17 @@ def toy_registered():
                             num_kv_heads=c["num_kv_heads"], head_dim=c["head_dim"], qkv_bias=False,
                             position=PartSpec.make("rotary_half_split", head_dim=c["head_dim"], theta=c["theta"]))
         toy = PartSpec.make("toy_running_state", hidden_size=c["hidden_size"], state_size=c["state_size"])
+        att2 = PartSpec.make("paged_gqa_attention", hidden_size=c["hidden_size"], num_heads=c["num_heads"],
+                             num_kv_heads=c["num_kv_heads"], head_dim=c["head_dim"], qkv_bias=False,
+                             position=PartSpec.make("toy_adjacent_pairs", head_dim=c["head_dim"], theta=c["theta"]))
+        routed = PartSpec.make("toy_sign_router", hidden_size=c["hidden_size"])
         names = (("norm1", "ln1"), ("mixer", "mix"), ("norm2", "ln2"), ("feed_forward", "ff"))
-        layers = tuple(LayerSpec("pre_norm", norm, m, ffn, prefix=f"toy.l{i}.", names=names)
-                       for i, m in enumerate((toy, att, att)))
-        # layer 2 reads layer 1's cache; layer 1 runs a second time, reading what it wrote
-        order = (LayerCall(0, 0), LayerCall(1, 1, True), LayerCall(2, 1, False), LayerCall(1, 1, False))
+        layers = tuple(LayerSpec("pre_norm", norm, m, f, prefix=f"toy.l{i}.", names=names)
+                       for i, (m, f) in enumerate(((toy, ffn), (att, ffn), (att, ffn), (att2, routed))))
+        # layer 2 reads layer 1's cache; layer 1 runs a second time, reading what it wrote;
+        # layer 3 has the other position encoding, the routed feed-forward and a cache of its own
+        order = (LayerCall(0, 0), LayerCall(1, 1, True), LayerCall(2, 1, False), LayerCall(1, 1, False),
+                 LayerCall(3, 3, True))
         return ModelPlan(c["vocab_size"], c["hidden_size"], layers, order, norm, True,
                          embedding_name="toy.embed.weight", final_norm_name="toy.norm.", head_name="toy.head.weight")
 
@@ -85,6 +137,8 @@ def toy_registered():
     yield
     unregister_architecture("ToyStateForCausalLM")
     unregister_part("mixer", "toy_running_state")
+    unregister_part("feed_forward", "toy_sign_router")
+    unregister_part("position", "toy_adjacent_pairs")
 
 
 def toy_plain(cfg, W, tokens):
@@ -125,6 +179,24 @@ def toy_plain(cfg, W, tokens):
         kv = kv or kv_new
         h = h + o
         h = h + ffn(i, PM.plain_rms_norm(h, W[f"toy.l{i}.ln2.weight"], cfg["eps"]))
+    # layer 3: adjacent pairs turned, then the routed feed-forward
+    p = "toy.l3.mix."
+    x = PM.plain_rms_norm(h, W["toy.l3.ln1.weight"], cfg["eps"])
+    ang = pos.float()[:, None] * torch.tensor([cfg["theta"] ** (-2.0 * i / D) for i in range(D // 2)])[None, :]
+    c, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def turn(t):
+        a, b = t[..., 0::2], t[..., 1::2]
+        out = torch.empty_like(t)
+        out[..., 0::2], out[..., 1::2] = a * c - b * sn, a * sn + b * c
+        return out
+    q = turn((x @ W[p + "q_proj.weight"].T).view(T, Hq, D))
+    k = turn((x @ W[p + "k_proj.weight"].T).view(T, Hkv, D))
+    v = (x @ W[p + "v_proj.weight"].T).view(T, Hkv, D)
+    h = h + PM.plain_attention(q, k, v) @ W[p + "o_proj.weight"].T
+    x = PM.plain_rms_norm(h, W["toy.l3.ln2.weight"], cfg["eps"])
+    up = (x @ W["toy.l3.ff.route"]) > 0
+    h = h + torch.where(up[:, None], x @ W["toy.l3.ff.w1.weight"].T, x @ W["toy.l3.ff.w0.weight"].T)
     return PM.plain_rms_norm(h, W["toy.norm.weight"], cfg["eps"]) @ W["toy.embed.weight"].T
 
 
@@ -142,8 +214,8 @@ def test_toy_architecture_steps_under_every_cut(toy_registered, tmp_path, dtype)
     for make in (schedules.whole, schedules.portions, lambda r: schedules.mixed(r, page=16, pool_tokens=192)):
         runner = load_runner(d, options=EngineOptions(dtype=dtype, page_size=16, num_sequences=4,
                                                        max_context=192, cache_tokens=192, use_graph=False))
-        assert [s is not None for s in runner.model.state_specs()] == [True, False, False]
-        assert len(runner.cache.groups) == 1 and runner.cache.groups[0].slots == [1, 2]
+        assert [s is not None for s in runner.model.state_specs()] == [True, False, False, False]
+        assert len(runner.cache.groups) == 1 and runner.cache.groups[0].slots == [1, 2, 3]
         got = schedules.run_schedule(runner, make(reqs))
         for r in reqs:
             check(got[r], want[r], dtype, f"toy {r}")
