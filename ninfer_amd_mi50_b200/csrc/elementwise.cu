@@ -6,6 +6,7 @@
 // sum of expert outputs replaces scale_rows (216-223) + scatter_add_rows
 // (src/ops/moe.hip:22-31, which races) by one pass with a fixed order and no atomics.
 // The residual stream is float32 in both modes.
+#define NF_CHAIN_CLASS 2
 #include "common.cuh"
 
 namespace nf {
@@ -84,7 +85,7 @@ __global__ void add_rmsnorm_x4_kernel(float* __restrict__ h, const T* __restrict
   __shared__ float red[33];
   const int r = blockIdx.x;
   chain_release();
-  chain_wait();
+  chain_wait(h, delta, rows);
   const int src = GATHER ? rows[r] : r;
   float* hr = h + (size_t)src * hidden;
   const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
@@ -177,6 +178,10 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __n
   *reinterpret_cast<uint4*>(act + (size_t)m * inner + i) = *reinterpret_cast<const uint4*>(o);
 }
 
+// set to 1 + token if a combine met a sorted position outside the step's pairs (read and reset by
+// nf_index_status)
+__device__ int g_combine_index_error = 0;
+
 __global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv,
                                           const float* __restrict__ wts,
                                           const __nv_bfloat16* __restrict__ shared,
@@ -185,13 +190,17 @@ __global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, c
   const int t = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   chain_release();
-  chain_wait();
+  chain_wait(y, inv, wts, shared, gate);
   if (i >= hidden) return;
   float acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   for (int j = 0; j < k; ++j) {
     const int p = inv[t * k + j];
+    if ((unsigned)p >= (unsigned)(gridDim.x * k)) {      // not a sorted position of this step: skip, and say so
+      atomicCAS(&g_combine_index_error, 0, 1 + t);
+      continue;
+    }
     const float w = wts[t * k + j];
     float v[8];
     load8(y + (size_t)p * hidden + i, v);
@@ -292,6 +301,14 @@ extern "C" int nf_moe_combine(const void* y, const int* inv, const float* wts, c
   else
     moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
   return check_launch("moe_combine");
+}
+
+// 0, or 1 + the token whose combine met an index outside the step's pairs since the last call.
+extern "C" int nf_combine_index_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_combine_index_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_combine_index_error, &zero, sizeof(int));
+  return v;
 }
 
 // out[p, :] = x[rows[p] / div, :] for n rows of `row_bytes` bytes (a multiple of 16).

@@ -48,6 +48,10 @@ __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, uns
 // half, so each accumulator pair (row g, row g + 8) is one rotation pair: bias, rotation by
 // pos * inv_freq (float32), and the result goes to Y (queries) or straight into the cache page
 // of (request, position) (keys, values) - the projection's output never makes a round trip.
+// set to a code if a grouped product met a group, a row range or a row index outside its operands
+// (1 group, 2 row range, 3 row index); read and reset by nf_skinny_index_status
+__device__ int g_skinny_index_error = 0;
+
 struct RopeEpilogue {
   const float* bias;          // [(Hq + 2 Hkv) D] or null
   const int* positions;       // [M]
@@ -70,7 +74,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
                    const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div,
-                   const int* __restrict__ group_map, int early_index, RopeEpilogue rope) {
+                   const int* __restrict__ group_map, int early_index, int n_groups, RopeEpilogue rope) {
   // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
   __shared__ float partial[kWarps][NT * 4 * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,12 +90,18 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
   // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
   const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
-  if (group < 0) {
+  if (group < 0 || group >= n_groups) {
+    if (group >= n_groups) atomicCAS(&g_skinny_index_error, 0, 1);
     if (!waited) chain_wait();
     return;
   }
   int row_begin = 0, row_end = M;
   if (offsets) { row_begin = offsets[group]; row_end = offsets[group + 1]; }
+  if (row_begin < 0 || row_end > M) {          // not offsets of this step's rows: do nothing, and say so
+    atomicCAS(&g_skinny_index_error, 0, 2);
+    if (!waited) chain_wait();
+    return;
+  }
   const int m0 = row_begin + blockIdx.x * (8 * NT);
   if (m0 >= row_end) {
     if (!waited) chain_wait();
@@ -140,7 +150,15 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   for (int nt = 0; nt < NT; ++nt) {
     const int r = m0 + nt * 8 + g;
     long src = -1;
-    if (r < row_end) src = x_rows ? (long)(x_rows[r] / x_div) : (long)r;
+    if (r < row_end) {
+      src = x_rows ? (long)x_rows[r] : (long)r;
+      if (src < 0 || src >= M) {               // (x_rows holds pair indices below M)
+        atomicCAS(&g_skinny_index_error, 0, 3);
+        src = -1;
+      } else if (x_rows) {
+        src /= x_div;
+      }
+    }
     xp[nt] = src >= 0 ? X + src * (long)ldx + 8 * t : nullptr;
   }
 
@@ -269,7 +287,7 @@ static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y,
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
   launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
                  (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
-                 x_div, group_map, early_index, RopeEpilogue{});
+                 x_div, group_map, early_index, groups, RopeEpilogue{});
   return check_launch("skinny_gemm");
 }
 
@@ -344,10 +362,19 @@ extern "C" int nf_skinny_qkv_rope(const void* X, int ldx, const void* W, void* Y
   if (M <= 8)
     launch_chained(skinny_gemm_kernel<1, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, r);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r);
   else
     launch_chained(skinny_gemm_kernel<2, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, r);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r);
   return check_launch("skinny_qkv_rope");
+}
+
+// 0, or the code of the first index a grouped product found outside its operands since the last
+// call (1 group, 2 row range, 3 row index).  Synchronises.
+extern "C" int nf_skinny_index_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_skinny_index_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_skinny_index_error, &zero, sizeof(int));
+  return v;
 }

@@ -238,6 +238,15 @@ def tensor_core_status() -> int:
     return gemm if gemm else (100 + attn if attn else 0)
 
 
+def index_status() -> int:
+    """0, or what a kernel that follows device-side indices found outside its operands since the
+    last call (it skips such an access): 201-203 the streaming product (group, row range, row
+    index), 300 + token + 1 the combine.  Synchronises the device."""
+    lib = _lib.load()
+    sk, cb = int(lib.nf_skinny_index_status()), int(lib.nf_combine_index_status())
+    return 200 + sk if sk else (300 + cb if cb else 0)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x [M, K] times w [N, K] transposed -> [M, N]; float32 accumulation."""
     _chk(x, "x"); _chk(w, "w", x.dtype)
