@@ -8,9 +8,10 @@
 // max(0, p - window + 1) <= j <= p, softmax and its sums in float32.
 //
 // Shape of the work.  A tile is up to 128 consecutive rows of one segment and one query head;
-// a CTA runs two tiles one after the other (a heavy one and a light one, see
-// `StepContext.paired_query_tiles`).  Keys and values come in blocks of 128 keys, aligned to
-// multiples of 128, so the order of a row's sums depends on its own position only.
+// a CTA runs the tiles of its entry of `tiles` one after the other (the caller gives one tile a
+// CTA, heaviest first, see `StepContext.paired_query_tiles`; a second one is taken if present).
+// Keys and values come in blocks of 128 keys, aligned to multiples of 128, so the order of a
+// row's sums depends on its own position only.
 //
 //   warp 0     producer of Q and K, warp 10 producer of V: TMA tensor copies (128-byte swizzle),
 //              page by page through the block table, into two-stage rings (a key stage is free
@@ -22,9 +23,9 @@
 //   warps 2-9  softmax: row r is tensor-memory lane r; two threads share a row (warps w and w + 4
 //              may touch the same 32 lanes) and take 64 of its 128 scores each: ``tcgen05.ld``,
 //              mask, a reference maximum that is only raised when a score exceeds it by more than
-//              2^8 (then O's row is rescaled in tensor memory), P = 2^(s - m) as bfloat16 into one
-//              of two shared-memory buffers in the swizzled K-major image; at the end of the tile
-//              O divided by the row sum is stored
+//              2^8 (then O's row is rescaled in tensor memory), P = 2^(s - m) as bfloat16 into
+//              shared memory in the swizzled K-major image; at the end of the tile O divided by
+//              the row sum is stored
 //
 // Everything between the roles goes through mbarriers; every wait is bounded: after a fixed
 // number of polls the kernel records a code in `g_fa_error`, tells its other warps to stop,
