@@ -40,6 +40,8 @@ constexpr int kBM = 128;          // features per CTA (MMA M)
 constexpr int kBK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kBNMax = 256;       // tokens per pass (MMA N, columns of one accumulator)
 constexpr int kTmemCols = 512;
+constexpr int kEpilogueWarps = 12; // three for each quadrant of tensor-memory lanes
+constexpr int kTcThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kXBox = 64;         // token rows per TMA box
 constexpr int kMaxStages = 8;
 constexpr int kMaxGroupsTc = 1024;   // groups one launch may have (their pass counts live in shared memory)
@@ -53,7 +55,7 @@ __device__ __forceinline__ unsigned instr_desc(int n) {
 }
 
 struct __align__(8) Barriers {
-  unsigned long long full[kMaxStages], empty[kMaxStages], acc_full, acc_empty;
+  unsigned long long full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
   unsigned tmem_base;
   int stop;
 };
@@ -62,12 +64,12 @@ struct __align__(8) Barriers {
 // cta, cta + grid, ... with feature tiles varying fastest, so CTAs that run together share an
 // expert's token rows in L2, and the passes of a heavily loaded expert - which re-read its
 // weights - run next to each other and find them in L2.  Items cost about the same, so the
-// static assignment stays balanced however unevenly the router loads the experts.  192 threads: warp 0 producer, warp 1 MMA + tensor memory, warps 2..5 epilogue.  The
+// static assignment stays balanced however unevenly the router loads the experts.  448 threads: warp 0 producer, warp 1 MMA + tensor memory, warps 2..13 epilogue.  The
 // producer is not held back by the epilogue: while the epilogue warps drain an item's
 // accumulator, the stages fill with the next item's first k tiles, so the memory pipe never
 // goes idle between items.  Wp: packed weights [groups][feature tiles][k tiles][A_ROWS][64].
 template <bool SWIGLU>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_constant__ CUtensorMap map_x,
                        const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int ldo,
                        int n_features, int K, int groups) {
@@ -91,6 +93,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
     if (mx) atomicMax(&s_max_rows, mx);
   }
   __syncthreads();
+  constexpr int kAccBuffers = SWIGLU ? 1 : 2;      // accumulators of kBNMax columns that fit beside each other
   const int max_boxes = (min(max(s_max_rows, 1), kBNMax) + kXBox - 1) / kXBox;
   const int stage_bytes = A_BYTES + max_boxes * BOX_BYTES;
   const int tail_bytes = (int)sizeof(Barriers) + (groups + 1) * (int)sizeof(int);
@@ -111,8 +114,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
-    mbar_init(&bars->acc_full, 1);
-    mbar_init(&bars->acc_empty, 4);
+    for (int b = 0; b < 2; ++b) { mbar_init(&bars->acc_full[b], 1); mbar_init(&bars->acc_empty[b], kEpilogueWarps); }
     bars->stop = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -174,7 +176,11 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
         const int pass = gp - s_pass_start[group];
         const int n_rows = offsets[group + 1] - offsets[group];
         {
-          if (!mbar_wait(&bars->acc_empty, (pass_ctr & 1) ^ 1, stop, 2, &g_tc_error)) { ok = false; break; }
+          // without the second (up) accumulator there is room for two: the epilogue of one item
+          // runs under the products of the next
+          const int ab = pass_ctr % kAccBuffers, aph = (pass_ctr / kAccBuffers) & 1;
+          const unsigned acc_tmem = tmem + ab * kBNMax;
+          if (!mbar_wait(&bars->acc_empty[ab], aph ^ 1, stop, 2, &g_tc_error)) { ok = false; break; }
           tc_fence_after();
           const int n = min(kBNMax, (n_rows - pass * kBNMax + 15) & ~15);
           const unsigned idesc = instr_desc(n);
@@ -190,18 +196,18 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
             for (int kk = 0; kk < kBK / 16; ++kk) {
               // 16 k = 32 bytes further along the swizzled row: +2 in the address field
               const unsigned acc = (ks > 0 || kk > 0) ? 1u : 0u;
-              tc_mma(tmem, a0 + 2 * kk, b + 2 * kk, idesc, acc);
-              if (SWIGLU) tc_mma(tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
+              tc_mma(acc_tmem, a0 + 2 * kk, b + 2 * kk, idesc, acc);
+              if (SWIGLU) tc_mma(acc_tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
             }
             tc_commit(&bars->empty[s]);          // the stage is free once these MMAs have read it
           }
-          if (ok) tc_commit(&bars->acc_full);    // the accumulator is complete once they have all run
+          if (ok) tc_commit(&bars->acc_full[ab]);   // the accumulator is complete once they have all run
         }
       }
     }
   } else {
-    // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31 ---------------------
-    const int quad = warp & 3;
+    // ---- epilogue: warps 2..13 read tensor-memory lanes 32 * (warp % 4) .. + 31 ---------------------
+    const int quad = warp & 3, half = (warp - 2) >> 2;     // the warps of a quadrant's lanes take 32 columns in turn
     int pass_ctr = 0;
     bool ok = true;
     int group = 0;
@@ -212,12 +218,13 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
       const int row_begin = offsets[group], n_rows = offsets[group + 1] - row_begin;
       const int f = ft * kBM + quad * 32 + lane;
       {
-        if (!mbar_wait(&bars->acc_full, pass_ctr & 1, stop, 4, &g_tc_error)) { ok = false; break; }
+        const int ab = pass_ctr % kAccBuffers, aph = (pass_ctr / kAccBuffers) & 1;
+        if (!mbar_wait(&bars->acc_full[ab], aph, stop, 4, &g_tc_error)) { ok = false; break; }
         tc_fence_after();
         const int p0 = row_begin + pass * kBNMax;
         const int valid = min(kBNMax, n_rows - pass * kBNMax);
-        const unsigned lane_addr = tmem + ((unsigned)(quad * 32) << 16);
-        for (int c0 = 0; c0 < valid; c0 += 32) {
+        const unsigned lane_addr = tmem + ab * kBNMax + ((unsigned)(quad * 32) << 16);
+        for (int c0 = half * 32; c0 < valid; c0 += 8 * kEpilogueWarps) {
           unsigned g[32], u[32];
           tc_ld32(lane_addr + c0, g);
           if (SWIGLU) tc_ld32(lane_addr + kBNMax + c0, u);
@@ -228,7 +235,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
               if (c0 + c < valid) {
                 float v = __uint_as_float(g[c]);
                 // the result is rounded to bfloat16 (2^-9): the fast exponential's 2^-21 is far below
-                if (SWIGLU) v = v / (1.f + __expf(-v)) * __uint_as_float(u[c]);
+                if (SWIGLU) v = __fdividef(v, 1.f + __expf(-v)) * __uint_as_float(u[c]);
                 out[(size_t)(p0 + c0 + c) * ldo + f] = __float2bfloat16_rn(v);
               }
             }
@@ -236,7 +243,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->acc_empty);
+        if (lane == 0) mbar_arrive(&bars->acc_empty[ab]);
       }
     }
   }
@@ -271,7 +278,7 @@ static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, 
   }
   // at least one pass per non-empty group; the kernel itself counts the exact number of items
   const int grid = n_sm;
-  grouped_gemm_tc_kernel<SWIGLU><<<grid, 192, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
+  grouped_gemm_tc_kernel<SWIGLU><<<grid, kTcThreads, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
                                                              (__nv_bfloat16*)out, ldo, n_features, K, groups);
   return check_launch("grouped_gemm_tc");
 }
