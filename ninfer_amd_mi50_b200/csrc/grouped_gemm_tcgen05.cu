@@ -42,6 +42,8 @@ constexpr int kBNMax = 256;       // tokens per pass (MMA N, columns of one accu
 constexpr int kTmemCols = 512;
 constexpr int kEpilogueWarps = 12; // three for each quadrant of tensor-memory lanes
 constexpr int kTcThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kWarpCols = 48;      // accumulator columns a warp holds in registers at a time
+constexpr int kRoundCols = kWarpCols * kEpilogueWarps / 4;
 constexpr int kXBox = 64;         // token rows per TMA box
 constexpr int kMaxStages = 8;
 constexpr int kMaxGroupsTc = 1024;   // groups one launch may have (their pass counts live in shared memory)
@@ -224,26 +226,47 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
         const int p0 = row_begin + pass * kBNMax;
         const int valid = min(kBNMax, n_rows - pass * kBNMax);
         const unsigned lane_addr = tmem + ab * kBNMax + ((unsigned)(quad * 32) << 16);
-        for (int c0 = half * 32; c0 < valid; c0 += 8 * kEpilogueWarps) {
-          unsigned g[32], u[32];
-          tc_ld32(lane_addr + c0, g);
-          if (SWIGLU) tc_ld32(lane_addr + kBNMax + c0, u);
-          tc_wait_ld();
-          if (f < n_features) {
+        // Each warp turns kWarpCols columns of every round of kRoundCols into bfloat16 values in
+        // registers; after the last round's loads the accumulator goes back to the MMA warp, and
+        // the stores run under the next item's products.
+        for (int r0 = 0; r0 < valid; r0 += kRoundCols) {
+          const int c0 = r0 + half * kWarpCols;
+          unsigned pk[kWarpCols / 2];       // two bfloat16 results a register
+          if (c0 < valid) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              if (c0 + c < valid) {
-                float v = __uint_as_float(g[c]);
-                // the result is rounded to bfloat16 (2^-9): the fast exponential's 2^-21 is far below
-                if (SWIGLU) v = __fdividef(v, 1.f + __expf(-v)) * __uint_as_float(u[c]);
-                out[(size_t)(p0 + c0 + c) * ldo + f] = __float2bfloat16_rn(v);
+            for (int j = 0; j < kWarpCols / 16; ++j) {
+              if (c0 + 16 * j < valid) {
+                unsigned g[16], u[16];
+                tc_ld16(lane_addr + c0 + 16 * j, g);
+                if (SWIGLU) tc_ld16(lane_addr + kBNMax + c0 + 16 * j, u);
+                tc_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                  float v0 = __uint_as_float(g[c]), v1 = __uint_as_float(g[c + 1]);
+                  // the result is rounded to bfloat16 (2^-9): the fast exponential's 2^-21 is far below
+                  if (SWIGLU) {
+                    v0 = __fdividef(v0, 1.f + __expf(-v0)) * __uint_as_float(u[c]);
+                    v1 = __fdividef(v1, 1.f + __expf(-v1)) * __uint_as_float(u[c + 1]);
+                  }
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                  pk[8 * j + c / 2] = *reinterpret_cast<const unsigned*>(&h);
+                }
               }
             }
           }
+          if (r0 + kRoundCols >= valid) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_empty[ab]);
+          }
+          if (c0 < valid && f < n_features) {
+#pragma unroll
+            for (int c = 0; c < kWarpCols; ++c)
+              if (c0 + c < valid)
+                out[(size_t)(p0 + c0 + c) * ldo + f] =
+                    __ushort_as_bfloat16((unsigned short)((c & 1) ? pk[c / 2] >> 16 : pk[c / 2] & 0xffffu));
+          }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->acc_empty[ab]);
       }
     }
   }
