@@ -136,6 +136,15 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // 8 consecutive bfloat16 (16 bytes) or 4 consecutive floats (16 bytes) as floats.
+__device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* out) {
   uint4 raw = *reinterpret_cast<const uint4*>(p);
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);

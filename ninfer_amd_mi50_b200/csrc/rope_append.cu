@@ -86,61 +86,90 @@ rope_append_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restri
                           const float* __restrict__ inv_freq, int Hq, int Hkv, int D,
                           __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table,
                           int bt_width, int page_size, int num_pages, int append) {
-  extern __shared__ float cs[];            // [D/2] cos, [D/2] sin
+  extern __shared__ __align__(16) float cs[];            // [D/2] cos, [D/2] sin
   const int t = blockIdx.x;
   const int half = D / 2;
   chain_release();
   chain_wait(qkv, positions, row_seg, block_table);
   const int pos = positions[t];
-  const float fpos = (float)pos;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float angle = fpos * inv_freq[i];
-    cs[i] = cosf(angle);
-    cs[half + i] = sinf(angle);
-  }
-  __syncthreads();
   const int W = (Hq + 2 * Hkv) * D;
   __nv_bfloat16* x = qkv + (size_t)t * W;
-  __nv_bfloat16* kdst = nullptr;
-  if (append) {
-    const int seg = row_seg[t];
-    const int lp = pos / page_size;
-    const int page = (lp >= 0 && lp < bt_width) ? block_table[(size_t)seg * bt_width + lp] : -1;
-    if (page >= 0 && page < num_pages)
-      kdst = pages + ((size_t)page * 2 * Hkv * page_size + (size_t)(pos - lp * page_size)) * D;
-  }
-  const size_t kv_head_stride = (size_t)page_size * D;
   const int groups = half / 8;             // 8-dim groups per half head
   const int heads = append ? Hq + 2 * Hkv : Hq;
-  for (int idx = threadIdx.x; idx < heads * groups; idx += blockDim.x) {
-    const int head = idx / groups, gi = idx - head * groups;
-    const bool is_q = head < Hq, is_v = head >= Hq + Hkv;
-    const size_t base = (size_t)head * D;
-    const int i0 = gi * 8, i1 = half + gi * 8;
-    float a[8], b[8];
-    load8(x + base + i0, a);
-    load8(x + base + i1, b);
-    if (bias) {
+  const int n_items = heads * groups;
+  bool have_table = false;
+  __nv_bfloat16* kdst = nullptr;
+  const size_t kv_head_stride = (size_t)page_size * D;
+  // Two items a thread and round: the row's values are asked for first, the cosines and sines
+  // and the page lookup are worked out while they are on their way.
+  for (int idx0 = threadIdx.x; idx0 - (int)threadIdx.x < n_items; idx0 += 2 * blockDim.x) {
+    uint4 ra[2], rb[2];
+    int head[2], gi[2];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { a[e] += bias[base + i0 + e]; b[e] += bias[base + i1 + e]; }
-    }
-    if (!is_v) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float c = cs[i0 + e], sn = cs[half + i0 + e];
-        const float ra = a[e] * c - b[e] * sn, rb = a[e] * sn + b[e] * c;
-        a[e] = ra; b[e] = rb;
+    for (int u = 0; u < 2; ++u) {
+      const int idx = idx0 + u * blockDim.x;
+      head[u] = idx / groups;
+      gi[u] = idx - head[u] * groups;
+      if (idx < n_items) {
+        const __nv_bfloat16* src = x + (size_t)head[u] * D + gi[u] * 8;
+        ra[u] = *reinterpret_cast<const uint4*>(src);
+        rb[u] = *reinterpret_cast<const uint4*>(src + half);
       }
     }
-    __align__(16) __nv_bfloat16 oa[8], ob[8];
+    if (!have_table) {
+      const float fpos = (float)pos;
+      for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = fpos * inv_freq[i];
+        cs[i] = cosf(angle);
+        cs[half + i] = sinf(angle);
+      }
+      if (append) {
+        const int seg = row_seg[t];
+        const int lp = pos / page_size;
+        const int page = (lp >= 0 && lp < bt_width) ? block_table[(size_t)seg * bt_width + lp] : -1;
+        if (page >= 0 && page < num_pages)
+          kdst = pages + ((size_t)page * 2 * Hkv * page_size + (size_t)(pos - lp * page_size)) * D;
+      }
+      __syncthreads();
+      have_table = true;
+    }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { oa[e] = __float2bfloat16_rn(a[e]); ob[e] = __float2bfloat16_rn(b[e]); }
-    __nv_bfloat16* dst = nullptr;
-    if (is_q) dst = x + base;
-    else if (kdst) dst = kdst + ((size_t)(is_v ? Hkv : 0) + (is_v ? head - Hq - Hkv : head - Hq)) * kv_head_stride;
-    if (dst) {
-      *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(oa);
-      *reinterpret_cast<uint4*>(dst + i1) = *reinterpret_cast<const uint4*>(ob);
+    for (int u = 0; u < 2; ++u) {
+      if (idx0 + u * (int)blockDim.x >= n_items) continue;
+      const bool is_q = head[u] < Hq, is_v = head[u] >= Hq + Hkv;
+      const size_t base = (size_t)head[u] * D;
+      const int i0 = gi[u] * 8, i1 = half + gi[u] * 8;
+      float a[8], b[8];
+      unpack8(ra[u], a);
+      unpack8(rb[u], b);
+      if (bias) {
+        // 16-byte loads: one float at a time, a warp's loads of a bias touch eight lines each
+        float ba[8], bb[8];
+        load8(bias + base + i0, ba);
+        load8(bias + base + i1, bb);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { a[e] += ba[e]; b[e] += bb[e]; }
+      }
+      if (!is_v) {
+        float c[8], sn[8];
+        load8(cs + i0, c);
+        load8(cs + half + i0, sn);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xa = a[e] * c[e] - b[e] * sn[e], xb = a[e] * sn[e] + b[e] * c[e];
+          a[e] = xa; b[e] = xb;
+        }
+      }
+      __align__(16) __nv_bfloat16 oa[8], ob[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { oa[e] = __float2bfloat16_rn(a[e]); ob[e] = __float2bfloat16_rn(b[e]); }
+      __nv_bfloat16* dst = nullptr;
+      if (is_q) dst = x + base;
+      else if (kdst) dst = kdst + ((size_t)(is_v ? Hkv : 0) + (is_v ? head[u] - Hq - Hkv : head[u] - Hq)) * kv_head_stride;
+      if (dst) {
+        *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(oa);
+        *reinterpret_cast<uint4*>(dst + i1) = *reinterpret_cast<const uint4*>(ob);
+      }
     }
   }
 }
@@ -161,7 +190,8 @@ extern "C" int nf_rope_append(void* qkv, const float* bias, const int* positions
   NF_REQUIRE(D % 2 == 0, "rope_append: head_dim %d must be even", D);
   const size_t smem = (size_t)rot * sizeof(float);
   NF_REQUIRE(smem <= 48 * 1024, "rope_append: rotary width %d too large", rot);
-  if (dtype == kBF16 && rot == D && D % 16 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)pages % 16 == 0) {
+  if (dtype == kBF16 && rot == D && D % 16 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)pages % 16 == 0 &&
+      (uintptr_t)bias % 16 == 0) {
     launch_chained(rope_append_bf16x8_kernel, dim3(T), dim3(256), smem, stream, (__nv_bfloat16*)qkv, bias, positions, row_seg, inv_freq, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, append);
     return check_launch("rope_append");
   }
