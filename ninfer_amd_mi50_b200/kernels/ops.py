@@ -32,8 +32,9 @@ TUNING = {
     "bf16_moe": "auto",           # "simt" | "auto"
     "skinny_max_rows": 16,        # dense products with more rows go to the library
     # routed experts: up to this many tokens the streaming kernel serves, beyond it the
-    # tensor-core kernel (measured: equal at 16 tokens, 25 % faster at 64)
-    "skinny_moe_max_tokens": 8,
+    # tensor-core kernel (measured decode steps: 4 % slower at 16 tokens, 7 % faster at 32,
+    # 10 % faster at 64)
+    "skinny_moe_max_tokens": 16,
     # prompt portions: steps with at least this many rows use the tcgen05 attention kernel (head
     # size 64 or 128), fewer the mma.sync one; a huge number turns the tensor-core kernel off
     "prefill_attention_tc_min_rows": 128,
