@@ -25,6 +25,7 @@ from ..registry import register_part
 from .base import FeedForward, Fetch, StepContext, TensorSpec
 
 
+_FORK_LATE_ROWS = 32
 _FORK_MAX_ROWS = 64
 _SIDE_STREAMS = {}
 
@@ -154,14 +155,24 @@ class SparseMoeSwiglu(FeedForward):
         # inside a captured graph that becomes a parallel branch.
         fork = self.has_shared and x.is_cuda and x.shape[0] <= _FORK_MAX_ROWS
         shared = None
-        if fork:
+
+        def start_shared():
             main, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 kernels.chain_break()       # its input comes from the other stream
-                shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
+                return main, side, kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
+
+        # With few rows the shared expert starts beside the router (whose kernels leave the memory
+        # idle); from some tens of rows on it is better started after it, beside the experts'
+        # products (measured on decode steps: 3 % faster at 48 and 64 rows, 5 % slower at 16).
+        late = x.shape[0] > _FORK_LATE_ROWS
+        if fork and not late:
+            main, side, shared = start_shared()
         idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
                                              split=self.w_router_split)
+        if fork and late:
+            main, side, shared = start_shared()
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
         act = kernels.moe_gemm1(x, self.w13, plan, k)
