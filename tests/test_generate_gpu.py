@@ -181,8 +181,8 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     check(got[:3], want[:3], dtype, "first tokens")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_graph_replay_equals_host_driven_steps(folders, dtype):
+@pytest.mark.parametrize("dtype,count", [("float32", 11), ("bfloat16", 11), ("bfloat16", 40)])
+def test_graph_replay_equals_host_driven_steps(folders, dtype, count):
     """Decode-only steps are replayed from CUDA graphs, with padding rows when the number of
     live requests is not one a graph was built for; the logits must be those of the same
     step driven from the host."""
@@ -190,23 +190,34 @@ def test_graph_replay_equals_host_driven_steps(folders, dtype):
     d, cfg, _, _ = folders["A"]
     outs = []
     for use_graph in (False, True):
-        eng = Ninfer(d, max_context=256, prefill_chunk=32, num_sequences=12, dtype=dtype, use_graph=use_graph)
+        eng = Ninfer(d, max_context=256, prefill_chunk=32, num_sequences=count + 1, dtype=dtype, use_graph=use_graph)
         assert (eng._runner.graphs is not None) == use_graph
-        sessions = [eng.session() for _ in range(11)]
+        sessions = [eng.session() for _ in range(count)]
         for i, s in enumerate(sessions):
-            s.prefill(random_tokens(3 + 7 * i, 1024, 90 + i))
+            s.prefill(random_tokens(3 + 7 * (i % 11), 1024, 90 + i))
         logs = []
         for step in range(5):
-            live = sessions[:11 - 2 * step]            # 11, 9, 7, 5, 3 rows: padded and exact graphs
+            # 11, 9, 7, 5, 3 rows: padded and exact graphs; 40 .. 32 rows: the shared expert's
+            # branch starts after the router
+            live = sessions[:count - 2 * step]
             logs.append(torch.from_numpy(eng.decode_batch(live, [(5 * step + j) % 1024 for j in range(len(live))])))
         outs.append(logs)
         if use_graph:
-            assert sorted(k[0] for k in eng._runner.graphs.graphs) == [3, 5, 7, 16]
+            assert sorted(k[0] for k in eng._runner.graphs.graphs) == ([3, 5, 7, 16] if count == 11 else [32, 64])
         for s in sessions:
             s.close()
         eng.close()
     for a, b in zip(*outs):
-        torch.testing.assert_close(a, b, rtol=0, atol=0)
+        if count <= 16:
+            torch.testing.assert_close(a, b, rtol=0, atol=0)
+        else:
+            # the graph is built for 64 rows and the host drives 40 and fewer: the library's
+            # dense products may round differently for the two row counts, so the bound is the
+            # one of bfloat16 rounding (a wrong row, page or branch order moves a row by the scale)
+            scale = b.abs().max().item()
+            row_err = (a - b).abs().max(dim=1).values
+            assert (row_err > 1.5e-2 * scale).sum().item() <= max(1, len(row_err) // 10)
+            assert row_err.max().item() <= 0.1 * scale
 
 
 def test_capture_survives_an_older_engine_waiting_for_the_collector(folders, monkeypatch):
@@ -283,28 +294,29 @@ def test_running_ahead_changes_no_token(folders, temperature):
     assert any(len(o) < 40 for o in runs[1][1])          # some request did stop early
 
 
-@pytest.mark.parametrize("name", ["A", "C"])
-def test_a_replayed_step_gives_the_same_bits_every_time(folders, name):
+@pytest.mark.parametrize("name,rows", [("A", 3), ("C", 3), ("A", 40), ("C", 40)])
+def test_a_replayed_step_gives_the_same_bits_every_time(folders, name, rows):
     """A captured decode step, replayed on unchanged inputs, must give the same logits bit for
     bit.  With the kernels of the step launched chained (each may begin while its predecessor
     drains), the first kernel after a wait on another stream - the shared expert's branch, and
     the combine that joins it - must be an ordinary launch: chained, it began before the other
-    stream's kernel had finished, and every replay of the step differed."""
+    stream's kernel had finished, and every replay of the step differed.  With 40 rows the
+    shared expert's branch starts after the router instead of beside it."""
     from ninfer_amd_mi50_b200.config import EngineOptions
     from ninfer_amd_mi50_b200.engine import StepEntry, load_runner
     d, cfg, _, _ = folders[name]
-    runner = load_runner(d, options=EngineOptions(dtype="bfloat16", page_size=64, num_sequences=4,
-                                                   max_context=256, cache_tokens=1024))
-    for r in range(3):
+    runner = load_runner(d, options=EngineOptions(dtype="bfloat16", page_size=64, num_sequences=rows + 1,
+                                                   max_context=256, cache_tokens=256 * (rows + 1)))
+    for r in range(rows):
         runner.open(r)
-        runner.step([StepEntry(r, random_tokens(70 + 9 * r, cfg["vocab_size"], 500 + r), [])])
+        runner.step([StepEntry(r, random_tokens(70 + 9 * (r % 7), cfg["vocab_size"], 500 + r), [])])
     for s in range(2):
-        runner.step([StepEntry(r, [5 + s + r], [0]) for r in range(3)])
+        runner.step([StepEntry(r, [5 + s + r], [0]) for r in range(rows)])
     torch.cuda.synchronize()
     (graph,) = runner.graphs.graphs.values()
     graph.graph.replay()
     torch.cuda.synchronize()
     ref = graph.logits.clone()
-    for _ in range(300):
+    for _ in range(300 if rows < 8 else 100):
         graph.graph.replay()
         assert torch.equal(graph.logits, ref)
