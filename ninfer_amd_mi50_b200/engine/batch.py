@@ -41,9 +41,10 @@ def validate_entries(entries: Sequence[StepEntry], cache: CacheManager, vocab_si
             raise BatchError(f"request {e.req!r} is not open")
         if len(e.tokens) == 0:
             raise BatchError(f"request {e.req!r} brings no tokens")
-        for t in e.tokens:
-            if not 0 <= int(t) < vocab_size:
-                raise BatchError(f"request {e.req!r}: token id {t} outside [0, {vocab_size})")
+        toks = np.asarray(e.tokens, dtype=np.int64)     # one pass in numpy: a long portion has thousands
+        bad = np.flatnonzero((toks < 0) | (toks >= vocab_size))
+        if bad.size:
+            raise BatchError(f"request {e.req!r}: token id {int(toks[bad[0]])} outside [0, {vocab_size})")
         for w in e.want:
             if not 0 <= int(w) < len(e.tokens):
                 raise BatchError(f"request {e.req!r}: wanted place {w} outside its {len(e.tokens)} tokens")
