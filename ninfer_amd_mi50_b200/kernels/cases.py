@@ -2,7 +2,11 @@
 profilers and quick timing:
 
     python -m ninfer_amd_mi50_b200.kernels.cases moe_prefill
-    ncu --set full -k regex:grouped_gemm_tc -c 2 python -m ninfer_amd_mi50_b200.kernels.cases moe_prefill
+    ncu --set full --clock-control none -k regex:grouped_gemm_tc -c 2 \
+        python -m ninfer_amd_mi50_b200.kernels.cases moe_prefill
+
+(run the plain command first and profile only after it exits 0; without `--clock-control none`
+a profiler locks the clocks of a GPU that others share.)
 
 Each case warms its kernels up and then runs them a few times; with `--time` it prints the
 median time per call from CUDA events with an L2 flush between calls.  A case holds about
