@@ -1,6 +1,6 @@
 from .model_config import (ConfigError, LayerCall, LayerSpec, ModelPlan, PartSpec,
-                           Qwen2MoeConfig, read_config_json)
+                           read_config_json)
 from .engine_options import EngineOptions
 
 __all__ = ["ConfigError", "LayerCall", "LayerSpec", "ModelPlan", "PartSpec",
-           "Qwen2MoeConfig", "read_config_json", "EngineOptions"]
+           "read_config_json", "EngineOptions"]

@@ -158,7 +158,9 @@ def layer_is_sparse(cfg: dict, l: int) -> bool:
 
 
 def layer_window(cfg: dict, l: int) -> Optional[int]:
-    if cfg.get("use_sliding_window") and l >= cfg["max_window_layers"]:
+    """The window of layer l, from config.json's own per-layer list; the reference has no
+    window (src/ops/attention.hip:216 masks by `j <= p` alone)."""
+    if cfg.get("use_sliding_window") and cfg["layer_types"][l] == "sliding_attention":
         return int(cfg["sliding_window"])
     return None
 

@@ -6,7 +6,8 @@ import pytest
 
 from tiny_configs import TINY_A, TINY_B, TINY_C
 
-from ninfer_amd_mi50_b200.config import ConfigError, EngineOptions, Qwen2MoeConfig
+from ninfer_amd_mi50_b200.config import ConfigError, EngineOptions
+from ninfer_amd_mi50_b200.models.qwen2_moe import Qwen2MoeConfig
 from ninfer_amd_mi50_b200.registry import architecture_names, architecture_of, get_architecture
 
 
@@ -32,7 +33,27 @@ def test_defaults_follow_the_reference_parser():
 def test_sparse_step_and_window_rules():
     c = Qwen2MoeConfig.from_dict(TINY_C)
     assert [c.layer_is_sparse(l) for l in range(4)] == [False, True, False, True]
-    assert [c.layer_window(l) for l in range(4)] == [None, None, 40, 40]
+    assert [c.layer_window(l) for l in range(4)] == [None, 40, 40, None]
+
+
+def test_window_layers_must_be_named_layer_by_layer():
+    d = dict(TINY_C)
+    del d["layer_types"]
+    d["max_window_layers"] = 2
+    with pytest.raises(ConfigError, match="layer_types is absent"):
+        Qwen2MoeConfig.from_dict(d)                     # never a guessed rule
+    d = dict(TINY_C, layer_types=["full_attention"] * 3)
+    with pytest.raises(ConfigError, match="3 entries for 4 layers"):
+        Qwen2MoeConfig.from_dict(d)
+    d = dict(TINY_C, layer_types=["full_attention", "chunked", "full_attention", "full_attention"])
+    with pytest.raises(ConfigError, match="chunked"):
+        Qwen2MoeConfig.from_dict(d)
+    d = dict(TINY_C, use_sliding_window=False)
+    with pytest.raises(ConfigError, match="use_sliding_window is not true"):
+        Qwen2MoeConfig.from_dict(d)
+    # a list of full_attention only, as newer exports of unwindowed models carry, is fine
+    d = dict(TINY_A, layer_types=["full_attention"] * 2)
+    assert [Qwen2MoeConfig.from_dict(d).layer_window(l) for l in range(2)] == [None, None]
 
 
 def test_rope_theta_inside_rope_parameters():

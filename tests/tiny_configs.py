@@ -1,6 +1,6 @@
 """Tiny Qwen2-MoE configurations for the tests.  A and B are the two named by the build's
 baseline description; they differ in every size and option.  C adds what A and B leave
-out: a sliding window on some layers, a sparse step of two, sizes that are no power of
+out: a sliding window on some layers (said layer by layer), a sparse step of two, sizes that are no power of
 two anywhere, a head size of 48, more query heads per group."""
 
 import random
@@ -37,7 +37,8 @@ TINY_C = {
     "shared_expert_intermediate_size": 104, "norm_topk_prob": True,
     "decoder_sparse_step": 2, "mlp_only_layers": [], "vocab_size": 777,
     "rope_theta": 50000.0, "rms_norm_eps": 3e-6, "tie_word_embeddings": False,
-    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 2,
+    "use_sliding_window": True, "sliding_window": 40,
+    "layer_types": ["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
     "hidden_act": "silu", "qkv_bias": True,
 }
 
