@@ -26,6 +26,7 @@ class EngineOptions:
     max_batched_tokens: Optional[int] = None  # token budget of one step
     use_graph: bool = True           # replay decode-only steps from CUDA graphs
     run_ahead: bool = True           # launch the next decode step before reading this one's tokens
+    status_every: int = 64           # decode steps between two reads of the kernels' status flags
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

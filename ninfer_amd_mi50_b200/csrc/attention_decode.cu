@@ -14,10 +14,15 @@
 // All query heads of a group share the CTA, so keys and values are read once per kv head.
 #define NF_CHAIN_CLASS 8
 #include "common.cuh"
+#include "decode_range.cuh"
 
 namespace nf {
 
 constexpr int kSplit = 128;        // keys per CTA
+
+// 1 + a row whose position lay beyond the key blocks that a call allowed for (see decode_range.cuh);
+// read and reset by nf_decode_attention_status
+__device__ int g_decode_split_range_error = 0;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -63,7 +68,8 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
                               const int* __restrict__ positions, const int* __restrict__ row_seg,
                               float* __restrict__ ws_acc, float* __restrict__ ws_ml, int Hq, int Hkv,
                               int page_size, int num_pages, int window, float scale, int nsplit,
-                              int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+                              int* __restrict__ counters, __nv_bfloat16* __restrict__ out,
+                              const int* __restrict__ row_list) {
   constexpr int LPR = D / 8;            // 16-byte pieces of one key row
   constexpr int RPL = 32 / LPR;         // key rows a warp copies at once
   constexpr int DS = D + 8;             // shared-memory row stride: 16 bytes of padding keep
@@ -77,14 +83,16 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int RH = min(G, HC);                                        // heads kept per pass
   float* red = sc + G * kSplit;                                     // [4 warps][RH][D]
   float* ml = red + 4 * RH * D;                                     // [G][2]
-  const int t = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  // wi: the row's place in this launch (workspace, counters); t: the row itself
+  const int wi = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   chain_release();
   chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by the kernel before
-  const int pos = positions[t];
-  int lo = 0;
-  if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
+  const int t = row_list ? row_list[wi] : wi;
+  int pos = positions[t], lo;
+  if (decode_key_range(pos, lo, window, nsplit, kSplit) && kvh == 0 && split == 0 && threadIdx.x == 0)
+    atomicCAS(&g_decode_split_range_error, 0, 1 + t);
   const int k_base = split * kSplit;
   const int k_begin = max(lo, k_base);
   const int k_end = min(pos + 1, k_base + kSplit);
@@ -227,13 +235,13 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
 #pragma unroll
       for (int w = 0; w < 4; ++w) s += red[(w * RH + hh) * D + d];
       const int hq = kvh * G + h0 + hh;
-      ws_acc[(((size_t)t * Hq + hq) * nsplit + split) * D + d] = s;
+      ws_acc[(((size_t)wi * Hq + hq) * nsplit + split) * D + d] = s;
     }
     __syncthreads();
   }
   for (int h = threadIdx.x; h < G; h += blockDim.x) {
     const int hq = kvh * G + h;
-    float* o = ws_ml + (((size_t)t * Hq + hq) * nsplit + split) * 2;
+    float* o = ws_ml + (((size_t)wi * Hq + hq) * nsplit + split) * 2;
     o[0] = ml[2 * h];
     o[1] = ml[2 * h + 1];
   }
@@ -244,19 +252,19 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   __shared__ int s_last;
   __threadfence();
   __syncthreads();
-  const int s0 = lo / kSplit, s1 = min(pos / kSplit, nsplit - 1);
+  const int s0 = lo / kSplit, s1 = pos / kSplit;
   if (threadIdx.x == 0) {
-    const int prev = atomicAdd(&counters[t * Hkv + kvh], 1);
+    const int prev = atomicAdd(&counters[wi * Hkv + kvh], 1);
     s_last = prev == s1 - s0;
-    if (s_last) counters[t * Hkv + kvh] = 0;
+    if (s_last) counters[wi * Hkv + kvh] = 0;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
   for (int h = 0; h < G; ++h) {
     const int hq = kvh * G + h;
-    const float* mlp = ws_ml + ((size_t)t * Hq + hq) * nsplit * 2;
-    const float* accp = ws_acc + ((size_t)t * Hq + hq) * nsplit * D;
+    const float* mlp = ws_ml + ((size_t)wi * Hq + hq) * nsplit * 2;
+    const float* accp = ws_acc + ((size_t)wi * Hq + hq) * nsplit * D;
     float m = -INFINITY;
     for (int s = s0; s <= s1; ++s) m = fmaxf(m, __ldcg(mlp + 2 * s));
     float l = 0.f;
@@ -281,20 +289,21 @@ template <typename T>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
                                               const float* __restrict__ ws_ml,
                                               const int* __restrict__ positions, T* __restrict__ out,
-                                              int Hq, int D, int window, int nsplit, int dthreads) {
+                                              int Hq, int D, int window, int nsplit, int dthreads,
+                                              const int* __restrict__ row_list) {
   extern __shared__ float runs[];      // [runs of this row][D]
   __shared__ float wgt[kMaxMergeSplits];
   __shared__ float s_m, s_inv;
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int wi = blockIdx.x, h = blockIdx.y;
   chain_release();
   chain_wait(ws_acc, ws_ml, positions);
-  const int pos = positions[t];
-  int lo = 0;
-  if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
-  const int s0 = lo / kSplit, s1 = min(pos / kSplit, nsplit - 1);      // first and last split with keys
+  const int t = row_list ? row_list[wi] : wi;
+  int pos = positions[t], lo;
+  decode_key_range(pos, lo, window, nsplit, kSplit);
+  const int s0 = lo / kSplit, s1 = pos / kSplit;                       // first and last split with keys
   const int n = s1 - s0 + 1;
-  const float* ml = ws_ml + (((size_t)t * Hq + h) * nsplit + s0) * 2;
-  const float* acc = ws_acc + (((size_t)t * Hq + h) * nsplit + s0) * D;
+  const float* ml = ws_ml + (((size_t)wi * Hq + h) * nsplit + s0) * 2;
+  const float* acc = ws_acc + (((size_t)wi * Hq + h) * nsplit + s0) * D;
   for (int s = threadIdx.x; s < n; s += blockDim.x) wgt[s] = ml[2 * s];          // m_s for now
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -348,7 +357,7 @@ template <int D>
 static int launch_split(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                         int bt_width, const int* positions, const int* row_seg, float* ws_acc,
                         float* ws_ml, int T, int Hq, int Hkv, int page_size, int num_pages, int window,
-                        float scale, int nsplit, int* counters, void* out, cudaStream_t stream) {
+                        float scale, int nsplit, int* counters, void* out, const int* row_list, cudaStream_t stream) {
   const int G = Hq / Hkv;
   const size_t smem = (size_t)2 * kSplit * (D + 8) * sizeof(__nv_bfloat16) +
                       ((size_t)G * kSplit + 4 * (G < 8 ? G : 8) * D + 2 * G) * sizeof(float);
@@ -362,7 +371,7 @@ static int launch_split(const void* qkv, int q_row_stride, const void* pages, co
   launch_chained(decode_attention_split_kernel<D>, grid, dim3(128), smem, stream,
                  (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width,
                  positions, row_seg, ws_acc, ws_ml, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters,
-                 (__nv_bfloat16*)out);
+                 (__nv_bfloat16*)out, row_list);
   return check_launch("decode_attention_split");
 }
 
@@ -374,13 +383,24 @@ int decode_attention_stream_fits(int T, int Hq, int Hkv, int D, int page_size);
 int decode_attention_stream(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                             int bt_width, const int* positions, const int* row_seg, float* ws_acc, float* ws_ml,
                             int T, int Hq, int Hkv, int D, int page_size, int num_pages, int window, float scale,
-                            int nsplit, cudaStream_t stream);
+                            int nsplit, const int* row_list, cudaStream_t stream);
+int decode_attention_stream_status();
 int g_decode_stream = 1;
 }  // namespace nf
 
 using namespace nf;
 
 extern "C" int nf_decode_attention_split_size() { return kSplit; }
+
+// 0, or 1 + a row whose position needed more key blocks than `nsplit` gave (its result is then
+// the attention over the first nsplit * 128 keys only).  Reads and clears; synchronises.
+extern "C" int nf_decode_attention_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_decode_split_range_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_decode_split_range_error, &zero, sizeof(int));
+  const int w = decode_attention_stream_status();
+  return v ? v : w;
+}
 
 // 0: one CTA per block of keys; 1 (default): the persistent streaming kernel where it fits.
 extern "C" int nf_set_decode_stream(int on) {
@@ -394,7 +414,8 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
                                  const int* block_table, int bt_width, const int* positions,
                                  const int* row_seg, void* out, float* ws_acc, float* ws_ml, int T,
                                  int Hq, int Hkv, int D, int page_size, int num_pages, int window,
-                                 float scale, int nsplit, int* counters, cudaStream_t stream) {
+                                 float scale, int nsplit, int* counters, const int* row_list,
+                                 cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && nsplit > 0, "decode attention: bad sizes T=%d Hq=%d Hkv=%d nsplit=%d", T, Hq, Hkv, nsplit);
   NF_REQUIRE(Hkv <= 65535 && nsplit <= kMaxMergeSplits, "decode attention: too many kv heads or key blocks (context beyond %d keys)", kMaxMergeSplits * kSplit);
@@ -404,14 +425,14 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
   if (g_decode_stream && !counters && (long long)T * Hkv * nsplit >= 1024 &&
       decode_attention_stream_fits(T, Hq, Hkv, D, page_size)) {
     rc = decode_attention_stream(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml,
-                                 T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, stream);
+                                 T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, row_list, stream);
   } else
   switch (D) {
-    case 16: rc = launch_split<16>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
-    case 32: rc = launch_split<32>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
-    case 64: rc = launch_split<64>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
-    case 128: rc = launch_split<128>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
-    case 256: rc = launch_split<256>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, stream); break;
+    case 16: rc = launch_split<16>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, row_list, stream); break;
+    case 32: rc = launch_split<32>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, row_list, stream); break;
+    case 64: rc = launch_split<64>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, row_list, stream); break;
+    case 128: rc = launch_split<128>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, row_list, stream); break;
+    case 256: rc = launch_split<256>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, counters, out, row_list, stream); break;
     default:
       set_error("decode attention: head_dim %d is not one of 16, 32, 64, 128, 256", D);
       return 1;
@@ -432,7 +453,7 @@ static int decode_attention_impl(const void* qkv, int q_row_stride, const void* 
   }
   launch_chained(decode_attention_merge_kernel<__nv_bfloat16>, grid, dim3(dthreads * groups), smem, stream,
                  (const float*)ws_acc, (const float*)ws_ml, positions, (__nv_bfloat16*)out, Hq, D, window, nsplit,
-                 dthreads);
+                 dthreads, row_list);
   return check_launch("decode_attention_merge");
 }
 
@@ -442,7 +463,23 @@ extern "C" int nf_decode_attention(const void* qkv, int q_row_stride, const void
                                    int Hq, int Hkv, int D, int page_size, int num_pages, int window,
                                    float scale, int nsplit, cudaStream_t stream) {
   return decode_attention_impl(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, out, ws_acc,
-                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, nullptr, stream);
+                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, nullptr, nullptr,
+                               stream);
+}
+
+// The same for some rows of a step: `row_list` (int32 [T] on the device) names the rows of qkv,
+// positions, row_seg and out that this call serves; the workspace is indexed by the place in
+// the list.  A step that mixes prompt portions and single decoded tokens sends the latter here.
+extern "C" int nf_decode_attention_rows(const void* qkv, int q_row_stride, const void* pages,
+                                        const int* block_table, int bt_width, const int* positions,
+                                        const int* row_seg, void* out, float* ws_acc, float* ws_ml,
+                                        const int* row_list, int T, int Hq, int Hkv, int D, int page_size,
+                                        int num_pages, int window, float scale, int nsplit,
+                                        cudaStream_t stream) {
+  NF_REQUIRE(row_list, "decode attention: the form for some rows needs its row list");
+  return decode_attention_impl(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, out, ws_acc,
+                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, nullptr, row_list,
+                               stream);
 }
 
 // The same in one launch: `counters` are T * Hkv ints that are zero before the call and are left
@@ -455,7 +492,8 @@ extern "C" int nf_decode_attention_fused(const void* qkv, int q_row_stride, cons
                                          cudaStream_t stream) {
   NF_REQUIRE(counters, "decode attention: the one-launch form needs its counters");
   return decode_attention_impl(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, out, ws_acc,
-                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, counters, stream);
+                               ws_ml, T, Hq, Hkv, D, page_size, num_pages, window, scale, nsplit, counters, nullptr,
+                               stream);
 }
 
 // ---- the entry point that allocates nothing ---------------------------------------------------

@@ -27,6 +27,7 @@
 // depend on what else is in the batch.
 #define NF_CHAIN_CLASS 8
 #include "common.cuh"
+#include "decode_range.cuh"
 
 namespace nf {
 
@@ -37,6 +38,11 @@ constexpr int kTile = 16;             // keys per ring stage
 constexpr int kWorkers = 8;           // warps per CTA
 constexpr int kMaxRows = 1024;        // rows one launch may have (their block counts live in shared memory)
 constexpr int kRingBytes = 24 * 1024; // per warp
+
+// A row whose position needs more key blocks than the caller's `nsplit` has its blocks beyond
+// nsplit - 1 left out (nothing is written outside the workspace) and 1 + row recorded here;
+// read and reset by nf_decode_attention_status.
+__device__ int g_decode_range_error = 0;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
@@ -71,7 +77,8 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
                                const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_table,
                                int bt_width, const int* __restrict__ positions, const int* __restrict__ row_seg,
                                float* __restrict__ ws_acc, float* __restrict__ ws_ml, int T, int Hq, int Hkv,
-                               int page_size, int num_pages, int window, float scale, int nsplit) {
+                               int page_size, int num_pages, int window, float scale, int nsplit,
+                               const int* __restrict__ row_list) {
   constexpr int PIECES = D / 8;                    // 16-byte pieces of a key row
   constexpr int TILE_BYTES = kTile * D * 2;        // keys (or values) of one tile
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -88,9 +95,13 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
   chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by kernels before
 
   // ---- every CTA lists the rows' blocks: row t has blocks s_first[t] .. of its key range -------
+  // Rows are counted by their place in this launch (0 .. T - 1: shared-memory lists, workspace);
+  // `row_of` gives the row itself (queries, positions, segments).
+  auto row_of = [&](int i) { return row_list ? row_list[i] : i; };
   for (int t = threadIdx.x; t < T; t += blockDim.x) {
-    const int pos = positions[t];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int pos = positions[row_of(t)], lo;
+    if (decode_key_range(pos, lo, window, nsplit, kBlockKeys) && blockIdx.x == 0)
+      atomicCAS(&g_decode_range_error, 0, 1 + t);  // the workspace has no slot for the row's last blocks
     s_first[t] = lo / kBlockKeys;
     s_cum[t + 1] = pos / kBlockKeys - lo / kBlockKeys + 1;
   }
@@ -125,15 +136,16 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
       if (s_cum[mid] <= rc) lo_t = mid; else hi_t = mid;
     }
     p_t = lo_t;
-    const int pos = positions[p_t];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int p_row = row_of(p_t);
+    int pos = positions[p_row], lo;
+    decode_key_range(pos, lo, window, nsplit, kBlockKeys);
     const int split = s_first[p_t] + (rc - s_cum[p_t]);
     p_kbase = split * kBlockKeys;
     p_kb = max(lo, p_kbase);
     p_ke = min(pos + 1, p_kbase + kBlockKeys);
     p_tile = (p_kb - p_kbase) / kTile;
     p_tile_end = (p_ke - 1 - p_kbase) / kTile + 1;
-    p_bt = block_table + (size_t)row_seg[p_t] * bt_width;
+    p_bt = block_table + (size_t)row_seg[p_row] * bt_width;
   };
   int issued = 0;                        // tiles asked for so far (ring position)
   auto produce = [&]() {                 // ask for the next tile, or commit an empty group at the end
@@ -181,9 +193,9 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
       const int mid = (lo_t + hi_t) >> 1;
       if (s_cum[mid] <= rc) lo_t = mid; else hi_t = mid;
     }
-    const int t = lo_t;
-    const int pos = positions[t];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int t = lo_t, q_row = row_of(lo_t);
+    int pos = positions[q_row], lo;
+    decode_key_range(pos, lo, window, nsplit, kBlockKeys);
     const int split = s_first[t] + (rc - s_cum[t]);
     const int k_base = split * kBlockKeys;
     const int k_begin = max(lo, k_base), k_end = min(pos + 1, k_base + kBlockKeys);
@@ -192,7 +204,7 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
     // query heads of the group as the rows of the A operand: row g and row g + 8
     unsigned qa[D / 16][4];
     {
-      const __nv_bfloat16* q0 = qkv + (size_t)t * q_row_stride + (size_t)(kvh * G + g) * D;
+      const __nv_bfloat16* q0 = qkv + (size_t)q_row * q_row_stride + (size_t)(kvh * G + g) * D;
       const __nv_bfloat16* q1 = q0 + 8 * D;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
@@ -308,7 +320,8 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
 template <int D>
 int launch_stream(const void* qkv, int q_row_stride, const void* pages, const int* block_table, int bt_width,
                   const int* positions, const int* row_seg, float* ws_acc, float* ws_ml, int T, int Hq, int Hkv,
-                  int page_size, int num_pages, int window, float scale, int nsplit, cudaStream_t stream) {
+                  int page_size, int num_pages, int window, float scale, int nsplit, const int* row_list,
+                  cudaStream_t stream) {
   constexpr int STAGE_BYTES = 2 * kTile * D * 2;
   constexpr int NS = kRingBytes / STAGE_BYTES < 8 ? kRingBytes / STAGE_BYTES : 8;
   const size_t smem = (size_t)kWorkers * NS * STAGE_BYTES + (size_t)(2 * T + 1) * sizeof(int);
@@ -333,11 +346,20 @@ int launch_stream(const void* qkv, int q_row_stride, const void* pages, const in
   const int grid = (int)(most_blocks < n_sm ? most_blocks : n_sm);
   launch_chained(decode_attention_stream_kernel<D>, dim3(grid), dim3(kWorkers * 32), smem, stream,
                  (const __nv_bfloat16*)qkv, q_row_stride, (const __nv_bfloat16*)pages, block_table, bt_width,
-                 positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit);
+                 positions, row_seg, ws_acc, ws_ml, T, Hq, Hkv, page_size, num_pages, window, scale, nsplit, row_list);
   return check_launch("decode_attention_stream");
 }
 
 }  // namespace
+
+// 0, or 1 + the first row whose position lay beyond the key blocks that the call allowed for since
+// the last call of this function (synchronises the device).
+int decode_attention_stream_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_decode_range_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_decode_range_error, &zero, sizeof(int));
+  return v;
+}
 
 // 1 if the streaming kernel takes these sizes (the caller then runs the merge kernel after it).
 int decode_attention_stream_fits(int T, int Hq, int Hkv, int D, int page_size) {
@@ -347,12 +369,12 @@ int decode_attention_stream_fits(int T, int Hq, int Hkv, int D, int page_size) {
 int decode_attention_stream(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                             int bt_width, const int* positions, const int* row_seg, float* ws_acc, float* ws_ml,
                             int T, int Hq, int Hkv, int D, int page_size, int num_pages, int window, float scale,
-                            int nsplit, cudaStream_t stream) {
+                            int nsplit, const int* row_list, cudaStream_t stream) {
   if (D == 64)
     return launch_stream<64>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T,
-                             Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream);
+                             Hq, Hkv, page_size, num_pages, window, scale, nsplit, row_list, stream);
   return launch_stream<128>(qkv, q_row_stride, pages, block_table, bt_width, positions, row_seg, ws_acc, ws_ml, T,
-                            Hq, Hkv, page_size, num_pages, window, scale, nsplit, stream);
+                            Hq, Hkv, page_size, num_pages, window, scale, nsplit, row_list, stream);
 }
 
 }  // namespace nf

@@ -329,6 +329,26 @@ extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const voi
   return launch_tc<false>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
 }
 
+// A wait that nothing will ever satisfy, given `polls` polls: the bounded wait runs out, records
+// code 9 and the kernel returns; the context stays usable.  It shows (to tests) that a wait
+// which gives up reaches the host as a status, the way the kernels above report theirs.
+__global__ void bounded_wait_selftest_kernel(unsigned polls) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int stop;
+  if (threadIdx.x == 0) {
+    stop = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(&bar, 0, &stop, 9, &g_tc_error, polls);
+  }
+}
+
+extern "C" int nf_bounded_wait_selftest(int polls, cudaStream_t stream) {
+  NF_REQUIRE(polls > 0 && polls <= (1 << 20), "bounded wait self-test: polls=%d must lie in [1, 2^20]", polls);
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>((unsigned)polls);
+  return check_launch("bounded_wait_selftest");
+}
+
 // 0 if no tensor-core kernel has given up on a wait since the last call; else the code of the
 // first wait that did (1 producer, 2 accumulator hand-back, 3 operands, 4 epilogue).  Synchronises.
 extern "C" int nf_grouped_gemm_tc_status() {

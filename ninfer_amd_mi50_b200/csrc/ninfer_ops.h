@@ -12,7 +12,13 @@ extern "C" {
 const char* nf_last_error(void);
 
 /* Decode attention (one query row per request, bfloat16, paged cache) with caller-provided
- * scratch: ws_acc float32 [T, Hq, nsplit, D], ws_ml float32 [T, Hq, nsplit, 2]. */
+ * scratch: ws_acc float32 [T, Hq, nsplit, D], ws_ml float32 [T, Hq, nsplit, 2].
+ *
+ * nsplit is the number of blocks of 128 keys the scratch has room for per row and head; it
+ * must be at least ceil((largest position + 1) / 128) over the rows of the call.  Positions
+ * live on the device, so the host cannot check this: a row that needs more blocks is
+ * computed over its first nsplit * 128 keys only, nothing is written outside the scratch,
+ * and nf_decode_attention_status() reports 1 + that row afterwards. */
 int nf_decode_attention(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                         int bt_width, const int* positions, const int* row_seg, void* out,
                         float* ws_acc, float* ws_ml, int T, int Hq, int Hkv, int D, int page_size,
@@ -34,6 +40,8 @@ int nf_decode_attention(const void* qkv, int q_row_stride, const void* pages, co
  * Limits and rules:
  *   - T * Hq * nsplit * (D + 2) * 4 bytes must fit the fixed array; larger calls are
  *     refused with an error, nothing is launched.
+ *   - nsplit follows the rule given at nf_decode_attention: at least
+ *     ceil((largest position + 1) / 128) over the rows of the call.
  *   - The first call on each device looks up the array's device address.  Make that first
  *     call with the device current and before any stream capture begins.
  *   - No cudaMalloc, cudaFree or allocating library routine is called, on any call.
@@ -45,6 +53,10 @@ int nf_decode_attention_static(const void* qkv, int q_row_stride, const void* pa
                                const int* row_seg, void* out, int T, int Hq, int Hkv, int D,
                                int page_size, int num_pages, int window, float scale, int nsplit,
                                cudaStream_t stream);
+
+/* 0, or 1 + the first row whose position needed more key blocks than a call's nsplit gave,
+ * since the last call of this function.  Reads and clears; synchronises the device. */
+int nf_decode_attention_status(void);
 
 /* Size of the fixed scratch array in bytes. */
 long long nf_decode_attention_static_scratch_bytes(void);

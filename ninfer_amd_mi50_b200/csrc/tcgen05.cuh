@@ -32,8 +32,9 @@ __device__ __forceinline__ bool mbar_try(void* bar, unsigned parity) {
 // Bounded wait.  Returns false if this wait ran out of polls or another role gave up (`stop`,
 // an int in shared memory); the first wait to run out records `code` in `*err` (a __device__ int
 // of the kernel's translation unit that the host reads afterwards).
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, volatile int* stop, int code, int* err) {
-  for (unsigned i = 0; i < kPollLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, volatile int* stop, int code, int* err,
+                                          unsigned polls = kPollLimit) {
+  for (unsigned i = 0; i < polls; ++i) {
     if (mbar_try(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *stop) return false;
   }

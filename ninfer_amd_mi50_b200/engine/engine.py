@@ -38,6 +38,7 @@ class Engine:
         self._copy_stream = None
         self._landing = [None, None]     # pinned buffers the drawn tokens land in, used in turn
         self._landing_turn = 0
+        self._steps_since_check = 0
 
     # ---- requests ---------------------------------------------------------------------
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -88,7 +89,23 @@ class Engine:
                 self._ahead = self._launch_ahead(batch, picked)
             tokens = self._finish_readback(landing)
             self.d2h_bytes += picked.numel() * 4
+        self._check_kernels(batch)
         return done + self.scheduler.update(batch, tokens)
+
+    def _check_kernels(self, batch) -> None:
+        """Read the kernels' status flags (a bounded wait that ran out, an index outside its
+        operands) and raise instead of handing on what such a step produced.  The read
+        synchronises the device, so steps with prompt portions (the tensor-core kernels run there
+        and the host has just waited for the step anyway) are checked at once, pure decode steps
+        every `status_every` steps."""
+        if self.runner.device.type != "cuda":
+            return
+        self._steps_since_check += 1
+        prompt_rows = any(len(s.tokens) > 1 for s in batch)
+        if prompt_rows or self._steps_since_check >= max(1, self.options.status_every):
+            self._steps_since_check = 0
+            from .. import kernels
+            kernels.check_status("engine step")
 
     # The drawn tokens come to the host on a stream of their own, into pinned memory: a copy
     # on the compute stream would queue behind the step that has just been launched ahead, and

@@ -49,8 +49,14 @@ class DecodeGraph:
         sizes = [S, S, S, S + 1, S, S, S] + [S * self.width for _ in cache.groups]
         self.offsets = np.cumsum([0] + sizes)
         total = int(self.offsets[-1])
-        self.host = torch.empty((total,), dtype=torch.int32).pin_memory()
-        self.np = self.host.numpy()
+        # Two pinned staging buffers used in turn, each with the event of its last copy: the host
+        # runs a step ahead of the device on purpose, so the copy out of a buffer may still be
+        # queued when the next step is being prepared; a buffer is rewritten only after its own
+        # last copy has finished.
+        self.hosts = [torch.empty((total,), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.nps = [h.numpy() for h in self.hosts]
+        self.copied: List[Optional[torch.cuda.Event]] = [None, None]
+        self.turn = 0
         self.dev = torch.zeros((total,), dtype=torch.int32, device=dev)
         parts = [self.dev[self.offsets[i]:self.offsets[i + 1]] for i in range(len(sizes))]
         self.ctx = StepContext(
@@ -62,11 +68,12 @@ class DecodeGraph:
             self.ctx.block_tables[g.index] = parts[7 + gi].view(S, self.width)
         # the parts of the buffer that never change
         o = self.offsets
-        self.np[o[2]:o[3]] = np.arange(S)
-        self.np[o[3]:o[4]] = np.arange(S + 1)
-        self.np[o[6]:o[7]] = np.arange(S)
-        self._fill([], [])
-        self.dev.copy_(self.host)
+        for a in self.nps:
+            a[o[2]:o[3]] = np.arange(S)
+            a[o[3]:o[4]] = np.arange(S + 1)
+            a[o[6]:o[7]] = np.arange(S)
+            self._fill(a, [], [])
+        self.dev.copy_(self.hosts[0])
         # warm up on a side stream (library handles, lazily set kernel attributes), then capture
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -92,8 +99,8 @@ class DecodeGraph:
         self.kernels = klib.launch_count() - before
         self.h2d_bytes = total * 4
 
-    def _fill(self, entries: Sequence[StepEntry], lengths: Sequence[int]) -> None:
-        cache, o, a, S = self.runner.cache, self.offsets, self.np, self.S
+    def _fill(self, a: np.ndarray, entries: Sequence[StepEntry], lengths: Sequence[int]) -> None:
+        cache, o, S = self.runner.cache, self.offsets, self.S
         n = len(entries)
         a[o[0]:o[0] + n] = [int(e.tokens[0]) for e in entries]
         a[o[0] + n:o[1]] = 0
@@ -118,8 +125,15 @@ class DecodeGraph:
         device) replace the entries' token ids: the tokens a step before has just drawn, which
         the host has not read yet."""
         lengths = [self.runner.cache.length(e.req) for e in entries]
-        self._fill(entries, lengths)
-        self.dev.copy_(self.host, non_blocking=True)
+        i = self.turn & 1
+        self.turn += 1
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()        # the copy that last read this buffer is done
+        self._fill(self.nps[i], entries, lengths)
+        self.dev.copy_(self.hosts[i], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(torch.cuda.current_stream(self.dev.device))
+        self.copied[i] = done
         if device_tokens is not None:
             self.dev[self.offsets[0]:self.offsets[0] + len(entries)].copy_(device_tokens)
         self.graph.replay()

@@ -40,6 +40,7 @@ def load_runner(model_dir: Optional[str] = None, *, config: Optional[Dict[str, A
             raise ValueError("give a model folder or a configuration")
         config = read_config_json(model_dir)
     typed, model = build_model(config)
+    model.check_limits(dtype, options.max_context, options.page_size)
     if random_seed is not None:
         source = RandomSource(model.tensor_specs(), random_seed,
                               gen_device=device if device.type == "cuda" else "cpu")

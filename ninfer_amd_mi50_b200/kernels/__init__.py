@@ -6,4 +6,4 @@ build or load anything; the first kernel call does.
 
 from .lib import KernelError, is_loaded, load
 from .ops import *  # noqa: F401,F403
-from .ops import MoePlan, PackedWeights, TUNING, check_head_dim, check_router_sizes, index_status, tensor_core_status
+from .ops import MoePlan, PackedWeights, TUNING, check_attention_limits, check_head_dim, check_router_sizes, check_status, index_status, tensor_core_status

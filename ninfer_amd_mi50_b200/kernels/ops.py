@@ -64,6 +64,21 @@ def check_head_dim(head_dim: int) -> None:
                          f"(multiples of 16 from 16 to 256)")
 
 
+DECODE_MAX_SPLITS = 1024                    # key blocks one row's merge takes
+
+
+def check_attention_limits(dtype: torch.dtype, head_dim: int, max_context: int, page_size: int) -> None:
+    """What the attention kernels cannot serve, said at start-up: the bfloat16 decode kernels
+    merge at most `DECODE_MAX_SPLITS` blocks of `DECODE_SPLIT` keys per row."""
+    check_head_dim(head_dim)
+    if dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS:
+        most = DECODE_MAX_SPLITS * DECODE_SPLIT
+        if max_context > most:
+            raise ValueError(f"max_context={max_context} is beyond the {most} keys a request may hold "
+                             f"in bfloat16 mode (decode attention merges at most {DECODE_MAX_SPLITS} "
+                             f"blocks of {DECODE_SPLIT} keys)")
+
+
 def check_router_sizes(num_experts: int, top_k: int) -> None:
     if not 1 <= num_experts <= MAX_EXPERTS:
         raise ValueError(f"num_experts={num_experts} is not supported (1..{MAX_EXPERTS})")
@@ -242,10 +257,29 @@ def tensor_core_status() -> int:
 def index_status() -> int:
     """0, or what a kernel that follows device-side indices found outside its operands since the
     last call (it skips such an access): 201-203 the streaming product (group, row range, row
-    index), 300 + token + 1 the combine.  Synchronises the device."""
+    index), 300 + token + 1 the combine, 100000 + row + 1 a decode-attention row whose position
+    lay beyond the key blocks its call allowed for.  Synchronises the device."""
     lib = _lib.load()
     sk, cb = int(lib.nf_skinny_index_status()), int(lib.nf_combine_index_status())
-    return 200 + sk if sk else (300 + cb if cb else 0)
+    da = int(lib.nf_decode_attention_status())
+    return 200 + sk if sk else (300 + cb if cb else (100000 + da if da else 0))
+
+
+def check_status(where: str = "") -> None:
+    """Raise `KernelError` if a kernel gave up on a bounded wait or skipped an access outside
+    its operands since the last check: its output is then not to be used.  Synchronises the
+    device, so it is called where the host waits anyway (after a step's logits or tokens have
+    been read) and every so many decode steps."""
+    tc = tensor_core_status()
+    ix = index_status()
+    if tc or ix:
+        what = []
+        if tc:
+            what.append(f"a tensor-core kernel gave up on a wait (code {tc})")
+        if ix:
+            what.append(f"a kernel met an index outside its operands (code {ix})")
+        raise _lib.KernelError((where + ": " if where else "") + "; ".join(what)
+                               + "; the results of the steps since the last check are invalid")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -363,50 +397,75 @@ def _zeroed_counters(device, n: int) -> torch.Tensor:
     return bufs[-1]
 
 
+def _tiles(ctx, rows_per_tile, window, keys_per_block, pair, min_rows):
+    if min_rows > 1:
+        return ctx.paired_query_tiles(rows_per_tile, window, keys_per_block, pair=pair, min_rows=min_rows)
+    return ctx.paired_query_tiles(rows_per_tile, window, keys_per_block, pair=pair)
+
+
+def _decode_attention(qkv, Hq, Hkv, D, pages, block_table, page_size, ctx, window, scale, out,
+                      rows: Optional[torch.Tensor], n: int) -> None:
+    """The split-key decode kernels on all rows of the step (`rows` None) or on the `n` rows
+    listed in `rows` (int32 on the device); writes those rows of `out`."""
+    nsplit = max(1, (int(ctx.max_context) + DECODE_SPLIT - 1) // DECODE_SPLIT)
+    ws_acc = torch.empty((n, Hq, nsplit, D), dtype=torch.float32, device=qkv.device)
+    ws_ml = torch.empty((n, Hq, nsplit, 2), dtype=torch.float32, device=qkv.device)
+    if rows is not None:
+        _lib.call("nf_decode_attention_rows", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+                  c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
+                  _p(ws_acc), _p(ws_ml), _p(rows), c_int(n), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                  c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
+    elif n > TUNING["decode_merge_fused_max_rows"]:
+        _lib.call("nf_decode_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+                  c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
+                  _p(ws_acc), _p(ws_ml), c_int(n), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
+                  c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
+    else:
+        counters = _zeroed_counters(qkv.device, n * Hkv)
+        _lib.call("nf_decode_attention_fused", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
+                  c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
+                  _p(ws_acc), _p(ws_ml), _p(counters), c_int(n), c_int(Hq), c_int(Hkv), c_int(D),
+                  c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit),
+                  _stream())
+
+
 def paged_attention(qkv: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.Tensor,
                     block_table: torch.Tensor, page_size: int, ctx, window: int, scale: float
                     ) -> torch.Tensor:
     """Causal attention of the rows' (rotated) queries in `qkv` over the cache -> [T, Hq*D].
 
-    bfloat16 steps in which every request brings one row use the split-key decode kernel;
-    everything else uses the kernel that takes any mix of rows."""
+    In bfloat16 a row is served according to its own segment: a segment of one row (a decoded
+    token) by the split-key decode kernel, a segment of several rows (a prompt portion) by a
+    flash kernel - whatever else the step holds.  A mixed step is therefore two launches."""
     _chk(qkv, "qkv"); _chk(pages, "pages", qkv.dtype)
     T = qkv.shape[0]
     out = torch.empty((T, Hq * D), dtype=qkv.dtype, device=qkv.device)
     if T == 0:
         return out
-    if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
-            and getattr(ctx, "all_single", False) and D in DECODE_HEAD_DIMS):
-        nsplit = max(1, (int(ctx.max_context) + DECODE_SPLIT - 1) // DECODE_SPLIT)
-        ws_acc = torch.empty((T, Hq, nsplit, D), dtype=torch.float32, device=qkv.device)
-        ws_ml = torch.empty((T, Hq, nsplit, 2), dtype=torch.float32, device=qkv.device)
-        if T > TUNING["decode_merge_fused_max_rows"]:
-            _lib.call("nf_decode_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
-                      c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
-                      _p(ws_acc), _p(ws_ml), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
-                      c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit), _stream())
-            return out
-        counters = _zeroed_counters(qkv.device, T * Hkv)
-        _lib.call("nf_decode_attention_fused", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
-                  c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.row_seg), _p(out),
-                  _p(ws_acc), _p(ws_ml), _p(counters), c_int(T), c_int(Hq), c_int(Hkv), c_int(D),
-                  c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(nsplit),
-                  _stream())
+    fast = qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
+    if fast and getattr(ctx, "all_single", False) and D in DECODE_HEAD_DIMS:
+        _decode_attention(qkv, Hq, Hkv, D, pages, block_table, page_size, ctx, window, scale, out, None, T)
         return out
-    if (qkv.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic"
-            and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
+    if (fast and D in PREFILL_HEAD_DIMS and getattr(ctx, "seg_len_host", None) is not None
             and getattr(ctx, "seg_pos0_host", None) is not None and qkv.shape[1] % 8 == 0):
+        min_rows = 1
+        if D in DECODE_HEAD_DIMS and hasattr(ctx, "single_rows"):
+            rows, n_single = ctx.single_rows()
+            if n_single:
+                _decode_attention(qkv, Hq, Hkv, D, pages, block_table, page_size, ctx, window, scale, out,
+                                  rows, n_single)
+                min_rows = 2
         if (T >= TUNING["prefill_attention_tc_min_rows"] and qkv.is_contiguous() and pages.is_contiguous()
                 and _lib.load().nf_prefill_attention_tc_fits(c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
                                                             c_longlong(pages.shape[0]))):
             # tcgen05 / TMEM / TMA: tiles of 128 rows, blocks of 128 keys
-            tiles, n_tiles = ctx.paired_query_tiles(128, window, 128, pair=False)
+            tiles, n_tiles = _tiles(ctx, 128, window, 128, False, min_rows)
             _lib.call("nf_prefill_attention_tc", _p(qkv), c_longlong(T), c_int(qkv.shape[1]), _p(pages),
                       _p(block_table), c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0),
                       _p(tiles), c_int(n_tiles), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),
                       c_int(pages.shape[0]), c_int(window), c_float(scale), _stream())
             return out
-        tiles, n_tiles = ctx.paired_query_tiles(PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK)
+        tiles, n_tiles = _tiles(ctx, PREFILL_TILE_ROWS, window, PREFILL_KEY_BLOCK, True, min_rows)
         _lib.call("nf_prefill_attention", _p(qkv), c_int(qkv.shape[1]), _p(pages), _p(block_table),
                   c_int(block_table.shape[1]), _p(ctx.positions), _p(ctx.seg_row0), _p(tiles),
                   c_int(n_tiles), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page_size),

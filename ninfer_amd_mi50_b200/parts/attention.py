@@ -71,6 +71,9 @@ class PagedGqaAttention(Mixer):
         kind = "window" if self.window else "full"
         return CacheSpec(kind, self.num_kv_heads, self.head_dim, self.window)
 
+    def check_limits(self, dtype: torch.dtype, max_context: int, page_size: int) -> None:
+        kernels.check_attention_limits(dtype, self.head_dim, max_context, page_size)
+
     # ---- forward ----------------------------------------------------------------------
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[CacheView],
                 state: Optional[torch.Tensor]) -> torch.Tensor:

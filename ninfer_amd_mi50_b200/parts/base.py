@@ -142,15 +142,34 @@ class StepContext:
         return t, n_tiles
 
 
+    def single_rows(self) -> Tuple[Optional[torch.Tensor], int]:
+        """Rows of the segments that bring exactly one row (decoded tokens, or a prompt's last
+        token arriving alone), as (int32 tensor on the device, count); (None, 0) if there are
+        none.  Attention serves such a row with its split-key kernel whatever else the step
+        holds.  Built on the host; not available in graph mode."""
+        if "single" in self._tiles:
+            return self._tiles["single"]
+        if self.seg_len_host is None:
+            raise RuntimeError("single_rows needs host segment lengths (not in graph mode)")
+        rows, row = [], 0
+        for n in self.seg_len_host:
+            if n == 1:
+                rows.append(row)
+            row += n
+        out = (torch.tensor(rows, dtype=torch.int32).to(self.device), len(rows)) if rows else (None, 0)
+        self._tiles["single"] = out
+        return out
+
     def paired_query_tiles(self, rows_per_tile: int, window: int, keys_per_block: int,
-                           pair: bool = True) -> Tuple[torch.Tensor, int]:
+                           pair: bool = True, min_rows: int = 1) -> Tuple[torch.Tensor, int]:
         """Query tiles two to a CTA, a heavy one with a light one.
 
         A tile late in a long prompt reads many more keys than an early one; giving each CTA
         the i-th heaviest and the i-th lightest tile makes CTAs about equally long.  Returns
         (int32 [n_pairs, 2, 2] of (segment, first row), second entry (-1, -1) if there is
-        none; n_pairs).  With `pair` false every CTA gets one tile, heaviest first."""
-        key = ("pairs", rows_per_tile, window, keys_per_block, pair)
+        none; n_pairs).  With `pair` false every CTA gets one tile, heaviest first.  Segments
+        with fewer than `min_rows` rows are left out (they are served elsewhere)."""
+        key = ("pairs", rows_per_tile, window, keys_per_block, pair, min_rows)
         if key in self._tiles:
             return self._tiles[key]
         if self.seg_len_host is None or self.seg_pos0_host is None:
@@ -158,7 +177,7 @@ class StepContext:
         tiles = []
         row = 0
         for s, (n, pos0) in enumerate(zip(self.seg_len_host, self.seg_pos0_host)):
-            for r in range(0, n, rows_per_tile):
+            for r in range(0, n if n >= min_rows else 0, rows_per_tile):
                 first = pos0 + r
                 last = pos0 + min(r + rows_per_tile, n) - 1
                 lo = max(0, first - window + 1) if window > 0 else 0
@@ -203,6 +222,10 @@ class Part:
     def weight_bytes(self) -> int:
         """Bytes of weights one forward call reads when every row uses everything."""
         return 0
+
+    def check_limits(self, dtype: torch.dtype, max_context: int, page_size: int) -> None:
+        """Raise ValueError if this part's kernels cannot serve the engine's options.  Called
+        once at start-up, so that a limit is met there and not in the middle of a request."""
 
 
 class Norm(Part):

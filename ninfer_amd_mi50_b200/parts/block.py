@@ -39,6 +39,10 @@ class PreNormBlock(Block):
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts())
 
+    def check_limits(self, dtype, max_context, page_size) -> None:
+        for p in self.parts():
+            p.check_limits(dtype, max_context, page_size)
+
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: Optional[CacheView], state: Optional[torch.Tensor]
                 ) -> Optional[torch.Tensor]:

@@ -68,6 +68,11 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
 
+    def check_limits(self, dtype: torch.dtype, max_context: int, page_size: int) -> None:
+        for b in self.blocks:
+            b.check_limits(dtype, max_context, page_size)
+        self.final_norm.check_limits(dtype, max_context, page_size)
+
     def weight_bytes(self) -> int:
         n = sum(b.weight_bytes() for b in self.blocks) + self.final_norm.weight_bytes()
         return n + self.head.numel() * self.head.element_size()

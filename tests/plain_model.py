@@ -107,40 +107,60 @@ def plain_swiglu_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
     return (plain_silu(x @ w_gate.T) * (x @ w_up.T)) @ w_down.T
 
 
-def plain_router(x: torch.Tensor, w_router: torch.Tensor, k: int, norm_topk: bool):
+def plain_router(x: torch.Tensor, w_router: torch.Tensor, k: int, norm_topk: bool,
+                 forced_idx: Optional[torch.Tensor] = None):
     """Logits, softmax over all experts with the maximum subtracted, the k largest in
     descending order (src/ops/moe.hip:63-76; ties to the lower index here), weights
     p_e / sum(selected) when norm_topk (moe.hip:77-82, the only form the reference has)
-    or p_e unchanged (Qwen2-MoE's norm_topk_prob=false)."""
+    or p_e unchanged (Qwen2-MoE's norm_topk_prob=false).
+
+    `forced_idx` [T, k] replaces the selection (not the probabilities): the comparison with
+    a reduced-precision engine uses the engine's own choice, so that a near-tie decided the
+    other way does not count as an error.  Returns (idx, weights, probabilities)."""
     logits = x @ w_router.T
     p = torch.softmax(logits, dim=-1)
     T, E = p.shape
     idx = torch.zeros(T, k, dtype=torch.long)
     wts = torch.zeros(T, k, dtype=x.dtype)
     for t in range(T):
-        order = sorted(range(E), key=lambda e: (-float(p[t, e]), e))[:k]
+        if forced_idx is not None:
+            order = [int(e) for e in forced_idx[t]]
+        else:
+            order = sorted(range(E), key=lambda e: (-float(p[t, e]), e))[:k]
         idx[t] = torch.tensor(order)
         wts[t] = p[t, order]
     if norm_topk:
         wts = wts / wts.sum(dim=-1, keepdim=True)
-    return idx, wts
+    return idx, wts, p
 
 
-def plain_sparse_ffn(x: torch.Tensor, weights: Dict[str, torch.Tensor], prefix: str, cfg: dict
+def plain_sparse_ffn(x: torch.Tensor, weights, prefix: str, cfg: dict,
+                     forced_idx: Optional[torch.Tensor] = None, slack: Optional[list] = None
                      ) -> torch.Tensor:
     """Routed experts summed in selection order with their routing weights
     (src/models/model.hip:355-433), plus the shared expert scaled by the sigmoid of its
-    gate logit (Qwen2-MoE; absent from the reference)."""
+    gate logit (Qwen2-MoE; absent from the reference).
+
+    With `forced_idx`, `slack` (a list) receives for every row how far the forced choice
+    falls short of the best one: (k-th largest probability - smallest forced probability)
+    / k-th largest, 0 when the choice is the plain one."""
     E, k = cfg["num_experts"], cfg["num_experts_per_tok"]
-    idx, wts = plain_router(x, weights[prefix + "gate.weight"], k, bool(cfg.get("norm_topk_prob", False)))
+    idx, wts, prob = plain_router(x, weights[prefix + "gate.weight"], k,
+                                  bool(cfg.get("norm_topk_prob", False)), forced_idx)
+    if forced_idx is not None and slack is not None:
+        kth = torch.topk(prob, k, dim=-1).values[:, -1]
+        worst = torch.gather(prob, 1, idx).min(dim=-1).values
+        slack.append(((kth - worst) / kth).clamp_min(0))
     out = torch.zeros_like(x)
-    for t in range(x.shape[0]):
-        for j in range(k):
-            e = int(idx[t, j])
+    # selection place by selection place, so that a row's sum runs in selection order; the
+    # rows that chose the same expert at the same place share one pass over its matrices
+    for j in range(k):
+        for e in sorted(set(int(v) for v in idx[:, j])):
+            rows = torch.nonzero(idx[:, j] == e).flatten()
             q = f"{prefix}experts.{e}."
-            y = plain_swiglu_mlp(x[t:t + 1], weights[q + "gate_proj.weight"],
+            y = plain_swiglu_mlp(x[rows], weights[q + "gate_proj.weight"],
                                  weights[q + "up_proj.weight"], weights[q + "down_proj.weight"])
-            out[t] += wts[t, j] * y[0]
+            out[rows] += wts[rows, j:j + 1] * y
     if cfg.get("shared_expert_intermediate_size", 0):
         q = prefix + "shared_expert."
         sh = plain_swiglu_mlp(x, weights[q + "gate_proj.weight"], weights[q + "up_proj.weight"],
@@ -167,9 +187,27 @@ def layer_window(cfg: dict, l: int) -> Optional[int]:
 
 # ---- the whole model ------------------------------------------------------------------
 
-def plain_forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int],
-                  dtype: torch.dtype = torch.float32) -> torch.Tensor:
+class _As:
+    """A name -> tensor mapping seen in another dtype, converted when asked for (the mapping
+    may draw its tensors on demand, so nothing is touched before it is needed)."""
+
+    def __init__(self, weights, dtype):
+        self.weights, self.dtype = weights, dtype
+
+    def __getitem__(self, name):
+        return self.weights[name].to(self.dtype)
+
+    def __contains__(self, name):
+        return name in self.weights
+
+
+def plain_forward(cfg: dict, weights, tokens: List[int], dtype: torch.dtype = torch.float32,
+                  forced: Optional[Dict[int, torch.Tensor]] = None, slack: Optional[list] = None
+                  ) -> torch.Tensor:
     """Logits [T, vocab] of one request's whole token list.
+
+    `forced` maps a sparse layer's index to the experts [T, k] its rows are to use (see
+    `plain_router`); `slack` collects how far those choices are from the plain ones.
 
     Layer order as src/models/model.hip:206-444: x1 = norm(h); qkv (+ bias, Qwen2-MoE);
     rotate q, k; attention; h += o_proj(attn); x2 = norm(h); ffn; h += ffn.  The
@@ -177,7 +215,7 @@ def plain_forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int]
     (model.hip:311 and 440-444); that is a defect and is not restated.  Final norm and
     the head (tied to the embedding when tie_word_embeddings, model.hip:497-499,
     727-755)."""
-    W = {n: t.to(dtype) for n, t in weights.items()}
+    W = _As(weights, dtype)
     H = cfg["hidden_size"]
     Hq = cfg["num_attention_heads"]
     Hkv = cfg.get("num_key_value_heads", Hq)
@@ -203,7 +241,7 @@ def plain_forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int]
         h = h + a @ W[p + "self_attn.o_proj.weight"].T
         x2 = plain_rms_norm(h, W[p + "post_attention_layernorm.weight"], eps)
         if layer_is_sparse(cfg, l):
-            f = plain_sparse_ffn(x2, W, p + "mlp.", cfg)
+            f = plain_sparse_ffn(x2, W, p + "mlp.", cfg, None if forced is None else forced[l], slack)
         else:
             f = plain_swiglu_mlp(x2, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
                                  W[p + "mlp.down_proj.weight"])

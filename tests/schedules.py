@@ -89,24 +89,46 @@ def mixed(reqs, max_live: int = 4, page: int = 64, pool_tokens: int = 0, tail: i
     return steps
 
 
-def run_schedule(runner, steps) -> Dict[str, List]:
-    """Drive a ModelRunner through a schedule; return per-request lists of logits rows."""
+def run_schedule(runner, steps, routing: Dict[str, Dict[int, List]] = None) -> Dict[str, List]:
+    """Drive a ModelRunner through a schedule; return per-request lists of logits rows.
+
+    `routing`, if given, is filled with the experts the engine chose:
+    routing[request][layer] = int64 tensor [request's tokens, k], layer by sparse layer."""
     import torch
     from ninfer_amd_mi50_b200.engine import StepEntry
+    from ninfer_amd_mi50_b200.parts.feedforward import SparseMoeSwiglu
     got: Dict[str, List] = {}
+    sparse_calls = [c.layer for c in runner.model.order
+                    if isinstance(runner.model.blocks[c.layer].feed_forward, SparseMoeSwiglu)]
+    chosen: Dict[str, Dict[int, List]] = {}
     for st in steps:
         entries = []
         for e in st["entries"]:
             if not runner.cache.is_open(e["id"]):
                 runner.open(e["id"])
             entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
-        out = runner.step(entries)
-        r = 0
+        if routing is not None:
+            SparseMoeSwiglu.record_routing = []
+        try:
+            out = runner.step(entries)
+            record = SparseMoeSwiglu.record_routing
+        finally:
+            SparseMoeSwiglu.record_routing = None
+        r = row = 0
         for e in st["entries"]:
             n = len(e["want"])
             got.setdefault(e["id"], []).append(out[r:r + n].float().cpu())
             r += n
+            if routing is not None:
+                assert len(record) == len(sparse_calls)
+                for layer, idx in zip(sparse_calls, record):
+                    chosen.setdefault(e["id"], {}).setdefault(layer, []).append(
+                        idx[row:row + len(e["tokens"])].long().cpu())
+            row += len(e["tokens"])
         for rid in st["end"]:
             runner.close(rid)
         runner.cache.check()
+    if routing is not None:
+        for rid, layers in chosen.items():
+            routing[rid] = {l: torch.cat(v) for l, v in layers.items()}
     return {k: torch.cat(v) for k, v in got.items()}

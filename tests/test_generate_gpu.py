@@ -108,9 +108,17 @@ def test_greedy_generation_through_the_entry_point(folders, name):
     eng.close()
     eng = Ninfer(d, max_context=128, prefill_chunk=16, num_sequences=3, dtype="bfloat16")
     got = eng.generate(prompts, max_new_tokens=8, temperature=0.0)
-    # bfloat16 may part from the plain tokens where two logits are within rounding; once it has,
-    # the sequences differ from there on.  The first tokens agree.
-    assert [g[:2] for g in got] == [w[:2] for w in want]
+    # bfloat16 may part from the plain tokens where two logits are within rounding, and the
+    # sequences differ from there on.  So every token is judged on the engine's own prefix: the
+    # plain model, given prompt and the tokens generated so far, must rate the engine's next
+    # token within twice the rounding bound (1.5 % of the largest logit) of its own best.
+    for p, g in zip(prompts, got):
+        assert len(g) == 8
+        logits = plain_model.plain_forward(pcfg, weights, p + g)[len(p) - 1:-1]
+        scale = logits.abs().max().item()
+        for i, tok in enumerate(g):
+            assert logits[i, tok].item() >= logits[i].max().item() - 3e-2 * scale, \
+                f"token {i} ({tok}) is not among the plain model's best"
     eng.close()
 
 
@@ -171,12 +179,14 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     """A prompt of one token, then 330 tokens one by one across several pages; the first
     positions (1, 2, 3 tokens of context) are checked like the rest."""
     import schedules
-    from test_replay_gpu import check, make_runner
+    from test_replay_gpu import check, make_runner, want_for
     d, cfg, pcfg, weights = folders["C"]
     toks = random_tokens(331, cfg["vocab_size"], 3)
     want = plain_model.plain_forward(pcfg, weights, toks)
     runner = make_runner(d, dtype, 384)
-    got = schedules.run_schedule(runner, schedules.tail_decoded({"r": toks}, tail=330))["r"]
+    routing = {}
+    got = schedules.run_schedule(runner, schedules.tail_decoded({"r": toks}, tail=330), routing)["r"]
+    want = want_for((pcfg, weights), {"r": toks}, {"r": want}, dtype, routing, "long decode")["r"]
     check(got, want, dtype, "long decode")
     check(got[:3], want[:3], dtype, "first tokens")
 

@@ -22,27 +22,55 @@ LENGTHS = [33, 150, 7, 97, 70, 201]
 # float32: the engine and the plain model differ by summation order only: 1e-4 of the
 # largest logit (measured: about 1e-6).
 # bfloat16: activations between kernels are rounded to 8 bits of mantissa (unit roundoff
-# 2^-9).  Two kinds of difference from the 32-bit plain model follow.  Rounding proper: a
-# random walk over some twenty roundings, measured at 0.4 % of the largest logit for the
-# worst element of a typical row; bound 1.5 %.  And routing: a rounding of 1e-3 in the router's
-# input swaps the k-th and (k+1)-th expert wherever their probabilities are closer than
-# that, which with 6 to 16 experts happens on about one row in fifty; such a row then carries
-# another expert's output, a few per cent of the largest logit.  So at most one row in ten
-# may pass the rounding bound, and none may pass 10 %: a wrong page, position or mask moves
-# a row by the whole scale and is caught by either limit, as it is at 1e-4 in float32.
+# 2^-9): a random walk over some twenty roundings, measured at 0.4 % of the largest logit for
+# the worst element of a typical row; bound 1.5 %, for every row.  Such a rounding in the
+# router's input also swaps the k-th and (k+1)-th expert wherever their probabilities are
+# closer than that (about one row in fifty), and the row then carries another expert's
+# output.  That is no error of the engine, so the plain model is run with the experts the
+# engine chose (its own probabilities, the engine's selection), and the selection is checked
+# apart: the least probable expert the engine chose may fall short of the plain model's k-th
+# by 5 % of that probability at most, which only a near-tie does.
 def check(got, want, dtype, what):
     scale = want.abs().max().item()
     row_err = (got - want).abs().max(dim=1).values
-    if dtype == "float32":
-        assert row_err.max().item() <= 1e-4 * scale, \
-            f"{what}: max error {row_err.max().item():.3e}, scale {scale:.3f}"
-    else:
-        over = (row_err > 1.5e-2 * scale).sum().item()
-        assert over <= max(1, len(row_err) // 10), \
-            f"{what}: {over} of {len(row_err)} rows beyond 1.5 % of scale {scale:.3f}"
-        assert row_err.max().item() <= 0.1 * scale, \
-            f"{what}: max error {row_err.max().item():.3e}, scale {scale:.3f}"
+    bound = 1e-4 if dtype == "float32" else 1.5e-2
+    worst = int(row_err.argmax())
+    assert row_err.max().item() <= bound * scale, \
+        f"{what}: row {worst} differs by {row_err.max().item():.3e}, scale {scale:.3f}"
     return row_err.median().item() / scale
+
+
+def check_loose(got, want, dtype, what):
+    """For two bfloat16 runs whose expert choices are not known to be the same (another way of
+    cutting, another process): rows that differ only by rounding stay within 1.5 %; a row in
+    which a near-tie fell the other way carries another expert's output, a few per cent.  At
+    most one row in ten may pass the first bound and none 10 %.  The strict comparison with
+    the plain model is `test_schedule_matches_plain`."""
+    if dtype == "float32":
+        return check(got, want, dtype, what)
+    scale = want.abs().max().item()
+    row_err = (got - want).abs().max(dim=1).values
+    over = (row_err > 1.5e-2 * scale).sum().item()
+    assert over <= max(1, len(row_err) // 10), \
+        f"{what}: {over} of {len(row_err)} rows beyond 1.5 % of scale {scale:.3f}"
+    assert row_err.max().item() <= 0.1 * scale, \
+        f"{what}: max error {row_err.max().item():.3e}, scale {scale:.3f}"
+    return row_err.median().item() / scale
+
+
+def want_for(model, reqs, want, dtype, routing, what):
+    """The plain logits to compare with: in float32 the plain model's own; in bfloat16 the
+    plain model run with the engine's expert choice, after checking that choice."""
+    if dtype == "float32":
+        return want
+    pcfg, weights = model
+    out = {}
+    for r, toks in reqs.items():
+        slack = []
+        out[r] = plain_model.plain_forward(pcfg, weights, toks, forced=routing[r], slack=slack)
+        for s in slack:
+            assert s.max().item() <= 0.05, f"{what} {r}: an expert was chosen that is no near-tie ({s.max().item():.3f})"
+    return out
 
 
 @pytest.fixture(scope="module", params=["A", "B", "C", "D"])
@@ -54,7 +82,7 @@ def folder(request, tmp_path_factory):
     pcfg, weights = plain_model.read_model_folder(d)
     reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 40 + i) for i, n in enumerate(LENGTHS)}
     want = {r: plain_model.plain_forward(pcfg, weights, t) for r, t in reqs.items()}
-    return d, cfg, reqs, want
+    return d, cfg, reqs, want, (pcfg, weights)
 
 
 def make_runner(d, dtype, tokens):
@@ -67,15 +95,17 @@ def make_runner(d, dtype, tokens):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("how", ["whole", "tail_decoded", "portions", "mixed"])
 def test_schedule_matches_plain(folder, dtype, how):
-    d, cfg, reqs, want = folder
+    d, cfg, reqs, want, model = folder
     if how == "mixed":
         steps = schedules.mixed(reqs, page=64, pool_tokens=448)
         runner = make_runner(d, dtype, 448)
     else:
         steps = getattr(schedules, how)(reqs)
         runner = make_runner(d, dtype, 256)
-    got = schedules.run_schedule(runner, steps)
+    routing = {}
+    got = schedules.run_schedule(runner, steps, routing)
     assert runner.cache.pages_free() == [g.pool.num_pages for g in runner.cache.groups]
+    want = want_for(model, reqs, want, dtype, routing, how)
     worst = max(check(got[r], want[r], dtype, f"{how} {r}") for r in reqs)
     print(f"\n[{dtype} {how}] worst error / scale = {worst:.2e}")
 
@@ -84,18 +114,18 @@ def test_schedule_matches_plain(folder, dtype, how):
 def test_cuts_agree_with_each_other(folder, dtype):
     """Whole prompts against portions and decoded tails: in 32-bit the same kernels see the
     same rows, so the logits agree to rounding of the last bits."""
-    d, cfg, reqs, want = folder
+    d, cfg, reqs, want, _ = folder
     a = schedules.run_schedule(make_runner(d, dtype, 256), schedules.whole(reqs))
     b = schedules.run_schedule(make_runner(d, dtype, 256), schedules.portions(reqs))
     c = schedules.run_schedule(make_runner(d, dtype, 256), schedules.tail_decoded(reqs))
     for r in reqs:
-        check(b[r], a[r], dtype, f"portions vs whole {r}")
-        check(c[r], a[r], dtype, f"tail vs whole {r}")
+        check_loose(b[r], a[r], dtype, f"portions vs whole {r}")
+        check_loose(c[r], a[r], dtype, f"tail vs whole {r}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(folder, dtype, tmp_path):
-    d, cfg, reqs, want = folder
+    d, cfg, reqs, want, _ = folder
     steps = schedules.mixed(reqs, page=64, pool_tokens=448)
     out = tmp_path / "out"
     lines = "".join(json.dumps({"step": i, **st}) + "\n" for i, st in enumerate(steps))
@@ -114,4 +144,9 @@ def test_trace_run_program(folder, dtype, tmp_path):
             got.setdefault(e["id"], []).append(torch.from_numpy(arr[r:r + len(e["want"])].copy()))
             r += len(e["want"])
     for r in reqs:
-        check(torch.cat(got[r]), want[r], dtype, f"trace_run {r}")
+        check_loose(torch.cat(got[r]), want[r], dtype, f"trace_run {r}")
+    # the program drives the very runner, cache and kernels of the in-process schedule above:
+    # same steps, same pool, same pages, hence the same bits
+    same = schedules.run_schedule(make_runner(d, dtype, 448), steps)
+    for r in reqs:
+        assert torch.equal(torch.cat(got[r]), same[r]), f"trace_run {r} differs from the in-process run"

@@ -68,6 +68,8 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
             assert rc == 0, lib.nf_last_error()
             torch.cuda.synchronize()
             torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=1.6e-2)
+            # same kernels, same order of sums, other scratch: the bits are the same too
+            assert torch.equal(got, want)
     # beyond the fixed array: refused with a message, nothing launched
     rc = lib.nf_decode_attention_static(vp(qkv.data_ptr()), ci(qkv.shape[1]), vp(pages.data_ptr()), vp(bt.data_ptr()),
                                         ci(bt.shape[1]), vp(positions.data_ptr()), vp(row_seg.data_ptr()),
