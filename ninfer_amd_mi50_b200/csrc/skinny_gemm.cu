@@ -32,8 +32,15 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
+// Rows of X: written by the kernel before this one, which may still be running when this kernel's
+// CTAs arrive (chained launch).  So never the non-coherent path (its contract is "read-only for the
+// kernel's lifetime", and this kernel's lifetime begins before X is complete): a load that is
+// served from L2, issued after the wait.
 __device__ __forceinline__ uint4 ld_cached(const void* p) {
-  return __ldg(reinterpret_cast<const uint4*>(p));
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
 }
 __device__ __forceinline__ void mma_bf16(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -194,6 +201,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     if (!waited) {
       // the rows of X (and, for the rotary epilogue, the step's tables) are read only from here on
       chain_wait(rope.positions, rope.row_seg, rope.block_table);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) chain_fresh(xp[nt]);      // no load of X may be placed above the wait
       waited = true;
     }
 #pragma unroll

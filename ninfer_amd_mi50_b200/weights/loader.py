@@ -5,7 +5,10 @@ single ``model.safetensors`` (src/models/model.hip:85-113), looks tensors up by 
 throws ``missing tensor in checkpoint: <name>`` at the first miss (model.hip:116-119); it
 never checks a shape.  Here every tensor the model's parts declare is checked against
 the file headers before a byte is read, and one error lists everything that is missing,
-everything that no part asked for, and every wrong shape.
+everything that no part asked for, and every wrong shape.  A file that only holds tensors
+nobody asked for beside all that are needed (older exports carry ``rotary_emb.inv_freq``
+buffers) still loads: the extra names are listed in a warning, or, with ``strict``, in the
+same error.
 
 Held dtypes (see `TensorSpec.role`): matrices in the engine dtype, norm weights, biases
 and routing matrices in float32, integer tables in int32.
@@ -13,14 +16,15 @@ and routing matrices in float32, integer tables in int32.
 
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
+from .. import log
 from ..parts.base import TensorSpec
+from . import counter_rng
 from .safetensors_io import SafetensorsError, SafetensorsFile
 
 
@@ -86,19 +90,15 @@ class CheckpointSource:
             f.close()
 
 
-def tensor_seed(seed: int, name: str) -> int:
-    """A 63-bit seed that depends on the model seed and the tensor's name only."""
-    return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little") >> 1
-
-
 class RandomSource:
     """Seeded random tensors for exactly the names the model declares.
 
-    Linear weights and biases N(0, 0.02); norm weights 1 + N(0, 0.05).  Each tensor has
-    its own generator keyed by (seed, name), so the values do not depend on the order in
-    which tensors are asked for.  With ``device='cpu'`` the values are the same on
-    every machine; on a CUDA device they are generated in place for models too large to
-    pass through host memory.
+    Linear weights and biases N(0, 0.02); norm weights 1 + N(0, 0.05); every value a
+    bfloat16 number.  An element is a function of (seed, tensor name, element index) alone
+    (`counter_rng`): the values do not depend on the order in which tensors are asked for,
+    nor on the device that draws them, so a model drawn in place on the GPU, a folder written
+    by `write_random_model` on the CPU and a plain implementation that restates the function
+    all hold the same numbers.
     """
 
     def __init__(self, specs: Sequence[TensorSpec], seed: int, gen_device="cpu"):
@@ -111,31 +111,29 @@ class RandomSource:
     def shape(self, name: str) -> Tuple[int, ...]:
         return self.specs[name].shape
 
-    def generate(self, name: str) -> torch.Tensor:
+    def generate(self, name: str, dtype: torch.dtype = torch.float32, device=None) -> torch.Tensor:
         spec = self.specs[name]
-        g = torch.Generator(device=self.gen_device)
-        g.manual_seed(tensor_seed(self.seed, name))
+        device = torch.device(device) if device is not None else self.gen_device
         if spec.role == "table":
-            return torch.zeros(spec.shape, dtype=torch.int32, device=self.gen_device)
-        t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=self.gen_device)
-        if spec.init == "norm":
-            return 1.0 + 0.05 * t
-        return 0.02 * t
+            return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        out = torch.empty(spec.shape, dtype=dtype, device=device)
+        return counter_rng.fill(out, counter_rng.tensor_keys(self.seed, name), spec.init)
 
     def read(self, name: str, spec: TensorSpec, dtype: torch.dtype, device) -> torch.Tensor:
-        t = self.generate(name)
-        if t.is_floating_point() and dtype.is_floating_point:
-            # values are defined as the bfloat16 rounding of the draw, so that a model
-            # written to disk in bfloat16 and one generated in place agree bit for bit
-            t = t.to(torch.bfloat16)
-        return t.to(device=device, dtype=dtype)
+        device = torch.device(device)
+        if dtype in (torch.float32, torch.bfloat16) and device.type == self.gen_device.type:
+            return self.generate(name, dtype, device)       # drawn where it stays, in its held dtype
+        return self.generate(name).to(device=device, dtype=dtype)
 
     def close(self) -> None:
         pass
 
 
-def check_specs(specs: Sequence[TensorSpec], source) -> None:
-    """Raise one `WeightError` naming every missing, unexpected and misshapen tensor."""
+def check_specs(specs: Sequence[TensorSpec], source, strict: bool = False) -> List[str]:
+    """Raise one `WeightError` naming every missing, unexpected and misshapen tensor.
+
+    Missing and misshapen tensors are always fatal.  Tensors that no part asked for are
+    fatal with `strict`; otherwise they are returned (and the caller warns)."""
     want = {}
     for s in specs:
         if s.name in want and want[s.name].shape != s.shape:
@@ -148,8 +146,8 @@ def check_specs(specs: Sequence[TensorSpec], source) -> None:
     for n, s in want.items():
         if n in have and tuple(source.shape(n)) != tuple(s.shape):
             wrong.append((n, tuple(s.shape), tuple(source.shape(n))))
-    if not (missing or unexpected or wrong):
-        return
+    if not (missing or wrong or (unexpected and strict)):
+        return unexpected
 
     def some(items, fmt=str, limit=12):
         shown = ", ".join(fmt(i) for i in items[:limit])
@@ -167,10 +165,14 @@ def check_specs(specs: Sequence[TensorSpec], source) -> None:
                       missing, unexpected, wrong)
 
 
-def load_model(model, source, engine_dtype: torch.dtype, device) -> None:
+def load_model(model, source, engine_dtype: torch.dtype, device, strict: bool = False) -> None:
     """Check everything, then let each part pull its tensors."""
     specs = model.tensor_specs()
-    check_specs(specs, source)
+    extra = check_specs(specs, source, strict)
+    if extra:
+        shown = ", ".join(extra[:12]) + (f", ... ({len(extra) - 12} more)" if len(extra) > 12 else "")
+        log.warn(f"checkpoint holds {len(extra)} tensors that no part of the model asked for "
+                 f"(not loaded): {shown}")
     by_name = {s.name: s for s in specs}
 
     def fetch(name: str) -> torch.Tensor:

@@ -42,12 +42,8 @@ def write_random_model(config: Dict[str, Any], seed: int, out_dir: str,
             if s.name in seen:
                 continue
             seen.add(s.name)
-            t = src.generate(s.name)
-            if s.role == "table":
-                yield s.name, t
-            else:
-                # every value is a bfloat16 number; stored widened when float32 is asked for
-                yield s.name, t.to(torch.bfloat16).to(_STORE[store_dtype])
+            # every value is a bfloat16 number; stored widened when float32 is asked for
+            yield s.name, src.generate(s.name, _STORE[store_dtype])
 
     write_safetensors(os.path.join(out_dir, "model.safetensors"), items(),
                       metadata={"format": "pt", "seed": str(seed)})

@@ -37,11 +37,115 @@ def read_model_folder(model_dir: str, dtype: torch.dtype = torch.float32):
     return cfg, weights
 
 
+# ---- random weights from a seed, without a file -------------------------------------------
+
+def plain_random_tensor(seed: int, name: str, shape, init: str, device="cpu") -> torch.Tensor:
+    """The engine's random-weights function restated (the reference has no such mode): element
+    i of tensor `name` is made from (seed, name, i) alone.
+
+        k1, k2 = first two little-endian 32-bit words of SHA-256("<seed>:<name>")
+        mix(x) = x ^= x >> 16; x *= 0x7feb352d; x ^= x >> 15; x *= 0x846ca68b; x ^= x >> 16  (mod 2^32)
+        s = mix(mix(lo32(i) ^ k1) ^ hi32(i) ^ k2)
+        n = sum over c in (0x9e3779b9, 0x85ebca6b, 0xc2b2ae35, 0x27d4eb2f) of the three 10-bit
+            fields of mix(s ^ c), minus 6138
+        z = float32(n) * float32(1 / sqrt(1048575))
+        value = bfloat16(0.02 * z) for "linear", bfloat16(1 + 0.05 * z) for "norm"
+
+    Written with 64-bit torch integers holding 32-bit values (products are taken in two
+    16-bit halves so that nothing overflows); runs on any torch device."""
+    import hashlib
+    digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    k1, k2 = int.from_bytes(digest[0:4], "little"), int.from_bytes(digest[4:8], "little")
+    mask = (1 << 32) - 1
+
+    def times(x, c):
+        low = (x % 65536) * c
+        high = ((x // 65536) * c) % 65536
+        return (low + high * 65536) % (1 << 32)
+
+    def mix(x):
+        x = x ^ (x // 65536)
+        x = times(x, 0x7FEB352D)
+        x = x ^ (x // 32768)
+        x = times(x, 0x846CA68B)
+        return x ^ (x // 65536)
+
+    count = 1
+    for d in shape:
+        count *= int(d)
+    out = torch.empty(count, dtype=torch.float32, device=device)
+    step = 1 << 24
+    for a in range(0, count, step):
+        i = torch.arange(a, min(count, a + step), dtype=torch.int64, device=device)
+        s = mix(mix((i & mask) ^ k1) ^ (i // (1 << 32)) ^ k2)
+        n = torch.zeros_like(s) - 6138
+        for c in (0x9E3779B9, 0x85EBCA6B, 0xC2B2AE35, 0x27D4EB2F):
+            w = mix(s ^ c)
+            n = n + (w % 1024) + ((w // 1024) % 1024) + ((w // 1048576) % 1024)
+        z = n.to(torch.float32) * float(np.float32(1.0 / math.sqrt(1048575.0)))
+        v = (z * float(np.float32(0.05)) + 1.0) if init == "norm" else z * float(np.float32(0.02))
+        out[a:a + len(i)] = v.to(torch.bfloat16).to(torch.float32)
+    return out.reshape(tuple(shape))
+
+
+class RandomWeights:
+    """name -> tensor for a Qwen2-MoE configuration, each drawn when asked for (nothing is kept:
+    a model of tens of gigabytes never exists as a whole).  Tensor names as in the checkpoints
+    the reference reads (src/models/model.hip:487-512, 530-532, 559, 576, 586-587, 619) plus
+    Qwen2-MoE's own (q/k/v biases, per-expert matrices, shared expert and its gate)."""
+
+    def __init__(self, cfg: dict, seed: int, device="cpu"):
+        self.seed, self.device = seed, device
+        H, V = cfg["hidden_size"], cfg["vocab_size"]
+        Hq = cfg["num_attention_heads"]
+        Hkv = cfg.get("num_key_value_heads", Hq)
+        D = cfg.get("head_dim") or H // Hq
+        t = {"model.embed_tokens.weight": ((V, H), "linear"), "model.norm.weight": ((H,), "norm")}
+        if not cfg.get("tie_word_embeddings"):
+            t["lm_head.weight"] = ((V, H), "linear")
+        for l in range(cfg["num_hidden_layers"]):
+            p = f"model.layers.{l}."
+            t[p + "input_layernorm.weight"] = ((H,), "norm")
+            t[p + "post_attention_layernorm.weight"] = ((H,), "norm")
+            for n, rows in (("q", Hq * D), ("k", Hkv * D), ("v", Hkv * D)):
+                t[p + f"self_attn.{n}_proj.weight"] = ((rows, H), "linear")
+                if cfg.get("qkv_bias", True):
+                    t[p + f"self_attn.{n}_proj.bias"] = ((rows,), "linear")
+            t[p + "self_attn.o_proj.weight"] = ((H, Hq * D), "linear")
+            if layer_is_sparse(cfg, l):
+                I, Is = cfg["moe_intermediate_size"], cfg.get("shared_expert_intermediate_size", 0)
+                t[p + "mlp.gate.weight"] = ((cfg["num_experts"], H), "linear")
+                for e in range(cfg["num_experts"]):
+                    q = f"{p}mlp.experts.{e}."
+                    t[q + "gate_proj.weight"], t[q + "up_proj.weight"] = ((I, H), "linear"), ((I, H), "linear")
+                    t[q + "down_proj.weight"] = ((H, I), "linear")
+                if Is:
+                    q = p + "mlp.shared_expert."
+                    t[q + "gate_proj.weight"], t[q + "up_proj.weight"] = ((Is, H), "linear"), ((Is, H), "linear")
+                    t[q + "down_proj.weight"] = ((H, Is), "linear")
+                    t[p + "mlp.shared_expert_gate.weight"] = ((1, H), "linear")
+            else:
+                I = cfg["intermediate_size"]
+                t[p + "mlp.gate_proj.weight"], t[p + "mlp.up_proj.weight"] = ((I, H), "linear"), ((I, H), "linear")
+                t[p + "mlp.down_proj.weight"] = ((H, I), "linear")
+        self.tensors = t
+
+    def __contains__(self, name):
+        return name in self.tensors
+
+    def __getitem__(self, name):
+        shape, init = self.tensors[name]
+        return plain_random_tensor(self.seed, name, shape, init, self.device)
+
+    def keys(self):
+        return self.tensors.keys()
+
+
 # ---- parts ----------------------------------------------------------------------------
 
 def plain_embedding(embed: torch.Tensor, tokens: List[int]) -> torch.Tensor:
     """h0[t] = embed[token[t]], no scaling (src/ops/kernels.hip:150-159)."""
-    return embed[torch.tensor(tokens, dtype=torch.long)]
+    return embed[torch.tensor(tokens, dtype=torch.long, device=embed.device)]
 
 
 def plain_rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -82,8 +186,8 @@ def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     rep = Hq // Hkv
-    out = torch.zeros(T, Hq, D, dtype=q.dtype)
-    idx = torch.arange(T)
+    out = torch.zeros(T, Hq, D, dtype=q.dtype, device=q.device)
+    idx = torch.arange(T, device=q.device)
     mask = idx[None, :] <= idx[:, None]
     if window:
         mask &= idx[None, :] > idx[:, None] - window
@@ -122,16 +226,17 @@ def plain_router(x: torch.Tensor, w_router: torch.Tensor, k: int, norm_topk: boo
     T, E = p.shape
     idx = torch.zeros(T, k, dtype=torch.long)
     wts = torch.zeros(T, k, dtype=x.dtype)
+    p_host = p.cpu()
     for t in range(T):
         if forced_idx is not None:
             order = [int(e) for e in forced_idx[t]]
         else:
-            order = sorted(range(E), key=lambda e: (-float(p[t, e]), e))[:k]
+            order = sorted(range(E), key=lambda e: (-float(p_host[t, e]), e))[:k]
         idx[t] = torch.tensor(order)
-        wts[t] = p[t, order]
+        wts[t] = p_host[t, order]
     if norm_topk:
         wts = wts / wts.sum(dim=-1, keepdim=True)
-    return idx, wts, p
+    return idx.to(x.device), wts.to(x.device), p
 
 
 def plain_sparse_ffn(x: torch.Tensor, weights, prefix: str, cfg: dict,
@@ -221,10 +326,10 @@ def plain_forward(cfg: dict, weights, tokens: List[int], dtype: torch.dtype = to
     Hkv = cfg.get("num_key_value_heads", Hq)
     D = cfg.get("head_dim") or H // Hq
     eps = cfg.get("rms_norm_eps", 1e-6)
-    inv_freq = plain_inv_freq(D, cfg.get("rope_theta", 1e6))
     T = len(tokens)
-    pos = torch.arange(T)
     h = plain_embedding(W["model.embed_tokens.weight"], tokens)
+    inv_freq = plain_inv_freq(D, cfg.get("rope_theta", 1e6)).to(h.device)
+    pos = torch.arange(T, device=h.device)
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}."
         x1 = plain_rms_norm(h, W[p + "input_layernorm.weight"], eps)

@@ -304,17 +304,34 @@ def test_running_ahead_changes_no_token(folders, temperature):
     assert any(len(o) < 40 for o in runs[1][1])          # some request did stop early
 
 
-@pytest.mark.parametrize("name,rows", [("A", 3), ("C", 3), ("A", 40), ("C", 40)])
-def test_a_replayed_step_gives_the_same_bits_every_time(folders, name, rows):
+@pytest.mark.parametrize("name,rows,chained", [("A", 3, -1), ("C", 3, -1), ("A", 40, -1), ("C", 40, -1), ("C", 3, 1)])
+def test_a_replayed_step_gives_the_same_bits_every_time(folders, name, rows, chained):
     """A captured decode step, replayed on unchanged inputs, must give the same logits bit for
     bit.  With the kernels of the step launched chained (each may begin while its predecessor
     drains), the first kernel after a wait on another stream - the shared expert's branch, and
     the combine that joins it - must be an ordinary launch: chained, it began before the other
     stream's kernel had finished, and every replay of the step differed.  With 40 rows the
-    shared expert's branch starts after the router instead of beside it."""
+    shared expert's branch starts after the router instead of beside it.
+
+    `chained` = 1 chains the streaming products only.  That timing showed a second fault: the
+    shared expert's second product, already resident while the first still ran beside the
+    high-priority router, read its input rows through the non-coherent path and got rows of an
+    earlier layer; a quarter of the replays differed.  A chained kernel reads what its
+    predecessor wrote with coherent loads issued after the wait."""
+    from ninfer_amd_mi50_b200 import kernels
     from ninfer_amd_mi50_b200.config import EngineOptions
     from ninfer_amd_mi50_b200.engine import StepEntry, load_runner
     d, cfg, _, _ = folders[name]
+    kernels.load().nf_set_chained_launch(chained)
+    try:
+        _replay_and_compare(d, cfg, rows)
+    finally:
+        kernels.load().nf_set_chained_launch(-1)
+
+
+def _replay_and_compare(d, cfg, rows):
+    from ninfer_amd_mi50_b200.config import EngineOptions
+    from ninfer_amd_mi50_b200.engine import StepEntry, load_runner
     runner = load_runner(d, options=EngineOptions(dtype="bfloat16", page_size=64, num_sequences=rows + 1,
                                                    max_context=256, cache_tokens=256 * (rows + 1)))
     for r in range(rows):

@@ -355,6 +355,163 @@ def test_prefill_attention_on_tensor_cores(K, Hq, Hkv, D, page, window):
     torch.testing.assert_close(out[few].float(), ref.float(), **tol(dtype))
 
 
+def _step_context(c, seg_lens, pos0s, dtype, max_context):
+    from ninfer_amd_mi50_b200.parts.base import StepContext
+    row0 = [0]
+    for n in seg_lens:
+        row0.append(row0[-1] + n)
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    return StepContext(dtype=dtype, device=torch.device("cuda"), T=row0[-1], S=len(seg_lens), token_ids=mk([0]),
+                       positions=c.positions, row_seg=c.row_seg, seg_row0=mk(row0), seg_pos0=mk(pos0s),
+                       seg_slot=mk([0] * len(seg_lens)), logit_rows=mk([]), seg_len_host=list(seg_lens),
+                       seg_pos0_host=list(pos0s), max_rows_per_seg=max(seg_lens), max_context=max_context)
+
+
+@pytest.mark.parametrize("keys", [4096, 8192])
+@pytest.mark.parametrize("Hq,Hkv", [(16, 16), (28, 4)])
+def test_attention_at_the_contexts_that_are_timed(K, Hq, Hkv, keys):
+    """Head counts of the two large configurations (16 kv heads for 16 query heads; 4 for 28:
+    seven heads a group), head size 128, pages of 64, contexts of 4,096 and 8,192 keys.
+    Decode rows through both split-key kernels, a prompt portion through both flash kernels;
+    all against the any-rows kernel, and against the plain twin on a few rows."""
+    from ninfer_amd_mi50_b200.kernels import lib as klib
+    dtype, D, page = torch.bfloat16, 128, 64
+    scale = 1 / math.sqrt(D)
+    # ---- decode: eight requests near the context length
+    lens = [keys - 1, keys - 2, keys - 129, keys // 2, keys - 64, keys - 65, 100, keys - 1000]
+    n_pages = sum((n + 1 + page - 1) // page for n in lens) + 1
+    pages, bt, ctx, qkv = make_cache_case(dtype, Hq, Hkv, D, page, [1] * len(lens), lens, n_pages, 61)
+    ctx.all_single, ctx.max_context = True, keys
+    assert len(lens) * Hkv * (keys // 128) >= 1024           # enough blocks for the streaming kernel
+    stream = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, 0, scale)
+    lib = klib.load()
+    try:
+        lib.nf_set_decode_stream(0)
+        block = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, 0, scale)
+    finally:
+        lib.nf_set_decode_stream(1)
+    ctx.all_single = False
+    gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, 0, scale)
+    assert not torch.equal(stream, block)
+    torch.testing.assert_close(stream.float(), gen.float(), **tol(dtype))
+    torch.testing.assert_close(block.float(), gen.float(), **tol(dtype))
+    few = [0, 6]
+    sub = SimpleNamespace(positions=ctx.positions[few], row_seg=ctx.row_seg[few])
+    ref = P.paged_attention(qkv[few], Hq, Hkv, D, pages, bt, page, sub, 0, scale)
+    torch.testing.assert_close(stream[few].float(), ref.float(), **tol(dtype))
+    assert K.index_status() == 0
+    del pages, qkv
+    # ---- a prompt portion of 384 rows that ends at the context length, beside a short fresh prompt
+    seg_lens, pos0s = [384, 130], [keys - 384, 0]
+    n_pages = sum((p + n + page - 1) // page for p, n in zip(pos0s, seg_lens)) + 1
+    pages, bt, c, qkv = make_cache_case(dtype, Hq, Hkv, D, page, seg_lens, pos0s, n_pages, 62)
+    out = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, _step_context(c, seg_lens, pos0s, dtype, keys), 0, scale)
+    assert K.tensor_core_status() == 0
+    old = dict(K.TUNING)
+    try:
+        K.TUNING.update(prefill_attention_tc_min_rows=10 ** 9)
+        flash = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, _step_context(c, seg_lens, pos0s, dtype, keys), 0, scale)
+        K.TUNING.update(bf16_attention="generic")
+        gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, _step_context(c, seg_lens, pos0s, dtype, keys), 0, scale)
+    finally:
+        K.TUNING.update(old)
+    assert not torch.equal(out, flash)
+    torch.testing.assert_close(out.float(), gen.float(), **tol(dtype))
+    torch.testing.assert_close(flash.float(), gen.float(), **tol(dtype))
+    few = [383, 384 + 129]
+    sub = SimpleNamespace(positions=c.positions[few], row_seg=c.row_seg[few])
+    ref = P.paged_attention(qkv[few], Hq, Hkv, D, pages, bt, page, sub, 0, scale)
+    torch.testing.assert_close(out[few].float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [(4, 2, 64, 16, 0), (16, 16, 128, 64, 0), (6, 1, 32, 16, 150)])
+def test_single_rows_of_a_mixed_step_take_the_decode_kernel(K, Hq, Hkv, D, page, window):
+    """A step that holds prompt portions and single decoded tokens: the single rows are served
+    by the split-key kernel through a list of rows and get, bit for bit, what they get in a
+    step that holds nothing else; the portions go to a flash kernel."""
+    dtype = torch.bfloat16
+    seg_lens = [1, 40, 1, 1, 150, 2, 1]
+    pos0s = [700, 10, 0, 129, 300, 64, 383]
+    n_pages = sum((p + n + page - 1) // page for p, n in zip(pos0s, seg_lens)) + 2
+    pages, bt, c, qkv = make_cache_case(dtype, Hq, Hkv, D, page, seg_lens, pos0s, n_pages, 63)
+    scale = 1 / math.sqrt(D)
+    ctx = _step_context(c, seg_lens, pos0s, dtype, 701)
+    rows, n = ctx.single_rows()
+    assert n == 4 and rows.tolist() == [0, 41, 42, 195]
+    mixed = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    K.TUNING["bf16_attention"] = "generic"
+    try:
+        gen = K.paged_attention(qkv, Hq, Hkv, D, pages, bt, page, ctx, window, scale)
+    finally:
+        K.TUNING["bf16_attention"] = "auto"
+    torch.testing.assert_close(mixed.float(), gen.float(), **tol(dtype))
+    # the same four rows alone, as a decode-only step over the same cache
+    single = rows.tolist()
+    alone = SimpleNamespace(positions=c.positions[single].contiguous(), row_seg=c.row_seg[single].contiguous(),
+                            all_single=True, max_context=701)
+    dec = K.paged_attention(qkv[single].contiguous(), Hq, Hkv, D, pages, bt, page, alone, window, scale)
+    assert torch.equal(mixed[single], dec)
+    assert K.index_status() == 0
+
+
+def test_decode_attention_with_too_few_key_blocks_is_cut_and_reported(K):
+    """The workspace of the split-key kernels has `nsplit` blocks of 128 keys per row; positions
+    live on the device, so a call cannot be refused for a row that needs more.  Such a row is
+    computed over the keys the workspace covers, nothing is written outside the workspace (the
+    slabs behind it keep their fill), and the status names the row."""
+    import ctypes
+    dtype, Hq, Hkv, D, page = torch.bfloat16, 4, 2, 64, 16
+    lens = [100, 700, 30, 5] * 44              # rows 1, 5, ... need 6 blocks
+    pages, bt, ctx, qkv = make_cache_case(dtype, Hq, Hkv, D, page, [1] * len(lens), lens,
+                                          sum((n + page) // page for n in lens) + 1, 64)
+    T, nsplit = len(lens), 3
+    lib = K.load()
+    vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    for stream_kernel in (1, 0):
+        lib.nf_set_decode_stream(stream_kernel)
+        try:
+            acc = torch.full((T * Hq * nsplit * D + 4096,), 7.0, dtype=torch.float32, device="cuda")
+            ml = torch.full((T * Hq * nsplit * 2 + 4096,), 7.0, dtype=torch.float32, device="cuda")
+            out = torch.zeros((T, Hq * D), dtype=dtype, device="cuda")
+            assert stream_kernel == 0 or T * Hkv * nsplit >= 1024
+            rc = lib.nf_decode_attention(vp(qkv.data_ptr()), ci(qkv.shape[1]), vp(pages.data_ptr()), vp(bt.data_ptr()),
+                                         ci(bt.shape[1]), vp(ctx.positions.data_ptr()), vp(ctx.row_seg.data_ptr()),
+                                         vp(out.data_ptr()), vp(acc.data_ptr()), vp(ml.data_ptr()), ci(T), ci(Hq),
+                                         ci(Hkv), ci(D), ci(page), ci(pages.shape[0]), ci(0), cf(0.125), ci(nsplit),
+                                         vp(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0
+            torch.cuda.synchronize()
+        finally:
+            lib.nf_set_decode_stream(1)
+        assert bool((acc[-4096:] == 7.0).all()) and bool((ml[-4096:] == 7.0).all())
+        status = K.index_status()
+        assert status > 100000 and (status - 100001) % 4 == 1       # one of the long rows
+        assert K.index_status() == 0                                 # reading clears it
+        # the rows that fit are right
+        ok = [t for t, n in enumerate(lens) if n < nsplit * 128][:12]
+        sub = SimpleNamespace(positions=ctx.positions[ok], row_seg=ctx.row_seg[ok])
+        ref = P.paged_attention(qkv[ok], Hq, Hkv, D, pages, bt, page, sub, 0, 0.125)
+        torch.testing.assert_close(out[ok].float(), ref.float(), **tol(dtype))
+
+
+def test_a_wait_that_runs_out_reaches_the_host_as_an_error(K):
+    """The tensor-core kernels bound every wait on a barrier and record a code when one gives
+    up.  A kernel whose only barrier nobody ever arrives at shows the path end to end: it
+    returns (the context stays usable), the status carries its code, `check_status` raises,
+    and the next check is clean."""
+    import ctypes
+    from ninfer_amd_mi50_b200.kernels import lib as klib
+    assert K.tensor_core_status() == 0
+    klib.call("nf_bounded_wait_selftest", ctypes.c_int(2000),
+              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    with pytest.raises(klib.KernelError, match="gave up on a wait .code 9."):
+        K.check_status("test")
+    K.check_status("test")
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0
+
+
 def test_attention_finds_one_far_key(K):
     """One key among hundreds is made to dominate; the output must be its value row."""
     Hq, Hkv, D, page = 2, 1, 64, 16

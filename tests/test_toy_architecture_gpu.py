@@ -195,9 +195,14 @@ def toy_plain(cfg, W, tokens):
     v = (x @ W[p + "v_proj.weight"].T).view(T, Hkv, D)
     h = h + PM.plain_attention(q, k, v) @ W[p + "o_proj.weight"].T
     x = PM.plain_rms_norm(h, W["toy.l3.ln2.weight"], cfg["eps"])
-    up = (x @ W["toy.l3.ff.route"]) > 0
+    side = x @ W["toy.l3.ff.route"]
+    up = side > 0
+    # how far a row is from the switch, as the cosine between the row and the routing vector: a
+    # row within rounding of it may go either way in bfloat16 (the layer is the last, so only
+    # the row's own logits depend on it)
+    margin = side.abs() / (x.norm(dim=-1) * W["toy.l3.ff.route"].norm())
     h = h + torch.where(up[:, None], x @ W["toy.l3.ff.w1.weight"].T, x @ W["toy.l3.ff.w0.weight"].T)
-    return PM.plain_rms_norm(h, W["toy.norm.weight"], cfg["eps"]) @ W["toy.embed.weight"].T
+    return PM.plain_rms_norm(h, W["toy.norm.weight"], cfg["eps"]) @ W["toy.embed.weight"].T, margin
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -205,12 +210,18 @@ def test_toy_architecture_steps_under_every_cut(toy_registered, tmp_path, dtype)
     from ninfer_amd_mi50_b200.config import EngineOptions
     from ninfer_amd_mi50_b200.engine import load_runner
     from ninfer_amd_mi50_b200.weights import write_random_model
-    from test_replay_gpu import check_loose as check
+    from test_replay_gpu import check
     d = str(tmp_path / "toy")
     write_random_model(TOY, 4, d)
     cfg, W = PM.read_model_folder(d)
     reqs = {f"r{i}": random_tokens(n, TOY["vocab_size"], 60 + i) for i, n in enumerate([40, 9, 77, 23, 58])}
-    want = {r: toy_plain(cfg, W, t) for r, t in reqs.items()}
+    want, clear = {}, {}
+    for r, t in reqs.items():
+        want[r], margin = toy_plain(cfg, W, t)
+        # float32 decides like the plain model; bfloat16 is judged on the rows that are not within
+        # rounding of the switch (every one of them, to the rounding bound)
+        clear[r] = torch.ones_like(margin, dtype=torch.bool) if dtype == "float32" else margin > 0.02
+        assert clear[r].sum().item() >= 0.8 * len(t)
     for make in (schedules.whole, schedules.portions, lambda r: schedules.mixed(r, page=16, pool_tokens=192)):
         runner = load_runner(d, options=EngineOptions(dtype=dtype, page_size=16, num_sequences=4,
                                                        max_context=192, cache_tokens=192, use_graph=False))
@@ -218,4 +229,4 @@ def test_toy_architecture_steps_under_every_cut(toy_registered, tmp_path, dtype)
         assert len(runner.cache.groups) == 1 and runner.cache.groups[0].slots == [1, 2, 3]
         got = schedules.run_schedule(runner, make(reqs))
         for r in reqs:
-            check(got[r], want[r], dtype, f"toy {r}")
+            check(got[r][clear[r]], want[r][clear[r]], dtype, f"toy {r}")

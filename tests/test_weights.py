@@ -106,6 +106,29 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert piece in msg
 
 
+def test_a_tensor_nobody_asked_for_is_a_warning_unless_strict(tmp_path, capsys):
+    """Older exports carry `rotary_emb.inv_freq` buffers: everything needed is there, so the
+    model loads and the extra names are listed on stderr; `strict` makes them an error."""
+    d = str(tmp_path / "a")
+    write_random_model(TINY_A, 0, d)
+    f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    tensors = {n: f.read(n).clone() for n in f.names()}
+    f.close()
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(32)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors.items())
+    _, model = build_model(TINY_A)
+    load_model(model, CheckpointSource(d), torch.float32, "cpu")
+    err = capsys.readouterr().err
+    assert "rotary_emb.inv_freq" in err and "no part of the model asked for" in err
+    _, ref = build_model(TINY_A)
+    load_model(ref, RandomSource(ref.tensor_specs(), 0), torch.float32, "cpu")
+    assert torch.equal(model.blocks[0].mixer.w_qkv, ref.blocks[0].mixer.w_qkv)
+    _, model = build_model(TINY_A)
+    with pytest.raises(WeightError, match="1 unexpected") as ei:
+        load_model(model, CheckpointSource(d), torch.float32, "cpu", strict=True)
+    assert ei.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and not ei.value.missing
+
+
 def test_no_checkpoint_in_folder(tmp_path):
     with pytest.raises(WeightError, match="no model.safetensors"):
         CheckpointSource(str(tmp_path))
@@ -150,3 +173,66 @@ def test_random_source_matches_written_folder(tmp_path):
     load_model(m2, RandomSource(m2.tensor_specs(), 5), torch.float32, "cpu")
     assert torch.equal(m1.blocks[1].feed_forward.w2, m2.blocks[1].feed_forward.w2)
     assert torch.equal(m1.final_norm.weight, m2.final_norm.weight)
+
+
+def _draw_with_python_integers(seed, name, i, init):
+    """A third statement of the random-weights function, in plain Python integers, for a few
+    single elements."""
+    import hashlib
+    import numpy as np
+    d = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+    k1, k2 = int.from_bytes(d[:4], "little"), int.from_bytes(d[4:8], "little")
+    M = 0xFFFFFFFF
+
+    def mix(x):
+        x ^= x >> 16
+        x = (x * 0x7FEB352D) & M
+        x ^= x >> 15
+        x = (x * 0x846CA68B) & M
+        return x ^ (x >> 16)
+
+    s = mix(mix((i & M) ^ k1) ^ (i >> 32) ^ k2)
+    n = -6138
+    for c in (0x9E3779B9, 0x85EBCA6B, 0xC2B2AE35, 0x27D4EB2F):
+        w = mix(s ^ c)
+        n += (w & 1023) + ((w >> 10) & 1023) + ((w >> 20) & 1023)
+    z = np.float32(n) * np.float32(1.0 / np.sqrt(np.float64(1048575.0)))
+    v = np.float32(1.0) + np.float32(0.05) * z if init == "norm" else np.float32(0.02) * z
+    return float(torch.tensor(float(v), dtype=torch.float32).to(torch.bfloat16))
+
+
+def test_counter_based_weights_three_statements_agree():
+    """The engine's generator (torch twin of the CUDA kernel), the plain model's restatement and
+    plain Python integers give the same bfloat16 values for (seed, name, index), also beyond
+    2^32 elements and whatever the chunking."""
+    import plain_model
+    from ninfer_amd_mi50_b200.weights import counter_rng
+    for seed, name, init in ((0, "model.embed_tokens.weight", "linear"), (7, "model.norm.weight", "norm")):
+        keys = counter_rng.tensor_keys(seed, name)
+        ours = counter_rng.draw(0, 5000, keys, init)
+        plain = plain_model.plain_random_tensor(seed, name, (50, 100), init).reshape(-1)
+        assert torch.equal(ours, plain)
+        for i in (0, 1, 77, 4999):
+            assert ours[i].item() == _draw_with_python_integers(seed, name, i, init)
+        far = (1 << 33) + 12345
+        assert counter_rng.draw(far, 3, keys, init)[2].item() == _draw_with_python_integers(seed, name, far + 2, init)
+        # the value of an element does not depend on where a chunk begins
+        assert torch.equal(counter_rng.draw(1000, 50, keys, init), ours[1000:1050])
+        out = torch.empty(5000, dtype=torch.bfloat16)
+        assert torch.equal(counter_rng.fill(out, keys, init).float(), ours)
+    z = counter_rng.draw(0, 1 << 18, counter_rng.tensor_keys(3, "x"), "linear") / 0.02
+    assert abs(z.mean().item()) < 0.01 and abs(z.std().item() - 1) < 0.01 and z.abs().max().item() < 6
+
+
+def test_plain_random_weights_name_the_tensors_of_a_written_folder(tmp_path):
+    """The plain model can rebuild, from configuration and seed alone, exactly the tensors that
+    `write_random_model` puts into a folder: same names, same shapes, same bits."""
+    import plain_model
+    for cfg, seed in ((TINY_A, 0), (TINY_B, 1)):
+        d = str(tmp_path / f"m{seed}")
+        write_random_model(cfg, seed, d)
+        pcfg, stored = plain_model.read_model_folder(d)
+        drawn = plain_model.RandomWeights(pcfg, seed)
+        assert sorted(drawn.keys()) == sorted(stored)
+        for name in list(stored)[::7] + ["model.norm.weight"]:
+            assert torch.equal(drawn[name], stored[name]), name
