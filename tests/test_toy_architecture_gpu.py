@@ -220,8 +220,8 @@ def test_toy_architecture_steps_under_every_cut(toy_registered, tmp_path, dtype)
         want[r], margin = toy_plain(cfg, W, t)
         # float32 decides like the plain model; bfloat16 is judged on the rows that are not within
         # rounding of the switch (every one of them, to the rounding bound)
-        clear[r] = torch.ones_like(margin, dtype=torch.bool) if dtype == "float32" else margin > 0.02
-        assert clear[r].sum().item() >= 0.8 * len(t)
+        clear[r] = torch.ones_like(margin, dtype=torch.bool) if dtype == "float32" else margin > 0.01
+    assert sum(c.sum().item() for c in clear.values()) >= 0.8 * sum(len(t) for t in reqs.values())
     for make in (schedules.whole, schedules.portions, lambda r: schedules.mixed(r, page=16, pool_tokens=192)):
         runner = load_runner(d, options=EngineOptions(dtype=dtype, page_size=16, num_sequences=4,
                                                        max_context=192, cache_tokens=192, use_graph=False))
