@@ -2,6 +2,9 @@
 """Decode and prefill throughput at Qwen1.5-MoE-A2.7B layer sizes with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --config 57b           # Qwen2-57B-A14B layer sizes: decode at batch 1 / 8 / 32 after 1,024-token contexts
+    python bench.py --long-prefill         # adds prefill of 8,192 and 32,768 tokens in portions of 2,048
+    python bench.py --config check-fp32    # the whole model in 32-bit at A2.7B sizes against the plain model
 
 One JSON line on stdout.  A "step" is one decode step of a batch of 8 requests, each
 holding a context of about 2,048 tokens (the context length of the named configuration's
@@ -41,6 +44,16 @@ CONFIG = {
 FULL_LAYERS = 24
 CONTEXT = 4096
 PROMPT = 2048
+# Qwen2-57B-A14B layer sizes (the fourth named configuration): 114.8 GB of bfloat16 weights
+CONFIG_57B = dict(CONFIG, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28,
+                  num_key_value_heads=4, intermediate_size=18944, num_experts=64, num_experts_per_tok=8,
+                  moe_intermediate_size=2560, shared_expert_intermediate_size=20480)
+# name -> (config.json, its layer count, model name, tokens each request holds when decode is timed,
+#          batch of `value`, batches of `points`)
+PROFILES = {
+    "a2.7b": (CONFIG, 24, "Qwen1.5-MoE-A2.7B", 2048, 8, (1, 64)),
+    "57b": (CONFIG_57B, 28, "Qwen2-57B-A14B", 1024, 8, (1, 32)),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -88,14 +101,91 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.rows)}
 
 
+def check_fp32(args) -> int:
+    """The fifth named configuration: the whole model in true 32-bit at Qwen1.5-MoE-A2.7B layer
+    sizes (57 GB of weights drawn on the device from seed 7) against the plain implementation of
+    tests/plain_model.py, which restates the same weights from the seed and runs in float32 on
+    the device too.  Requests with prompt lengths uniform in [1, 1024] go through the engine
+    whole, in portions of 256, mixed (up to four live, portions of some beside single tokens of
+    others, a pool so small that pages are used again) and, for the first eight, with the last
+    32 tokens one by one; every position's logits are compared.  Prints one JSON line."""
+    import random
+
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_model
+    import schedules
+    from ninfer_amd_mi50_b200 import kernels
+    from ninfer_amd_mi50_b200.config import EngineOptions
+    from ninfer_amd_mi50_b200.engine import load_runner
+
+    kernels.load()
+    cfg = dict(CONFIG, num_hidden_layers=args.layers or FULL_LAYERS)
+    seed, n = 7, args.requests
+    rnd = random.Random(11)
+    reqs = {f"r{i}": [rnd.randrange(cfg["vocab_size"]) for _ in range(rnd.randint(1, 1024))] for i in range(n)}
+
+    class Kept:
+        def __init__(self, drawn):
+            self.drawn, self.kept = drawn, {}
+
+        def __contains__(self, name):
+            return name in self.drawn
+
+        def __getitem__(self, name):
+            if name not in self.kept:
+                self.kept[name] = self.drawn[name]
+            return self.kept[name]
+
+    t0 = time.time()
+    weights = Kept(plain_model.RandomWeights(cfg, seed, device="cuda"))
+    pool = 4 * 1024
+    runner = load_runner(config=cfg, random_seed=seed,
+                         options=EngineOptions(dtype="float32", page_size=64, num_sequences=4, max_context=1024,
+                                               cache_tokens=pool, use_graph=False))
+    sys.stderr.write(f"[check-fp32] engine ready in {time.time() - t0:.0f}s\n")
+    # Eight requests at a time, so that the logits of all positions (0.6 MB a token) fit in memory.
+    names = list(reqs)
+    worst = {"whole": 0.0, "portions_of_256": 0.0, "mixed": 0.0, "tail_decoded": 0.0}
+    steps_run = {k: 0 for k in worst}
+    for g0 in range(0, n, 8):
+        group = {r: reqs[r] for r in names[g0:g0 + 8]}
+        plans = {"whole": schedules.whole(group),
+                 "portions_of_256": schedules.portions(group, cuts=[256]),
+                 "mixed": schedules.mixed(group, page=64, pool_tokens=pool, cuts=[256, 64, 7, 2, 130])}
+        if g0 == 0:
+            plans["tail_decoded"] = schedules.tail_decoded(group)
+        want = {r: plain_model.plain_forward(cfg, weights, t).cpu() for r, t in group.items()}
+        for how, steps in plans.items():
+            got = schedules.run_schedule(runner, steps)
+            kernels.check_status(how)
+            steps_run[how] += len(steps)
+            for r in group:
+                scale = want[r].abs().max().item()
+                worst[how] = max(worst[how], (got[r] - want[r]).abs().max().item() / scale)
+            del got
+        sys.stderr.write(f"[check-fp32] requests {g0}..{g0 + len(group) - 1}: worst error / largest logit so far "
+                         + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()) + f" ({time.time() - t0:.0f}s)\n")
+    ok = all(v <= 1e-4 for v in worst.values())
+    print(json.dumps({"check": "float32 whole model against the plain model", "model": "Qwen1.5-MoE-A2.7B sizes",
+                      "layers": cfg["num_hidden_layers"], "requests": n, "tokens": sum(len(t) for t in reqs.values()),
+                      "steps": steps_run,
+                      "worst_error_over_largest_logit": {k: float(f"{v:.3e}") for k, v in worst.items()},
+                      "bound": 1e-4, "ok": ok}))
+    return 0 if ok else 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers, for a quick look")
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--config", default="a2.7b", choices=sorted(PROFILES) + ["check-fp32"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers, for a quick look")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--long-prefill", action="store_true", help="also time prompts of 8,192 and 32,768 tokens")
+    ap.add_argument("--requests", type=int, default=64, help="check-fp32: number of requests")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
@@ -110,6 +200,12 @@ def main() -> int:
         return 2
     W = max(3, args.warmup)
     K = max(1, args.steps)
+    if args.config == "check-fp32":
+        return check_fp32(args)
+    CONFIG, FULL_LAYERS, model_name, PROMPT, value_batch, point_batches = PROFILES[args.config]
+    args.layers = args.layers or FULL_LAYERS
+    args.batch = args.batch or value_batch
+    long_context = 32768 if args.long_prefill else CONTEXT
 
     import torch
     from ninfer_amd_mi50_b200 import kernels
@@ -121,10 +217,10 @@ def main() -> int:
     kernels.load()
     pk = peaks()
     cfg = dict(CONFIG, num_hidden_layers=args.layers)
-    max_batch = 64 if not args.skip_points else args.batch
-    opts = EngineOptions(dtype="bfloat16", max_context=CONTEXT, prefill_chunk=PROMPT,
+    max_batch = max(point_batches + (args.batch,)) if not args.skip_points else args.batch
+    opts = EngineOptions(dtype="bfloat16", max_context=long_context, prefill_chunk=2048,
                          num_sequences=max_batch, page_size=64, cache_tokens=max_batch * CONTEXT,
-                         max_batched_tokens=PROMPT)
+                         max_batched_tokens=2048)
     t0 = time.time()
     engine = Engine(config=cfg, random_seed=2, options=opts)
     runner, cache, model = engine.runner, engine.cache, engine.runner.model
@@ -207,13 +303,15 @@ def main() -> int:
     achieved = (wbytes + kvbytes) / (ms / 1e3) / 1e9
 
     # ---- prefill of one 2,048-token prompt -------------------------------------------------
-    ptoks = torch.randint(0, V, (PROMPT,), generator=g).tolist()
+    PREFILL = 2048
+    ptoks = torch.randint(0, V, (32768 if args.long_prefill else PREFILL,), generator=g).tolist()
 
-    def prefill_once():
+    def prefill_once(tokens=PREFILL):
         cache.open("prefill")
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        runner.step([StepEntry("prefill", ptoks, [PROMPT - 1])])
+        for a in range(0, tokens, PREFILL):
+            runner.step([StepEntry("prefill", ptoks[a:a + PREFILL], [PREFILL - 1] if a + PREFILL >= tokens else [])])
         e1.record()
         torch.cuda.synchronize()
         cache.close("prefill")
@@ -229,15 +327,23 @@ def main() -> int:
     experts = c["num_experts_per_tok"] * 6 * H * c["moe_intermediate_size"]
     shared = 6 * H * c["shared_expert_intermediate_size"]
     router = 2 * H * (c["num_experts"] + 1)
-    attn = 4 * c["num_attention_heads"] * c["head_dim"] * (PROMPT + 1) / 2      # causal half, per token
-    pflops = PROMPT * L * (qkvo + experts + shared + router + attn) + 2 * H * V
-    prefill = {"value": round(PROMPT / (pms / 1e3), 1), "tokens": PROMPT, "ms": round(pms, 3),
-               "frac": round(pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    def prefill_flops(tokens):
+        attn = 4 * c["num_attention_heads"] * c["head_dim"] * (tokens + 1) / 2      # causal half, per token
+        return tokens * L * (qkvo + experts + shared + router + attn) + 2 * H * V
+
+    prefill = {"value": round(PREFILL / (pms / 1e3), 1), "tokens": PREFILL, "ms": round(pms, 3),
+               "frac": round(prefill_flops(PREFILL) / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    if args.long_prefill:
+        for n in (8192, 32768):
+            prefill_once(n)
+            lms = min(prefill_once(n) for _ in range(2))
+            prefill[f"tokens_{n}"] = {"value": round(n / (lms / 1e3), 1), "ms": round(lms, 3), "frac": round(
+                prefill_flops(n) / (lms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at batch 1 and 64 ----------------------------------------------------------
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
+        for b in point_batches:
             pm, _ = time_decode(b, max(8, K // 2), W)
             points[f"decode_b{b}"] = round(b / (pm / 1e3), 1)
 
@@ -267,12 +373,12 @@ def main() -> int:
             engine.scheduler._finish(r, "length")
 
     out = {
-        "metric": "decode tok/s @ batch 8 (Qwen1.5-MoE-A2.7B layer sizes, context 2048+)",
+        "metric": f"decode tok/s @ batch {args.batch} ({model_name} layer sizes, context {PROMPT}+)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cache)",
         "impl": "ours",
-        "config": {"model": "Qwen1.5-MoE-A2.7B sizes", "layers": L, "layers_full": FULL_LAYERS,
+        "config": {"model": f"{model_name} sizes", "layers": L, "layers_full": FULL_LAYERS,
                    "hidden": H, "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
                    "head_dim": c["head_dim"], "experts": c["num_experts"], "top_k": c["num_experts_per_tok"],
                    "moe_intermediate": c["moe_intermediate_size"],

@@ -143,8 +143,10 @@ class Ninfer:
             self._tokenizer = Tokenizer(path)
         return self._tokenizer
 
-    def tokenize(self, text: str) -> List[int]:
-        return self._tok().encode(text)
+    def tokenize(self, text: str, special: bool = False) -> List[int]:
+        """Raw text -> ids; with `special`, chat markers written in the text (``<|im_start|>`` ...)
+        become their own ids, as a rendered chat prompt needs (src/runtime/engine.cpp:115-120)."""
+        return self._tok().encode_with_special(text) if special else self._tok().encode(text)
 
     def detokenize(self, ids: Sequence[int]) -> str:
         return self._tok().decode(ids)
@@ -181,6 +183,13 @@ class Ninfer:
                  stop_ids: Iterable[int] = ()) -> List[List[int]]:
         p = SamplingParams(temperature, top_k, top_p, repetition_penalty, seed, max_new_tokens)
         return self._engine.generate(prompts, p, stop_ids)
+
+    def stream(self, prompt: Sequence[int], max_new_tokens: int = 512, temperature: float = 0.7,
+               top_k: int = 50, top_p: float = 0.95, repetition_penalty: float = 1.0, seed: int = 0,
+               stop_ids: Iterable[int] = ()):
+        """Token ids of one generation, each as soon as it exists."""
+        p = SamplingParams(temperature, top_k, top_p, repetition_penalty, seed, max_new_tokens)
+        return self._engine.stream(prompt, p, stop_ids)
 
     def close(self) -> None:
         self._engine = None

@@ -188,6 +188,22 @@ class Engine:
         self.run_until_idle()
         return [list(self.requests[i].generated) for i in ids]
 
+    def stream(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+               stop_ids: Iterable[int] = ()):
+        """Generate for one prompt and yield each token id as soon as its step has been read
+        back (the reference's CLI prints text as it comes, src/apps/ninfer.cpp:121-138).  Other
+        requests that are live meanwhile keep running in the same steps."""
+        rid = self.submit(prompt, params, stop_ids)
+        req = self.requests[rid]
+        sent = 0
+        while True:
+            while sent < len(req.generated):
+                yield req.generated[sent]
+                sent += 1
+            if req.status == "finished" or self.scheduler.idle:
+                return
+            self.step()
+
     def io_bytes(self):
         """(host-to-device, device-to-host) bytes moved by the steps so far: the packed step
         inputs in, the sampled token ids out."""

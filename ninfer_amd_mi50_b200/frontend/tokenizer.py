@@ -120,7 +120,10 @@ class Tokenizer:
         return out
 
     # ---- decoding -------------------------------------------------------------------
-    def decode(self, ids: Sequence[int], skip_special: bool = False) -> str:
+    def decode_bytes(self, ids: Sequence[int], skip_special: bool = False) -> bytes:
+        """The bytes the ids stand for.  A multi-byte character may be split between two tokens,
+        so text that is printed token by token is cut at the last complete character of these
+        bytes, not of each token's own."""
         buf = bytearray()
         for i in ids:
             tok = self.id_to_token.get(int(i))
@@ -131,4 +134,7 @@ class Tokenizer:
                     buf += tok.encode("utf-8")
                 continue
             buf += bytes(self.char_to_byte.get(c, ord("?")) for c in tok)
-        return buf.decode("utf-8", errors="replace")
+        return bytes(buf)
+
+    def decode(self, ids: Sequence[int], skip_special: bool = False) -> str:
+        return self.decode_bytes(ids, skip_special).decode("utf-8", errors="replace")
