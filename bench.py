@@ -108,7 +108,11 @@ def check_fp32(args) -> int:
     the device too.  Requests with prompt lengths uniform in [1, 1024] go through the engine
     whole, in portions of 256, mixed (up to four live, portions of some beside single tokens of
     others, a pool so small that pages are used again) and, for the first eight, with the last
-    32 tokens one by one; every position's logits are compared.  Prints one JSON line."""
+    32 tokens one by one; every position's logits are compared.  Where the engine and the plain
+    model pick different experts for a row (two router probabilities that agree to 1e-4 of their
+    value: among hundreds of thousands of selections a few fall that close), the plain model is
+    run again with the engine's choice, so that a tie broken the other way is not counted as an
+    error of 1e-2.  Prints one JSON line."""
     import random
 
     import torch
@@ -148,6 +152,7 @@ def check_fp32(args) -> int:
     names = list(reqs)
     worst = {"whole": 0.0, "portions_of_256": 0.0, "mixed": 0.0, "tail_decoded": 0.0}
     steps_run = {k: 0 for k in worst}
+    ties = 0
     for g0 in range(0, n, 8):
         group = {r: reqs[r] for r in names[g0:g0 + 8]}
         plans = {"whole": schedules.whole(group),
@@ -155,21 +160,31 @@ def check_fp32(args) -> int:
                  "mixed": schedules.mixed(group, page=64, pool_tokens=pool, cuts=[256, 64, 7, 2, 130])}
         if g0 == 0:
             plans["tail_decoded"] = schedules.tail_decoded(group)
-        want = {r: plain_model.plain_forward(cfg, weights, t).cpu() for r, t in group.items()}
+        want, own = {}, {}
+        for r, t in group.items():
+            own[r] = {}
+            want[r] = plain_model.plain_forward(cfg, weights, t, chosen=own[r]).cpu()
         for how, steps in plans.items():
-            got = schedules.run_schedule(runner, steps)
+            routing = {}
+            got = schedules.run_schedule(runner, steps, routing)
             kernels.check_status(how)
             steps_run[how] += len(steps)
-            for r in group:
-                scale = want[r].abs().max().item()
-                worst[how] = max(worst[how], (got[r] - want[r]).abs().max().item() / scale)
+            for r, toks in group.items():
+                ref = want[r]
+                if any(not torch.equal(routing[r][l], own[r][l]) for l in own[r]):
+                    slack = []
+                    ref = plain_model.plain_forward(cfg, weights, toks, forced=routing[r], slack=slack).cpu()
+                    ties += sum(int((routing[r][l] != own[r][l]).any(dim=1).sum()) for l in own[r])
+                    assert max(s.max().item() for s in slack) <= 1e-4, "the engine chose an expert that is no tie"
+                scale = ref.abs().max().item()
+                worst[how] = max(worst[how], (got[r] - ref).abs().max().item() / scale)
             del got
         sys.stderr.write(f"[check-fp32] requests {g0}..{g0 + len(group) - 1}: worst error / largest logit so far "
                          + ", ".join(f"{k} {v:.2e}" for k, v in worst.items()) + f" ({time.time() - t0:.0f}s)\n")
     ok = all(v <= 1e-4 for v in worst.values())
     print(json.dumps({"check": "float32 whole model against the plain model", "model": "Qwen1.5-MoE-A2.7B sizes",
                       "layers": cfg["num_hidden_layers"], "requests": n, "tokens": sum(len(t) for t in reqs.values()),
-                      "steps": steps_run,
+                      "steps": steps_run, "rows_with_a_tie_broken_the_other_way": ties,
                       "worst_error_over_largest_logit": {k: float(f"{v:.3e}") for k, v in worst.items()},
                       "bound": 1e-4, "ok": ok}))
     return 0 if ok else 1

@@ -88,6 +88,28 @@ inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
                                                   // did not keep it as its last error
 }
 
+// The same with the CTAs launched as clusters of `cluster_x` consecutive blocks of grid.x.
+template <typename... KArgs, typename... Args>
+inline void launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                   int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = cluster_x;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = chain_this_launch(NF_CHAIN_CLASS, stream) ? 2 : 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) note_launch_error(e);
+}
+
 #define NF_REQUIRE(cond, ...)            \
   do {                                   \
     if (!(cond)) {                       \

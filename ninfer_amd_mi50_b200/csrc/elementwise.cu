@@ -205,19 +205,95 @@ __global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, c
     float v[8];
     load8(y + (size_t)p * hidden + i, v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += w * v[e];
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, v[e], acc[e]);
   }
   if (shared) {
     float v[8];
     load8(shared + (size_t)t * hidden + i, v);
     const float gsc = gate ? 1.f / (1.f + expf(-gate[(size_t)t * gate_stride])) : 1.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += v[e] * gsc;
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(v[e], gsc, acc[e]);
   }
   __align__(16) __nv_bfloat16 o[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
   *reinterpret_cast<uint4*>(out + (size_t)t * hidden + i) = *reinterpret_cast<const uint4*>(o);
+}
+
+// The combine above and add_rmsnorm_x4_kernel in one pass over a row: the weighted sum of the
+// row's expert outputs (+ gated shared expert), rounded to bfloat16 as the separate combine
+// stores it, is added to the float32 residual row, and the row is normalised.  Same thread-to-
+// element map, same order of every sum as the two separate kernels, hence the same bits; one
+// launch and one round trip of [T, hidden] less.  A thread keeps its elements in registers:
+// rows of up to kFusedIters * 4 * blockDim elements.
+constexpr int kFusedIters = 8;
+
+template <bool GATHER>
+__global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv,
+                                               const float* __restrict__ wts,
+                                               const __nv_bfloat16* __restrict__ shared,
+                                               const float* __restrict__ gate, int gate_stride,
+                                               float* __restrict__ h, const int* __restrict__ rows,
+                                               const float* __restrict__ w, float eps,
+                                               __nv_bfloat16* __restrict__ out, int hidden, int k, int n_pairs) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  chain_release();
+  chain_wait(y, inv, wts, shared, gate, h, rows);
+  const int t = GATHER ? rows[r] : r;
+  float* hr = h + (size_t)t * hidden;
+  const float gsc = (shared && gate) ? 1.f / (1.f + expf(-gate[(size_t)t * gate_stride])) : 1.f;
+  float keep[kFusedIters][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < kFusedIters; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < k; ++j) {
+        const int p = inv[t * k + j];
+        if ((unsigned)p >= (unsigned)n_pairs) {        // not a sorted position of this step: skip, and say so
+          atomicCAS(&g_combine_index_error, 0, 1 + t);
+          continue;
+        }
+        const float wj = wts[t * k + j];
+        float v[4];
+        load4(y + (size_t)p * hidden + i, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(wj, v[e], acc[e]);
+      }
+      if (shared) {
+        float v[4];
+        load4(shared + (size_t)t * hidden + i, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(v[e], gsc, acc[e]);
+      }
+      float v[4];
+      load4(hr + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] += __bfloat162float(__float2bfloat16_rn(acc[e]));
+      if (!GATHER) store4(hr + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ss += v[e] * v[e];
+        keep[it][e] = v[e];
+      }
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv_rms = rsqrtf(ss / (float)hidden + eps);
+  __nv_bfloat16* o = out + (size_t)r * hidden;
+#pragma unroll
+  for (int it = 0; it < kFusedIters; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) {
+      float wv[4], v[4];
+      load4(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = keep[it][e] * inv_rms * wv[e];
+      store4(o + i, v);
+    }
+  }
 }
 
 static inline int row_threads(int n) {
@@ -301,6 +377,33 @@ extern "C" int nf_moe_combine(const void* y, const int* inv, const float* wts, c
   else
     moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)y, inv, wts, (const __nv_bfloat16*)shared, gate, gate_stride, (__nv_bfloat16*)out, hidden, k);
   return check_launch("moe_combine");
+}
+
+// 1 if the fused combine + add + norm kernel takes these sizes (bfloat16 only).
+extern "C" int nf_moe_combine_add_rmsnorm_fits(int hidden) {
+  if (hidden <= 0 || hidden % 4) return 0;
+  return hidden <= kFusedIters * 4 * row_threads(hidden / 4) ? 1 : 0;
+}
+
+// h[t] += bfloat16(sum_j wts[t, j] * y[inv[t, j]] + sigmoid(gate[t]) * shared[t]); out[r] = rmsnorm(h[t]) * w
+// for t = r (rows null; h is updated) or t = rows[r] (h is left as it is).  T: rows of h's step
+// (inv and wts have T * k entries), R: rows written.
+extern "C" int nf_moe_combine_add_rmsnorm(const void* y, const int* inv, const float* wts, const void* shared,
+                                          const float* gate, int gate_stride, float* h, const int* rows,
+                                          const float* w, float eps, void* out, int T, int R, int hidden,
+                                          int k, cudaStream_t stream) {
+  if (R == 0) return 0;
+  NF_REQUIRE(T > 0 && R > 0 && k > 0 && nf_moe_combine_add_rmsnorm_fits(hidden), "moe_combine_add_rmsnorm: bad sizes T=%d R=%d hidden=%d k=%d", T, R, hidden, k);
+  NF_REQUIRE((uintptr_t)y % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 8 == 0 && (uintptr_t)w % 16 == 0 &&
+             (!shared || (uintptr_t)shared % 8 == 0), "moe_combine_add_rmsnorm: operands must be 16-byte aligned");
+  const int t4 = row_threads(hidden / 4);
+  if (rows)
+    launch_chained(moe_combine_add_rmsnorm_kernel<true>, dim3(R), dim3(t4), 0, stream, (const __nv_bfloat16*)y, inv, wts,
+                   (const __nv_bfloat16*)shared, gate, gate_stride, h, rows, w, eps, (__nv_bfloat16*)out, hidden, k, T * k);
+  else
+    launch_chained(moe_combine_add_rmsnorm_kernel<false>, dim3(R), dim3(t4), 0, stream, (const __nv_bfloat16*)y, inv, wts,
+                   (const __nv_bfloat16*)shared, gate, gate_stride, h, rows, w, eps, (__nv_bfloat16*)out, hidden, k, T * k);
+  return check_launch("moe_combine_add_rmsnorm");
 }
 
 // 0, or 1 + the token whose combine met an index outside the step's pairs since the last call.

@@ -18,6 +18,13 @@
 // group; its 8 warps take interleaved 32-wide chunks of k and their partial sums are added
 // in warp order in shared memory.  The order of summation depends on K only, so a row's
 // result does not depend on the batch it is in.
+//
+// A product with few features and a long k (the shared expert's down projection: 2048 features
+// make 128 CTAs, each with 180 KB of weights to stream and nothing else on its SM) is launched
+// as clusters of 2 or 4 CTAs that share a feature tile and split k between them; the members'
+// sums meet in the first member's shared memory (distributed shared memory, the hardware
+// cluster barrier) and are added there in member order.  How many members is decided by the
+// product's shape alone.
 #define NF_CHAIN_CLASS 1
 #include "common.cuh"
 
@@ -25,6 +32,7 @@ namespace nf {
 
 constexpr int kWarps = 8;
 constexpr int kUnroll = 4;      // chunks of k in flight per warp (8 costs registers and occupancy: measured slower)
+constexpr int kMaxSplit = 4;    // most cluster members that split k between them
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v;
@@ -77,13 +85,19 @@ struct RopeEpilogue {
 // ROPE: the rotate-and-append epilogue (dense, unpacked, bfloat16 out); blockIdx.y then counts
 // (head, 8-dim group of the low half) instead of 16-feature tiles.
 template <int NT, bool SWIGLU, bool PACKED, typename TC, bool ROPE = false>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, NT == 1 ? 4 : 3)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bfloat16* __restrict__ W,
                    size_t w_group_stride, TC* __restrict__ Y, int ldy, int M, int N, int K,
                    const int* __restrict__ offsets, const int* __restrict__ x_rows, int x_div,
-                   const int* __restrict__ group_map, int early_index, int n_groups, RopeEpilogue rope) {
+                   const int* __restrict__ group_map, int early_index, int n_groups, RopeEpilogue rope, int ksplit) {
   // N: output columns (SWIGLU: the inner width; W has 2N rows, gate rows first)
+  // ksplit > 1: blockIdx.x counts (row tile, cluster member); member s takes the s-th part of k
   __shared__ float partial[kWarps][NT * 4 * 32];
+  __shared__ float others[kMaxSplit - 1][NT * 2 * 32 * 2];     // members 1.. leave their sums here, in member 0
+  const int member = ksplit > 1 ? (int)(blockIdx.x % (unsigned)ksplit) : 0;
+  const int row_tile = ksplit > 1 ? (int)(blockIdx.x / (unsigned)ksplit) : (int)blockIdx.x;
+  // every member announces itself; a member waits for the others right before its first remote store
+  if (ksplit > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   chain_release();
@@ -96,6 +110,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   if (!dense) chain_wait(X, offsets, x_rows, group_map);
   // row tiles vary fastest, so CTAs that share weight rows run together; with a group map,
   // blockIdx.z counts only the groups that have rows (a decode step uses few of the experts)
+  // (grouped products are never split over k: the early returns below leave no cluster waiting)
   const int group = group_map ? group_map[blockIdx.z] : blockIdx.z;
   if (group < 0 || group >= n_groups) {
     if (group >= n_groups) atomicCAS(&g_skinny_index_error, 0, 1);
@@ -109,8 +124,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     if (!waited) chain_wait();
     return;
   }
-  const int m0 = row_begin + blockIdx.x * (8 * NT);
-  if (m0 >= row_end) {
+  const int m0 = row_begin + row_tile * (8 * NT);
+  if (m0 >= row_end && ksplit <= 1) {
     if (!waited) chain_wait();
     return;
   }
@@ -175,8 +190,14 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
 
-  const int nchunks = (K + 31) >> 5;
-  for (int c0 = warp; c0 < nchunks; c0 += kWarps * kUnroll) {
+  // this member's chunks of k: [chunk_begin, nchunks)
+  int chunk_begin = 0, nchunks = (K + 31) >> 5;
+  if (ksplit > 1) {
+    const int per = (nchunks + ksplit - 1) / ksplit;
+    chunk_begin = min(member * per, nchunks);
+    nchunks = min(chunk_begin + per, nchunks);
+  }
+  for (int c0 = chunk_begin + warp; c0 < nchunks; c0 += kWarps * kUnroll) {
     // a round: ask for the weights and the matching pieces of X of kUnroll chunks at once, so
     // that the (L2) latency of X hides behind the (DRAM) latency of W
     uint4 a[kUnroll], b[kUnroll], xv[kUnroll][NT];
@@ -235,6 +256,31 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 #pragma unroll
     for (int i = 0; i < 4; ++i) partial[warp][(nt * 4 + i) * 32 + lane] = acc[nt][i];
   __syncthreads();
+  if (ksplit > 1) {
+    // members 1.. hand their sums to member 0 and are done; member 0 adds them in member order
+    if (member > 0) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");       // member 0 is running
+      for (int e = threadIdx.x; e < NT * 2 * 32; e += blockDim.x) {
+        const int l = e & 31, h = (e >> 5) & 1, nt = e >> 6;
+        float lo = 0.f, hi = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          lo += partial[w][(nt * 4 + h) * 32 + l];
+          hi += partial[w][(nt * 4 + h + 2) * 32 + l];
+        }
+        const unsigned a = (unsigned)__cvta_generic_to_shared(&others[member - 1][2 * e]);
+        unsigned remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(0));
+        asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote), "f"(lo), "f"(hi) : "memory");
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      return;
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");         // the others' sums are here
+  }
   for (int e = threadIdx.x; e < ntiles * 2 * 32; e += blockDim.x) {
     // e -> (tile nt, column half h of the fragment, lane l); this thread owns fragment
     // entries (c[h], c[h + 2]) = (row g, row g + 8) of token column 2 t + h
@@ -244,6 +290,10 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     for (int w = 0; w < kWarps; ++w) {
       lo += partial[w][(nt * 4 + h) * 32 + l];
       hi += partial[w][(nt * 4 + h + 2) * 32 + l];
+    }
+    for (int s = 1; s < ksplit; ++s) {
+      lo += others[s - 1][2 * e];
+      hi += others[s - 1][2 * e + 1];
     }
     const int gg = l >> 2, tt = l & 3;
     const int row = m0 + nt * 8 + 2 * tt + h;          // token (sorted position) of this column
@@ -287,6 +337,8 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
   }
 }
 
+int g_skinny_max_split = kMaxSplit;      // nf_set_skinny_max_split(): 1 turns the split over k off
+
 template <int NT, bool SWIGLU, bool PACKED, typename TC>
 static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y, int ldy, int M, int N,
                      int K, int groups, int max_rows, const int* offsets, const int* x_rows, int x_div,
@@ -294,9 +346,24 @@ static int launch_nt(const void* X, int ldx, const void* W, size_t wgs, void* Y,
   const int feat = SWIGLU ? 8 : 16;
   dim3 grid((max_rows + 8 * NT - 1) / (8 * NT), (N + feat - 1) / feat, group_map ? n_mapped : groups);
   NF_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "skinny_gemm: too many feature tiles or groups");
-  launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
-                 (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
-                 x_div, group_map, early_index, groups, RopeEpilogue{});
+  // A dense product whose CTAs would not even fill the SMs twice over splits k between the
+  // members of a cluster, as long as every member's warps still get a chunk each.
+  int ksplit = 1;
+  if (groups == 1 && !offsets && !x_rows && !group_map) {
+    const long long ctas = (long long)grid.x * grid.y;
+    const int nchunks = (K + 31) / 32;
+    while (ksplit * 2 <= g_skinny_max_split && ctas * ksplit * 2 <= 4 * 148 && nchunks / (ksplit * 2) >= kWarps) ksplit *= 2;
+  }
+  if (ksplit > 1) {
+    grid.x *= ksplit;
+    launch_chained_cluster(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream, ksplit,
+                           (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets,
+                           x_rows, x_div, group_map, early_index, groups, RopeEpilogue{}, ksplit);
+  } else {
+    launch_chained(skinny_gemm_kernel<NT, SWIGLU, PACKED, TC>, grid, dim3(kWarps * 32), 0, stream,
+                   (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, wgs, (TC*)Y, ldy, M, N, K, offsets, x_rows,
+                   x_div, group_map, early_index, groups, RopeEpilogue{}, 1);
+  }
   return check_launch("skinny_gemm");
 }
 
@@ -348,6 +415,12 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   return launch_sw<false, float>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
 }
 
+// Most cluster members a dense product may split k between (1, 2 or 4; 1: never split).
+extern "C" int nf_set_skinny_max_split(int n) {
+  nf::g_skinny_max_split = n < 1 ? 1 : (n > nf::kMaxSplit ? nf::kMaxSplit : n);
+  return 0;
+}
+
 // qkv = X Wqkv^T with bias, rotation and the append to the cache in the epilogue (see
 // RopeEpilogue): queries land rotated in Y [M, (Hq + 2 Hkv) D] (its key and value columns are
 // left untouched), keys and values in `pages` at (block_table[row_seg[r]], positions[r]).
@@ -371,11 +444,11 @@ extern "C" int nf_skinny_qkv_rope(const void* X, int ldx, const void* W, void* Y
   if (M <= 8)
     launch_chained(skinny_gemm_kernel<1, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r, 1);
   else
     launch_chained(skinny_gemm_kernel<2, false, false, __nv_bfloat16, true>, grid, dim3(kWarps * 32), 0, stream,
                    (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, (size_t)0, (__nv_bfloat16*)Y, ldy, M, N, K,
-                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r);
+                   (const int*)nullptr, (const int*)nullptr, 1, (const int*)nullptr, 0, 1, r, 1);
   return check_launch("skinny_qkv_rope");
 }
 

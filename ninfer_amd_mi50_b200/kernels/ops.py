@@ -47,6 +47,11 @@ TUNING = {
     # decode attention can merge its key blocks in the same launch (the last CTA of a row does
     # it); measured slower than the separate merge kernel at every batch size, so it is off
     "decode_merge_fused_max_rows": 0,
+    # the routed experts' weighted sum joins the residual add and the next norm in one kernel, up
+    # to this many rows (same bits either way; measured on B200: no difference to a decode step,
+    # which only loses a launch, and a prompt of 2,048 tokens 2 % slower fused, because the
+    # separate combine reads 16 bytes a lane and spreads a row over more CTAs); 0 turns it off
+    "fuse_combine_norm_max_rows": 64,
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -680,6 +685,27 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optio
               c_int(gate.shape[1] if gate is not None else 0), _p(out), c_int(T), c_int(H), c_int(k),
               c_int(_dt(y)), _stream())
     return out
+
+
+def can_fuse_combine_norm(y: torch.Tensor, hidden: int, rows: int) -> bool:
+    """Whether `moe_combine_add_rmsnorm` serves these operands (bfloat16 on the device, a row that
+    the kernel's threads can keep in registers, few enough rows)."""
+    return (y.is_cuda and y.dtype == torch.bfloat16 and rows <= TUNING["fuse_combine_norm_max_rows"]
+            and bool(_lib.load().nf_moe_combine_add_rmsnorm_fits(c_int(hidden))))
+
+
+def moe_combine_add_rmsnorm(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optional[torch.Tensor],
+                            gate: Optional[torch.Tensor], h: torch.Tensor, rows: Optional[torch.Tensor],
+                            weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """`moe_combine` and `add_rmsnorm` (`rows` None: h updated in place) or `add_rmsnorm_rows` in
+    one launch, bit for bit what the two give one after the other."""
+    _chk(y, "y", torch.bfloat16); _chk(wts, "wts", torch.float32); _chk(h, "h", torch.float32)
+    _chk(weight, "weight", torch.float32); _chk(out, "out", torch.bfloat16)
+    T, k = wts.shape
+    R = T if rows is None else rows.numel()
+    _lib.call("nf_moe_combine_add_rmsnorm", _p(y), _p(plan.inv), _p(wts), _p(shared), _p(gate),
+              c_int(gate.shape[1] if gate is not None else 0), _p(h), _p(rows), _p(weight), c_float(eps),
+              _p(out), c_int(T), c_int(R), c_int(h.shape[1]), c_int(k), _stream())
 
 
 # ---------------------------------------------------------------------------------------

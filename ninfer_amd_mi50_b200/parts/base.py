@@ -228,12 +228,41 @@ class Part:
         once at start-up, so that a limit is met there and not in the middle of a request."""
 
 
+@dataclass
+class RoutedSum:
+    """A feed-forward's output that has not been added up yet:
+
+        out[t] = sum_j wts[t, j] * y[plan.inv[t * k + j]]  (+ sigmoid(gate[t]) * shared[t])
+
+    A block hands it on as its pending contribution; a norm that knows the form (`takes_unsummed`)
+    adds it up inside its own kernel, any other consumer calls `materialize()` first.
+    """
+    y: torch.Tensor                      # [T * k, hidden] expert outputs in sorted order
+    plan: object                         # the routing plan (`inv` is what is used)
+    wts: torch.Tensor                    # float32 [T, k]
+    shared: Optional[torch.Tensor]       # [T, hidden] or None
+    gate: Optional[torch.Tensor]         # float32 [T, 1] gate logits or None
+    dtype: torch.dtype = torch.bfloat16
+
+    def materialize(self) -> torch.Tensor:
+        from .. import kernels
+        return kernels.moe_combine(self.y, self.plan, self.wts, self.shared, self.gate, self.dtype)
+
+
+def summed(delta):
+    """`delta` as a tensor (None stays None)."""
+    return delta.materialize() if isinstance(delta, RoutedSum) else delta
+
+
 class Norm(Part):
     """Normalisation fused with the residual sum.
 
     The residual stream `h` is float32 in both modes; `delta` is the previous part's
-    output in the engine dtype (or None).
+    output in the engine dtype (or None).  A norm with `takes_unsummed` also accepts a
+    `RoutedSum` as `delta`.
     """
+
+    takes_unsummed = False
 
     def add_norm(self, h: torch.Tensor, delta: Optional[torch.Tensor],
                  out_dtype: torch.dtype) -> torch.Tensor:
@@ -281,8 +310,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        """x [T, hidden] -> [T, hidden], both in the engine dtype."""
+    def forward(self, x: torch.Tensor, ctx: StepContext):
+        """x [T, hidden] -> [T, hidden], both in the engine dtype.  A routed feed-forward may
+        return a `RoutedSum` instead of the tensor (see there); `summed()` turns either into
+        the tensor."""
         raise NotImplementedError
 
 
@@ -291,12 +322,12 @@ class Block(Part):
 
     mixer: Mixer
 
-    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
-                cache: Optional[CacheView], state: Optional[torch.Tensor]
-                ) -> Optional[torch.Tensor]:
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext,
+                cache: Optional[CacheView], state: Optional[torch.Tensor]):
         """Advance the float32 residual stream `h` in place.
 
         `pending` is a contribution not yet added to `h` (so that the sum fuses with the
-        next norm); the return value is this block's own pending contribution.
+        next norm): a tensor, a `RoutedSum` or None; the return value is this block's own
+        pending contribution.
         """
         raise NotImplementedError

@@ -14,7 +14,7 @@ from typing import List, Optional
 import torch
 
 from ..registry import register_part
-from .base import Block, CacheView, FeedForward, Fetch, Mixer, Norm, StepContext, TensorSpec
+from .base import Block, CacheView, FeedForward, Fetch, Mixer, Norm, StepContext, TensorSpec, summed
 
 
 @register_part("block", "pre_norm")
@@ -46,6 +46,8 @@ class PreNormBlock(Block):
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: Optional[CacheView], state: Optional[torch.Tensor]
                 ) -> Optional[torch.Tensor]:
+        if not self.norm1.takes_unsummed:
+            pending = summed(pending)
         x1 = self.norm1.add_norm(h, pending, ctx.dtype)
         a = self.mixer.forward(x1, ctx, cache, state)
         x2 = self.norm2.add_norm(h, a, ctx.dtype)

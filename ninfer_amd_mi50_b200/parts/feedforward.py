@@ -22,7 +22,7 @@ import torch
 
 from .. import kernels
 from ..registry import register_part
-from .base import FeedForward, Fetch, StepContext, TensorSpec
+from .base import FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
 
 
 _FORK_LATE_ROWS = 32
@@ -179,7 +179,9 @@ class SparseMoeSwiglu(FeedForward):
         y = kernels.moe_gemm2(act, self.w2, plan, plan_is_older=True)
         if fork:
             main.wait_stream(side)
-            kernels.chain_break()           # the combine also reads what the other stream produced
+            kernels.chain_break()           # the kernel that adds up also reads what the other stream produced
         elif self.has_shared:
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
-        return kernels.moe_combine(y, plan, wts, shared, gate, x.dtype)
+        # not added up here: the next norm does it inside its own kernel (`RoutedSum`); whoever
+        # cannot calls `materialize()`, which is `kernels.moe_combine`
+        return RoutedSum(y, plan, wts, shared, gate, x.dtype)

@@ -17,7 +17,7 @@ import torch
 from .. import kernels
 from ..config.model_config import LayerCall, ModelPlan
 from ..registry import build_part, part_class
-from .base import CacheSpec, CacheView, Fetch, StateSpec, StepContext, TensorSpec
+from .base import CacheSpec, CacheView, Fetch, StateSpec, StepContext, TensorSpec, summed
 
 
 class DecoderModel:
@@ -91,5 +91,7 @@ class DecoderModel:
         R = ctx.logit_rows.numel()
         if R == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=ctx.device)
+        if not self.final_norm.takes_unsummed:
+            pending = summed(pending)
         x = self.final_norm.add_norm_rows(h, pending, ctx.logit_rows, ctx.dtype)
         return kernels.linear(x, self.head, out_dtype=torch.float32)

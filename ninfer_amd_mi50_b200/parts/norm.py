@@ -15,12 +15,13 @@ import torch
 
 from .. import kernels
 from ..registry import register_part
-from .base import Fetch, Norm, TensorSpec
+from .base import Fetch, Norm, RoutedSum, TensorSpec, summed
 
 
 @register_part("norm", "rms_norm")
 class RmsNorm(Norm):
     graph_safe = True
+    takes_unsummed = True
 
     def __init__(self, size: int, eps: float, prefix: str):
         self.size, self.eps, self.prefix = int(size), float(eps), prefix
@@ -35,12 +36,25 @@ class RmsNorm(Norm):
     def weight_bytes(self) -> int:
         return self.size * 4
 
+    def _fusable(self, delta, out_dtype, rows: int) -> bool:
+        return (isinstance(delta, RoutedSum) and out_dtype == torch.bfloat16
+                and kernels.can_fuse_combine_norm(delta.y, self.size, rows))
+
     def add_norm(self, h, delta, out_dtype):
         out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
-        kernels.add_rmsnorm(h, delta, self.weight, self.eps, out)
+        if self._fusable(delta, out_dtype, h.shape[0]):
+            # the experts' weighted sum, the residual add and the norm in one kernel
+            kernels.moe_combine_add_rmsnorm(delta.y, delta.plan, delta.wts, delta.shared, delta.gate, h, None,
+                                            self.weight, self.eps, out)
+        else:
+            kernels.add_rmsnorm(h, summed(delta), self.weight, self.eps, out)
         return out
 
     def add_norm_rows(self, h, delta, rows, out_dtype):
         out = torch.empty((rows.numel(), h.shape[1]), dtype=out_dtype, device=h.device)
-        kernels.add_rmsnorm_rows(h, delta, rows, self.weight, self.eps, out)
+        if self._fusable(delta, out_dtype, rows.numel()):
+            kernels.moe_combine_add_rmsnorm(delta.y, delta.plan, delta.wts, delta.shared, delta.gate, h, rows,
+                                            self.weight, self.eps, out)
+        else:
+            kernels.add_rmsnorm_rows(h, summed(delta), rows, self.weight, self.eps, out)
         return out

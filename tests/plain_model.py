@@ -240,18 +240,21 @@ def plain_router(x: torch.Tensor, w_router: torch.Tensor, k: int, norm_topk: boo
 
 
 def plain_sparse_ffn(x: torch.Tensor, weights, prefix: str, cfg: dict,
-                     forced_idx: Optional[torch.Tensor] = None, slack: Optional[list] = None
-                     ) -> torch.Tensor:
+                     forced_idx: Optional[torch.Tensor] = None, slack: Optional[list] = None,
+                     chosen: Optional[list] = None) -> torch.Tensor:
     """Routed experts summed in selection order with their routing weights
     (src/models/model.hip:355-433), plus the shared expert scaled by the sigmoid of its
     gate logit (Qwen2-MoE; absent from the reference).
 
     With `forced_idx`, `slack` (a list) receives for every row how far the forced choice
     falls short of the best one: (k-th largest probability - smallest forced probability)
-    / k-th largest, 0 when the choice is the plain one."""
+    / k-th largest, 0 when the choice is the plain one.  `chosen` (a list) receives the experts
+    used, [T, k]."""
     E, k = cfg["num_experts"], cfg["num_experts_per_tok"]
     idx, wts, prob = plain_router(x, weights[prefix + "gate.weight"], k,
                                   bool(cfg.get("norm_topk_prob", False)), forced_idx)
+    if chosen is not None:
+        chosen.append(idx.cpu())
     if forced_idx is not None and slack is not None:
         kth = torch.topk(prob, k, dim=-1).values[:, -1]
         worst = torch.gather(prob, 1, idx).min(dim=-1).values
@@ -307,12 +310,13 @@ class _As:
 
 
 def plain_forward(cfg: dict, weights, tokens: List[int], dtype: torch.dtype = torch.float32,
-                  forced: Optional[Dict[int, torch.Tensor]] = None, slack: Optional[list] = None
-                  ) -> torch.Tensor:
+                  forced: Optional[Dict[int, torch.Tensor]] = None, slack: Optional[list] = None,
+                  chosen: Optional[Dict[int, torch.Tensor]] = None) -> torch.Tensor:
     """Logits [T, vocab] of one request's whole token list.
 
     `forced` maps a sparse layer's index to the experts [T, k] its rows are to use (see
-    `plain_router`); `slack` collects how far those choices are from the plain ones.
+    `plain_router`); `slack` collects how far those choices are from the plain ones; `chosen`
+    (a dictionary) receives the experts each sparse layer used.
 
     Layer order as src/models/model.hip:206-444: x1 = norm(h); qkv (+ bias, Qwen2-MoE);
     rotate q, k; attention; h += o_proj(attn); x2 = norm(h); ffn; h += ffn.  The
@@ -346,7 +350,10 @@ def plain_forward(cfg: dict, weights, tokens: List[int], dtype: torch.dtype = to
         h = h + a @ W[p + "self_attn.o_proj.weight"].T
         x2 = plain_rms_norm(h, W[p + "post_attention_layernorm.weight"], eps)
         if layer_is_sparse(cfg, l):
-            f = plain_sparse_ffn(x2, W, p + "mlp.", cfg, None if forced is None else forced[l], slack)
+            used = [] if chosen is not None else None
+            f = plain_sparse_ffn(x2, W, p + "mlp.", cfg, None if forced is None else forced[l], slack, used)
+            if chosen is not None:
+                chosen[l] = used[0]
         else:
             f = plain_swiglu_mlp(x2, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
                                  W[p + "mlp.down_proj.weight"])

@@ -103,6 +103,31 @@ def test_linear(K, dtype, M, N, K_, bf16_path):
         close(out, ref, out.dtype)
 
 
+@pytest.mark.parametrize("M,N,K_", [(1, 2048, 5632), (8, 2048, 2048), (16, 3584, 20480), (3, 200, 1000), (9, 96, 1288)])
+def test_dense_product_split_over_k_by_a_cluster(K, M, N, K_):
+    """Few features and a long k: clusters of 2 or 4 CTAs share a feature tile, split k and add
+    their sums in the first member's shared memory, in member order.  Against the plain twin,
+    against the same kernel without the split (another order of the sum: close, not equal), and
+    twice (same bits)."""
+    dtype = torch.bfloat16
+    x, w = rnd((M, K_), dtype, 71), rnd((N, K_), dtype, 72, 0.05)
+    lib = K.load()
+    split = [K.linear(x, w) for _ in range(2)]
+    head = K.linear(x, w, out_dtype=torch.float32)
+    try:
+        lib.nf_set_skinny_max_split(1)
+        whole = K.linear(x, w)
+    finally:
+        lib.nf_set_skinny_max_split(4)
+    assert torch.equal(split[0], split[1])
+    close(split[0], P.linear(x, w), dtype)
+    close(split[0], whole, dtype)
+    close(head, x.float() @ w.float().T, torch.float32 if False else dtype)
+    gu = rnd((2 * 104, K_), dtype, 73, 0.05)
+    a = K.linear_swiglu(x, gu)
+    close(a, P.linear_swiglu(x, gu), dtype)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,I,K_", [(1, 72, 200), (37, 100, 96), (70, 33, 300), (9, 1408, 2048)])
 def test_linear_swiglu_and_silu_mul(K, dtype, M, I, K_, bf16_path):

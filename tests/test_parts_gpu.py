@@ -111,6 +111,7 @@ def test_attention_part(dtype, Hq, Hkv, D, window, bias):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_dense_and_sparse_feed_forward_parts(dtype):
+    from ninfer_amd_mi50_b200.parts.base import summed
     from ninfer_amd_mi50_b200.parts.feedforward import DenseSwiglu, SparseMoeSwiglu
     H = 200
     x = torch.randn(23, H).to(torch.bfloat16).float()
@@ -128,13 +129,54 @@ def test_dense_and_sparse_feed_forward_parts(dtype):
         cfg = {"num_experts": 6, "num_experts_per_tok": 3, "norm_topk_prob": norm_topk,
                "shared_expert_intermediate_size": shared}
         want = PM.plain_sparse_ffn(x, t, "m.", cfg)
-        got = moe.forward(x.cuda().to(dtype), ctx).float().cpu()
+        got = summed(moe.forward(x.cuda().to(dtype), ctx)).float().cpu()
         if dtype == torch.float32:
             torch.testing.assert_close(got, want, **tol(dtype))
         else:
             # a row whose k-th and (k+1)-th experts are within rounding may take the other one
             bad = ((got - want).abs().max(dim=1).values > 3e-2).sum().item()
             assert bad <= 2
+
+
+@pytest.mark.parametrize("H,k,T", [(200, 3, 23), (2048, 4, 9), (3584, 8, 130), (8192, 2, 3)])
+@pytest.mark.parametrize("with_shared", [True, False])
+def test_norm_adds_up_the_routed_sum_in_its_own_kernel(H, k, T, with_shared):
+    """A routed feed-forward hands its output on unsummed; the RMS norm adds it up, adds it to
+    the residual row and normalises in one kernel.  The bits are those of the three steps done
+    apart (combine, add, norm), for whole steps (the residual is updated) and for chosen rows
+    (it is not)."""
+    from ninfer_amd_mi50_b200 import kernels
+    from ninfer_amd_mi50_b200.parts.base import RoutedSum
+    from ninfer_amd_mi50_b200.parts.norm import RmsNorm
+    g = torch.Generator().manual_seed(H + k)
+    E = 2 * k + 1
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    plan = kernels.moe_plan(idx, E)
+    y = torch.randn(T * k, H, generator=g).to(torch.bfloat16).cuda()
+    wts = torch.rand(T, k, generator=g).cuda()
+    shared = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda() if with_shared else None
+    gate = torch.randn(T, 1, generator=g).cuda() if with_shared else None
+    norm = RmsNorm(size=H, eps=1e-6, prefix="n.")
+    norm.weight = (1 + 0.05 * torch.randn(H, generator=g)).cuda()
+    h0 = torch.randn(T, H, generator=g).cuda()
+    delta = RoutedSum(y, plan, wts, shared, gate, torch.bfloat16)
+    assert norm._fusable(delta, torch.bfloat16, min(T, 64))
+    kernels.TUNING["fuse_combine_norm_max_rows"] = 10 ** 9
+    h1, h2 = h0.clone(), h0.clone()
+    fused = norm.add_norm(h1, delta, torch.bfloat16)
+    apart = norm.add_norm(h2, delta.materialize(), torch.bfloat16)
+    assert torch.equal(fused, apart) and torch.equal(h1, h2) and not torch.equal(h1, h0)
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32).cuda()
+    h3 = h0.clone()
+    fused = norm.add_norm_rows(h3, delta, rows, torch.bfloat16)
+    apart = norm.add_norm_rows(h0.clone(), delta.materialize(), rows, torch.bfloat16)
+    assert torch.equal(fused, apart) and torch.equal(h3, h0)
+    kernels.TUNING["fuse_combine_norm_max_rows"] = 64
+    assert kernels.index_status() == 0
+    # a wider row than the kernel keeps in registers, many rows, or float32: the three steps are done apart
+    assert not kernels.can_fuse_combine_norm(y, 8192 + 4, 1)
+    assert not kernels.can_fuse_combine_norm(y, H, 65)
+    assert not norm._fusable(RoutedSum(y.float(), plan, wts, None, None, torch.float32), torch.float32, 1)
 
 
 def test_rotary_table_follows_single_precision_pow():
