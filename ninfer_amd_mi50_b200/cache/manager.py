@@ -3,8 +3,8 @@ and slots of fixed-size per-request state.
 
 Layers whose mixers need the same kind of cache (all keys; a window of them) with the
 same geometry form a *group*.  Each group has its own page pool, its own device tensor
-``[layers_in_group, num_pages + 1, 2, kv_heads, page_size, head_dim]`` and its own block
-table per request.  Page ``num_pages`` of every group is a null page that padding rows of
+``[layers_in_group, num_pages + 1, *page shape]`` (the page shape is the spec's: keys and values
+``[2, kv_heads, page_size, head_dim]``, or rows of any width) and its own block table per request.  Page ``num_pages`` of every group is a null page that padding rows of
 a replayed graph write to; it is never handed out.
 
 A request's pages are given back when it is closed; in a window group, also as soon as
@@ -79,9 +79,8 @@ class CacheManager:
             g.slots.append(slot)
         if allocate:
             for g in self.groups:
-                s = g.spec
-                g.pages = torch.zeros((len(g.slots), num_pages + 1, 2, s.num_kv_heads,
-                                       self.page_size, s.head_dim), dtype=dtype, device=self.device)
+                g.pages = torch.zeros((len(g.slots), num_pages + 1, *g.spec.page_shape(self.page_size)),
+                                      dtype=dtype, device=self.device)
         # state slots
         self._free_slots = list(range(self.max_requests - 1, -1, -1))
         self.state_specs = list(state_specs)
@@ -102,7 +101,7 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Cache bytes one token occupies across all layers (window groups included)."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * 2 * g.spec.num_kv_heads * g.spec.head_dim * el for g in self.groups)
+        return sum(len(g.slots) * g.spec.elements_per_token() * el for g in self.groups)
 
     def total_bytes(self) -> int:
         return sum(g.pages.numel() * g.pages.element_size() for g in self.groups if g.pages is not None)

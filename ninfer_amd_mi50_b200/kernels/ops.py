@@ -52,6 +52,12 @@ TUNING = {
     # which only loses a launch, and a prompt of 2,048 tokens 2 % slower fused, because the
     # separate combine reads 16 bytes a lane and spreads a row over more CTAs); 0 turns it off
     "fuse_combine_norm_max_rows": 64,
+    # a shared expert runs beside the routed path, on a second stream, in steps of up to
+    # `shared_fork_max_rows` rows (larger steps fill the device with either alone); it is started
+    # beside the router up to `shared_fork_late_rows` rows and after it beyond (measured on decode
+    # steps at A2.7B sizes: starting late is 3 % faster at 48 and 64 rows, 5 % slower at 16)
+    "shared_fork_max_rows": 64,
+    "shared_fork_late_rows": 32,
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))

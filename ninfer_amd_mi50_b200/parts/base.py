@@ -49,19 +49,35 @@ Fetch = Callable[[str], torch.Tensor]   # tensor name -> device tensor in its ro
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """Paged keys and values for one cache slot.
+    """What one cache slot keeps per token, in pages.
 
-    kind "full": every key stays until the request ends.
-    kind "window": only the last `window` keys are read; pages that the window has
+    kind "full": every entry stays until the request ends.
+    kind "window": only the last `window` entries are read; pages that the window has
     passed go back to the pool.
+
+    The usual form is keys and values of `num_kv_heads` heads of `head_dim`: a page is
+    ``[2, num_kv_heads, page_size, head_dim]`` (keys, then values; one head's keys of a page are
+    one contiguous run), which is what the attention kernels read.  A mixer that keeps
+    something else per token (one compressed latent row, keys and values of different widths
+    packed side by side) gives `row_width` instead: a page is then ``[page_size, row_width]``
+    and the mixer reads and writes it itself.  The cache manager only ever asks `page_shape`.
     """
     kind: str
-    num_kv_heads: int
-    head_dim: int
+    num_kv_heads: int = 0
+    head_dim: int = 0
     window: Optional[int] = None
+    row_width: int = 0
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        if self.row_width:
+            return (page_size, self.row_width)
+        return (2, self.num_kv_heads, page_size, self.head_dim)
+
+    def elements_per_token(self) -> int:
+        return self.row_width if self.row_width else 2 * self.num_kv_heads * self.head_dim
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.row_width)
 
 
 @dataclass(frozen=True)
@@ -75,7 +91,7 @@ class StateSpec:
 class CacheView:
     """What a mixer call sees of one cache slot during a step."""
     spec: CacheSpec
-    pages: torch.Tensor          # [num_pages + 1, 2, kv_heads, page_size, head_dim]
+    pages: torch.Tensor          # [num_pages + 1, *spec.page_shape(page_size)]
     block_table: torch.Tensor    # int32 [S, width]: page of (segment, position // page_size)
     page_size: int
     append: bool = True
@@ -318,9 +334,21 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """Arrangement of norms, mixer and feed-forward around the residual stream."""
+    """Arrangement of norms, mixer and feed-forward around the residual stream.
+
+    The model asks the block, not the mixer, what the layer keeps between steps: pages
+    (`cache_spec`) and a slab of fixed-size state per request (`state_spec`).  The usual block
+    passes its mixer's answers on; an arrangement whose feed-forward (or the block itself)
+    keeps state answers for it and hands `state` to whichever part it belongs to.
+    """
 
     mixer: Mixer
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return self.mixer.cache_spec()
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return self.mixer.state_spec()
 
     def forward(self, h: torch.Tensor, pending, ctx: StepContext,
                 cache: Optional[CacheView], state: Optional[torch.Tensor]):

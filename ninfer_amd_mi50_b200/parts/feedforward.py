@@ -25,8 +25,6 @@ from ..registry import register_part
 from .base import FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
 
 
-_FORK_LATE_ROWS = 32
-_FORK_MAX_ROWS = 64
 _SIDE_STREAMS = {}
 
 
@@ -153,7 +151,7 @@ class SparseMoeSwiglu(FeedForward):
         # The shared expert needs nothing from the router, so on small steps (where kernels are
         # too short to fill the device) it runs beside the routed path on a second stream;
         # inside a captured graph that becomes a parallel branch.
-        fork = self.has_shared and x.is_cuda and x.shape[0] <= _FORK_MAX_ROWS
+        fork = self.has_shared and x.is_cuda and x.shape[0] <= kernels.TUNING["shared_fork_max_rows"]
         shared = None
 
         def start_shared():
@@ -166,7 +164,7 @@ class SparseMoeSwiglu(FeedForward):
         # With few rows the shared expert starts beside the router (whose kernels leave the memory
         # idle); from some tens of rows on it is better started after it, beside the experts'
         # products (measured on decode steps: 3 % faster at 48 and 64 rows, 5 % slower at 16).
-        late = x.shape[0] > _FORK_LATE_ROWS
+        late = x.shape[0] > kernels.TUNING["shared_fork_late_rows"]
         if fork and not late:
             main, side, shared = start_shared()
         idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,

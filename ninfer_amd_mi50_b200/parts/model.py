@@ -58,11 +58,11 @@ class DecoderModel:
         self.head = self.embedding if self.plan.tie_word_embeddings else fetch(self.plan.head_name)
 
     def cache_specs(self) -> List[Optional[CacheSpec]]:
-        """Slot i belongs to layer i's mixer; None if that mixer keeps no keys/values."""
-        return [b.mixer.cache_spec() for b in self.blocks]
+        """Slot i belongs to layer i; None if that layer keeps nothing in pages."""
+        return [b.cache_spec() for b in self.blocks]
 
     def state_specs(self) -> List[Optional[StateSpec]]:
-        return [b.mixer.state_spec() for b in self.blocks]
+        return [b.state_spec() for b in self.blocks]
 
     @property
     def graph_safe(self) -> bool:
