@@ -57,27 +57,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
 
 // Four elements a thread per step (float4 of h, 4 values of delta / out); same sums in the
 // same order per thread as the scalar kernel would give with a stride of 4 * blockDim.
-__device__ __forceinline__ void load4(const float* p, float* v) {
-  const float4 a = *reinterpret_cast<const float4*>(p);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-}
-__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-}
-__device__ __forceinline__ void store4(float* p, const float* v) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-__device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-  uint2 raw;
-  raw.x = *reinterpret_cast<unsigned*>(&a);
-  raw.y = *reinterpret_cast<unsigned*>(&b);
-  *reinterpret_cast<uint2*>(p) = raw;
-}
-
 template <typename T, bool GATHER>
 __global__ void add_rmsnorm_x4_kernel(float* __restrict__ h, const T* __restrict__ delta,
                                       const int* __restrict__ rows, const float* __restrict__ w,

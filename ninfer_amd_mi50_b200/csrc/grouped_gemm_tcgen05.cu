@@ -70,20 +70,29 @@ struct __align__(8) Barriers {
 // producer is not held back by the epilogue: while the epilogue warps drain an item's
 // accumulator, the stages fill with the next item's first k tiles, so the memory pipe never
 // goes idle between items.  Wp: packed weights [groups][feature tiles][k tiles][A_ROWS][64].
-template <bool SWIGLU>
+// PAIR (second product only): an item is two neighbouring feature tiles of one expert, with an
+// accumulator each, over the same token rows.  With a hundred and more rows an expert, a tile's
+// token rows (rows x K) weigh as much as its weights (128 x K), and every feature tile of the
+// expert fetches them again from L2; the CTA's load pipe, not HBM, is then the bound.  Two tiles
+// an item halve that traffic.  (The first product has gate and up in one item already.)
+template <bool SWIGLU, bool PAIR>
 __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_constant__ CUtensorMap map_x,
                        const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int ldo,
                        int n_features, int K, int groups) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = (SWIGLU ? 2 : 1) * kBM * kBK * 2;     // gate (+ up) tile
+  static_assert(!(SWIGLU && PAIR), "the first product already has two weight tiles an item");
+  constexpr int TILE_BYTES = kBM * kBK * 2;
+  constexpr int A_BYTES = (SWIGLU || PAIR ? 2 : 1) * TILE_BYTES;     // gate (+ up) tile, or two feature tiles
+  constexpr int FT_STEP = PAIR ? 2 : 1;                               // feature tiles an item covers
   constexpr int BOX_BYTES = kXBox * kBK * 2;
   __shared__ int s_max_rows;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_steps = (K + kBK - 1) / kBK;
   const int n_ftiles = (n_features + kBM - 1) / kBM;
+  const int n_fitems = (n_ftiles + FT_STEP - 1) / FT_STEP;      // items along the features
 
   // stage geometry, the same for every item: weights + as many 64-row boxes as the largest
   // pass of any group needs
@@ -95,7 +104,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
     if (mx) atomicMax(&s_max_rows, mx);
   }
   __syncthreads();
-  constexpr int kAccBuffers = SWIGLU ? 1 : 2;      // accumulators of kBNMax columns that fit beside each other
+  constexpr int kAccBuffers = (SWIGLU || PAIR) ? 1 : 2;      // accumulators of kBNMax columns that fit beside each other
   const int max_boxes = (min(max(s_max_rows, 1), kBNMax) + kXBox - 1) / kXBox;
   const int stage_bytes = A_BYTES + max_boxes * BOX_BYTES;
   const int tail_bytes = (int)sizeof(Barriers) + (groups + 1) * (int)sizeof(int);
@@ -112,7 +121,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
     s_pass_start[groups] = run;
   }
   __syncthreads();
-  const int n_items = s_pass_start[groups] * n_ftiles;
+  const int n_items = s_pass_start[groups] * n_fitems;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -136,12 +145,15 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
       bool ok = true;
       int group = 0;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const int gp = item / n_ftiles, ft = item - gp * n_ftiles;      // global pass index, feature tile
+        const int gp = item / n_fitems, ft = (item - gp * n_fitems) * FT_STEP;      // global pass index, feature tile
         while (s_pass_start[group + 1] <= gp) ++group;
         const int pass = gp - s_pass_start[group];
         const int row_begin = offsets[group], n_rows = offsets[group + 1] - row_begin;
+        constexpr int W_TILE_BYTES = SWIGLU ? 2 * TILE_BYTES : TILE_BYTES;    // one feature tile's weights of one k step
         const unsigned char* w_tile = reinterpret_cast<const unsigned char*>(Wp) +
-                                      ((size_t)group * n_ftiles + ft) * k_steps * A_BYTES;
+                                      ((size_t)group * n_ftiles + ft) * k_steps * W_TILE_BYTES;
+        const bool second = PAIR && ft + 1 < n_ftiles;                    // the pair's second tile exists
+        const int a_bytes = PAIR ? (second ? 2 : 1) * TILE_BYTES : A_BYTES;
         {
           const int x_row = row_begin + pass * kBNMax;
           const int boxes = (min(kBNMax, n_rows - pass * kBNMax) + kXBox - 1) / kXBox;
@@ -149,8 +161,14 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
             const int s = it % stages;
             if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1, &g_tc_error)) { ok = false; break; }
             unsigned char* st = smem + (size_t)s * stage_bytes;
-            mbar_expect_tx(&bars->full[s], A_BYTES + boxes * BOX_BYTES);
-            bulk_load(st, w_tile + (size_t)ks * A_BYTES, A_BYTES, &bars->full[s]);
+            mbar_expect_tx(&bars->full[s], a_bytes + boxes * BOX_BYTES);
+            if (PAIR) {
+              bulk_load(st, w_tile + (size_t)ks * TILE_BYTES, TILE_BYTES, &bars->full[s]);
+              if (second)
+                bulk_load(st + TILE_BYTES, w_tile + ((size_t)k_steps + ks) * TILE_BYTES, TILE_BYTES, &bars->full[s]);
+            } else {
+              bulk_load(st, w_tile + (size_t)ks * A_BYTES, A_BYTES, &bars->full[s]);
+            }
             for (int b = 0; b < boxes; ++b)
               tma_load_2d(st + A_BYTES + b * BOX_BYTES, &map_x, ks * kBK, x_row + b * kXBox, &bars->full[s]);
             issued = it + 1;
@@ -173,10 +191,11 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
       bool ok = true;
       int group = 0;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++pass_ctr) {
-        const int gp = item / n_ftiles;
+        const int gp = item / n_fitems;
         while (s_pass_start[group + 1] <= gp) ++group;
         const int pass = gp - s_pass_start[group];
         const int n_rows = offsets[group + 1] - offsets[group];
+        const bool second = SWIGLU || (PAIR && (item - gp * n_fitems) * FT_STEP + 1 < n_ftiles);
         {
           // without the second (up) accumulator there is room for two: the epilogue of one item
           // runs under the products of the next
@@ -199,7 +218,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
               // 16 k = 32 bytes further along the swizzled row: +2 in the address field
               const unsigned acc = (ks > 0 || kk > 0) ? 1u : 0u;
               tc_mma(acc_tmem, a0 + 2 * kk, b + 2 * kk, idesc, acc);
-              if (SWIGLU) tc_mma(acc_tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
+              if (second) tc_mma(acc_tmem + kBNMax, a1 + 2 * kk, b + 2 * kk, idesc, acc);
             }
             tc_commit(&bars->empty[s]);          // the stage is free once these MMAs have read it
           }
@@ -214,21 +233,23 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
     bool ok = true;
     int group = 0;
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++pass_ctr) {
-      const int gp = item / n_ftiles, ft = item - gp * n_ftiles;
+      const int gp = item / n_fitems, ft0 = (item - gp * n_fitems) * FT_STEP;
       while (s_pass_start[group + 1] <= gp) ++group;
       const int pass = gp - s_pass_start[group];
       const int row_begin = offsets[group], n_rows = offsets[group + 1] - row_begin;
-      const int f = ft * kBM + quad * 32 + lane;
+      const int tiles_here = (PAIR && ft0 + 1 < n_ftiles) ? 2 : 1;      // accumulators of this item to drain
       {
         const int ab = pass_ctr % kAccBuffers, aph = (pass_ctr / kAccBuffers) & 1;
         if (!mbar_wait(&bars->acc_full[ab], aph, stop, 4, &g_tc_error)) { ok = false; break; }
         tc_fence_after();
         const int p0 = row_begin + pass * kBNMax;
         const int valid = min(kBNMax, n_rows - pass * kBNMax);
-        const unsigned lane_addr = tmem + ab * kBNMax + ((unsigned)(quad * 32) << 16);
         // Each warp turns kWarpCols columns of every round of kRoundCols into bfloat16 values in
         // registers; after the last round's loads the accumulator goes back to the MMA warp, and
         // the stores run under the next item's products.
+        for (int tile = 0; tile < tiles_here; ++tile) {
+        const int f = (ft0 + tile) * kBM + quad * 32 + lane;
+        const unsigned lane_addr = tmem + (ab + tile) * kBNMax + ((unsigned)(quad * 32) << 16);
         for (int r0 = 0; r0 < valid; r0 += kRoundCols) {
           const int c0 = r0 + half * kWarpCols;
           unsigned pk[kWarpCols / 2];       // two bfloat16 results a register
@@ -254,7 +275,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
               }
             }
           }
-          if (r0 + kRoundCols >= valid) {
+          if (r0 + kRoundCols >= valid && tile + 1 == tiles_here) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->acc_empty[ab]);
@@ -266,6 +287,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
                 out[(size_t)(p0 + c0 + c) * ldo + f] =
                     __ushort_as_bfloat16((unsigned short)((c & 1) ? pk[c / 2] >> 16 : pk[c / 2] & 0xffffu));
           }
+        }
         }
       }
     }
@@ -281,13 +303,13 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
 
 // ---- host ---------------------------------------------------------------------------------------
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool PAIR>
 static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, void* out, int ldo,
                      int n_features, int K, int groups, cudaStream_t stream) {
   const size_t smem = (size_t)kSmemBudget + 1024;
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<SWIGLU>,
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<SWIGLU, PAIR>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     NF_REQUIRE(e == cudaSuccess, "grouped_gemm_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     set = true;
@@ -301,14 +323,26 @@ static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, 
   }
   // at least one pass per non-empty group; the kernel itself counts the exact number of items
   const int grid = n_sm;
-  grouped_gemm_tc_kernel<SWIGLU><<<grid, kTcThreads, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
+  grouped_gemm_tc_kernel<SWIGLU, PAIR><<<grid, kTcThreads, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
                                                              (__nv_bfloat16*)out, ldo, n_features, K, groups);
   return check_launch("grouped_gemm_tc");
 }
 
 }  // namespace nf
 
+namespace nf {
+int g_tc_pair = 1, g_tc_pair_min_rows = 64;
+}
+
 using namespace nf;
+
+// 0: the second product never pairs feature tiles; otherwise it does from `min_rows` rows an
+// expert (on average) on.
+extern "C" int nf_set_grouped_gemm_pair(int on, int min_rows) {
+  g_tc_pair = on ? 1 : 0;
+  if (min_rows > 0) g_tc_pair_min_rows = min_rows;
+  return 0;
+}
 
 // out[p, :n_features] for sorted rows p of every group.  X holds the rows in sorted order
 // ([total_rows, K], already gathered).  Wp holds the groups' weights packed as
@@ -325,8 +359,12 @@ extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const voi
   NF_REQUIRE(groups <= kMaxGroupsTc, "grouped_gemm_tc: %d groups, at most %d", groups, kMaxGroupsTc);
   CUtensorMap mx;
   if (int rc = make_map(&mx, X, total_rows, K, kXBox)) return rc;
-  if (swiglu) return launch_tc<true>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
-  return launch_tc<false>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
+  if (swiglu) return launch_tc<true, false>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
+  // two feature tiles an item once an expert's rows weigh about as much as a tile's weights
+  // (decided by the counts the host knows: all rows, all groups)
+  if (g_tc_pair && total_rows >= (long long)g_tc_pair_min_rows * groups)
+    return launch_tc<false, true>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
+  return launch_tc<false, false>(Wp, mx, offsets, out, ldo, n_features, K, groups, stream);
 }
 
 // A wait that nothing will ever satisfy, given `polls` polls: the bounded wait runs out, records

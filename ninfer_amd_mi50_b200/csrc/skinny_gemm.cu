@@ -197,19 +197,16 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
     chunk_begin = min(member * per, nchunks);
     nchunks = min(chunk_begin + per, nchunks);
   }
-  // Rounds of equal size: a warp with 6 chunks asks for 3 + 3, not 4 + 2, so that its last round
-  // keeps as many loads in flight as its first.
-  const int per_warp = (nchunks - chunk_begin + kWarps - 1) / kWarps;
-  const int rounds = (per_warp + kUnroll - 1) / kUnroll;
-  const int round_chunks = rounds > 0 ? (per_warp + rounds - 1) / rounds : kUnroll;
-  for (int c0 = chunk_begin + warp; c0 < nchunks; c0 += kWarps * round_chunks) {
+  // (rounds of equal size - 3 + 3 chunks instead of 4 + 2 - were tried: the run-time round size cost
+  // 15 % of a decode step)
+  for (int c0 = chunk_begin + warp; c0 < nchunks; c0 += kWarps * kUnroll) {
     // a round: ask for the weights and the matching pieces of X of kUnroll chunks at once, so
     // that the (L2) latency of X hides behind the (DRAM) latency of W
     uint4 a[kUnroll], b[kUnroll], xv[kUnroll][NT];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int k = (c0 + u * kWarps) * 32;
-      const bool live = u < round_chunks && c0 + u * kWarps < nchunks;
+      const bool live = c0 + u * kWarps < nchunks;
       if (PACKED && live) {
         const int kk = k + 8 * t;                   // < padded K: the padding holds zeros
         const __nv_bfloat16* tile = Wg + ptile + (size_t)(kk >> 6) * (TROWS * 64);
@@ -234,7 +231,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int k = (c0 + u * kWarps) * 32;
-      const bool in = u < round_chunks && c0 + u * kWarps < nchunks && k + 8 * t + 8 <= K;
+      const bool in = c0 + u * kWarps < nchunks && k + 8 * t + 8 <= K;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         xv[u][nt] = make_uint4(0, 0, 0, 0);

@@ -42,6 +42,8 @@ def load() -> ctypes.CDLL:
                 # kernel classes that keep the attribute: 1 streaming products, 2 norm and combine,
                 # 4 rotary, 8 decode attention, 16 router
                 lib.nf_set_chained_launch(int(mask))
+            if os.environ.get("NINFER_SKINNY_MAX_SPLIT"):
+                lib.nf_set_skinny_max_split(int(os.environ["NINFER_SKINNY_MAX_SPLIT"]))   # 1: no split over k
             if os.environ.get("NINFER_CHAINED_OUTSIDE_CAPTURE") == "1":
                 lib.nf_set_chained_launch_outside_capture(1)     # experiments only
             _lib = lib
