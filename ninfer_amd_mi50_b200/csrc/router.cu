@@ -312,27 +312,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// The norm in front of the router, done by the same kernel: member c of the cluster adds
-// `delta[c]` to the float32 residual row `h[c]`, normalises it and writes the row to `x` (the
-// kernel's own input, then); after a cluster barrier every member reads all rows of `x` as it
-// would have read its input.  Thread-to-element map and order of sums are those of
-// add_rmsnorm_x4_kernel, so `h` and `x` get the bits the separate kernel gives them.  One launch
-// less in front of the routed experts.  h == nullptr: no such prologue, `x` is an input.
-template <typename T>
-struct NormPrologue {
-  float* h;            // [n_tokens, hidden] residual stream, updated in place
-  const T* delta;      // [n_tokens, hidden] to be added (may be null)
-  const float* w;      // [hidden] norm weight
-  float eps;
-};
-
 template <typename T>
 __global__ void __launch_bounds__(256)
-router_cluster_kernel(T* __restrict__ x, const float* __restrict__ wr, int n_tokens, int hidden,
+router_cluster_kernel(const T* __restrict__ x, const float* __restrict__ wr, int n_tokens, int hidden,
                       int E, int extra, int k, int norm_topk, float* __restrict__ logits_out,
                       int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ extra_out,
                       int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv,
-                      int* __restrict__ active, int n_active_max, NormPrologue<T> norm) {
+                      int* __restrict__ active, int n_active_max) {
   extern __shared__ __align__(16) float rs[];
   const int rows = E + extra;
   const int n = n_tokens * k;
@@ -345,6 +331,10 @@ router_cluster_kernel(T* __restrict__ x, const float* __restrict__ wr, int n_tok
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned cta = cluster_ctarank();
   const int e0 = (int)cta * 8 + warp;
+  // A CTA's shared memory may only be written from another CTA once that CTA is running: every
+  // thread announces itself here, and waits for all the others right before its first remote
+  // store (the dot products pass in between, so the meeting costs nothing).
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
   constexpr int kPre = 16;
   const bool vec = (hidden & 3) == 0 && ((uintptr_t)wr & 15) == 0;
@@ -358,46 +348,7 @@ router_cluster_kernel(T* __restrict__ x, const float* __restrict__ wr, int n_tok
       wv[j] = i < hidden ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
-  if (norm.h) {
-    __shared__ float red[33];
-    chain_wait(norm.h, norm.delta);
-    if ((int)cta < n_tokens) {
-      float* hr = norm.h + (size_t)cta * hidden;
-      const T* dr = norm.delta ? norm.delta + (size_t)cta * hidden : nullptr;
-      T* o = x + (size_t)cta * hidden;
-      float ss = 0.f;
-      for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
-        float v[4];
-        load4(hr + i, v);
-        if (dr) {
-          float d[4];
-          load4(dr + i, d);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) v[e] += d[e];
-          store4(hr + i, v);
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
-      }
-      ss = block_sum(ss, red);
-      const float inv_rms = rsqrtf(ss / (float)hidden + norm.eps);
-      for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
-        float v[4], wv4[4];
-        load4(hr + i, v);
-        load4(norm.w + i, wv4);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = v[e] * inv_rms * wv4[e];
-        store4(o + i, v);
-      }
-    }
-    cluster_sync_all();          // every member's row of x is written and visible to the others
-  } else {
-    chain_wait(x);
-  }
-  // A CTA's shared memory may only be written from another CTA once that CTA is running: every
-  // thread announces itself here, and waits for all the others right before its first remote
-  // store (the dot products pass in between, so the meeting costs nothing).
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  chain_wait(x);
   {
     // x -> float32 in shared memory, 16 bytes of x a thread a step where alignment allows
     const int total = n_tokens * hidden;
@@ -409,7 +360,7 @@ router_cluster_kernel(T* __restrict__ x, const float* __restrict__ wr, int n_tok
         uint4 raw[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          if (i0 + u * step < total) raw[u] = __ldcg(reinterpret_cast<const uint4*>(x + i0 + u * step));
+          if (i0 + u * step < total) raw[u] = *reinterpret_cast<const uint4*>(x + i0 + u * step);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (i0 + u * step < total) {
@@ -423,7 +374,7 @@ router_cluster_kernel(T* __restrict__ x, const float* __restrict__ wr, int n_tok
         }
       }
     } else {
-      for (int i = threadIdx.x; i < total; i += blockDim.x) xs[i] = to_float(__ldcg(x + i));
+      for (int i = threadIdx.x; i < total; i += blockDim.x) xs[i] = to_float(x[i]);
     }
   }
   __syncthreads();
@@ -655,11 +606,10 @@ extern "C" int nf_router_cluster_fits(int T, int hidden, int E, int extra, int k
   return T > 0 && T <= 32 && E < 65536 && words * sizeof(float) <= 180 * 1024 ? 1 : 0;
 }
 
-static int router_cluster_launch(void* x, const float* wr, int T, int hidden, int E, int extra, int k,
+extern "C" int nf_router_cluster(const void* x, const float* wr, int T, int hidden, int E, int extra, int k,
                                  int norm_topk, float* logits, int* topk_idx, float* topk_w,
                                  float* extra_out, int* offsets, int* order, int* inv, int* active,
-                                 int n_active_max, int dtype, float* h, const void* delta, const float* norm_w,
-                                 float eps, cudaStream_t stream) {
+                                 int n_active_max, int dtype, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && hidden > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d hidden=%d E=%d k=%d", T, hidden, E, k);
   NF_REQUIRE(nf_router_cluster_fits(T, hidden, E, extra, k), "router: sizes too large for the cluster kernel");
@@ -695,42 +645,15 @@ static int router_cluster_launch(void* x, const float* wr, int T, int hidden, in
   cudaError_t e;
   if (dtype == kF32) {
     if (smem > allowed_f) { cudaFuncSetAttribute(router_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_f = smem; }
-    e = cudaLaunchKernelEx(&cfg, router_cluster_kernel<float>, (float*)x, wr, T, hidden, E, extra, k, norm_topk,
-                           logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max,
-                           NormPrologue<float>{h, (const float*)delta, norm_w, eps});
+    e = cudaLaunchKernelEx(&cfg, router_cluster_kernel<float>, (const float*)x, wr, T, hidden, E, extra, k, norm_topk,
+                           logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max);
   } else {
     if (smem > allowed_b) { cudaFuncSetAttribute(router_cluster_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); allowed_b = smem; }
-    e = cudaLaunchKernelEx(&cfg, router_cluster_kernel<__nv_bfloat16>, (__nv_bfloat16*)x, wr, T, hidden, E, extra, k,
-                           norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max,
-                           NormPrologue<__nv_bfloat16>{h, (const __nv_bfloat16*)delta, norm_w, eps});
+    e = cudaLaunchKernelEx(&cfg, router_cluster_kernel<__nv_bfloat16>, (const __nv_bfloat16*)x, wr, T, hidden, E, extra, k,
+                           norm_topk, logits, topk_idx, topk_w, extra_out, offsets, order, inv, active, n_active_max);
   }
   if (e != cudaSuccess) note_launch_error(e);
   return check_launch("router_cluster");
-}
-
-extern "C" int nf_router_cluster(const void* x, const float* wr, int T, int hidden, int E, int extra, int k,
-                                 int norm_topk, float* logits, int* topk_idx, float* topk_w,
-                                 float* extra_out, int* offsets, int* order, int* inv, int* active,
-                                 int n_active_max, int dtype, cudaStream_t stream) {
-  return router_cluster_launch(const_cast<void*>(x), wr, T, hidden, E, extra, k, norm_topk, logits, topk_idx, topk_w,
-                               extra_out, offsets, order, inv, active, n_active_max, dtype, nullptr, nullptr, nullptr,
-                               0.f, stream);
-}
-
-// The same with the residual add and the RMS norm in front (see NormPrologue): h += delta;
-// x = rmsnorm(h) * norm_w is written (x is an output here) and routed.  T <= 8 rows (one a
-// cluster member), hidden % 4 == 0, 16-byte aligned rows.
-extern "C" int nf_add_rmsnorm_router_cluster(float* h, const void* delta, const float* norm_w, float eps, void* x,
-                                             const float* wr, int T, int hidden, int E, int extra, int k,
-                                             int norm_topk, int* topk_idx, float* topk_w, float* extra_out,
-                                             int* offsets, int* order, int* inv, int* active, int n_active_max,
-                                             int dtype, cudaStream_t stream) {
-  NF_REQUIRE(h && norm_w && x, "add_rmsnorm_router: missing operands");
-  NF_REQUIRE(T <= kRouterCluster && hidden % 4 == 0, "add_rmsnorm_router: T=%d rows (at most %d) of %d (a multiple of 4)", T, kRouterCluster, hidden);
-  NF_REQUIRE((uintptr_t)h % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)norm_w % 16 == 0 &&
-             (!delta || (uintptr_t)delta % 16 == 0), "add_rmsnorm_router: operands must be 16-byte aligned");
-  return router_cluster_launch(x, wr, T, hidden, E, extra, k, norm_topk, nullptr, topk_idx, topk_w, extra_out, offsets,
-                               order, inv, active, n_active_max, dtype, h, delta, norm_w, eps, stream);
 }
 
 // Selection alone, from float32 logits that something else has produced: logits[t, e] at

@@ -58,8 +58,6 @@ TUNING = {
     # steps at A2.7B sizes: starting late is 3 % faster at 48 and 64 rows, 5 % slower at 16)
     "shared_fork_max_rows": 64,
     "shared_fork_late_rows": 32,
-    # steps of up to 8 rows: the norm in front of the router runs inside the router's kernel
-    "fuse_norm_router": True,
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -605,38 +603,6 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
               c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
               _p(inv), _p(active), c_int(active.numel()), _p(_TICKETS[key]), c_int(_dt(x)), _stream())
     return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
-
-
-def add_norm_route(h: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
-                   out_dtype: torch.dtype, w_router: torch.Tensor, E: int, k: int, norm_topk: bool):
-    """`add_rmsnorm` and `route` in one launch for a step of few rows: h += delta (in place),
-    x = rmsnorm(h) * norm_weight, then routing of x.  Returns (x, idx, weights, extra, plan), the
-    bits of the two done apart; or None if this step is not one the cluster kernel serves (the
-    caller then does the two apart)."""
-    T, H = h.shape
-    extra = w_router.shape[0] - E
-    if not (h.is_cuda and 0 < T <= min(8, TUNING["router_cluster_max_rows"]) and TUNING["fuse_norm_router"]
-            and H % 4 == 0 and out_dtype in _DT and (delta is None or delta.dtype == out_dtype)
-            and _lib.load().nf_router_cluster_fits(T, H, E, extra, k)):
-        return None
-    _chk(h, "h", torch.float32); _chk(norm_weight, "norm_weight", torch.float32)
-    _chk(w_router, "w_router", torch.float32)
-    if delta is not None:
-        _chk(delta, "delta", out_dtype)
-    dev = h.device
-    x = torch.empty((T, H), dtype=out_dtype, device=dev)
-    idx = torch.empty((T, k), dtype=torch.int32, device=dev)
-    wts = torch.empty((T, k), dtype=torch.float32, device=dev)
-    ext = torch.empty((T, extra), dtype=torch.float32, device=dev) if extra > 0 else None
-    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
-    order = torch.empty((T * k,), dtype=torch.int32, device=dev)
-    inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
-    active = torch.empty((min(E, T * k),), dtype=torch.int32, device=dev)
-    _lib.call("nf_add_rmsnorm_router_cluster", _p(h), _p(delta), _p(norm_weight), c_float(eps), _p(x), _p(w_router),
-              c_int(T), c_int(H), c_int(E), c_int(extra), c_int(k), c_int(1 if norm_topk else 0), _p(idx), _p(wts),
-              _p(ext), _p(offsets), _p(order), _p(inv), _p(active), c_int(active.numel()), c_int(_DT[out_dtype]),
-              _stream())
-    return x, idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
 
 
 def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:

@@ -270,36 +270,6 @@ def summed(delta):
     return delta.materialize() if isinstance(delta, RoutedSum) else delta
 
 
-class DeferredNorm:
-    """The input of a feed-forward that has not been normalised yet: `norm.add_norm(h, delta)`
-    still to be done.  A feed-forward with `takes_deferred_norm` may do it inside a kernel of
-    its own (it asks `norm.rms_parameters()` for what it needs); everybody else calls
-    `materialize()`, which runs the norm the ordinary way, once."""
-
-    def __init__(self, norm, h: torch.Tensor, delta, dtype: torch.dtype):
-        self.norm, self.h, self.delta, self.dtype = norm, h, delta, dtype
-        self._done: Optional[torch.Tensor] = None
-
-    @property
-    def shape(self):
-        return self.h.shape
-
-    def materialize(self) -> torch.Tensor:
-        if self._done is None:
-            self._done = self.norm.add_norm(self.h, self.delta, self.dtype)
-        return self._done
-
-    def done_by(self, x: torch.Tensor) -> torch.Tensor:
-        """Record that a fused kernel has done the norm (h is updated, `x` holds the rows)."""
-        self._done = x
-        return x
-
-
-def normed(x) -> torch.Tensor:
-    """`x` as the normalised rows, running the norm if it was deferred."""
-    return x.materialize() if isinstance(x, DeferredNorm) else x
-
-
 class Norm(Part):
     """Normalisation fused with the residual sum.
 
@@ -309,11 +279,6 @@ class Norm(Part):
     """
 
     takes_unsummed = False
-
-    def rms_parameters(self) -> Optional[Tuple[torch.Tensor, float]]:
-        """(weight, eps) if this norm is `x * rsqrt(mean(x^2) + eps) * weight` over the whole row,
-        so that another part's kernel may do it; None otherwise."""
-        return None
 
     def add_norm(self, h: torch.Tensor, delta: Optional[torch.Tensor],
                  out_dtype: torch.dtype) -> torch.Tensor:
@@ -361,9 +326,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    # True if `forward` also accepts a `DeferredNorm` as `x`
-    takes_deferred_norm = False
-
     def forward(self, x: torch.Tensor, ctx: StepContext):
         """x [T, hidden] -> [T, hidden], both in the engine dtype.  A routed feed-forward may
         return a `RoutedSum` instead of the tensor (see there); `summed()` turns either into

@@ -14,8 +14,7 @@ from typing import List, Optional
 import torch
 
 from ..registry import register_part
-from .base import (Block, CacheView, DeferredNorm, FeedForward, Fetch, Mixer, Norm, StepContext, TensorSpec,
-                   summed)
+from .base import Block, CacheView, FeedForward, Fetch, Mixer, Norm, StepContext, TensorSpec, summed
 
 
 @register_part("block", "pre_norm")
@@ -51,8 +50,5 @@ class PreNormBlock(Block):
             pending = summed(pending)
         x1 = self.norm1.add_norm(h, pending, ctx.dtype)
         a = self.mixer.forward(x1, ctx, cache, state)
-        if self.feed_forward.takes_deferred_norm:
-            # the feed-forward may run this norm inside a kernel of its own
-            return self.feed_forward.forward(DeferredNorm(self.norm2, h, a, ctx.dtype), ctx)
         x2 = self.norm2.add_norm(h, a, ctx.dtype)
         return self.feed_forward.forward(x2, ctx)

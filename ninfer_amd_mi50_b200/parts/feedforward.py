@@ -22,7 +22,7 @@ import torch
 
 from .. import kernels
 from ..registry import register_part
-from .base import DeferredNorm, FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
+from .base import FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
 
 
 _SIDE_STREAMS = {}
@@ -66,7 +66,6 @@ class DenseSwiglu(FeedForward):
 @register_part("feed_forward", "sparse_moe_swiglu")
 class SparseMoeSwiglu(FeedForward):
     graph_safe = True
-    takes_deferred_norm = True
 
     # set to a list to collect each call's selected experts (measurement only)
     record_routing = None
@@ -147,17 +146,8 @@ class SparseMoeSwiglu(FeedForward):
         """Bytes of one routed expert's matrices."""
         return self._expert_total_bytes() // self.num_experts
 
-    def forward(self, x, ctx: StepContext):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         E, k = self.num_experts, self.top_k
-        routed = None
-        if isinstance(x, DeferredNorm):
-            # A step of few rows: the norm in front of this part runs inside the router's kernel.
-            rms = x.norm.rms_parameters()
-            delta = x.delta
-            if rms is not None and (delta is None or isinstance(delta, torch.Tensor)) and x.h.is_cuda:
-                routed = kernels.add_norm_route(x.h, delta, rms[0], rms[1], x.dtype, self.w_router, E, k,
-                                                self.norm_topk_prob)
-            x = x.done_by(routed[0]) if routed is not None else x.materialize()
         # The shared expert needs nothing from the router, so on small steps (where kernels are
         # too short to fill the device) it runs beside the routed path on a second stream;
         # inside a captured graph that becomes a parallel branch.
@@ -173,16 +163,12 @@ class SparseMoeSwiglu(FeedForward):
 
         # With few rows the shared expert starts beside the router (whose kernels leave the memory
         # idle); from some tens of rows on it is better started after it, beside the experts'
-        # products (measured on decode steps: 3 % faster at 48 and 64 rows, 5 % slower at 16).  When
-        # the router's kernel also did the norm, the shared expert's input exists only after it.
-        late = x.shape[0] > kernels.TUNING["shared_fork_late_rows"] or routed is not None
+        # products (measured on decode steps: 3 % faster at 48 and 64 rows, 5 % slower at 16).
+        late = x.shape[0] > kernels.TUNING["shared_fork_late_rows"]
         if fork and not late:
             main, side, shared = start_shared()
-        if routed is not None:
-            _, idx, wts, gate, plan = routed
-        else:
-            idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
-                                                 split=self.w_router_split)
+        idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
+                                             split=self.w_router_split)
         if fork and late:
             main, side, shared = start_shared()
         if SparseMoeSwiglu.record_routing is not None:

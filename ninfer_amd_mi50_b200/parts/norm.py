@@ -36,9 +36,6 @@ class RmsNorm(Norm):
     def weight_bytes(self) -> int:
         return self.size * 4
 
-    def rms_parameters(self):
-        return self.weight, self.eps
-
     def _fusable(self, delta, out_dtype, rows: int) -> bool:
         return (isinstance(delta, RoutedSum) and out_dtype == torch.bfloat16
                 and kernels.can_fuse_combine_norm(delta.y, self.size, rows))

@@ -624,36 +624,6 @@ def test_route_in_one_launch(K, dtype, T, H, E, k, norm, extra):
         assert torch.equal(seen[0][1], seen[1][1])
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H,E,k,norm,extra", [(1, 2048, 60, 4, False, 1), (8, 2048, 60, 4, False, 1), (5, 200, 6, 3, True, 1),
-                                                (3, 3584, 64, 8, False, 1), (8, 1000, 130, 8, True, 0)])
-def test_norm_in_front_of_the_router_inside_its_kernel(K, dtype, T, H, E, k, norm, extra):
-    """Steps of up to 8 rows: the residual add and the RMS norm run inside the router's cluster
-    kernel (a member a row).  Residual stream, normalised rows, selection, weights, gate logits
-    and plan have the bits of the norm kernel followed by the router kernel."""
-    x0 = rnd((T, H), torch.float32, 81)
-    delta = rnd((T, H), dtype, 82)
-    nw = 1 + 0.05 * rnd((H,), torch.float32, 83)
-    wr = rnd((E + extra, H), torch.float32, 84, 0.05)
-    for d in (delta, None):
-        h1, h2 = x0.clone(), x0.clone()
-        fused = K.add_norm_route(h1, d, nw, 1e-6, dtype, wr, E, k, norm)
-        assert fused is not None
-        x1, idx1, w1, e1, p1 = fused
-        x2 = torch.empty((T, H), dtype=dtype, device="cuda")
-        K.add_rmsnorm(h2, d, nw, 1e-6, x2)
-        idx2, w2, e2, p2 = K.route(x2, wr, E, k, norm)
-        assert torch.equal(h1, h2) and torch.equal(x1, x2)
-        assert torch.equal(idx1, idx2) and torch.equal(w1, w2)
-        assert (e1 is None and e2 is None) or torch.equal(e1, e2)
-        for name in ("offsets", "order", "inv", "active"):
-            assert torch.equal(getattr(p1, name), getattr(p2, name)), name
-    # nine rows, or a width that is no multiple of 4: done apart
-    assert K.add_norm_route(rnd((9, H), torch.float32, 85), None, nw, 1e-6, dtype, wr, E, k, norm) is None
-    assert K.add_norm_route(rnd((2, 202), torch.float32, 86), None, nw[:202].contiguous(), 1e-6, dtype,
-                            wr[:, :202].contiguous(), E, k, norm) is None
-
-
 def test_router_ties_go_to_lower_index(K):
     x = torch.ones((2, 64), dtype=torch.float32, device="cuda")
     w = torch.zeros((8, 64), dtype=torch.float32, device="cuda")
