@@ -26,7 +26,7 @@
 // expert's row count; one elected thread issues the MMAs,
 // whose float32 accumulators live in tensor memory (gate in columns [0, 256), up in
 // [256, 512)); `tcgen05.commit` hands stages back to the producer and the finished
-// accumulator to four epilogue warps, which read it with `tcgen05.ld`, apply the epilogue
+// accumulator to twelve epilogue warps, which read it with `tcgen05.ld`, apply the epilogue
 // and store bfloat16.  No TMA multicast, no clusters.
 //
 // Every wait on an mbarrier is bounded: after a fixed number of polls the kernel records a

@@ -1,5 +1,5 @@
-"""Representative kernel workloads at Qwen1.5-MoE-A2.7B layer sizes, one layer's worth, for
-profilers and quick timing:
+"""Representative kernel workloads, one layer's worth, for profilers and quick timing; the layer
+sizes come from a named set (`--sizes`, by default those of Qwen1.5-MoE-A2.7B):
 
     python -m ninfer_amd_mi50_b200.kernels.cases moe_prefill
     ncu --set full --clock-control none -k regex:grouped_gemm_tc -c 2 \
@@ -22,9 +22,20 @@ from types import SimpleNamespace
 
 import torch
 
-H, I, IS, E, K_TOP, V = 2048, 1408, 5632, 60, 4, 151936
-HQ = HKV = 16
-D, PAGE = 128, 64
+# name -> layer sizes (config.json's meanings): the two large configurations that are measured
+SIZES = {
+    "a2.7b": dict(H=2048, I=1408, IS=5632, E=60, K_TOP=4, V=151936, HQ=16, HKV=16, D=128),
+    "57b-a14b": dict(H=3584, I=2560, IS=20480, E=64, K_TOP=8, V=151936, HQ=28, HKV=4, D=128),
+}
+PAGE = 64
+H = I = IS = E = K_TOP = V = HQ = HKV = D = 0     # set from SIZES by `use_sizes`
+
+
+def use_sizes(name: str) -> None:
+    globals().update(SIZES[name])
+
+
+use_sizes("a2.7b")
 
 
 def _routing(tokens: int, seed: int, device):
@@ -64,7 +75,7 @@ def case_attention_prefill(tokens: int, device):
                       row_seg=torch.zeros(tokens, dtype=torch.int32, device=device), seg_row0=mk([0, tokens]),
                       seg_pos0=mk([0]), seg_slot=mk([0]), logit_rows=mk([]), seg_len_host=[tokens],
                       seg_pos0_host=[0], max_rows_per_seg=tokens, max_context=tokens)
-    qkv = torch.randn(tokens, 3 * HQ * D, device=device).bfloat16()
+    qkv = torch.randn(tokens, (HQ + 2 * HKV) * D, device=device).bfloat16()
     return [("prefill_attention", lambda: paged_attention(qkv, HQ, HKV, D, pages, bt, PAGE, ctx, 0, 1 / math.sqrt(D)))]
 
 
@@ -77,7 +88,7 @@ def case_attention_decode(batch: int, context: int, device):
     ctx = SimpleNamespace(positions=torch.full((batch,), context, dtype=torch.int32, device=device),
                           row_seg=torch.arange(batch, dtype=torch.int32, device=device), all_single=True,
                           max_context=context + 1)
-    qkv = torch.randn(batch, 3 * HQ * D, device=device).bfloat16()
+    qkv = torch.randn(batch, (HQ + 2 * HKV) * D, device=device).bfloat16()
     return [("decode_attention", lambda: paged_attention(qkv, HQ, HKV, D, pages, bt, PAGE, ctx, 0, 1 / math.sqrt(D)))]
 
 
@@ -85,11 +96,29 @@ def case_dense_decode(batch: int, device):
     """The dense products of a decode step: QKV, O, shared expert, LM head."""
     from . import linear, linear_swiglu
     mk = lambda n, k: (torch.randn(n, k, device=device) * 0.02).bfloat16()
-    wqkv, wo, ws13, ws2, head = mk(3 * HQ * D, H), mk(H, HQ * D), mk(2 * IS, H), mk(H, IS), mk(V, H)
+    wqkv, wo, ws13, ws2, head = mk((HQ + 2 * HKV) * D, H), mk(H, HQ * D), mk(2 * IS, H), mk(H, IS), mk(V, H)
     x, xs = torch.randn(batch, H, device=device).bfloat16(), torch.randn(batch, IS, device=device).bfloat16()
     return [("qkv", lambda: linear(x, wqkv)), ("o_proj", lambda: linear(x, wo)),
             ("shared_gate_up", lambda: linear_swiglu(x, ws13)), ("shared_down", lambda: linear(xs, ws2)),
             ("lm_head", lambda: linear(x, head, out_dtype=torch.float32))]
+
+
+def case_small_decode(batch: int, device):
+    """The short kernels between a decode step's products: norm with residual add, router with
+    plan, weighted sum of the experts' outputs joined with the next norm."""
+    from . import add_rmsnorm, moe_combine_add_rmsnorm, moe_plan, route
+    h = torch.randn(batch, H, device=device)
+    delta = torch.randn(batch, H, device=device).bfloat16()
+    w = torch.ones(H, device=device)
+    out = torch.empty(batch, H, device=device, dtype=torch.bfloat16)
+    wr = torch.randn(E + 1, H, device=device) * 0.02
+    plan = moe_plan(_routing(batch, batch, device), E)
+    y = torch.randn(batch * K_TOP, H, device=device).bfloat16()
+    wts = torch.rand(batch, K_TOP, device=device)
+    gate = torch.randn(batch, 1, device=device)
+    return [("add_rmsnorm", lambda: add_rmsnorm(h, delta, w, 1e-6, out)),
+            ("route", lambda: route(out, wr, E, K_TOP, False)),
+            ("combine_add_rmsnorm", lambda: moe_combine_add_rmsnorm(y, plan, wts, delta, gate, h, None, w, 1e-6, out))]
 
 
 CASES = {
@@ -100,16 +129,20 @@ CASES = {
     "attention_decode8": lambda dev: case_attention_decode(8, 2048, dev),
     "attention_decode64": lambda dev: case_attention_decode(64, 2048, dev),
     "dense_decode8": lambda dev: case_dense_decode(8, dev),
+    "dense_decode1": lambda dev: case_dense_decode(1, dev),
+    "small_decode8": lambda dev: case_small_decode(8, dev),
 }
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=sorted(CASES))
+    ap.add_argument("--sizes", default="a2.7b", choices=sorted(SIZES))
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--time", action="store_true", help="print the median time per call")
     args = ap.parse_args(argv)
     from . import load, tensor_core_status
+    use_sizes(args.sizes)
     load()
     ops = CASES[args.case]("cuda")
     for _, fn in ops:
