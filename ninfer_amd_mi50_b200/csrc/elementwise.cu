@@ -206,6 +206,7 @@ __global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, c
 // launch and one round trip of [T, hidden] less.  A thread keeps its elements in registers:
 // rows of up to kFusedIters * 4 * blockDim elements.
 constexpr int kFusedIters = 8;
+constexpr int kFusedMaxK = 32;     // most experts a token (the row's positions and weights sit in shared memory)
 
 template <bool GATHER>
 __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv,
@@ -216,41 +217,53 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
                                                const float* __restrict__ w, float eps,
                                                __nv_bfloat16* __restrict__ out, int hidden, int k, int n_pairs) {
   __shared__ float red[33];
+  __shared__ int s_pos[kFusedMaxK];
+  __shared__ float s_wt[kFusedMaxK];
   const int r = blockIdx.x;
   chain_release();
   chain_wait(y, inv, wts, shared, gate, h, rows);
   const int t = GATHER ? rows[r] : r;
   float* hr = h + (size_t)t * hidden;
+  // the row's k sorted positions and weights first, so that the sums below are nothing but
+  // independent loads of expert rows (a position outside the step's pairs is skipped, and said)
+  if (threadIdx.x < k) {
+    int p = inv[t * k + threadIdx.x];
+    if ((unsigned)p >= (unsigned)n_pairs) {
+      atomicCAS(&g_combine_index_error, 0, 1 + t);
+      p = -1;
+    }
+    s_pos[threadIdx.x] = p;
+    s_wt[threadIdx.x] = wts[t * k + threadIdx.x];
+  }
   const float gsc = (shared && gate) ? 1.f / (1.f + expf(-gate[(size_t)t * gate_stride])) : 1.f;
+  __syncthreads();
   float keep[kFusedIters][4];
   float ss = 0.f;
 #pragma unroll
   for (int it = 0; it < kFusedIters; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 4;
     if (i < hidden) {
+      float hv[4], sv[4] = {0.f, 0.f, 0.f, 0.f};
+      load4(hr + i, hv);
+      if (shared) load4(shared + (size_t)t * hidden + i, sv);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
       for (int j = 0; j < k; ++j) {
-        const int p = inv[t * k + j];
-        if ((unsigned)p >= (unsigned)n_pairs) {        // not a sorted position of this step: skip, and say so
-          atomicCAS(&g_combine_index_error, 0, 1 + t);
-          continue;
-        }
-        const float wj = wts[t * k + j];
+        const int p = s_pos[j];
+        if (p < 0) continue;
+        const float wj = s_wt[j];
         float v[4];
         load4(y + (size_t)p * hidden + i, v);
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[e] = fmaf(wj, v[e], acc[e]);
       }
       if (shared) {
-        float v[4];
-        load4(shared + (size_t)t * hidden + i, v);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] = fmaf(v[e], gsc, acc[e]);
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(sv[e], gsc, acc[e]);
       }
       float v[4];
-      load4(hr + i, v);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] += __bfloat162float(__float2bfloat16_rn(acc[e]));
+      for (int e = 0; e < 4; ++e) v[e] = hv[e] + __bfloat162float(__float2bfloat16_rn(acc[e]));
       if (!GATHER) store4(hr + i, v);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -372,7 +385,7 @@ extern "C" int nf_moe_combine_add_rmsnorm(const void* y, const int* inv, const f
                                           const float* w, float eps, void* out, int T, int R, int hidden,
                                           int k, cudaStream_t stream) {
   if (R == 0) return 0;
-  NF_REQUIRE(T > 0 && R > 0 && k > 0 && nf_moe_combine_add_rmsnorm_fits(hidden), "moe_combine_add_rmsnorm: bad sizes T=%d R=%d hidden=%d k=%d", T, R, hidden, k);
+  NF_REQUIRE(T > 0 && R > 0 && k > 0 && k <= kFusedMaxK && nf_moe_combine_add_rmsnorm_fits(hidden), "moe_combine_add_rmsnorm: bad sizes T=%d R=%d hidden=%d k=%d", T, R, hidden, k);
   NF_REQUIRE((uintptr_t)y % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 8 == 0 && (uintptr_t)w % 16 == 0 &&
              (!shared || (uintptr_t)shared % 8 == 0), "moe_combine_add_rmsnorm: operands must be 16-byte aligned");
   const int t4 = row_threads(hidden / 4);

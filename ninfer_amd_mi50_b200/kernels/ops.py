@@ -693,11 +693,14 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optio
     return out
 
 
-def can_fuse_combine_norm(y: torch.Tensor, hidden: int, rows: int) -> bool:
+FUSED_COMBINE_MAX_K = 32
+
+
+def can_fuse_combine_norm(y: torch.Tensor, hidden: int, rows: int, k: int = 1) -> bool:
     """Whether `moe_combine_add_rmsnorm` serves these operands (bfloat16 on the device, a row that
     the kernel's threads can keep in registers, few enough rows)."""
     return (y.is_cuda and y.dtype == torch.bfloat16 and rows <= TUNING["fuse_combine_norm_max_rows"]
-            and bool(_lib.load().nf_moe_combine_add_rmsnorm_fits(c_int(hidden))))
+            and k <= FUSED_COMBINE_MAX_K and bool(_lib.load().nf_moe_combine_add_rmsnorm_fits(c_int(hidden))))
 
 
 def moe_combine_add_rmsnorm(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optional[torch.Tensor],

@@ -38,7 +38,7 @@ class RmsNorm(Norm):
 
     def _fusable(self, delta, out_dtype, rows: int) -> bool:
         return (isinstance(delta, RoutedSum) and out_dtype == torch.bfloat16
-                and kernels.can_fuse_combine_norm(delta.y, self.size, rows))
+                and kernels.can_fuse_combine_norm(delta.y, self.size, rows, delta.wts.shape[1]))
 
     def add_norm(self, h, delta, out_dtype):
         out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
