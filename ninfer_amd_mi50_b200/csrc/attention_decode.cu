@@ -295,7 +295,7 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
   __shared__ float wgt[kMaxMergeSplits];
   __shared__ float s_m, s_inv;
   const int wi = blockIdx.x, h = blockIdx.y;
-  chain_release();
+  chain_release_if_small();
   chain_wait(ws_acc, ws_ml, positions);
   const int t = row_list ? row_list[wi] : wi;
   int pos = positions[t], lo;

@@ -49,6 +49,12 @@ __device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.l
 // launch be prepared early.
 __device__ __forceinline__ void chain_release() {}
 #endif
+// A release at the top of a kernel that does not fill the device (a norm over 8 rows, the merge
+// of a decode step): its successor's CTAs find free SMs anyway, become resident at once and ask
+// for their first weights while this kernel's few CTAs work through their latency chain.
+__device__ __forceinline__ void chain_release_if_small() {
+  if (gridDim.x * gridDim.y * gridDim.z <= 148u) asm volatile("griddepcontrol.launch_dependents;");
+}
 // A release late in a kernel, once its CTA has asked for all it will read: the successor's
 // CTAs then arrive while this one reduces and writes.
 __device__ __forceinline__ void chain_release_late() { asm volatile("griddepcontrol.launch_dependents;"); }

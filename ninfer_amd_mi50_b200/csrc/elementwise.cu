@@ -63,7 +63,7 @@ __global__ void add_rmsnorm_x4_kernel(float* __restrict__ h, const T* __restrict
                                       float eps, T* __restrict__ out, int hidden) {
   __shared__ float red[33];
   const int r = blockIdx.x;
-  chain_release();
+  chain_release_if_small();
   chain_wait(h, delta, rows);
   const int src = GATHER ? rows[r] : r;
   float* hr = h + (size_t)src * hidden;
@@ -220,7 +220,7 @@ __global__ void moe_combine_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__
   __shared__ int s_pos[kFusedMaxK];
   __shared__ float s_wt[kFusedMaxK];
   const int r = blockIdx.x;
-  chain_release();
+  chain_release_if_small();
   chain_wait(y, inv, wts, shared, gate, h, rows);
   const int t = GATHER ? rows[r] : r;
   float* hr = h + (size_t)t * hidden;
