@@ -87,7 +87,7 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int wi = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
-  chain_release();
+  chain_release_if_small();
   chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by the kernel before
   const int t = row_list ? row_list[wi] : wi;
   int pos = positions[t], lo;

@@ -92,6 +92,9 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int G = Hq / Hkv;
+  // one CTA an SM with nearly all of its shared memory: the merge kernel's small CTAs fit beside
+  // it and are then in place when the last partial result is written
+  asm volatile("griddepcontrol.launch_dependents;");
   chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by kernels before
 
   // ---- every CTA lists the rows' blocks: row t has blocks s_first[t] .. of its key range -------
@@ -314,7 +317,6 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
     }
   }
   cp_wait<0>();
-  chain_release_late();
 }
 
 template <int D>
