@@ -88,9 +88,13 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
   chain_release_if_small();
-  chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by the kernel before
+  // Positions, row list, segments and block table are the step's inputs, complete before the
+  // step's kernels began.  The kernel before this one wrote the queries and, into the pages, the
+  // keys and values of each row's own (newest) position - nothing else.  So everything but that
+  // one row of keys and values is asked for before the wait, while that kernel still runs.
   const int t = row_list ? row_list[wi] : wi;
-  int pos = positions[t], lo;
+  const int newest = positions[t];
+  int pos = newest, lo;
   if (decode_key_range(pos, lo, window, nsplit, kSplit) && kvh == 0 && split == 0 && threadIdx.x == 0)
     atomicCAS(&g_decode_split_range_error, 0, 1 + t);
   const int k_base = split * kSplit;
@@ -101,12 +105,15 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
   const int* bt = block_table + (size_t)seg * bt_width;
   const size_t head_stride = (size_t)page_size * D;
   const size_t page_stride = (size_t)2 * Hkv * head_stride;
+  const size_t v_off = (size_t)Hkv * head_stride;
   const int n0 = k_begin - k_base, n1 = k_end - k_base;
   const int sub = lane / LPR, li = lane % LPR;
+  const int new_row = (newest >= k_begin && newest < k_end) ? newest - k_base : -1;   // the row written a kernel ago
 
   // ---- ask for keys, then values; rows outside the key range become zeros --------------------
   // Lane l looks up the page of row 32 w + l once; the copy loop fetches each row's address
   // from the lane that knows it.
+  const __nv_bfloat16* new_src = nullptr;
   {
     const int myrow = warp * 32 + lane;
     const __nv_bfloat16* my_src = nullptr;
@@ -117,7 +124,6 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
       if (page >= 0 && page < num_pages)
         my_src = pages + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(j - lp * page_size) * D;
     }
-    const size_t v_off = (size_t)Hkv * head_stride;
 #pragma unroll
     for (int kv = 0; kv < 2; ++kv) {
       __nv_bfloat16* dst = kv ? Vs : Ks;
@@ -127,7 +133,8 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
         const unsigned long long src = __shfl_sync(0xffffffffu, (unsigned long long)my_src, rl);
         const int r = warp * 32 + rl;
         if (rl < 32) {
-          if (src) cp_async16(dst + r * DS + li * 8, reinterpret_cast<const __nv_bfloat16*>(src) + (kv ? v_off : 0) + li * 8);
+          if (r == new_row) new_src = reinterpret_cast<const __nv_bfloat16*>(src);      // after the wait
+          else if (src) cp_async16(dst + r * DS + li * 8, reinterpret_cast<const __nv_bfloat16*>(src) + (kv ? v_off : 0) + li * 8);
           else *reinterpret_cast<uint4*>(dst + r * DS + li * 8) = make_uint4(0, 0, 0, 0);
         }
       }
@@ -135,7 +142,23 @@ decode_attention_split_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_s
     }
   }
   for (int i = threadIdx.x; i < G * kSplit; i += blockDim.x) sc[i] = 0.f;
-  cp_async_wait<1>();          // keys have landed (values may still be on their way)
+  chain_wait(qkv, pages);
+  if (new_row >= 0) {
+    // the lanes that met the newest row in the loop above fetch it now (keys and values)
+    if (warp == new_row / 32 && sub == (new_row & 31) % RPL) {
+      if (new_src) {
+        cp_async16(Ks + new_row * DS + li * 8, new_src + li * 8);
+        cp_async16(Vs + new_row * DS + li * 8, new_src + v_off + li * 8);
+      } else {
+        *reinterpret_cast<uint4*>(Ks + new_row * DS + li * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(Vs + new_row * DS + li * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<0>();        // all three groups
+  } else {
+    cp_async_wait<1>();        // keys have landed (values may still be on their way)
+  }
   __syncthreads();
 
   const __nv_bfloat16* qrow = qkv + (size_t)t * q_row_stride + (size_t)kvh * G * D;
@@ -296,10 +319,12 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
   __shared__ float s_m, s_inv;
   const int wi = blockIdx.x, h = blockIdx.y;
   chain_release_if_small();
-  chain_wait(ws_acc, ws_ml, positions);
+  // positions and the row list are the step's inputs, complete before the kernels of the step
+  // began; the partial results are the predecessor's
   const int t = row_list ? row_list[wi] : wi;
   int pos = positions[t], lo;
   decode_key_range(pos, lo, window, nsplit, kSplit);
+  chain_wait(ws_acc, ws_ml);
   const int s0 = lo / kSplit, s1 = pos / kSplit;                       // first and last split with keys
   const int n = s1 - s0 + 1;
   const float* ml = ws_ml + (((size_t)wi * Hq + h) * nsplit + s0) * 2;

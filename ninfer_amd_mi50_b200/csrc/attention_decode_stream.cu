@@ -95,7 +95,6 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
   // one CTA an SM with nearly all of its shared memory: the merge kernel's small CTAs fit beside
   // it and are then in place when the last partial result is written
   asm volatile("griddepcontrol.launch_dependents;");
-  chain_wait(qkv, pages, block_table, positions, row_seg);   // queries and this step's keys were written by kernels before
 
   // ---- every CTA lists the rows' blocks: row t has blocks s_first[t] .. of its key range -------
   // Rows are counted by their place in this launch (0 .. T - 1: shared-memory lists, workspace);
@@ -115,6 +114,11 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
     for (int t = 0; t < T; ++t) { const int n = s_cum[t + 1]; run += n; s_cum[t + 1] = run; }
   }
   __syncthreads();
+  // The lists above need only the step's positions (and the row list), which the caller wrote
+  // before the kernel that precedes this one began, like the segments and the block table.  What
+  // that kernel writes is the queries and, in the pages, each row's keys and values at its own
+  // (newest) position: the wait stands before the first tile that holds such a position and
+  // before the first use of a query, and the ring is filled up to there meanwhile.
   const int total = s_cum[T] * Hkv;                // blocks of the launch: (row, block) major, kv head minor
   const int W = gridDim.x * kWorkers;
   const int wid = warp * gridDim.x + blockIdx.x;   // workers of one CTA are W / 8 apart: CTAs stay level
@@ -128,7 +132,7 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
   // A worker's tiles form one sequence over its blocks; the producer runs NS - 1 tiles ahead of
   // the consumer.  Producer state: block pc (in the flattened list), its row and key range, the
   // next tile index pt inside the block.
-  int pc = wid, p_t = 0, p_kvh = 0, p_kbase = 0, p_kb = 0, p_ke = 0, p_tile = 0, p_tile_end = 0;
+  int pc = wid, p_t = 0, p_kvh = 0, p_kbase = 0, p_kb = 0, p_ke = 0, p_tile = 0, p_tile_end = 0, p_new = 0;
   const int* p_bt = nullptr;
   auto producer_open = [&]() {           // set the producer's state for block pc (pc < total)
     const int rc = pc / Hkv;
@@ -141,6 +145,7 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
     p_t = lo_t;
     const int p_row = row_of(p_t);
     int pos = positions[p_row], lo;
+    p_new = pos;                         // the position whose keys and values the kernel before this one wrote
     decode_key_range(pos, lo, window, nsplit, kBlockKeys);
     const int split = s_first[p_t] + (rc - s_cum[p_t]);
     p_kbase = split * kBlockKeys;
@@ -184,8 +189,16 @@ decode_attention_stream_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_
   };
 
   if (pc < total) producer_open();
+  int filled = 0;
 #pragma unroll 1
-  for (int i = 0; i < NS - 1; ++i) produce();
+  for (; filled < NS - 1; ++filled) {
+    const int j0 = p_kbase + p_tile * kTile;
+    if (pc < total && p_new >= j0 && p_new < j0 + kTile) break;      // this tile holds a newest position
+    produce();
+  }
+  chain_wait(qkv, pages);
+#pragma unroll 1
+  for (; filled < NS - 1; ++filled) produce();
 
   // ---- the consumer ---------------------------------------------------------------------------------
   int used = 0;                          // tiles multiplied so far

@@ -18,7 +18,12 @@ const char* nf_last_error(void);
  * must be at least ceil((largest position + 1) / 128) over the rows of the call.  Positions
  * live on the device, so the host cannot check this: a row that needs more blocks is
  * computed over its first nsplit * 128 keys only, nothing is written outside the scratch,
- * and nf_decode_attention_status() reports 1 + that row afterwards. */
+ * and nf_decode_attention_status() reports 1 + that row afterwards.
+ *
+ * Inside a stream capture the library chains its kernels (each may begin while the one before it
+ * drains) and these kernels read `positions` and the row list before they wait for their
+ * predecessor: those two must have been written before the kernel that precedes this call in the
+ * stream was launched (by a copy at the start of the step, as the engine does), not by it. */
 int nf_decode_attention(const void* qkv, int q_row_stride, const void* pages, const int* block_table,
                         int bt_width, const int* positions, const int* row_seg, void* out,
                         float* ws_acc, float* ws_ml, int T, int Hq, int Hkv, int D, int page_size,
