@@ -315,7 +315,7 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
                                               int Hq, int D, int window, int nsplit, int dthreads,
                                               const int* __restrict__ row_list) {
   extern __shared__ float runs[];      // [runs of this row][D]
-  __shared__ float wgt[kMaxMergeSplits];
+  __shared__ float wgt[kMaxMergeSplits], wl[kMaxMergeSplits];
   __shared__ float s_m, s_inv;
   const int wi = blockIdx.x, h = blockIdx.y;
   chain_release_if_small();
@@ -329,19 +329,25 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ ws_acc,
   const int n = s1 - s0 + 1;
   const float* ml = ws_ml + (((size_t)wi * Hq + h) * nsplit + s0) * 2;
   const float* acc = ws_acc + (((size_t)wi * Hq + h) * nsplit + s0) * D;
-  for (int s = threadIdx.x; s < n; s += blockDim.x) wgt[s] = ml[2 * s];          // m_s for now
+  // every block's (m, l) in one parallel read; the serial parts below then walk shared memory
+  for (int s = threadIdx.x; s < n; s += blockDim.x) {
+    const float2 v = *reinterpret_cast<const float2*>(ml + 2 * s);
+    wgt[s] = v.x;          // m_s for now
+    wl[s] = v.y;
+  }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
     float m = -INFINITY;
-    for (int s = 0; s < n; ++s) m = fmaxf(m, wgt[s]);
-    s_m = m;
+    for (int s = threadIdx.x; s < n; s += 32) m = fmaxf(m, wgt[s]);
+    m = warp_max(m);
+    if (threadIdx.x == 0) s_m = m;
   }
   __syncthreads();
   for (int s = threadIdx.x; s < n; s += blockDim.x) wgt[s] = expf(wgt[s] - s_m);  // now exp(m_s - m)
   __syncthreads();
   if (threadIdx.x == 0) {
     float l = 0.f;
-    for (int s = 0; s < n; ++s) l += ml[2 * s + 1] * wgt[s];                      // ascending order
+    for (int s = 0; s < n; ++s) l += wl[s] * wgt[s];                              // ascending order
     s_inv = l > 0.f ? 1.f / l : 0.f;
   }
   __syncthreads();
