@@ -58,9 +58,11 @@ class CacheManager:
     def __init__(self, cache_specs: Sequence[Optional[CacheSpec]],
                  state_specs: Sequence[Optional[StateSpec]], *, page_size: int, num_pages: int,
                  max_requests: int, max_context: int, dtype: torch.dtype = torch.float32,
-                 device="cpu", allocate: bool = True):
+                 device="cpu", allocate: bool = True, clear_reused_pages: bool = True):
         self.page_size, self.max_requests = int(page_size), int(max_requests)
         self.max_context = int(max_context)
+        self.clear_reused_pages = bool(clear_reused_pages)
+        self.pages_cleared = 0
         self.max_pages_per_request = (self.max_context + self.page_size - 1) // self.page_size
         self.dtype, self.device = dtype, torch.device(device)
         self.groups: List[CacheGroup] = []
@@ -174,7 +176,24 @@ class CacheManager:
                 raise OutOfPages(f"request {req!r}: group {g.index} needs {n} pages, "
                                  f"{g.pool.num_free} free")
         for n, g, table in zip(need, self.groups, ent.tables):
-            table.extend(g.pool.take(n))
+            taken, again = g.pool.take_marking_reuse(n)
+            table.extend(taken)
+            if again and self.clear_reused_pages and g.pages is not None:
+                # A page that is handed out again still holds its earlier owner's entries.  Kernels
+                # that copy whole pages multiply what lies beyond the new owner's position by a
+                # zero probability, which keeps a result right only while those entries are
+                # finite; zeros are.  On the stream, so it is ordered after whatever still reads
+                # the page for its earlier owner (a step launched ahead).
+                # (runs of neighbouring pages, one fill each: no index list has to cross to the device)
+                again.sort()
+                a = 0
+                while a < len(again):
+                    b = a
+                    while b + 1 < len(again) and again[b + 1] == again[b] + 1:
+                        b += 1
+                    g.pages[:, again[a]:again[b] + 1].zero_()
+                    a = b + 1
+                self.pages_cleared += len(again)
         ent.reserved = max(ent.reserved, new_length)
 
     def commit(self, req: Hashable, new_length: int) -> None:

@@ -22,6 +22,7 @@ class PagePool:
         self.num_pages = int(num_pages)
         self._free: List[int] = list(range(self.num_pages - 1, -1, -1))  # pop() gives page 0 first
         self._held = [False] * self.num_pages
+        self._used_before = [False] * self.num_pages
 
     @property
     def num_free(self) -> int:
@@ -43,6 +44,15 @@ class PagePool:
                 raise AssertionError(f"page {p} handed out while held")
             self._held[p] = True
         return out
+
+    def take_marking_reuse(self, n: int):
+        """`take`, and which of the pages taken have been held before (they hold an earlier
+        owner's entries; a page never handed out still has the zeros it was created with)."""
+        out = self.take(n)
+        again = [p for p in out if self._used_before[p]]
+        for p in out:
+            self._used_before[p] = True
+        return out, again
 
     def give_back(self, pages) -> None:
         for p in pages:

@@ -27,6 +27,7 @@ class EngineOptions:
     use_graph: bool = True           # replay decode-only steps from CUDA graphs
     run_ahead: bool = True           # launch the next decode step before reading this one's tokens
     status_every: int = 64           # decode steps between two reads of the kernels' status flags
+    clear_reused_pages: bool = True  # zero a cache page when it is handed out a second time
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

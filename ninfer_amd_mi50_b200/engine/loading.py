@@ -51,7 +51,8 @@ def load_runner(model_dir: Optional[str] = None, *, config: Optional[Dict[str, A
     source.close()
     cache = CacheManager(model.cache_specs(), model.state_specs(), page_size=options.page_size,
                          num_pages=options.num_pages, max_requests=options.num_sequences,
-                         max_context=options.max_context, dtype=dtype, device=device)
+                         max_context=options.max_context, dtype=dtype, device=device,
+                         clear_reused_pages=options.clear_reused_pages)
     runner = ModelRunner(model, cache, dtype, device, use_graph=options.use_graph)
     runner.config = typed
     runner.options = options

@@ -145,3 +145,31 @@ def test_random_orders_lose_no_page(seed):
         m.close(r)
     m.check()
     assert m.pages_free() == [10, 10]
+
+
+def test_a_page_is_cleared_when_it_is_handed_out_again():
+    """A page that goes to a second owner is zeroed first (what lies beyond the new owner's
+    position in it is multiplied by zero probabilities, and must be finite); a page handed out
+    for the first time still has the zeros it was made with and is left alone."""
+    import torch
+    from ninfer_amd_mi50_b200.cache.manager import CacheManager
+    from ninfer_amd_mi50_b200.parts.base import CacheSpec
+    spec = CacheSpec("full", 2, 8)
+    cm = CacheManager([spec, spec], [None, None], page_size=4, num_pages=6, max_requests=2, max_context=24)
+    (g,) = cm.groups
+    cm.open("a")
+    cm.reserve("a", 9)                       # three pages, first use
+    assert cm.pages_cleared == 0
+    held = list(cm.block_table(0, "a"))
+    g.pages[:, held] = float("nan")          # whatever "a" left there
+    cm.commit("a", 9)
+    cm.close("a")
+    cm.open("b")
+    cm.reserve("b", 17)                      # five pages: the three of "a" again and two fresh ones
+    again = [p for p in cm.block_table(0, "b") if p in held]
+    assert sorted(again) == sorted(held) and cm.pages_cleared == 3
+    assert bool(torch.isfinite(g.pages).all()) and float(g.pages[:, cm.block_table(0, "b")].abs().sum()) == 0.0
+    off = CacheManager([spec], [None], page_size=4, num_pages=2, max_requests=1, max_context=8, clear_reused_pages=False)
+    off.open("a"); off.reserve("a", 8); off.groups[0].pages[:, :2] = 1.0; off.commit("a", 8); off.close("a")
+    off.open("b"); off.reserve("b", 8)
+    assert off.pages_cleared == 0 and float(off.groups[0].pages[:, :2].sum()) > 0

@@ -150,3 +150,38 @@ def test_trace_run_program(folder, dtype, tmp_path):
     same = schedules.run_schedule(make_runner(d, dtype, 448), steps)
     for r in reqs:
         assert torch.equal(torch.cat(got[r]), same[r]), f"trace_run {r} differs from the in-process run"
+
+
+def test_a_reused_page_with_non_finite_leftovers_does_no_harm(tmp_path):
+    """The tensor-core attention copies whole pages and multiplies what lies beyond a request's
+    position by zero probabilities, so leftovers of a page's earlier owner must be finite.  The
+    cache manager zeroes a page when it hands it out again: a request that inherits pages full of
+    NaN gets the plain model's logits.  With the clearing switched off the same request shows
+    what the rule is for."""
+    from ninfer_amd_mi50_b200.config import EngineOptions
+    from ninfer_amd_mi50_b200.engine import StepEntry, load_runner
+    from ninfer_amd_mi50_b200.weights import write_random_model
+    cfg, seed = CONFIGS["A"]
+    d = str(tmp_path / "A")
+    write_random_model(cfg, seed, d)
+    pcfg, weights = plain_model.read_model_folder(d)
+    first, second = random_tokens(256, cfg["vocab_size"], 7), random_tokens(150, cfg["vocab_size"], 8)
+    want = plain_model.plain_forward(pcfg, weights, second)
+    for clear in (True, False):
+        runner = load_runner(d, options=EngineOptions(dtype="bfloat16", page_size=64, num_sequences=2, max_context=256,
+                                                       cache_tokens=256, use_graph=False, clear_reused_pages=clear))
+        runner.open("a")
+        runner.step([StepEntry("a", first, [])])
+        runner.close("a")
+        for g in runner.cache.groups:
+            g.pages[:, :g.pool.num_pages] = float("nan")          # what an earlier owner might have left
+        runner.open("b")
+        SparseRouting = {}
+        got = schedules.run_schedule(runner, [{"entries": [{"id": "b", "tokens": second, "want": list(range(150))}],
+                                              "end": ["b"]}], SparseRouting)["b"]
+        if clear:
+            ref = want_for((pcfg, weights), {"b": second}, {"b": want}, "bfloat16", SparseRouting, "reused page")["b"]
+            check(got, ref, "bfloat16", "reused page")
+            assert runner.cache.pages_cleared == 3
+        else:
+            assert not bool(torch.isfinite(got).all())
