@@ -102,13 +102,21 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
     mx = fmaxf(mx, v);
   }
   mx = warp_max(mx);
+  // A logit that is not a number (a broken checkpoint, an overflow upstream) must not become an
+  // index: such a probability counts as zero in the selection, so the k experts chosen are
+  // always valid ones, and the row's weights are made NaN so that its output shows the fault
+  // instead of hiding it.
+  bool bad = false;
   float sum = 0.f;
   for (int e = lane; e < E; e += 32) {
-    const float p = expf(lg[e] - mx);
+    float p = expf(lg[e] - mx);
+    if (!(p >= 0.f && p <= 1.f)) { p = 0.f; bad = true; }
     lg[e] = p;
     sum += p;
   }
   sum = warp_sum(sum);
+  bad = __any_sync(0xffffffffu, bad) || !(sum > 0.f);
+  if (bad) sum = 1.f;
   __syncwarp();
   float sel_sum = 0.f;
   for (int j = 0; j < k; ++j) {
@@ -124,9 +132,10 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
       const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
     }
+    // (k <= E and every probability is >= 0 > -1, and a taken one is -2: best_e is a valid expert)
     if (lane == 0) {
       topk_idx[(size_t)t * k + j] = best_e;
-      topk_w[(size_t)t * k + j] = best / sum;
+      topk_w[(size_t)t * k + j] = bad ? __int_as_float(0x7fc00000) : best / sum;
       if (chosen) chosen[(size_t)t * k + j] = (unsigned short)best_e;
       lg[best_e] = -2.f;                           // taken
     }

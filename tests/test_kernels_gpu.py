@@ -776,3 +776,29 @@ def test_router_many_rows_through_split_matrix(K, exact_bf16):
     assert same.float().mean() > 0.995          # a tie within 2^-17 may fall the other way
     torch.testing.assert_close(wts[same], rwts[same], rtol=2e-4, atol=1e-6)
     torch.testing.assert_close(ext, rext, rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_router_with_logits_that_are_not_numbers_still_names_valid_experts(K, dtype):
+    """A row of NaN (a broken checkpoint, an overflow upstream) must not become an expert index:
+    the selection still names k distinct valid experts, the plan stays inside its arrays, and the
+    row's weights are NaN so that its output shows the fault.  Other rows are untouched."""
+    T, H, E, k = 6, 256, 8, 2
+    x = rnd((T, H), dtype, 91)
+    x[2] = float("nan")
+    x[4, 7] = float("inf")
+    wr = rnd((E + 1, H), torch.float32, 92, 0.05)
+    clean = x.clone()
+    clean[2] = 0
+    clean[4] = 0
+    for fn in (K.route, lambda *a: K.router_topk(*a) + (None,)):
+        idx, wts, ext, plan = fn(x, wr, E, k, False)
+        ref_idx, ref_wts, _, _ = fn(clean, wr, E, k, False)
+        assert int(idx.min()) >= 0 and int(idx.max()) < E
+        assert all(len(set(row)) == k for row in idx.tolist())
+        assert bool(torch.isnan(wts[2]).all()) and bool(torch.isnan(wts[4]).all())
+        ok = [0, 1, 3, 5]
+        assert torch.equal(idx[ok], ref_idx[ok]) and torch.equal(wts[ok], ref_wts[ok])
+        if plan is not None:
+            assert int(plan.offsets[-1]) == T * k and sorted(plan.order.tolist()) == list(range(T * k))
+    assert K.index_status() == 0
