@@ -176,24 +176,22 @@ class CacheManager:
                 raise OutOfPages(f"request {req!r}: group {g.index} needs {n} pages, "
                                  f"{g.pool.num_free} free")
         for n, g, table in zip(need, self.groups, ent.tables):
+            first_new = len(table)
             taken, again = g.pool.take_marking_reuse(n)
             table.extend(taken)
-            if again and self.clear_reused_pages and g.pages is not None:
-                # A page that is handed out again still holds its earlier owner's entries.  Kernels
-                # that copy whole pages multiply what lies beyond the new owner's position by a
-                # zero probability, which keeps a result right only while those entries are
-                # finite; zeros are.  On the stream, so it is ordered after whatever still reads
-                # the page for its earlier owner (a step launched ahead).
-                # (runs of neighbouring pages, one fill each: no index list has to cross to the device)
-                again.sort()
-                a = 0
-                while a < len(again):
-                    b = a
-                    while b + 1 < len(again) and again[b + 1] == again[b] + 1:
-                        b += 1
-                    g.pages[:, again[a]:again[b] + 1].zero_()
-                    a = b + 1
-                self.pages_cleared += len(again)
+            if not (again and self.clear_reused_pages and g.pages is not None):
+                continue
+            # A page that is handed out again still holds its earlier owner's entries.  Kernels
+            # that copy whole pages multiply what lies beyond the new owner's position by a zero
+            # probability, which keeps a result right only while those entries are finite; zeros
+            # are.  Pages that this reservation covers to their last row are overwritten by the
+            # step before anything reads them; the one it covers in part is zeroed here - on the
+            # stream, so after whatever still reads it for its earlier owner (a step launched ahead).
+            for i, p in enumerate(taken):
+                covered_to = (first_new + i + 1) * self.page_size
+                if covered_to > new_length and p in again:
+                    g.pages[:, p].zero_()
+                    self.pages_cleared += 1
         ent.reserved = max(ent.reserved, new_length)
 
     def commit(self, req: Hashable, new_length: int) -> None:

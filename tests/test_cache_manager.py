@@ -147,10 +147,12 @@ def test_random_orders_lose_no_page(seed):
     assert m.pages_free() == [10, 10]
 
 
-def test_a_page_is_cleared_when_it_is_handed_out_again():
-    """A page that goes to a second owner is zeroed first (what lies beyond the new owner's
-    position in it is multiplied by zero probabilities, and must be finite); a page handed out
-    for the first time still has the zeros it was made with and is left alone."""
+def test_a_partly_covered_page_is_cleared_when_it_is_handed_out_again():
+    """A page that goes to a second owner and is not covered to its last row by the reservation
+    is zeroed first (what lies beyond the new owner's position in it is multiplied by zero
+    probabilities, and must be finite).  Pages covered completely are overwritten by the step
+    before anything reads them, and a page handed out for the first time still has the zeros it
+    was made with: both are left alone."""
     import torch
     from ninfer_amd_mi50_b200.cache.manager import CacheManager
     from ninfer_amd_mi50_b200.parts.base import CacheSpec
@@ -158,18 +160,23 @@ def test_a_page_is_cleared_when_it_is_handed_out_again():
     cm = CacheManager([spec, spec], [None, None], page_size=4, num_pages=6, max_requests=2, max_context=24)
     (g,) = cm.groups
     cm.open("a")
-    cm.reserve("a", 9)                       # three pages, first use
+    cm.reserve("a", 9)                       # three pages, first use: nothing to clear
     assert cm.pages_cleared == 0
     held = list(cm.block_table(0, "a"))
     g.pages[:, held] = float("nan")          # whatever "a" left there
     cm.commit("a", 9)
     cm.close("a")
     cm.open("b")
-    cm.reserve("b", 17)                      # five pages: the three of "a" again and two fresh ones
-    again = [p for p in cm.block_table(0, "b") if p in held]
-    assert sorted(again) == sorted(held) and cm.pages_cleared == 3
-    assert bool(torch.isfinite(g.pages).all()) and float(g.pages[:, cm.block_table(0, "b")].abs().sum()) == 0.0
+    cm.reserve("b", 6)                       # two of "a"'s pages again: rows 0-3 and 4-5 (+ two stale rows)
+    t = cm.block_table(0, "b")
+    assert set(t) <= set(held) and cm.pages_cleared == 1
+    assert bool(torch.isnan(g.pages[:, t[0]]).all())                   # covered whole: the step overwrites it
+    assert float(g.pages[:, t[1]].abs().sum()) == 0.0                 # covered in part: zeroed
+    cm.commit("b", 6)
+    cm.reserve("b", 8)                       # same page, further rows: it is not taken again
+    cm.reserve("b", 9)                       # the third of "a"'s pages, one row of four
+    assert cm.pages_cleared == 2 and float(g.pages[:, cm.block_table(0, "b")[2]].abs().sum()) == 0.0
     off = CacheManager([spec], [None], page_size=4, num_pages=2, max_requests=1, max_context=8, clear_reused_pages=False)
     off.open("a"); off.reserve("a", 8); off.groups[0].pages[:, :2] = 1.0; off.commit("a", 8); off.close("a")
-    off.open("b"); off.reserve("b", 8)
+    off.open("b"); off.reserve("b", 7)
     assert off.pages_cleared == 0 and float(off.groups[0].pages[:, :2].sum()) > 0

@@ -182,6 +182,6 @@ def test_a_reused_page_with_non_finite_leftovers_does_no_harm(tmp_path):
         if clear:
             ref = want_for((pcfg, weights), {"b": second}, {"b": want}, "bfloat16", SparseRouting, "reused page")["b"]
             check(got, ref, "bfloat16", "reused page")
-            assert runner.cache.pages_cleared == 3
+            assert runner.cache.pages_cleared == 1          # 150 tokens: two pages covered whole, the third in part
         else:
             assert not bool(torch.isfinite(got).all())
