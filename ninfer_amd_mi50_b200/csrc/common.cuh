@@ -30,11 +30,12 @@ void note_launch_error(cudaError_t e);
 // For the first kernel after a wait on another stream's event: its dependency is then not the
 // kernel before it in its own stream, and a programmatic edge does not describe it.
 bool take_chain_break();
-// Whether a launch of class `cls` on `stream` gets the attribute: the class is switched on, no
-// break is pending, and the stream is being captured into a graph.  Outside a capture launches
-// are ordinary: a step driven from the host gains nothing (the host is slower than the
-// kernels), and on streams driven that way one decode step in some ten thousand came out
-// different with the attribute on - never with it off, and never in replayed graphs.
+// Whether a launch of class `cls` on `stream` gets the attribute: the class is switched on and no
+// break is pending.  (It used to be given only while the stream was being captured: driven from
+// the host, one decode step in some ten thousand came out different.  That was the stale read
+// through the non-coherent path that skinny_gemm.cu describes, not the attribute; with it gone,
+// 48,000 host-driven steps run twice agree bit for bit, and a prompt of 2,048 tokens, whose
+// kernels are launched one by one from the host, is 2 % faster.)
 bool chain_this_launch(int cls, cudaStream_t stream);
 extern int g_chained_launch;   // nf_set_chained_launch(): a mask over NF_CHAIN_CLASS bits; 0 turns the attribute off
 #ifndef NF_CHAIN_CLASS

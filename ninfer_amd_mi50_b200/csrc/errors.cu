@@ -13,7 +13,7 @@ bool take_chain_break() {
   return b;
 }
 void set_chain_break() { g_chain_break = true; }
-int g_chain_outside_capture = 0;      // nf_set_chained_launch_outside_capture(): for experiments
+int g_chain_outside_capture = 1;      // nf_set_chained_launch_outside_capture(0): chain only while a stream captures
 bool chain_this_launch(int cls, cudaStream_t stream) {
   const bool pending_break = take_chain_break();          // consumed by this launch either way
   if (!(g_chained_launch & cls) || pending_break) return false;
@@ -55,8 +55,8 @@ extern "C" const char* nf_last_error() { return nf::g_error; }
 
 extern "C" int nf_abi_version() { return 1; }
 
-// 1: kernels of the decode path are launched with programmatic stream serialization (they may
-// begin while their predecessor drains); 0: ordinary launches.
+// 1 (default): kernels are launched with programmatic stream serialization (they may begin while
+// their predecessor drains) whether or not the stream is being captured; 0: only inside a capture.
 extern "C" int nf_set_chained_launch_outside_capture(int on) {
   nf::g_chain_outside_capture = on ? 1 : 0;
   return 0;

@@ -44,8 +44,8 @@ def load() -> ctypes.CDLL:
                 lib.nf_set_chained_launch(int(mask))
             if os.environ.get("NINFER_SKINNY_MAX_SPLIT"):
                 lib.nf_set_skinny_max_split(int(os.environ["NINFER_SKINNY_MAX_SPLIT"]))   # 1: no split over k
-            if os.environ.get("NINFER_CHAINED_OUTSIDE_CAPTURE") == "1":
-                lib.nf_set_chained_launch_outside_capture(1)     # experiments only
+            if os.environ.get("NINFER_CHAINED_OUTSIDE_CAPTURE") == "0":
+                lib.nf_set_chained_launch_outside_capture(0)     # chained launches only inside a stream capture
             _lib = lib
     return _lib
 
