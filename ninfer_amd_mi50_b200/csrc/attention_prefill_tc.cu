@@ -154,6 +154,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   tc_fence_after();
   const unsigned tmem = bars->tmem_base;
   const unsigned tmem_o = tmem + 2 * kKeys;       // S buffers at columns 0 and 128, O at 256
+  // Launched chained: the zero-fill, the barriers and the tensor-memory allocation above touch
+  // nothing outside the SM and ran while the kernel before this one drained; queries, keys and
+  // values (and the first write of `out`) come after the wait.
+  chain_wait(block_table, positions, seg_row0, tiles);
 
   if (warp == 0 || warp == 10) {
     // ---- producers: warp 0 brings Q and the keys, warp 10 the values --------------------------------
@@ -453,9 +457,8 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const int* 
     set = true;
   }
   dim3 grid(Hq, n_tiles);
-  prefill_attention_tc_kernel<D><<<grid, kFaThreads, smem, stream>>>(mq, mkv, block_table, bt_width, positions, seg_row0,
-                                                                    tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size,
-                                                                    num_pages, window, scale);
+  launch_chained(prefill_attention_tc_kernel<D>, grid, dim3(kFaThreads), smem, stream, mq, mkv, block_table, bt_width,
+                 positions, seg_row0, tiles, (__nv_bfloat16*)out, Hq, Hkv, page_size, num_pages, window, scale);
   return check_launch("prefill_attention_tc");
 }
 

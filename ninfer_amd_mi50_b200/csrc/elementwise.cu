@@ -15,6 +15,7 @@ template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int hidden, int vocab) {
   const int t = blockIdx.x;
+  chain_wait();          // before the first write too: `out` may be memory that the kernel before still reads
   const int id = ids[t];
   float* o = out + (size_t)t * hidden;
   if (id < 0 || id >= vocab) {
@@ -137,6 +138,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ rows, int div,
                                    uint4* __restrict__ out, int pieces) {
   const int p = blockIdx.x;
+  chain_wait(x, rows);
   const uint4* src = x + (size_t)(rows[p] / div) * pieces;
   uint4* dst = out + (size_t)p * pieces;
   for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
@@ -147,6 +149,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __n
                                        int inner) {
   const int m = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  chain_wait(gu);
   if (i >= inner) return;
   float g[8], u[8];
   load8(gu + (size_t)m * 2 * inner + i, g);
@@ -303,9 +306,9 @@ extern "C" int nf_embed_rows(const void* table, const int* ids, float* out, int 
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && hidden > 0 && vocab > 0, "embed_rows: bad sizes T=%d hidden=%d vocab=%d", T, hidden, vocab);
   if (dtype == kF32)
-    embed_rows_kernel<float><<<T, row_threads(hidden), 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    launch_chained(embed_rows_kernel<float>, dim3(T), dim3(row_threads(hidden)), 0, stream, (const float*)table, ids, out, hidden, vocab);
   else
-    embed_rows_kernel<__nv_bfloat16><<<T, row_threads(hidden), 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    launch_chained(embed_rows_kernel<__nv_bfloat16>, dim3(T), dim3(row_threads(hidden)), 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
   return check_launch("embed_rows");
 }
 
@@ -343,7 +346,7 @@ extern "C" int nf_silu_mul(const void* gu, void* act, int M, int inner, int dtyp
   NF_REQUIRE(M > 0 && inner > 0, "silu_mul: bad sizes M=%d inner=%d", M, inner);
   if (dtype == kBF16 && inner % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)act % 16 == 0) {
     dim3 g8(M, (inner / 8 + 127) / 128);
-    silu_mul_bf16x8_kernel<<<g8, 128, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inner);
+    launch_chained(silu_mul_bf16x8_kernel, g8, dim3(128), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inner);
     return check_launch("silu_mul");
   }
   dim3 grid(M, (inner + 255) / 256);
@@ -412,6 +415,6 @@ extern "C" int nf_gather_rows(const void* x, const int* rows, int div, void* out
   if (n == 0) return 0;
   NF_REQUIRE(n > 0 && div > 0 && row_bytes > 0 && row_bytes % 16 == 0, "gather_rows: rows of %d bytes are not whole 16-byte pieces", row_bytes);
   NF_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0), "gather_rows: operands must be 16-byte aligned");
-  gather_rows_kernel<<<n, row_threads(row_bytes / 16), 0, stream>>>((const uint4*)x, rows, div, (uint4*)out, row_bytes / 16);
+  launch_chained(gather_rows_kernel, dim3(n), dim3(row_threads(row_bytes / 16)), 0, stream, (const uint4*)x, rows, div, (uint4*)out, row_bytes / 16);
   return check_launch("gather_rows");
 }

@@ -90,6 +90,9 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
   __shared__ int s_max_rows;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // launched chained: resident while the kernel before it drains; everything below reads what
+  // that kernel (or the routing before it) wrote
+  chain_wait(offsets);
   const int k_steps = (K + kBK - 1) / kBK;
   const int n_ftiles = (n_features + kBM - 1) / kBM;
   const int n_fitems = (n_ftiles + FT_STEP - 1) / FT_STEP;      // items along the features
@@ -323,8 +326,8 @@ static int launch_tc(const void* Wp, const CUtensorMap& mx, const int* offsets, 
   }
   // at least one pass per non-empty group; the kernel itself counts the exact number of items
   const int grid = n_sm;
-  grouped_gemm_tc_kernel<SWIGLU, PAIR><<<grid, kTcThreads, smem, stream>>>((const __nv_bfloat16*)Wp, mx, offsets,
-                                                             (__nv_bfloat16*)out, ldo, n_features, K, groups);
+  launch_chained(grouped_gemm_tc_kernel<SWIGLU, PAIR>, dim3(grid), dim3(kTcThreads), smem, stream,
+                 (const __nv_bfloat16*)Wp, mx, offsets, (__nv_bfloat16*)out, ldo, n_features, K, groups);
   return check_launch("grouped_gemm_tc");
 }
 

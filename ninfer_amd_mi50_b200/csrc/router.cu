@@ -155,6 +155,7 @@ router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp
   extern __shared__ float smem[];      // [4 warps][E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
+  chain_wait(logits);
   if (t >= n_tokens) return;
   // logits[t, e] sits at t * tok_stride + e * exp_stride (either may be the unit stride)
   select_token(logits + (size_t)t * tok_stride, exp_stride, smem + warp * E, t, E, extra, k, norm_topk,
@@ -488,6 +489,8 @@ moe_rank_kernel(const int* __restrict__ topk_idx, int n, int* __restrict__ count
   // warp w takes the contiguous chunk w of the pairs: count, prefix over warps, then rank
   __shared__ int warp_tot[32];
   const int e = blockIdx.x;
+  chain_release_if_small();
+  chain_wait(topk_idx);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   const int chunk = ((n + nwarp - 1) / nwarp + 31) & ~31;
   const int lo = warp * chunk, hi = min(n, lo + chunk);
@@ -515,6 +518,8 @@ moe_scatter_kernel(const int* __restrict__ topk_idx, int n, int E, const int* __
                    int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ inv,
                    int* __restrict__ active, int n_active_max) {
   extern __shared__ int off[];        // [E + 1]
+  chain_release_if_small();
+  chain_wait(topk_idx, counts);
   if (threadIdx.x == 0) {
     int run = 0, na = 0;
     const bool list = active && blockIdx.x == 0;
@@ -674,7 +679,7 @@ extern "C" int nf_router_select(const float* logits, long long tok_stride, long 
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && E > 0 && k > 0 && k <= E && extra >= 0, "router: bad sizes T=%d E=%d k=%d", T, E, k);
   NF_REQUIRE((size_t)4 * E * 4 <= 48 * 1024, "router: %d experts are more than the selection kernel holds (3072)", E);
-  router_select_kernel<<<(T + 3) / 4, 128, (size_t)4 * E * sizeof(float), stream>>>(logits, (long)tok_stride, (long)exp_stride, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
+  launch_chained(router_select_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), stream, logits, (long)tok_stride, (long)exp_stride, T, E, extra, k, norm_topk, topk_idx, topk_w, extra_out);
   return check_launch("router_select");
 }
 
@@ -684,9 +689,9 @@ extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int*
                            int* counts, int* active, int n_active_max, cudaStream_t stream) {
   NF_REQUIRE(n >= 0 && E > 0 && E <= 8192, "moe_plan: bad sizes n=%d E=%d", n, E);
   if (n > 2048 && counts) {
-    moe_rank_kernel<<<E, 1024, 0, stream>>>(topk_idx, n, counts, inv);
+    launch_chained(moe_rank_kernel, dim3(E), dim3(1024), 0, stream, topk_idx, n, counts, inv);
     if (int rc = check_launch("moe_rank")) return rc;
-    moe_scatter_kernel<<<(n + 255) / 256, 256, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, counts, offsets, order, inv, active, n_active_max);
+    launch_chained(moe_scatter_kernel, dim3((n + 255) / 256), dim3(256), (E + 1) * sizeof(int), stream, topk_idx, n, E, (const int*)counts, offsets, order, inv, active, n_active_max);
     return check_launch("moe_scatter");
   }
   const size_t staged = (size_t)(E + 1) * sizeof(int) + (size_t)n * sizeof(unsigned short);
