@@ -90,56 +90,69 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
   __shared__ int s_max_rows;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // launched chained: resident while the kernel before it drains; everything below reads what
-  // that kernel (or the routing before it) wrote
-  chain_wait(offsets);
   const int k_steps = (K + kBK - 1) / kBK;
   const int n_ftiles = (n_features + kBM - 1) / kBM;
   const int n_fitems = (n_ftiles + FT_STEP - 1) / FT_STEP;      // items along the features
 
-  // stage geometry, the same for every item: weights + as many 64-row boxes as the largest
-  // pass of any group needs
-  if (threadIdx.x == 0) s_max_rows = 0;
-  __syncthreads();
-  {
-    int mx = 0;
-    for (int g = threadIdx.x; g < groups; g += blockDim.x) mx = max(mx, offsets[g + 1] - offsets[g]);
-    if (mx) atomicMax(&s_max_rows, mx);
-  }
-  __syncthreads();
-  constexpr int kAccBuffers = (SWIGLU || PAIR) ? 1 : 2;      // accumulators of kBNMax columns that fit beside each other
-  const int max_boxes = (min(max(s_max_rows, 1), kBNMax) + kXBox - 1) / kXBox;
-  const int stage_bytes = A_BYTES + max_boxes * BOX_BYTES;
-  const int tail_bytes = (int)sizeof(Barriers) + (groups + 1) * (int)sizeof(int);
-  const int stages = min(kMaxStages, (kSmemBudget - tail_bytes) / stage_bytes);
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + (size_t)stages * stage_bytes);
+  // Barriers and the groups' pass table at the head of shared memory, the stages behind them.
+  // Launched chained, the CTA is resident while the kernel before it drains: barriers and
+  // tensor memory are set up meanwhile, and everything that reads what that kernel (or the
+  // routing before it) wrote comes after the wait.
+  Barriers* bars = reinterpret_cast<Barriers*>(smem);
   int* s_pass_start = reinterpret_cast<int*>(bars + 1);     // [groups + 1] first pass index of every group
+  const int head_bytes = ((int)sizeof(Barriers) + (groups + 1) * (int)sizeof(int) + 1023) & ~1023;
+  unsigned char* stage0 = smem + head_bytes;
   volatile int* stop = &bars->stop;
   if (threadIdx.x == 0) {
-    int run = 0;
-    for (int g = 0; g < groups; ++g) {
-      s_pass_start[g] = run;
-      run += (offsets[g + 1] - offsets[g] + kBNMax - 1) / kBNMax;
-    }
-    s_pass_start[groups] = run;
-  }
-  __syncthreads();
-  const int n_items = s_pass_start[groups] * n_fitems;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int s = 0; s < kMaxStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&bars->acc_full[b], 1); mbar_init(&bars->acc_empty[b], kEpilogueWarps); }
     bars->stop = 0;
+    s_max_rows = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  chain_wait(offsets);
+
+  // stage geometry, the same for every item: weights + as many 64-row boxes as the largest
+  // pass of any group needs.  Thread g counts the passes of group g; warp 0 adds them up.
+  __syncthreads();
+  {
+    int mx = 0;
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+      const int n = offsets[g + 1] - offsets[g];
+      mx = max(mx, n);
+      s_pass_start[g + 1] = (n + kBNMax - 1) / kBNMax;
+    }
+    if (mx) atomicMax(&s_max_rows, mx);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int run = 0;
+    if (lane == 0) s_pass_start[0] = 0;
+    for (int g0 = 0; g0 < groups; g0 += 32) {
+      const int g = g0 + lane;
+      int v = g < groups ? s_pass_start[g + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += o;
+      }
+      if (g < groups) s_pass_start[g + 1] = run + v;
+      run += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  constexpr int kAccBuffers = (SWIGLU || PAIR) ? 1 : 2;      // accumulators of kBNMax columns that fit beside each other
+  const int max_boxes = (min(max(s_max_rows, 1), kBNMax) + kXBox - 1) / kXBox;
+  const int stage_bytes = A_BYTES + max_boxes * BOX_BYTES;
+  const int stages = min(kMaxStages, (kSmemBudget - head_bytes) / stage_bytes);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const unsigned tmem = bars->tmem_base;
+  const int n_items = s_pass_start[groups] * n_fitems;
 
   if (warp == 0) {
     // ---- producer ---------------------------------------------------------------------------
@@ -163,7 +176,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
           for (int ks = 0; ks < k_steps; ++ks, ++it) {
             const int s = it % stages;
             if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, stop, 1, &g_tc_error)) { ok = false; break; }
-            unsigned char* st = smem + (size_t)s * stage_bytes;
+            unsigned char* st = stage0 + (size_t)s * stage_bytes;
             mbar_expect_tx(&bars->full[s], a_bytes + boxes * BOX_BYTES);
             if (PAIR) {
               bulk_load(st, w_tile + (size_t)ks * TILE_BYTES, TILE_BYTES, &bars->full[s]);
@@ -212,7 +225,7 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
             const int s = it % stages;
             if (!mbar_wait(&bars->full[s], (it / stages) & 1, stop, 3, &g_tc_error)) { ok = false; break; }
             tc_fence_after();
-            unsigned char* st = smem + (size_t)s * stage_bytes;
+            unsigned char* st = stage0 + (size_t)s * stage_bytes;
             const unsigned long long a0 = smem_desc(st);
             const unsigned long long a1 = smem_desc(st + kBM * kBK * 2);
             const unsigned long long b = smem_desc(st + A_BYTES);
