@@ -58,6 +58,10 @@ TUNING = {
     # steps at A2.7B sizes: starting late is 3 % faster at 48 and 64 rows, 5 % slower at 16)
     "shared_fork_max_rows": 64,
     "shared_fork_late_rows": 32,
+    # in steps of at least this many rows the routing (logits, selection, plan, gather: short
+    # kernels of a few CTAs, one waiting for the other) runs on a second stream of higher
+    # priority while the shared expert's products fill the device; 0 turns it off
+    "route_beside_shared_min_rows": 256,
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -605,10 +609,27 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
     return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
 
 
-def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
+def moe_uses_gathered_rows(x: torch.Tensor, w13) -> bool:
+    """Whether `moe_gemm1` would first copy the rows of `x` into sorted order (`moe_gather`)."""
+    return isinstance(w13, PackedWeights) and x.shape[0] > TUNING["skinny_moe_max_tokens"]
+
+
+def moe_gather(x: torch.Tensor, plan: MoePlan, k: int) -> torch.Tensor:
+    """Row p of the result is row order[p] // k of `x`: the tokens in the experts' order."""
+    _chk(x, "x")
+    T, H = x.shape
+    xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
+    if T:
+        _lib.call("nf_gather_rows", _p(x), _p(plan.order), c_int(k), _p(xp), c_int(T * k),
+                  c_int(H * x.element_size()), _stream())
+    return xp
+
+
+def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int, gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sorted pair p (token order[p] // k, expert e) -> silu(x Wgate_e^T) * (x Wup_e^T)  [T*k, I].
 
-    `w13` is [E, 2I, H] (gate rows first), or `PackedWeights` of it for the bfloat16 kernels."""
+    `w13` is [E, 2I, H] (gate rows first), or `PackedWeights` of it for the bfloat16 kernels.
+    `gathered`: `moe_gather(x, plan, k)` if the caller has it already."""
     _chk(x, "x")
     T, H = x.shape
     packed = isinstance(w13, PackedWeights)
@@ -629,9 +650,7 @@ def moe_gemm1(x: torch.Tensor, w13, plan: MoePlan, k: int) -> torch.Tensor:
                     k, True, packed=True, group_map=plan.active)
         else:
             # rows in sorted order, then one tensor-core launch over all experts
-            xp = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
-            _lib.call("nf_gather_rows", _p(x), _p(plan.order), c_int(k), _p(xp), c_int(T * k),
-                      c_int(H * 2), _stream())
+            xp = gathered if gathered is not None else moe_gather(x, plan, k)
             _lib.call("nf_grouped_gemm_tc", _p(xp), c_longlong(T * k), _p(w13.data), c_int(E),
                       c_int(inner), c_int(H), _p(plan.offsets), _p(act), c_int(inner), c_int(1), _stream())
         return act

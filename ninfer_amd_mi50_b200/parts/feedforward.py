@@ -28,10 +28,11 @@ from .base import FeedForward, Fetch, RoutedSum, StepContext, TensorSpec
 _SIDE_STREAMS = {}
 
 
-def _side_stream(device: torch.device) -> "torch.cuda.Stream":
-    key = str(device)
+def _side_stream(device: torch.device, urgent: bool = False) -> "torch.cuda.Stream":
+    """The second stream of a device; `urgent`: the one whose CTAs are placed before others'."""
+    key = (str(device), urgent)
     if key not in _SIDE_STREAMS:
-        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device, priority=-1 if urgent else 0)
     return _SIDE_STREAMS[key]
 
 
@@ -165,20 +166,38 @@ class SparseMoeSwiglu(FeedForward):
         # idle); from some tens of rows on it is better started after it, beside the experts'
         # products (measured on decode steps: 3 % faster at 48 and 64 rows, 5 % slower at 16).
         late = x.shape[0] > kernels.TUNING["shared_fork_late_rows"]
+        # In large steps it is the other way round: the shared expert's products fill the device,
+        # and the routing - a chain of short kernels of a few CTAs - runs beside them.
+        beside = kernels.TUNING["route_beside_shared_min_rows"]
+        beside = self.has_shared and x.is_cuda and not fork and 0 < beside <= x.shape[0]
         if fork and not late:
             main, side, shared = start_shared()
-        idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
-                                             split=self.w_router_split)
+        gathered = None
+        if beside:
+            main, side = torch.cuda.current_stream(x.device), _side_stream(x.device, urgent=True)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                kernels.chain_break()
+                idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
+                                                     split=self.w_router_split)
+                if kernels.moe_uses_gathered_rows(x, self.w13):
+                    gathered = kernels.moe_gather(x, plan, k)
+            shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
+            main.wait_stream(side)
+            kernels.chain_break()
+        else:
+            idx, wts, gate, plan = kernels.route(x, self.w_router, E, k, self.norm_topk_prob,
+                                                 split=self.w_router_split)
         if fork and late:
             main, side, shared = start_shared()
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
-        act = kernels.moe_gemm1(x, self.w13, plan, k)
+        act = kernels.moe_gemm1(x, self.w13, plan, k, gathered=gathered)
         y = kernels.moe_gemm2(act, self.w2, plan, plan_is_older=True)
         if fork:
             main.wait_stream(side)
             kernels.chain_break()           # the kernel that adds up also reads what the other stream produced
-        elif self.has_shared:
+        elif self.has_shared and not beside:
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         # not added up here: the next norm does it inside its own kernel (`RoutedSum`); whoever
         # cannot calls `materialize()`, which is `kernels.moe_combine`
