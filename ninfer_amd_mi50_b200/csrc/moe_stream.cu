@@ -1,0 +1,591 @@
+// The routed experts of a decode step in one persistent launch: both products of every
+// selected expert, streamed through one ring of shared memory that never runs dry.
+//
+// Reference counterpart: the per-expert loop of the MoE branch (src/models/model.hip:355-427),
+// which launches a fused gate/up GEMV and a down GEMV for each selected expert of one token.
+// A decode batch selects a few dozen experts, each with one to a handful of rows; the time of
+// the step is the time to read their weights once.  Two launches of a weight-streaming kernel
+// (skinny_gemm.cu) leave the memory idle at their start, between them and at their end, and
+// their CTAs hold few bytes in flight; this kernel instead keeps one CTA on every SM for the
+// whole MoE branch:
+//
+//   * a producer thread walks the work items - (expert, 16*Q features) of the gate/up product,
+//     then of the down product - and copies their weights, block after block (16 Q rows x 64 k,
+//     contiguous in the packed tile layout), into a ring of shared memory with bulk copies
+//     (`cp.async.bulk`, completion on an mbarrier); it runs ahead of the consumers by the whole
+//     ring, across item and product boundaries, so every SM always has about 100 KB in flight;
+//   * eight consumer warps read the blocks with `ldmatrix` and multiply with
+//     `mma.sync.m16n8k16` (float32 sums) against rows of X in shared memory: the step's hidden
+//     rows, all of them, are loaded once a CTA, and an expert's rows are picked by the
+//     `ldmatrix` row addresses; SwiGLU in the epilogue;
+//   * an item of the second product needs every feature of its expert's activations: the first
+//     product counts finished items per expert in global memory; a loader thread waits
+//     (bounded) for the count and then brings the expert's activation rows in with bulk copies,
+//     one item ahead of the consumers (two buffers where shared memory allows);
+//   * items are handed out by a ticket counter, so the SMs stay balanced whatever the sizes of
+//     the two products.  Tickets are handed out in order and first-product items never wait, so
+//     the wait for activations cannot deadlock as long as the grid's CTAs run.
+//
+// The sums of a row are formed in an order that depends on the sizes and on Q only (k tiles in
+// order, k groups added in order), never on the batch or on which CTA took the item.  Every
+// wait is bounded; the first to give up records a code and the CTA leaves.
+#define NF_CHAIN_CLASS 0x20
+#include "tcgen05.cuh"
+
+namespace nf {
+
+constexpr int kMsConsumers = 8;                          // consumer warps
+constexpr int kMsThreads = 32 * (kMsConsumers + 2);      // + the weight producer's warp + the activation loader's
+constexpr int kMsMaxStages = 32;
+constexpr int kMsSlotBytes = 16 * 1024;                  // a stage: 128 weight rows x 64 k, or 64 x 128, or 32 x 256
+constexpr int kMsMinStages = 4;
+constexpr int kMsMaxActive = 256;                        // experts with rows in one step
+constexpr int kMsMaxPairs = 256;                         // (token, expert) pairs of one step
+constexpr int kMsMaxRows = 16;                           // rows an expert may have in one step
+constexpr int kMsFifo = 64;                              // item ids between producer, loader and consumers
+constexpr unsigned kMsCountPolls = 1u << 20;             // polls of an expert's counter (about a second)
+
+// 1-3 ring waits, 4 the wait for an expert's activations, 5-7 a plan that does not fit, 8 the
+// consumers' barrier, 9-11 the loader's waits, 12-13 the consumers' waits for activation rows and hidden rows
+__device__ int g_moe_stream_error = 0;
+
+struct MsHeader {
+  unsigned long long full[kMsMaxStages], empty[kMsMaxStages];
+  unsigned long long meet;                 // the consumer warps' own barrier
+  unsigned long long xfull[2], xempty[2];  // activation-row buffers: filled by the loader, released by the consumers
+  unsigned long long xready;               // the step's hidden rows have arrived
+  int fifo[kMsFifo];
+  int stop, n_active, published, loaded;   // published / loaded: items the producer has named / the loader has read
+  int max_rows, pad0, pad1, pad2;
+  int expert[kMsMaxActive], row_begin[kMsMaxActive], rows[kMsMaxActive];
+  int order[kMsMaxPairs];                  // sorted pair -> token
+};
+
+struct MsArgs {
+  const __nv_bfloat16* X;      // [T, H] hidden rows
+  const __nv_bfloat16* W13;    // packed [E][ceil(I/128)][ceil(H/64)][256][64]
+  const __nv_bfloat16* W2;     // packed [E][ceil(H/128)][ceil(I/64)][128][64]
+  __nv_bfloat16* act;          // [M, I] sorted pairs
+  __nv_bfloat16* Y;            // [M, H] sorted pairs
+  const int* offsets;          // [E + 1]
+  const int* order;            // [M] sorted pair -> pair index (token * k + slot)
+  const int* active;           // [n_mapped] experts with rows, ascending, -1 padded
+  int* work;                   // [2 + kMsMaxActive]: ticket, finished CTAs, items done per active expert; all zero between launches
+  long long gs13, gs2;         // group strides in elements
+  int ldx, M, T, H, I, E, k, n_mapped;
+  int x_stride, a_stride;      // bytes between rows of X / of activations in shared memory
+  int red_bytes, smem_bytes;   // the k groups' meeting place; all of the launch's dynamic shared memory
+};
+
+__device__ __forceinline__ void ldsm4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm2(unsigned addr, unsigned& r0, unsigned& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ms_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void add_release(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// what the kernel before wrote is read from L2, never through a cache that may hold an older line
+__device__ __forceinline__ int ld_l2_int(const int* p) {
+  int v;
+  asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// bounded spin on an int in shared memory until it exceeds `than`
+__device__ __forceinline__ bool spin_above(volatile int* v, int than, volatile int* stop, int code) {
+  for (unsigned i = 0; i < kPollLimit; ++i) {
+    if (*v > than) return true;
+    if ((i & 255u) == 255u && *stop) return false;
+    __nanosleep(32);
+  }
+  *stop = 1;
+  atomicCAS(&g_moe_stream_error, 0, code);
+  return false;
+}
+
+// A position in the ring: slot and the parity of its current use.
+struct MsRing {
+  int s, parity, stages;
+  __device__ __forceinline__ void next() {
+    if (++s == stages) { s = 0; parity ^= 1; }
+  }
+};
+
+// An item id -> (product, active expert, sub-tile of 16 Q features).
+struct MsItem {
+  int second, a, sub;
+};
+__device__ __forceinline__ MsItem ms_decode(int id, int n1, int n2, int items1) {
+  MsItem it;
+  it.second = id >= items1;
+  const int r = it.second ? id - items1 : id;
+  const int per = it.second ? n2 : n1;
+  it.a = r / per;
+  it.sub = r - it.a * per;
+  return it;
+}
+
+// The k loop of one item for one consumer warp.  Q: the item has 16 Q weight rows, and a stage
+// holds them for G = 8 / Q consecutive k tiles (block g of the stage: k tile j G + g); warp
+// (row group rg, k group kg) takes block kg.  SECOND: the down product, one set of sums; else
+// stages alternate between the gate rows and the up rows of the same k tiles, two sets.
+// NT: 8-row tiles of X.  The item's first stage has been waited for.  False if a wait gave up.
+template <int Q, int NT, bool SECOND>
+__device__ __forceinline__ bool ms_k_loop(MsHeader* hd, unsigned char* ring, MsRing& at, int kt, int kg, int a_row,
+                                          int a_hi, unsigned b_lane, float (&acc)[2][2][4]) {
+  constexpr int G = kMsConsumers / Q;
+  constexpr int BLOCK_BYTES = Q * 2048;
+  volatile int* stop = &hd->stop;
+  const int lane = threadIdx.x & 31;
+  bool first = true;
+  for (int t0 = 0; t0 < kt; t0 += G) {
+#pragma unroll
+    for (int half = 0; half < (SECOND ? 1 : 2); ++half) {
+      if (!first && !mbar_wait(&hd->full[at.s], at.parity, stop, 3, &g_moe_stream_error)) return false;
+      first = false;
+      if (t0 + kg < kt) {
+        const unsigned block = smem_u32(ring + (size_t)at.s * kMsSlotBytes) + kg * BLOCK_BYTES;
+        const unsigned b_addr = b_lane + (unsigned)(t0 + kg) * 128;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          unsigned a0, a1, a2, a3;
+          ldsm4(block + a_row * 128 + (((2 * ks + a_hi) ^ (a_row & 7)) << 4), a0, a1, a2, a3);
+          if (NT == 1) {
+            unsigned b0, b1;
+            ldsm2(b_addr + ks * 32, b0, b1);
+            ms_mma(acc[half][0], a0, a1, a2, a3, b0, b1);
+          } else {
+            unsigned b0, b1, b2, b3;
+            ldsm4(b_addr + ks * 32, b0, b1, b2, b3);
+            ms_mma(acc[half][0], a0, a1, a2, a3, b0, b1);
+            ms_mma(acc[half][1], a0, a1, a2, a3, b2, b3);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hd->empty[at.s]);
+      at.next();
+    }
+  }
+  return true;
+}
+
+// Q: an item is 16 Q features (2, 4 or 8 sixteen-row groups); the 8 consumer warps are Q row
+// groups x 8 / Q k groups.  (At most 102 registers a thread, so that kernels of another stream -
+// the shared expert's - still find room on the SM.)
+template <int Q>
+__global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs p) {
+  extern __shared__ unsigned char ms_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)ms_smem_raw + 1023) & ~(uintptr_t)1023);
+  static_assert(Q == 2 || Q == 4 || Q == 8, "16 Q features an item");
+  constexpr int G = kMsConsumers / Q;                  // k groups = k tiles a stage
+  constexpr int BLOCK_BYTES = Q * 2048;
+  constexpr int HEADER_BYTES = (sizeof(MsHeader) + 1023) & ~1023;
+  MsHeader* hd = reinterpret_cast<MsHeader*>(smem);
+  float* red = reinterpret_cast<float*>(smem + HEADER_BYTES);
+  unsigned char* xs = smem + HEADER_BYTES + p.red_bytes;                  // [T rows + a row of zeros][x_stride]
+  unsigned char* as = xs + (size_t)(p.T + 1) * p.x_stride;                // [buffers][rows][a_stride], then the ring
+  unsigned char* smem_end = ms_smem_raw + p.smem_bytes;
+  volatile int* stop = &hd->stop;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ int s_last;
+
+  // ---- set-up that needs nothing from the kernel before ------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMsMaxStages; ++s) { mbar_init(&hd->full[s], 1); mbar_init(&hd->empty[s], kMsConsumers); }
+    mbar_init(&hd->meet, kMsConsumers);
+    for (int b = 0; b < 2; ++b) { mbar_init(&hd->xfull[b], 1); mbar_init(&hd->xempty[b], kMsConsumers); }
+    mbar_init(&hd->xready, 1);
+    hd->stop = 0;
+    hd->n_active = 0;
+    hd->max_rows = 1;
+    hd->published = 0;
+    hd->loaded = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  {
+    // rows of X and of activations start as zeros (the padding of k stays zero for good)
+    const int n16 = (int)(((size_t)(p.T + 1) * p.x_stride + (size_t)2 * kMsMaxRows * p.a_stride) / 16);
+    uint4* z = reinterpret_cast<uint4*>(xs);
+    for (int i = threadIdx.x; i < n16 && reinterpret_cast<unsigned char*>(z + i + 1) <= smem_end; i += blockDim.x)
+      z[i] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();                               // bulk copies will write over these zeros
+  }
+  const int* offsets = p.offsets;
+  const int* active = p.active;
+  const int* order = p.order;
+  const __nv_bfloat16* X = p.X;
+  int* ticket = p.work;
+  int* finished = p.work + 1;
+  int* done = p.work + 2;
+  chain_wait(offsets, active, order, X, ticket);
+  __syncthreads();
+
+  // ---- the step: its experts, its pairs and its hidden rows (read from L2: the kernel before wrote them)
+  int first_id = 0;
+  if (warp == kMsConsumers && lane == 0) first_id = atomicAdd(ticket, 1);      // under way while the plan is read
+  if (warp == 0) {
+    int n = 0, most = 1;
+    for (int i0 = 0; i0 < p.n_mapped; i0 += 32) {
+      const int i = i0 + lane;
+      int e = i < p.n_mapped ? ld_l2_int(active + i) : -1;
+      int rb = 0, re = 0;
+      if (e >= p.E) { atomicCAS(&g_moe_stream_error, 0, 5); e = -1; }
+      if (e >= 0) {
+        rb = ld_l2_int(offsets + e);
+        re = ld_l2_int(offsets + e + 1);
+        if (rb < 0 || re > p.M || re - rb > kMsMaxRows) { atomicCAS(&g_moe_stream_error, 0, 6); e = -1; }
+        else if (re <= rb) e = -1;
+      }
+      const unsigned has = __ballot_sync(0xffffffffu, e >= 0);
+      const int at = n + __popc(has & ((1u << lane) - 1));
+      if (e >= 0 && at < kMsMaxActive) { hd->expert[at] = e; hd->row_begin[at] = rb; hd->rows[at] = re - rb; most = max(most, re - rb); }
+      n += __popc(has);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
+    if (lane == 0) {
+      if (n > kMsMaxActive) { atomicCAS(&g_moe_stream_error, 0, 7); n = kMsMaxActive; }
+      hd->n_active = n;
+      hd->max_rows = most;
+    }
+  } else if (warp == 1) {
+    for (int i = lane; i < p.M; i += 32) {
+      const int pair = ld_l2_int(order + i);
+      int tok = pair / p.k;
+      if (pair < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = p.T; }     // the row of zeros
+      hd->order[i] = tok;
+    }
+  } else if (warp == 2 && lane == 0) {
+    mbar_expect_tx(&hd->xready, (unsigned)p.T * p.H * 2);
+    for (int r = 0; r < p.T; ++r) bulk_load(xs + (size_t)r * p.x_stride, X + (size_t)r * p.ldx, (unsigned)p.H * 2, &hd->xready);
+  }
+  __syncthreads();
+  const int n_active = hd->n_active;
+  const int kt1 = (p.H + 63) >> 6, kt2 = (p.I + 63) >> 6;               // k tiles of the two products
+  const int n1 = (p.I + 16 * Q - 1) / (16 * Q), n2 = (p.H + 16 * Q - 1) / (16 * Q);     // items an expert
+  const int items1 = n_active * n1, total = items1 + n_active * n2;
+  const int target = n1 * kMsConsumers;                                 // counts that say "this expert's activations are complete"
+  // activation buffers of as many rows as the busiest expert has: two if the ring keeps enough stages beside them
+  const int a_rows = hd->max_rows;
+  const size_t a_buf_bytes = (size_t)a_rows * p.a_stride;
+  const size_t room = (size_t)(smem_end - as);
+  const int a_bufs = room >= 2 * a_buf_bytes + 1024 + (size_t)(kMsMinStages + 2) * kMsSlotBytes ? 2 : 1;
+  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)(as + a_bufs * a_buf_bytes) + 1023) & ~(uintptr_t)1023);
+  const int stages = min(kMsMaxStages, (int)((smem_end - ring) / kMsSlotBytes));
+  if (smem_end < ring || stages < 2) {             // (the host's check of the sizes rules this out)
+    if (threadIdx.x == 0) atomicCAS(&g_moe_stream_error, 0, 7);
+  } else if (warp == kMsConsumers) {
+    // ---- weight producer -----------------------------------------------------------------------------
+    if (lane == 0) {
+      MsRing at = {0, 1, stages};               // parity of the "empty" wait: a fresh slot counts as released
+      int issued = 0, seq = 0;
+      bool ok = true;
+      while (ok) {
+        const int id = seq == 0 ? first_id : atomicAdd(ticket, 1);
+        const bool last = id >= total;
+        // name the item for the loader and the consumers (the loader must have read the slot's last tenant)
+        if (seq >= kMsFifo && !spin_above(&hd->loaded, seq - kMsFifo, stop, 9)) break;
+        hd->fifo[seq % kMsFifo] = last ? -1 : id;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&hd->published) = seq + 1;
+        ++seq;
+        if (last) {
+          if (mbar_wait(&hd->empty[at.s], at.parity, stop, 1, &g_moe_stream_error)) mbar_arrive(&hd->full[at.s]);   // an empty stage that carries the end mark
+          break;
+        }
+        const MsItem item = ms_decode(id, n1, n2, items1);
+        const int e = hd->expert[item.a];
+        const int f0 = item.sub * 16 * Q, ft = f0 >> 7, r0 = f0 & 127;
+        // first product: tile (ft, kt) holds 256 rows, gate rows at r0, up rows at 128 + r0; second: 128 rows
+        const int kt = item.second ? kt2 : kt1;
+        const size_t tile = item.second ? 128 * 64 : 256 * 64;
+        const __nv_bfloat16* src = item.second ? p.W2 + (size_t)e * p.gs2 + ((size_t)ft * kt2 * 128 + r0) * 64
+                                               : p.W13 + (size_t)e * p.gs13 + ((size_t)ft * kt1 * 256 + r0) * 64;
+        for (int t0 = 0; t0 < kt && ok; t0 += G) {
+          const int nblk = min(G, kt - t0);
+          for (int half = 0; half < (item.second ? 1 : 2); ++half) {
+            if (!mbar_wait(&hd->empty[at.s], at.parity, stop, 1, &g_moe_stream_error)) { ok = false; break; }
+            unsigned char* dst = ring + (size_t)at.s * kMsSlotBytes;
+            mbar_expect_tx(&hd->full[at.s], nblk * BLOCK_BYTES);
+            for (int b = 0; b < nblk; ++b)
+              bulk_load(dst + b * BLOCK_BYTES, src + (size_t)(t0 + b) * tile + half * (128 * 64), BLOCK_BYTES, &hd->full[at.s]);
+            at.next();
+            ++issued;
+          }
+        }
+      }
+      if (!ok) {
+        // gave up: let every copy that was started land before the CTA's shared memory goes away
+        int s = at.s, parity = at.parity ^ 1;       // "full" parity of the slot issued last is the "empty" parity it was waited with, flipped
+        for (int j = 0; j < min(issued, stages); ++j) {
+          if (--s < 0) { s = stages - 1; parity ^= 1; }
+          for (unsigned i = 0; i < (1u << 20); ++i)
+            if (mbar_try(&hd->full[s], parity)) break;
+        }
+      }
+    }
+  } else if (warp == kMsConsumers + 1) {
+    // ---- activation loader: the rows of the next second-product item, as soon as they are complete ----
+    if (lane == 0) {
+      int seq = 0, n = 0;               // items read, second-product items served
+      while (true) {
+        if (!spin_above(&hd->published, seq, stop, 10)) break;
+        const int id = reinterpret_cast<volatile int*>(hd->fifo)[seq % kMsFifo];
+        ++seq;
+        *reinterpret_cast<volatile int*>(&hd->loaded) = seq;
+        if (id < 0) break;
+        const MsItem item = ms_decode(id, n1, n2, items1);
+        if (!item.second) continue;
+        const int buf = n % a_bufs, use = n / a_bufs;
+        if (!mbar_wait(&hd->xempty[buf], (use & 1) ^ 1, stop, 11, &g_moe_stream_error)) break;
+        bool there = false;
+        for (unsigned i = 0; i < kMsCountPolls; ++i) {
+          if (ld_acquire(done + item.a) >= target) { there = true; break; }
+          if ((i & 255u) == 255u && *stop) break;
+        }
+        if (!there) {
+          *stop = 1;
+          atomicCAS(&g_moe_stream_error, 0, 4);
+          break;
+        }
+        const int rows = hd->rows[item.a], row_begin = hd->row_begin[item.a];
+        const unsigned bytes = (unsigned)p.I * 2;
+        unsigned char* dst = as + (size_t)buf * a_buf_bytes;
+        asm volatile("fence.proxy.async;" ::: "memory");      // the rows were written by ordinary stores of other SMs
+        mbar_expect_tx(&hd->xfull[buf], rows * bytes);
+        for (int r = 0; r < rows; ++r)
+          bulk_load(dst + (size_t)r * p.a_stride, p.act + (size_t)(row_begin + r) * p.I, bytes, &hd->xfull[buf]);
+        ++n;
+      }
+      if (*stop && n > 0) {
+        // let the last rows that were asked for land (the consumers may have left without them)
+        const int m = n - 1, buf = m % a_bufs, use = m / a_bufs;
+        for (unsigned i = 0; i < (1u << 20); ++i)
+          if (mbar_try(&hd->xfull[buf], use & 1)) break;
+      }
+    }
+  } else {
+    // ---- consumers --------------------------------------------------------------------------------
+    const int rg = warp % Q, kg = warp / Q;
+    const int g = lane >> 2, t = lane & 3;
+    // ldmatrix addresses inside a block of 16 Q rows x 64 k: this lane's row and 16-byte piece parity
+    const int a_row = 16 * rg + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int a_hi = lane >> 4;                  // second pair of matrices: k + 8
+    // B: matrices (rows 0-7, k..k+7), (rows 0-7, k+8..), [rows 8-15 likewise]: this lane's row and k half
+    const int b_row1 = lane & 7, b_row2 = (lane & 7) + (lane >> 4) * 8;
+    const unsigned b_half = ((lane >> 3) & 1) * 16;
+    MsRing at = {0, 0, stages};
+    int seq = 0, n_second = 0;
+    unsigned meets = 0;                          // how often the consumers have met
+    bool x_there = false;
+    while (true) {
+      if (!mbar_wait(&hd->full[at.s], at.parity, stop, 2, &g_moe_stream_error)) break;
+      const int id = hd->fifo[seq % kMsFifo];
+      ++seq;
+      if (id < 0) break;
+      const MsItem item = ms_decode(id, n1, n2, items1);
+      const int row_begin = hd->row_begin[item.a], rows = hd->rows[item.a];
+      const bool wide = rows > 8;                // two 8-row tiles
+
+      float acc[2][2][4];
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[b][nt][i] = 0.f;
+      bool ok;
+      const int b_row = wide ? b_row2 : b_row1;
+      if (!item.second) {
+        // the expert's rows among the step's hidden rows (a row of zeros beyond its last)
+        if (!x_there && !mbar_wait(&hd->xready, 0, stop, 13, &g_moe_stream_error)) break;
+        x_there = true;
+        const int tok = b_row < rows ? hd->order[row_begin + b_row] : p.T;
+        const unsigned b_lane = smem_u32(xs) + (unsigned)tok * p.x_stride + b_half;
+        ok = wide ? ms_k_loop<Q, 2, false>(hd, ring, at, kt1, kg, a_row, a_hi, b_lane, acc)
+                  : ms_k_loop<Q, 1, false>(hd, ring, at, kt1, kg, a_row, a_hi, b_lane, acc);
+      } else {
+        const int buf = n_second % a_bufs, use = n_second / a_bufs;
+        ++n_second;
+        if (!mbar_wait(&hd->xfull[buf], use & 1, stop, 12, &g_moe_stream_error)) break;
+        // (rows beyond the expert's last hold what an earlier item left: they only reach columns that are not stored)
+        const unsigned b_lane = smem_u32(as) + (unsigned)(buf * a_buf_bytes) + (unsigned)min(b_row, a_rows - 1) * p.a_stride + b_half;
+        ok = wide ? ms_k_loop<Q, 2, true>(hd, ring, at, kt2, kg, a_row, a_hi, b_lane, acc)
+                  : ms_k_loop<Q, 1, true>(hd, ring, at, kt2, kg, a_row, a_hi, b_lane, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hd->xempty[buf]);
+      }
+      if (!ok) break;
+
+      // ---- k groups meet, in order --------------------------------------------------------------
+      if (G > 1) {
+        // (two meeting places in turn: a warp may write the next item's sums while the sums of
+        // this one are still being read, and the meeting after that orders the rest)
+        float* red_now = red + (meets & 1) * (kMsConsumers * 2 * 2 * 4 * 32);
+        if (kg > 0) {
+#pragma unroll
+          for (int b = 0; b < 2; ++b)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (nt == 0 || wide) red_now[(((warp * 2 + b) * 2 + nt) * 4 + i) * 32 + lane] = acc[b][nt][i];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hd->meet);
+        const bool met = mbar_wait(&hd->meet, meets & 1, stop, 8, &g_moe_stream_error);
+        ++meets;
+        if (!met) break;
+        if (kg == 0) {
+          for (int o = 1; o < G; ++o) {
+            const int w = o * Q + rg;
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+              for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  if (nt == 0 || wide) acc[b][nt][i] += red_now[(((w * 2 + b) * 2 + nt) * 4 + i) * 32 + lane];
+          }
+        }
+      }
+
+      // ---- epilogue: lane holds features (f, f + 8) of rows (2t, 2t + 1) of every tile ------------
+      if (kg == 0) {
+        const int f_lo = item.sub * 16 * Q + 16 * rg + g;
+        const int N = item.second ? p.H : p.I;
+        __nv_bfloat16* out = item.second ? p.Y : p.act;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = nt * 8 + 2 * t + (i & 1), f = f_lo + (i >> 1) * 8;
+            if (r < rows && f < N) {
+              float v = acc[0][nt][i];
+              if (!item.second) v = v / (1.f + expf(-v)) * acc[1][nt][i];
+              out[(size_t)(row_begin + r) * N + f] = __float2bfloat16_rn(v);
+            }
+          }
+      }
+      if (!item.second) {
+        // this warp's share of the item is in memory: count it (8 counts an item)
+        __syncwarp();
+        if (lane == 0) add_release(done + item.a, 1);
+      }
+    }
+  }
+
+  // ---- the last CTA to finish puts the counters back to zero ------------------------------------
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(finished, 1) == (int)gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last) {
+    for (int i = threadIdx.x; i < kMsMaxActive; i += blockDim.x) done[i] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *ticket = 0;
+      __threadfence();
+      *finished = 0;
+    }
+  }
+}
+
+template <int Q>
+static int launch_ms(const MsArgs& a, int grid, size_t smem, cudaStream_t stream) {
+  static size_t set_bytes = 0;
+  if (smem > set_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(moe_stream_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    NF_REQUIRE(e == cudaSuccess, "moe_stream: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    set_bytes = smem;
+  }
+  launch_chained(moe_stream_kernel<Q>, dim3(grid), dim3(kMsThreads), smem, stream, a);
+  return check_launch("moe_stream");
+}
+
+// The fixed part of a launch's shared memory (header, k groups' meeting place, hidden rows) and
+// what one buffer of activation rows needs at worst (every row of the step with one expert).
+// Returns false if that and a ring of the smallest size do not fit into `budget` bytes.
+static bool ms_layout(int q, int T, int H, int I, size_t budget, MsArgs* a) {
+  const int x_stride = (H + 63) / 64 * 64 * 2 + 16, a_stride = (I + 63) / 64 * 64 * 2 + 16;
+  const int red = q < 8 ? 2 * kMsConsumers * 2 * 2 * 4 * 32 * 4 : 0;
+  const size_t fixed = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red + (size_t)(T + 1) * x_stride;
+  const size_t worst = fixed + (size_t)(T < kMsMaxRows ? T : kMsMaxRows) * a_stride + 1024 + (size_t)kMsMinStages * kMsSlotBytes;
+  if (worst > budget) return false;
+  if (a) { a->x_stride = x_stride; a->a_stride = a_stride; a->red_bytes = red; a->smem_bytes = (int)budget; }
+  return true;
+}
+
+}  // namespace nf
+
+using namespace nf;
+
+// How many ints of zeroed device memory a launch needs as `work`.
+extern "C" int nf_moe_stream_work_ints() { return 2 + kMsMaxActive; }
+
+// 1 if the sizes fit the kernel: T <= 16 tokens, `pairs` (token, expert) pairs, and room for the
+// rows and a ring inside `smem_bytes` of shared memory.
+extern "C" int nf_moe_stream_fits(int H, int I, int T, int pairs, int n_mapped, int q, int smem_bytes) {
+  if (!(q == 2 || q == 4 || q == 8) || T < 1 || T > kMsMaxRows || n_mapped > kMsMaxActive || pairs > kMsMaxPairs) return 0;
+  if (H % 8 || I % 8 || smem_bytes > 227 * 1024) return 0;
+  return ms_layout(q, T, H, I, (size_t)smem_bytes, nullptr) ? 1 : 0;
+}
+
+// act[M, I] = silu(x Wgate_e^T) * (x Wup_e^T) and Y[M, H] = act Wdown_e^T for the sorted pairs of
+// every expert that has rows, in one persistent launch.  X [T, H] bfloat16 (row stride ldx),
+// W13 / W2 packed (strides in elements), offsets / order / active from the routing plan, M = T k
+// pairs, T <= 16.  q: an item is 16 q features (2, 4, 8).  `work`: nf_moe_stream_work_ints() ints,
+// zero before the first launch; the kernel leaves them zero.  smem_bytes: shared memory the
+// launch takes (what is left stays free for kernels of other streams on the same SM).
+extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long gs13, const void* W2, long long gs2,
+                             void* act, void* Y, int M, int T, int H, int I, int E, int k, const int* offsets,
+                             const int* order, const int* active, int n_mapped, int* work, int q,
+                             int smem_bytes, cudaStream_t stream) {
+  if (M == 0) return 0;
+  NF_REQUIRE(M > 0 && T > 0 && k > 0 && E > 0 && ldx % 8 == 0, "moe_stream: bad sizes");
+  NF_REQUIRE(nf_moe_stream_fits(H, I, T, M, n_mapped, q, smem_bytes), "moe_stream: sizes do not fit (H=%d I=%d T=%d pairs=%d experts=%d q=%d smem=%d)",
+             H, I, T, M, n_mapped, q, smem_bytes);
+  NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W13 % 16 == 0) && ((uintptr_t)W2 % 16 == 0) && ((uintptr_t)act % 16 == 0) &&
+             gs13 % 8 == 0 && gs2 % 8 == 0, "moe_stream: operands must be 16-byte aligned");
+  MsArgs a;
+  a.X = (const __nv_bfloat16*)X; a.W13 = (const __nv_bfloat16*)W13; a.W2 = (const __nv_bfloat16*)W2;
+  a.act = (__nv_bfloat16*)act; a.Y = (__nv_bfloat16*)Y;
+  a.offsets = offsets; a.order = order; a.active = active; a.work = work;
+  a.gs13 = gs13; a.gs2 = gs2;
+  a.ldx = ldx; a.M = M; a.T = T; a.H = H; a.I = I; a.E = E; a.k = k; a.n_mapped = n_mapped;
+  ms_layout(q, T, H, I, (size_t)smem_bytes, &a);
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm <= 0) n_sm = 1;
+  }
+  if (q == 2) return launch_ms<2>(a, n_sm, (size_t)smem_bytes, stream);
+  if (q == 4) return launch_ms<4>(a, n_sm, (size_t)smem_bytes, stream);
+  return launch_ms<8>(a, n_sm, (size_t)smem_bytes, stream);
+}
+
+// 0, or the code of the first wait the kernel gave up on / the first bad plan entry since the
+// last call (synchronises the device).
+extern "C" int nf_moe_stream_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_moe_stream_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_moe_stream_error, &zero, sizeof(int));
+  return v;
+}

@@ -62,6 +62,16 @@ TUNING = {
     # kernels of a few CTAs, one waiting for the other) runs on a second stream of higher
     # priority while the shared expert's products fill the device; 0 turns it off
     "route_beside_shared_min_rows": 256,
+    # decode steps of `moe_stream_min_tokens` to `moe_stream_max_tokens` tokens run both products
+    # of the routed experts in one persistent launch (packed bfloat16 weights); a max of 0: always
+    # two launches of the streaming product.  Measured at A2.7B sizes, whole decode steps: 6 %
+    # slower at 4 tokens (few experts: the launch's start and the wait between its products show),
+    # 4.5 % faster at 8, 12.5 % faster at 16.  `moe_stream_smem_kb`: shared memory that launch
+    # takes on every SM - what is left stays free for the shared expert's kernels, which run
+    # beside it on a second stream (176 to 200: the same at 8 tokens; 176 is too little at 16)
+    "moe_stream_min_tokens": 6,
+    "moe_stream_max_tokens": 16,
+    "moe_stream_smem_kb": 192,
 }
 
 SUPPORTED_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -262,11 +272,13 @@ def chain_break() -> None:
 
 
 def tensor_core_status() -> int:
-    """0, or the code of the first bounded wait that a tensor-core kernel gave up on since the
-    last call (synchronises the device): 1-4 from the grouped GEMM, 101-110 from attention."""
+    """0, or the code of the first bounded wait that a kernel with a shared-memory ring gave up on
+    since the last call (synchronises the device): 1-4 from the grouped GEMM, 101-110 from
+    attention, 401-413 from the persistent experts' kernel (405-407: a plan that does not fit it)."""
     lib = _lib.load()
     gemm, attn = int(lib.nf_grouped_gemm_tc_status()), int(lib.nf_prefill_attention_tc_status())
-    return gemm if gemm else (100 + attn if attn else 0)
+    ms = int(lib.nf_moe_stream_status())
+    return gemm if gemm else (100 + attn if attn else (400 + ms if ms else 0))
 
 
 def index_status() -> int:
@@ -696,6 +708,59 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
                 group_map=plan.active, early_index=plan_is_older)
     else:
         _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
+    return y
+
+
+_STREAM_WORK = {}
+
+
+def _stream_items(x: torch.Tensor, w13, w2, plan: MoePlan, k: int) -> int:
+    """Sixteen-feature groups an item of the persistent experts' kernel covers (8, 4 or 2), or 0 if
+    the step does not fit the kernel.  The fewer experts a step selects, the finer the items, so
+    that every SM has some; a finer item also needs a smaller ring."""
+    T, H = x.shape
+    if not (isinstance(w13, PackedWeights) and isinstance(w2, PackedWeights) and x.is_cuda and plan.active is not None):
+        return 0
+    if T < max(TUNING["moe_stream_min_tokens"], 1) or T > TUNING["moe_stream_max_tokens"] or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        return 0
+    if w13.K != H or w2.n_features != H or w2.K != w13.n_features or not w13.swiglu or w2.swiglu:
+        return 0
+    pairs = T * k
+    q = 8 if pairs >= 16 else (4 if pairs >= 8 else 2)
+    fits = _lib.load().nf_moe_stream_fits
+    while q >= 2 and not fits(H, w13.n_features, T, pairs, plan.active.numel(), q, TUNING["moe_stream_smem_kb"] * 1024):
+        q //= 2
+    return q if q >= 2 else 0
+
+
+def moe_experts_fit_stream(x: torch.Tensor, w13, w2, plan: MoePlan, k: int) -> bool:
+    """Whether `moe_experts` serves this step with the one persistent launch."""
+    return _stream_items(x, w13, w2, plan, k) > 0
+
+
+def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
+                gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Both products of the routed experts: sorted pair p of expert e ->
+    (silu(x Wgate_e^T) * (x Wup_e^T)) Wdown_e^T  [T*k, H].
+
+    A decode step with packed bfloat16 weights is one persistent launch that streams the weights
+    of both products through one ring (`moe_stream.cu`); everything else is `moe_gemm1` followed
+    by `moe_gemm2`."""
+    q = _stream_items(x, w13, w2, plan, k)
+    if not q:
+        return moe_gemm2(moe_gemm1(x, w13, plan, k, gathered=gathered), w2, plan, plan_is_older=True)
+    T, H = x.shape
+    inner = w13.n_features
+    key = str(x.device)
+    if key not in _STREAM_WORK:
+        _STREAM_WORK[key] = torch.zeros((int(_lib.load().nf_moe_stream_work_ints()),), dtype=torch.int32, device=x.device)
+    act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
+    y = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
+    _lib.call("nf_moe_stream", _p(x), c_int(x.stride(0)), _p(w13.data), c_longlong(w13.group_stride), _p(w2.data),
+              c_longlong(w2.group_stride), _p(act), _p(y), c_int(T * k), c_int(T), c_int(H), c_int(inner),
+              c_int(w13.groups), c_int(k), _p(plan.offsets), _p(plan.order), _p(plan.active),
+              c_int(plan.active.numel()), _p(_STREAM_WORK[key]), c_int(q),
+              c_int(TUNING["moe_stream_smem_kb"] * 1024), _stream())
     return y
 
 

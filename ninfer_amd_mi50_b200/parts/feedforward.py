@@ -192,8 +192,7 @@ class SparseMoeSwiglu(FeedForward):
             main, side, shared = start_shared()
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
-        act = kernels.moe_gemm1(x, self.w13, plan, k, gathered=gathered)
-        y = kernels.moe_gemm2(act, self.w2, plan, plan_is_older=True)
+        y = kernels.moe_experts(x, self.w13, self.w2, plan, k, gathered=gathered)
         if fork:
             main.wait_stream(side)
             kernels.chain_break()           # the kernel that adds up also reads what the other stream produced

@@ -165,7 +165,11 @@ def route(x, w_router, E, k, norm_topk, split=None):
     return idx, wts, ext, moe_plan(idx, E)
 
 
-def moe_gemm1(x, w13, plan, k):
+def moe_experts(x, w13, w2, plan, k, gathered=None):
+    return moe_gemm2(moe_gemm1(x, w13, plan, k), w2, plan)
+
+
+def moe_gemm1(x, w13, plan, k, gathered=None):
     T, H = x.shape
     E, two_i, _ = w13.shape
     inner = two_i // 2
@@ -231,7 +235,7 @@ def check_router_sizes(num_experts, top_k):
 
 
 NAMES = ["chain_break", "can_pack", "PackedWeights", "split_router", "embed_rows", "add_rmsnorm", "add_rmsnorm_rows", "silu_mul", "linear", "linear_swiglu",
-         "rope_append", "linear_rope_append", "paged_attention", "router_topk", "route", "moe_plan", "moe_gemm1", "moe_gemm2",
+         "rope_append", "linear_rope_append", "paged_attention", "router_topk", "route", "moe_plan", "moe_experts", "moe_gemm1", "moe_gemm2",
          "moe_combine", "argmax_rows"]
 
 

@@ -759,6 +759,76 @@ def test_streaming_experts_with_an_early_start(K, T, H, I, E, k):
     close(y0, P.moe_gemm2(ract, w2, plan), dtype)
 
 
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 256, 128, 4, 2), (2, 2048, 1408, 60, 4), (5, 200, 136, 6, 3),
+                                       (8, 2048, 1408, 60, 4), (13, 512, 264, 7, 2), (3, 40, 24, 3, 1),
+                                       (16, 2048, 1408, 60, 4), (8, 3584, 2560, 64, 8), (4, 2048, 1408, 60, 4),
+                                       (1, 2048, 1408, 60, 4)])
+def test_experts_in_one_persistent_launch(K, T, H, I, E, k):
+    """Decode steps run both products of the routed experts in one persistent launch that streams
+    the packed weights through a ring of shared memory: close to the plain twin, the same bits
+    when run again, a token's rows the same bits whatever else is in the batch (as long as the
+    item size is the same), its counters back at zero, and no wait given up."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(T * 17 + I)
+    x = rnd((T, H), dtype, 81)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 82, 0.1), rnd((E, H, I), dtype, 83, 0.1)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    plan = K.moe_plan(idx, E)
+    pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
+    old = dict(K.TUNING)
+    K.TUNING.update(moe_stream_min_tokens=1)
+    try:
+        _persistent_experts_case(K, x, w13, w2, pw13, pw2, idx, plan, T, E, k, dtype)
+    finally:
+        K.TUNING.update(old)
+
+
+def _persistent_experts_case(K, x, w13, w2, pw13, pw2, idx, plan, T, E, k, dtype):
+    assert K.moe_experts_fit_stream(x, pw13, pw2, plan, k)
+    y = K.moe_experts(x, pw13, pw2, plan, k)
+    again = K.moe_experts(x, pw13, pw2, plan, k)
+    assert torch.equal(y, again)
+    ry = P.moe_gemm2(P.moe_gemm1(x, w13, plan, k), w2, plan)
+    close(y, ry, dtype)
+    K.TUNING.update(moe_stream_max_tokens=0)
+    assert not K.moe_experts_fit_stream(x, pw13, pw2, plan, k)
+    close(K.moe_experts(x, pw13, pw2, plan, k), ry, dtype)      # the two-launch path, same answer
+    K.TUNING.update(moe_stream_max_tokens=16)
+    from ninfer_amd_mi50_b200.kernels import ops
+    half = T // 2
+    if half:
+        # the first half of the batch alone: where the item size is the same, every row must come out the same
+        xh, plan_h = x[:half].contiguous(), K.moe_plan(idx[:half].contiguous(), E)
+        yh = K.moe_experts(xh, pw13, pw2, plan_h, k)
+        pairs = torch.arange(half * k, device="cuda")
+        if ops._stream_items(xh, pw13, pw2, plan_h, k) == ops._stream_items(x, pw13, pw2, plan, k):
+            assert torch.equal(yh[plan_h.inv.long()[pairs]], y[plan.inv.long()[pairs]])
+        else:
+            close(yh[plan_h.inv.long()[pairs]], y[plan.inv.long()[pairs]], dtype)
+    assert K.tensor_core_status() == 0 and K.index_status() == 0
+    assert int(ops._STREAM_WORK[str(x.device)].abs().sum()) == 0
+
+
+def test_persistent_experts_launch_is_refused_where_it_does_not_fit(K):
+    """Sixteen rows of a very wide model leave too little shared memory for the ring: the
+    two-launch path serves the step, with the same answer."""
+    T, H, I, E, k = 16, 5120, 2560, 8, 2
+    x = rnd((T, H), torch.bfloat16, 84)
+    w13, w2 = rnd((E, 2 * I, H), torch.bfloat16, 85, 0.1), rnd((E, H, I), torch.bfloat16, 86, 0.1)
+    g = torch.Generator().manual_seed(3)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    plan = K.moe_plan(idx, E)
+    pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
+    old = dict(K.TUNING)
+    K.TUNING.update(moe_stream_min_tokens=1)
+    try:
+        assert not K.moe_experts_fit_stream(x, pw13, pw2, plan, k)
+        assert K.moe_experts_fit_stream(x[:4].contiguous(), pw13, pw2, K.moe_plan(idx[:4].contiguous(), E), k)
+    finally:
+        K.TUNING.update(old)
+    close(K.moe_experts(x, pw13, pw2, plan, k), P.moe_gemm2(P.moe_gemm1(x, w13, plan, k), w2, plan), torch.bfloat16)
+
+
 @pytest.mark.parametrize("exact_bf16", [True, False])
 def test_router_many_rows_through_split_matrix(K, exact_bf16):
     """More than 128 bfloat16 rows: the logits come from library products over the routing
