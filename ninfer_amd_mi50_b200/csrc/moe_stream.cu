@@ -15,13 +15,14 @@
 //     (`cp.async.bulk`, completion on an mbarrier); it runs ahead of the consumers by the whole
 //     ring, across item and product boundaries, so every SM always has about 100 KB in flight;
 //   * eight consumer warps read the blocks with `ldmatrix` and multiply with
-//     `mma.sync.m16n8k16` (float32 sums) against rows of X in shared memory: the step's hidden
-//     rows, all of them, are loaded once a CTA, and an expert's rows are picked by the
-//     `ldmatrix` row addresses; SwiGLU in the epilogue;
-//   * an item of the second product needs every feature of its expert's activations: the first
-//     product counts finished items per expert in global memory; a loader thread waits
-//     (bounded) for the count and then brings the expert's activation rows in with bulk copies,
-//     one item ahead of the consumers (two buffers where shared memory allows);
+//     `mma.sync.m16n8k16` (float32 sums) against up to eight rows of X in shared memory; SwiGLU
+//     in the epilogue.  An expert with more than eight rows in the step is served as several
+//     row groups of eight (its weights then come from L2 the second time);
+//   * a loader thread brings each item's rows of X in with bulk copies, one item ahead of the
+//     consumers (two buffers): the hidden rows of the group's tokens for the first product, the
+//     group's activation rows for the second.  The second product needs every feature of those:
+//     the first product counts finished items per row group in global memory, and the loader
+//     waits (bounded) for the count;
 //   * items are handed out by a ticket counter, so the SMs stay balanced whatever the sizes of
 //     the two products.  Tickets are handed out in order and first-product items never wait, so
 //     the wait for activations cannot deadlock as long as the grid's CTAs run.
@@ -35,29 +36,29 @@
 namespace nf {
 
 constexpr int kMsConsumers = 8;                          // consumer warps
-constexpr int kMsThreads = 32 * (kMsConsumers + 2);      // + the weight producer's warp + the activation loader's
+constexpr int kMsThreads = 32 * (kMsConsumers + 2);      // + the weight producer's warp + the row loader's
 constexpr int kMsMaxStages = 32;
 constexpr int kMsSlotBytes = 16 * 1024;                  // a stage: 128 weight rows x 64 k, or 64 x 128, or 32 x 256
 constexpr int kMsMinStages = 4;
-constexpr int kMsMaxActive = 256;                        // experts with rows in one step
-constexpr int kMsMaxPairs = 256;                         // (token, expert) pairs of one step
-constexpr int kMsMaxRows = 16;                           // rows an expert may have in one step
+constexpr int kMsMaxGroups = 512;                        // row groups (an expert's rows, eight at a time) of one step
+constexpr int kMsMaxPairs = 512;                         // (token, expert) pairs of one step
+constexpr int kMsRows = 8;                               // rows of a group
 constexpr int kMsFifo = 64;                              // item ids between producer, loader and consumers
-constexpr unsigned kMsCountPolls = 1u << 20;             // polls of an expert's counter (about a second)
+constexpr unsigned kMsCountPolls = 1u << 20;             // polls of a group's counter (about a second)
 
-// 1-3 ring waits, 4 the wait for an expert's activations, 5-7 a plan that does not fit, 8 the
-// consumers' barrier, 9-11 the loader's waits, 12-13 the consumers' waits for activation rows and hidden rows
+// 1-3 ring waits, 4 the wait for a group's activations, 5-7 a plan that does not fit, 8 the
+// consumers' barrier, 9-11 the loader's waits, 12 the consumers' wait for an item's rows
 __device__ int g_moe_stream_error = 0;
+__device__ __align__(16) unsigned char g_ms_zeros[128];   // source of the zeros behind a row's last k
 
 struct MsHeader {
   unsigned long long full[kMsMaxStages], empty[kMsMaxStages];
   unsigned long long meet;                 // the consumer warps' own barrier
-  unsigned long long xfull[2], xempty[2];  // activation-row buffers: filled by the loader, released by the consumers
-  unsigned long long xready;               // the step's hidden rows have arrived
+  unsigned long long xfull[2], xempty[2];  // row buffers: filled by the loader, released by the consumers
   int fifo[kMsFifo];
-  int stop, n_active, published, loaded;   // published / loaded: items the producer has named / the loader has read
+  int stop, n_groups, published, loaded;   // published / loaded: items the producer has named / the loader has read
   int max_rows, pad0, pad1, pad2;
-  int expert[kMsMaxActive], row_begin[kMsMaxActive], rows[kMsMaxActive];
+  int expert[kMsMaxGroups], row_begin[kMsMaxGroups], rows[kMsMaxGroups];
   int order[kMsMaxPairs];                  // sorted pair -> token
 };
 
@@ -70,10 +71,10 @@ struct MsArgs {
   const int* offsets;          // [E + 1]
   const int* order;            // [M] sorted pair -> pair index (token * k + slot)
   const int* active;           // [n_mapped] experts with rows, ascending, -1 padded
-  int* work;                   // [2 + kMsMaxActive]: ticket, finished CTAs, items done per active expert; all zero between launches
+  int* work;                   // [2 + kMsMaxGroups]: ticket, finished CTAs, items done per row group; all zero between launches
   long long gs13, gs2;         // group strides in elements
   int ldx, M, T, H, I, E, k, n_mapped;
-  int x_stride, a_stride;      // bytes between rows of X / of activations in shared memory
+  int b_stride;                // bytes between rows of X (hidden rows or activations) in shared memory
   int red_bytes, smem_bytes;   // the k groups' meeting place; all of the launch's dynamic shared memory
 };
 
@@ -123,7 +124,7 @@ struct MsRing {
   }
 };
 
-// An item id -> (product, active expert, sub-tile of 16 Q features).
+// An item id -> (product, row group, sub-tile of 16 Q features).
 struct MsItem {
   int second, a, sub;
 };
@@ -141,10 +142,10 @@ __device__ __forceinline__ MsItem ms_decode(int id, int n1, int n2, int items1) 
 // holds them for G = 8 / Q consecutive k tiles (block g of the stage: k tile j G + g); warp
 // (row group rg, k group kg) takes block kg.  SECOND: the down product, one set of sums; else
 // stages alternate between the gate rows and the up rows of the same k tiles, two sets.
-// NT: 8-row tiles of X.  The item's first stage has been waited for.  False if a wait gave up.
-template <int Q, int NT, bool SECOND>
+// The item's first stage has been waited for.  False if a wait gave up.
+template <int Q, bool SECOND>
 __device__ __forceinline__ bool ms_k_loop(MsHeader* hd, unsigned char* ring, MsRing& at, int kt, int kg, int a_row,
-                                          int a_hi, unsigned b_lane, float (&acc)[2][2][4]) {
+                                          int a_hi, unsigned b_lane, float (&acc)[2][4]) {
   constexpr int G = kMsConsumers / Q;
   constexpr int BLOCK_BYTES = Q * 2048;
   volatile int* stop = &hd->stop;
@@ -160,18 +161,10 @@ __device__ __forceinline__ bool ms_k_loop(MsHeader* hd, unsigned char* ring, MsR
         const unsigned b_addr = b_lane + (unsigned)(t0 + kg) * 128;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          unsigned a0, a1, a2, a3;
+          unsigned a0, a1, a2, a3, b0, b1;
           ldsm4(block + a_row * 128 + (((2 * ks + a_hi) ^ (a_row & 7)) << 4), a0, a1, a2, a3);
-          if (NT == 1) {
-            unsigned b0, b1;
-            ldsm2(b_addr + ks * 32, b0, b1);
-            ms_mma(acc[half][0], a0, a1, a2, a3, b0, b1);
-          } else {
-            unsigned b0, b1, b2, b3;
-            ldsm4(b_addr + ks * 32, b0, b1, b2, b3);
-            ms_mma(acc[half][0], a0, a1, a2, a3, b0, b1);
-            ms_mma(acc[half][1], a0, a1, a2, a3, b2, b3);
-          }
+          ldsm2(b_addr + ks * 32, b0, b1);
+          ms_mma(acc[half], a0, a1, a2, a3, b0, b1);
         }
       }
       __syncwarp();
@@ -195,8 +188,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   constexpr int HEADER_BYTES = (sizeof(MsHeader) + 1023) & ~1023;
   MsHeader* hd = reinterpret_cast<MsHeader*>(smem);
   float* red = reinterpret_cast<float*>(smem + HEADER_BYTES);
-  unsigned char* xs = smem + HEADER_BYTES + p.red_bytes;                  // [T rows + a row of zeros][x_stride]
-  unsigned char* as = xs + (size_t)(p.T + 1) * p.x_stride;                // [buffers][rows][a_stride], then the ring
+  unsigned char* xs = smem + HEADER_BYTES + p.red_bytes;                  // [buffers][rows][b_stride], then the ring
   unsigned char* smem_end = ms_smem_raw + p.smem_bytes;
   volatile int* stop = &hd->stop;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -207,17 +199,16 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     for (int s = 0; s < kMsMaxStages; ++s) { mbar_init(&hd->full[s], 1); mbar_init(&hd->empty[s], kMsConsumers); }
     mbar_init(&hd->meet, kMsConsumers);
     for (int b = 0; b < 2; ++b) { mbar_init(&hd->xfull[b], 1); mbar_init(&hd->xempty[b], kMsConsumers); }
-    mbar_init(&hd->xready, 1);
     hd->stop = 0;
-    hd->n_active = 0;
+    hd->n_groups = 0;
     hd->max_rows = 1;
     hd->published = 0;
     hd->loaded = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   {
-    // rows of X and of activations start as zeros (the padding of k stays zero for good)
-    const int n16 = (int)(((size_t)(p.T + 1) * p.x_stride + (size_t)2 * kMsMaxRows * p.a_stride) / 16);
+    // the row buffers start as zeros: a row that no copy has written yet must not hold a NaN
+    const int n16 = (int)((size_t)2 * kMsRows * p.b_stride / 16);
     uint4* z = reinterpret_cast<uint4*>(xs);
     for (int i = threadIdx.x; i < n16 && reinterpret_cast<unsigned char*>(z + i + 1) <= smem_end; i += blockDim.x)
       z[i] = make_uint4(0, 0, 0, 0);
@@ -233,7 +224,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   chain_wait(offsets, active, order, X, ticket);
   __syncthreads();
 
-  // ---- the step: its experts, its pairs and its hidden rows (read from L2: the kernel before wrote them)
+  // ---- the step: its row groups and its pairs (read from L2: the kernel before wrote them) ---------
   int first_id = 0;
   if (warp == kMsConsumers && lane == 0) first_id = atomicAdd(ticket, 1);      // under way while the plan is read
   if (warp == 0) {
@@ -241,49 +232,59 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     for (int i0 = 0; i0 < p.n_mapped; i0 += 32) {
       const int i = i0 + lane;
       int e = i < p.n_mapped ? ld_l2_int(active + i) : -1;
-      int rb = 0, re = 0;
+      int rb = 0, cnt = 0;
       if (e >= p.E) { atomicCAS(&g_moe_stream_error, 0, 5); e = -1; }
       if (e >= 0) {
         rb = ld_l2_int(offsets + e);
-        re = ld_l2_int(offsets + e + 1);
-        if (rb < 0 || re > p.M || re - rb > kMsMaxRows) { atomicCAS(&g_moe_stream_error, 0, 6); e = -1; }
-        else if (re <= rb) e = -1;
+        const int re = ld_l2_int(offsets + e + 1);
+        if (rb < 0 || re > p.M) atomicCAS(&g_moe_stream_error, 0, 6);
+        else cnt = max(re - rb, 0);
       }
-      const unsigned has = __ballot_sync(0xffffffffu, e >= 0);
-      const int at = n + __popc(has & ((1u << lane) - 1));
-      if (e >= 0 && at < kMsMaxActive) { hd->expert[at] = e; hd->row_begin[at] = rb; hd->rows[at] = re - rb; most = max(most, re - rb); }
-      n += __popc(has);
+      // an expert's rows, eight at a time
+      const int ng = (cnt + kMsRows - 1) / kMsRows;
+      int incl = ng;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      const int at = n + incl - ng;
+      for (int j = 0; j < ng; ++j)
+        if (at + j < kMsMaxGroups) {
+          hd->expert[at + j] = e;
+          hd->row_begin[at + j] = rb + j * kMsRows;
+          hd->rows[at + j] = min(kMsRows, cnt - j * kMsRows);
+        }
+      most = max(most, min(cnt, kMsRows));
+      n += __shfl_sync(0xffffffffu, incl, 31);
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
     if (lane == 0) {
-      if (n > kMsMaxActive) { atomicCAS(&g_moe_stream_error, 0, 7); n = kMsMaxActive; }
-      hd->n_active = n;
+      if (n > kMsMaxGroups) { atomicCAS(&g_moe_stream_error, 0, 7); n = kMsMaxGroups; }
+      hd->n_groups = n;
       hd->max_rows = most;
     }
-  } else if (warp == 1) {
-    for (int i = lane; i < p.M; i += 32) {
+  } else if (warp >= 1 && warp < kMsConsumers) {
+    for (int i = threadIdx.x - 32; i < p.M && i < kMsMaxPairs; i += (kMsConsumers - 1) * 32) {
       const int pair = ld_l2_int(order + i);
       int tok = pair / p.k;
-      if (pair < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = p.T; }     // the row of zeros
+      if (pair < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = -1; }     // no row is copied for it
       hd->order[i] = tok;
     }
-  } else if (warp == 2 && lane == 0) {
-    mbar_expect_tx(&hd->xready, (unsigned)p.T * p.H * 2);
-    for (int r = 0; r < p.T; ++r) bulk_load(xs + (size_t)r * p.x_stride, X + (size_t)r * p.ldx, (unsigned)p.H * 2, &hd->xready);
   }
   __syncthreads();
-  const int n_active = hd->n_active;
+  const int n_groups = hd->n_groups;
   const int kt1 = (p.H + 63) >> 6, kt2 = (p.I + 63) >> 6;               // k tiles of the two products
-  const int n1 = (p.I + 16 * Q - 1) / (16 * Q), n2 = (p.H + 16 * Q - 1) / (16 * Q);     // items an expert
-  const int items1 = n_active * n1, total = items1 + n_active * n2;
-  const int target = n1 * kMsConsumers;                                 // counts that say "this expert's activations are complete"
-  // activation buffers of as many rows as the busiest expert has: two if the ring keeps enough stages beside them
-  const int a_rows = hd->max_rows;
-  const size_t a_buf_bytes = (size_t)a_rows * p.a_stride;
-  const size_t room = (size_t)(smem_end - as);
-  const int a_bufs = room >= 2 * a_buf_bytes + 1024 + (size_t)(kMsMinStages + 2) * kMsSlotBytes ? 2 : 1;
-  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)(as + a_bufs * a_buf_bytes) + 1023) & ~(uintptr_t)1023);
+  const int n1 = (p.I + 16 * Q - 1) / (16 * Q), n2 = (p.H + 16 * Q - 1) / (16 * Q);     // items a row group
+  const int items1 = n_groups * n1, total = items1 + n_groups * n2;
+  const int target = n1 * kMsConsumers;                                 // counts that say "this group's activations are complete"
+  // row buffers of as many rows as the largest group has: two if the ring keeps enough stages beside them
+  const int b_rows = hd->max_rows;
+  const size_t buf_bytes = (size_t)b_rows * p.b_stride;
+  const size_t room = (size_t)(smem_end - xs);
+  const int n_bufs = room >= 2 * buf_bytes + 1024 + (size_t)(kMsMinStages + 1) * kMsSlotBytes ? 2 : 1;
+  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)(xs + n_bufs * buf_bytes) + 1023) & ~(uintptr_t)1023);
   const int stages = min(kMsMaxStages, (int)((smem_end - ring) / kMsSlotBytes));
   if (smem_end < ring || stages < 2) {             // (the host's check of the sizes rules this out)
     if (threadIdx.x == 0) atomicCAS(&g_moe_stream_error, 0, 7);
@@ -338,43 +339,59 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
       }
     }
   } else if (warp == kMsConsumers + 1) {
-    // ---- activation loader: the rows of the next second-product item, as soon as they are complete ----
+    // ---- row loader: the rows of X of the next item, as soon as they are complete ---------------------
     if (lane == 0) {
-      int seq = 0, n = 0;               // items read, second-product items served
+      int seq = 0;                      // items read = items served
+      int issued_buf = -1, issued_use = 0;
+      const unsigned pad1 = (unsigned)(kt1 * 128 - p.H * 2), pad2 = (unsigned)(kt2 * 128 - p.I * 2);   // bytes behind a row's last k
       while (true) {
         if (!spin_above(&hd->published, seq, stop, 10)) break;
         const int id = reinterpret_cast<volatile int*>(hd->fifo)[seq % kMsFifo];
+        const int n = seq;
         ++seq;
         *reinterpret_cast<volatile int*>(&hd->loaded) = seq;
         if (id < 0) break;
         const MsItem item = ms_decode(id, n1, n2, items1);
-        if (!item.second) continue;
-        const int buf = n % a_bufs, use = n / a_bufs;
+        const int buf = n % n_bufs, use = n / n_bufs;
         if (!mbar_wait(&hd->xempty[buf], (use & 1) ^ 1, stop, 11, &g_moe_stream_error)) break;
-        bool there = false;
-        for (unsigned i = 0; i < kMsCountPolls; ++i) {
-          if (ld_acquire(done + item.a) >= target) { there = true; break; }
-          if ((i & 255u) == 255u && *stop) break;
-        }
-        if (!there) {
-          *stop = 1;
-          atomicCAS(&g_moe_stream_error, 0, 4);
-          break;
-        }
         const int rows = hd->rows[item.a], row_begin = hd->row_begin[item.a];
-        const unsigned bytes = (unsigned)p.I * 2;
-        unsigned char* dst = as + (size_t)buf * a_buf_bytes;
-        asm volatile("fence.proxy.async;" ::: "memory");      // the rows were written by ordinary stores of other SMs
-        mbar_expect_tx(&hd->xfull[buf], rows * bytes);
-        for (int r = 0; r < rows; ++r)
-          bulk_load(dst + (size_t)r * p.a_stride, p.act + (size_t)(row_begin + r) * p.I, bytes, &hd->xfull[buf]);
-        ++n;
+        unsigned char* dst = xs + (size_t)buf * buf_bytes;
+        if (item.second) {
+          bool there = false;
+          for (unsigned i = 0; i < kMsCountPolls; ++i) {
+            if (ld_acquire(done + item.a) >= target) { there = true; break; }
+            if ((i & 255u) == 255u && *stop) break;
+          }
+          if (!there) {
+            *stop = 1;
+            atomicCAS(&g_moe_stream_error, 0, 4);
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");      // the rows were written by ordinary stores of other SMs
+          const unsigned bytes = (unsigned)p.I * 2;
+          mbar_expect_tx(&hd->xfull[buf], rows * (bytes + pad2));
+          for (int r = 0; r < rows; ++r) {
+            bulk_load(dst + (size_t)r * p.b_stride, p.act + (size_t)(row_begin + r) * p.I, bytes, &hd->xfull[buf]);
+            if (pad2) bulk_load(dst + (size_t)r * p.b_stride + bytes, g_ms_zeros, pad2, &hd->xfull[buf]);
+          }
+        } else {
+          const unsigned bytes = (unsigned)p.H * 2;
+          int live = 0;
+          for (int r = 0; r < rows; ++r) live += hd->order[row_begin + r] >= 0;
+          mbar_expect_tx(&hd->xfull[buf], live * bytes + rows * pad1);
+          for (int r = 0; r < rows; ++r) {
+            const int tok = hd->order[row_begin + r];
+            if (tok >= 0) bulk_load(dst + (size_t)r * p.b_stride, X + (size_t)tok * p.ldx, bytes, &hd->xfull[buf]);
+            if (pad1) bulk_load(dst + (size_t)r * p.b_stride + bytes, g_ms_zeros, pad1, &hd->xfull[buf]);
+          }
+        }
+        issued_buf = buf;
+        issued_use = use;
       }
-      if (*stop && n > 0) {
+      if (*stop && issued_buf >= 0) {
         // let the last rows that were asked for land (the consumers may have left without them)
-        const int m = n - 1, buf = m % a_bufs, use = m / a_bufs;
         for (unsigned i = 0; i < (1u << 20); ++i)
-          if (mbar_try(&hd->xfull[buf], use & 1)) break;
+          if (mbar_try(&hd->xfull[issued_buf], issued_use & 1)) break;
       }
     }
   } else {
@@ -384,65 +401,44 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     // ldmatrix addresses inside a block of 16 Q rows x 64 k: this lane's row and 16-byte piece parity
     const int a_row = 16 * rg + ((lane >> 3) & 1) * 8 + (lane & 7);
     const int a_hi = lane >> 4;                  // second pair of matrices: k + 8
-    // B: matrices (rows 0-7, k..k+7), (rows 0-7, k+8..), [rows 8-15 likewise]: this lane's row and k half
-    const int b_row1 = lane & 7, b_row2 = (lane & 7) + (lane >> 4) * 8;
-    const unsigned b_half = ((lane >> 3) & 1) * 16;
+    // B: matrices (rows 0-7, k..k+7), (rows 0-7, k+8..): this lane's row and k half.  (Rows beyond
+    // the group's last hold what an earlier item left: they only reach columns that are not stored.)
+    const unsigned b_off = (unsigned)min(lane & 7, b_rows - 1) * p.b_stride + ((lane >> 3) & 1) * 16;
     MsRing at = {0, 0, stages};
-    int seq = 0, n_second = 0;
+    int seq = 0;
     unsigned meets = 0;                          // how often the consumers have met
-    bool x_there = false;
     while (true) {
       if (!mbar_wait(&hd->full[at.s], at.parity, stop, 2, &g_moe_stream_error)) break;
       const int id = hd->fifo[seq % kMsFifo];
+      const int buf = seq % n_bufs, use = seq / n_bufs;
       ++seq;
       if (id < 0) break;
       const MsItem item = ms_decode(id, n1, n2, items1);
       const int row_begin = hd->row_begin[item.a], rows = hd->rows[item.a];
-      const bool wide = rows > 8;                // two 8-row tiles
 
-      float acc[2][2][4];
+      float acc[2][4];
 #pragma unroll
       for (int b = 0; b < 2; ++b)
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[b][nt][i] = 0.f;
-      bool ok;
-      const int b_row = wide ? b_row2 : b_row1;
-      if (!item.second) {
-        // the expert's rows among the step's hidden rows (a row of zeros beyond its last)
-        if (!x_there && !mbar_wait(&hd->xready, 0, stop, 13, &g_moe_stream_error)) break;
-        x_there = true;
-        const int tok = b_row < rows ? hd->order[row_begin + b_row] : p.T;
-        const unsigned b_lane = smem_u32(xs) + (unsigned)tok * p.x_stride + b_half;
-        ok = wide ? ms_k_loop<Q, 2, false>(hd, ring, at, kt1, kg, a_row, a_hi, b_lane, acc)
-                  : ms_k_loop<Q, 1, false>(hd, ring, at, kt1, kg, a_row, a_hi, b_lane, acc);
-      } else {
-        const int buf = n_second % a_bufs, use = n_second / a_bufs;
-        ++n_second;
-        if (!mbar_wait(&hd->xfull[buf], use & 1, stop, 12, &g_moe_stream_error)) break;
-        // (rows beyond the expert's last hold what an earlier item left: they only reach columns that are not stored)
-        const unsigned b_lane = smem_u32(as) + (unsigned)(buf * a_buf_bytes) + (unsigned)min(b_row, a_rows - 1) * p.a_stride + b_half;
-        ok = wide ? ms_k_loop<Q, 2, true>(hd, ring, at, kt2, kg, a_row, a_hi, b_lane, acc)
-                  : ms_k_loop<Q, 1, true>(hd, ring, at, kt2, kg, a_row, a_hi, b_lane, acc);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&hd->xempty[buf]);
-      }
+        for (int i = 0; i < 4; ++i) acc[b][i] = 0.f;
+      if (!mbar_wait(&hd->xfull[buf], use & 1, stop, 12, &g_moe_stream_error)) break;
+      const unsigned b_lane = smem_u32(xs) + (unsigned)(buf * buf_bytes) + b_off;
+      const bool ok = item.second ? ms_k_loop<Q, true>(hd, ring, at, kt2, kg, a_row, a_hi, b_lane, acc)
+                                  : ms_k_loop<Q, false>(hd, ring, at, kt1, kg, a_row, a_hi, b_lane, acc);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hd->xempty[buf]);
       if (!ok) break;
 
       // ---- k groups meet, in order --------------------------------------------------------------
       if (G > 1) {
         // (two meeting places in turn: a warp may write the next item's sums while the sums of
         // this one are still being read, and the meeting after that orders the rest)
-        float* red_now = red + (meets & 1) * (kMsConsumers * 2 * 2 * 4 * 32);
+        float* red_now = red + (meets & 1) * (kMsConsumers * 2 * 4 * 32);
         if (kg > 0) {
 #pragma unroll
           for (int b = 0; b < 2; ++b)
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                if (nt == 0 || wide) red_now[(((warp * 2 + b) * 2 + nt) * 4 + i) * 32 + lane] = acc[b][nt][i];
+            for (int i = 0; i < 4; ++i) red_now[((warp * 2 + b) * 4 + i) * 32 + lane] = acc[b][i];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&hd->meet);
@@ -455,30 +451,25 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
 #pragma unroll
             for (int b = 0; b < 2; ++b)
 #pragma unroll
-              for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  if (nt == 0 || wide) acc[b][nt][i] += red_now[(((w * 2 + b) * 2 + nt) * 4 + i) * 32 + lane];
+              for (int i = 0; i < 4; ++i) acc[b][i] += red_now[((w * 2 + b) * 4 + i) * 32 + lane];
           }
         }
       }
 
-      // ---- epilogue: lane holds features (f, f + 8) of rows (2t, 2t + 1) of every tile ------------
+      // ---- epilogue: lane holds features (f, f + 8) of rows (2t, 2t + 1) --------------------------
       if (kg == 0) {
         const int f_lo = item.sub * 16 * Q + 16 * rg + g;
         const int N = item.second ? p.H : p.I;
         __nv_bfloat16* out = item.second ? p.Y : p.act;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int r = nt * 8 + 2 * t + (i & 1), f = f_lo + (i >> 1) * 8;
-            if (r < rows && f < N) {
-              float v = acc[0][nt][i];
-              if (!item.second) v = v / (1.f + expf(-v)) * acc[1][nt][i];
-              out[(size_t)(row_begin + r) * N + f] = __float2bfloat16_rn(v);
-            }
+        for (int i = 0; i < 4; ++i) {
+          const int r = 2 * t + (i & 1), f = f_lo + (i >> 1) * 8;
+          if (r < rows && f < N) {
+            float v = acc[0][i];
+            if (!item.second) v = v / (1.f + expf(-v)) * acc[1][i];
+            out[(size_t)(row_begin + r) * N + f] = __float2bfloat16_rn(v);
           }
+        }
       }
       if (!item.second) {
         // this warp's share of the item is in memory: count it (8 counts an item)
@@ -496,7 +487,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   }
   __syncthreads();
   if (s_last) {
-    for (int i = threadIdx.x; i < kMsMaxActive; i += blockDim.x) done[i] = 0;
+    for (int i = threadIdx.x; i < kMsMaxGroups; i += blockDim.x) done[i] = 0;
     __syncthreads();
     if (threadIdx.x == 0) {
       *ticket = 0;
@@ -518,16 +509,16 @@ static int launch_ms(const MsArgs& a, int grid, size_t smem, cudaStream_t stream
   return check_launch("moe_stream");
 }
 
-// The fixed part of a launch's shared memory (header, k groups' meeting place, hidden rows) and
-// what one buffer of activation rows needs at worst (every row of the step with one expert).
-// Returns false if that and a ring of the smallest size do not fit into `budget` bytes.
-static bool ms_layout(int q, int T, int H, int I, size_t budget, MsArgs* a) {
-  const int x_stride = (H + 63) / 64 * 64 * 2 + 16, a_stride = (I + 63) / 64 * 64 * 2 + 16;
-  const int red = q < 8 ? 2 * kMsConsumers * 2 * 2 * 4 * 32 * 4 : 0;
-  const size_t fixed = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red + (size_t)(T + 1) * x_stride;
-  const size_t worst = fixed + (size_t)(T < kMsMaxRows ? T : kMsMaxRows) * a_stride + 1024 + (size_t)kMsMinStages * kMsSlotBytes;
+// The row stride and the k groups' meeting place of a launch, and whether the header, one buffer
+// of eight rows and a ring of the smallest size fit into `budget` bytes of shared memory.
+static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a) {
+  const int widest = H > I ? H : I;
+  const int b_stride = (widest + 63) / 64 * 64 * 2 + 16;      // + 16: rows eight apart do not share a bank
+  const int red = q < 8 ? 2 * kMsConsumers * 2 * 4 * 32 * 4 : 0;
+  const size_t worst = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red + (size_t)kMsRows * b_stride + 1024 +
+                       (size_t)kMsMinStages * kMsSlotBytes;
   if (worst > budget) return false;
-  if (a) { a->x_stride = x_stride; a->a_stride = a_stride; a->red_bytes = red; a->smem_bytes = (int)budget; }
+  if (a) { a->b_stride = b_stride; a->red_bytes = red; a->smem_bytes = (int)budget; }
   return true;
 }
 
@@ -536,30 +527,31 @@ static bool ms_layout(int q, int T, int H, int I, size_t budget, MsArgs* a) {
 using namespace nf;
 
 // How many ints of zeroed device memory a launch needs as `work`.
-extern "C" int nf_moe_stream_work_ints() { return 2 + kMsMaxActive; }
+extern "C" int nf_moe_stream_work_ints() { return 2 + kMsMaxGroups; }
 
-// 1 if the sizes fit the kernel: T <= 16 tokens, `pairs` (token, expert) pairs, and room for the
-// rows and a ring inside `smem_bytes` of shared memory.
-extern "C" int nf_moe_stream_fits(int H, int I, int T, int pairs, int n_mapped, int q, int smem_bytes) {
-  if (!(q == 2 || q == 4 || q == 8) || T < 1 || T > kMsMaxRows || n_mapped > kMsMaxActive || pairs > kMsMaxPairs) return 0;
+// 1 if the sizes fit the kernel: `pairs` (token, expert) pairs, `n_mapped` listed experts, and
+// room for a row buffer and a ring inside `smem_bytes` of shared memory.
+extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, int smem_bytes) {
+  if (!(q == 2 || q == 4 || q == 8) || pairs < 1 || pairs > kMsMaxPairs) return 0;
+  if (n_mapped + pairs / kMsRows > kMsMaxGroups) return 0;           // row groups at worst
   if (H % 8 || I % 8 || smem_bytes > 227 * 1024) return 0;
-  return ms_layout(q, T, H, I, (size_t)smem_bytes, nullptr) ? 1 : 0;
+  return ms_layout(q, H, I, (size_t)smem_bytes, nullptr) ? 1 : 0;
 }
 
 // act[M, I] = silu(x Wgate_e^T) * (x Wup_e^T) and Y[M, H] = act Wdown_e^T for the sorted pairs of
 // every expert that has rows, in one persistent launch.  X [T, H] bfloat16 (row stride ldx),
 // W13 / W2 packed (strides in elements), offsets / order / active from the routing plan, M = T k
-// pairs, T <= 16.  q: an item is 16 q features (2, 4, 8).  `work`: nf_moe_stream_work_ints() ints,
-// zero before the first launch; the kernel leaves them zero.  smem_bytes: shared memory the
-// launch takes (what is left stays free for kernels of other streams on the same SM).
+// pairs.  q: an item is 16 q features (2, 4, 8).  `work`: nf_moe_stream_work_ints() ints, zero
+// before the first launch; the kernel leaves them zero.  smem_bytes: shared memory the launch
+// takes (what is left stays free for kernels of other streams on the same SM).
 extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long gs13, const void* W2, long long gs2,
                              void* act, void* Y, int M, int T, int H, int I, int E, int k, const int* offsets,
                              const int* order, const int* active, int n_mapped, int* work, int q,
                              int smem_bytes, cudaStream_t stream) {
   if (M == 0) return 0;
   NF_REQUIRE(M > 0 && T > 0 && k > 0 && E > 0 && ldx % 8 == 0, "moe_stream: bad sizes");
-  NF_REQUIRE(nf_moe_stream_fits(H, I, T, M, n_mapped, q, smem_bytes), "moe_stream: sizes do not fit (H=%d I=%d T=%d pairs=%d experts=%d q=%d smem=%d)",
-             H, I, T, M, n_mapped, q, smem_bytes);
+  NF_REQUIRE(nf_moe_stream_fits(H, I, M, n_mapped, q, smem_bytes), "moe_stream: sizes do not fit (H=%d I=%d pairs=%d experts=%d q=%d smem=%d)",
+             H, I, M, n_mapped, q, smem_bytes);
   NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W13 % 16 == 0) && ((uintptr_t)W2 % 16 == 0) && ((uintptr_t)act % 16 == 0) &&
              gs13 % 8 == 0 && gs2 % 8 == 0, "moe_stream: operands must be 16-byte aligned");
   MsArgs a;
@@ -568,7 +560,7 @@ extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long 
   a.offsets = offsets; a.order = order; a.active = active; a.work = work;
   a.gs13 = gs13; a.gs2 = gs2;
   a.ldx = ldx; a.M = M; a.T = T; a.H = H; a.I = I; a.E = E; a.k = k; a.n_mapped = n_mapped;
-  ms_layout(q, T, H, I, (size_t)smem_bytes, &a);
+  ms_layout(q, H, I, (size_t)smem_bytes, &a);
   static int n_sm = 0;
   if (!n_sm) {
     int dev = 0;

@@ -62,15 +62,17 @@ TUNING = {
     # kernels of a few CTAs, one waiting for the other) runs on a second stream of higher
     # priority while the shared expert's products fill the device; 0 turns it off
     "route_beside_shared_min_rows": 256,
-    # decode steps of `moe_stream_min_tokens` to `moe_stream_max_tokens` tokens run both products
-    # of the routed experts in one persistent launch (packed bfloat16 weights); a max of 0: always
-    # two launches of the streaming product.  Measured at A2.7B sizes, whole decode steps: 6 %
-    # slower at 4 tokens (few experts: the launch's start and the wait between its products show),
-    # 4.5 % faster at 8, 12.5 % faster at 16.  `moe_stream_smem_kb`: shared memory that launch
-    # takes on every SM - what is left stays free for the shared expert's kernels, which run
-    # beside it on a second stream (176 to 200: the same at 8 tokens; 176 is too little at 16)
+    # steps of `moe_stream_min_tokens` to `moe_stream_max_tokens` tokens run both products of the
+    # routed experts in one persistent launch (packed bfloat16 weights); a max of 0: always two
+    # launches.  Measured at A2.7B sizes, whole decode steps against the two launches (the
+    # streaming product up to 16 tokens, the tensor-core grouped product beyond): the same at 4
+    # tokens, 3 % faster at 6, 6 % at 8, 16 % at 16, 10 % at 32, 3.5 % at 64, 2 % slower at 96 and
+    # 128 (experts with more than eight rows are served eight at a time and stream their weights
+    # again).  `moe_stream_smem_kb`: shared memory that launch takes on every SM - what is left
+    # stays free for the shared expert's kernels, which run beside it on a second stream (160
+    # instead of 192: the same up to 16 tokens, 2 % slower at 32 and 64)
     "moe_stream_min_tokens": 6,
-    "moe_stream_max_tokens": 16,
+    "moe_stream_max_tokens": 64,
     "moe_stream_smem_kb": 192,
 }
 
@@ -728,7 +730,7 @@ def _stream_items(x: torch.Tensor, w13, w2, plan: MoePlan, k: int) -> int:
     pairs = T * k
     q = 8 if pairs >= 16 else (4 if pairs >= 8 else 2)
     fits = _lib.load().nf_moe_stream_fits
-    while q >= 2 and not fits(H, w13.n_features, T, pairs, plan.active.numel(), q, TUNING["moe_stream_smem_kb"] * 1024):
+    while q >= 2 and not fits(H, w13.n_features, pairs, plan.active.numel(), q, TUNING["moe_stream_smem_kb"] * 1024):
         q //= 2
     return q if q >= 2 else 0
 

@@ -762,12 +762,14 @@ def test_streaming_experts_with_an_early_start(K, T, H, I, E, k):
 @pytest.mark.parametrize("T,H,I,E,k", [(1, 256, 128, 4, 2), (2, 2048, 1408, 60, 4), (5, 200, 136, 6, 3),
                                        (8, 2048, 1408, 60, 4), (13, 512, 264, 7, 2), (3, 40, 24, 3, 1),
                                        (16, 2048, 1408, 60, 4), (8, 3584, 2560, 64, 8), (4, 2048, 1408, 60, 4),
-                                       (1, 2048, 1408, 60, 4)])
+                                       (1, 2048, 1408, 60, 4), (24, 512, 264, 3, 2), (64, 2048, 1408, 60, 4),
+                                       (33, 200, 136, 6, 3)])
 def test_experts_in_one_persistent_launch(K, T, H, I, E, k):
     """Decode steps run both products of the routed experts in one persistent launch that streams
     the packed weights through a ring of shared memory: close to the plain twin, the same bits
     when run again, a token's rows the same bits whatever else is in the batch (as long as the
-    item size is the same), its counters back at zero, and no wait given up."""
+    item size is the same), its counters back at zero, and no wait given up.  Experts with more
+    than eight rows are served eight rows at a time."""
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(T * 17 + I)
     x = rnd((T, H), dtype, 81)
@@ -776,7 +778,7 @@ def test_experts_in_one_persistent_launch(K, T, H, I, E, k):
     plan = K.moe_plan(idx, E)
     pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
     old = dict(K.TUNING)
-    K.TUNING.update(moe_stream_min_tokens=1)
+    K.TUNING.update(moe_stream_min_tokens=1, moe_stream_max_tokens=64)
     try:
         _persistent_experts_case(K, x, w13, w2, pw13, pw2, idx, plan, T, E, k, dtype)
     finally:
@@ -793,7 +795,7 @@ def _persistent_experts_case(K, x, w13, w2, pw13, pw2, idx, plan, T, E, k, dtype
     K.TUNING.update(moe_stream_max_tokens=0)
     assert not K.moe_experts_fit_stream(x, pw13, pw2, plan, k)
     close(K.moe_experts(x, pw13, pw2, plan, k), ry, dtype)      # the two-launch path, same answer
-    K.TUNING.update(moe_stream_max_tokens=16)
+    K.TUNING.update(moe_stream_max_tokens=64)
     from ninfer_amd_mi50_b200.kernels import ops
     half = T // 2
     if half:
@@ -810,9 +812,9 @@ def _persistent_experts_case(K, x, w13, w2, pw13, pw2, idx, plan, T, E, k, dtype
 
 
 def test_persistent_experts_launch_is_refused_where_it_does_not_fit(K):
-    """Sixteen rows of a very wide model leave too little shared memory for the ring: the
+    """Eight rows of a very wide model leave too little shared memory for the ring: the
     two-launch path serves the step, with the same answer."""
-    T, H, I, E, k = 16, 5120, 2560, 8, 2
+    T, H, I, E, k = 8, 8192, 512, 8, 2
     x = rnd((T, H), torch.bfloat16, 84)
     w13, w2 = rnd((E, 2 * I, H), torch.bfloat16, 85, 0.1), rnd((E, H, I), torch.bfloat16, 86, 0.1)
     g = torch.Generator().manual_seed(3)
@@ -823,7 +825,8 @@ def test_persistent_experts_launch_is_refused_where_it_does_not_fit(K):
     K.TUNING.update(moe_stream_min_tokens=1)
     try:
         assert not K.moe_experts_fit_stream(x, pw13, pw2, plan, k)
-        assert K.moe_experts_fit_stream(x[:4].contiguous(), pw13, pw2, K.moe_plan(idx[:4].contiguous(), E), k)
+        assert K.moe_experts_fit_stream(x[:, :4096].contiguous(), K.pack_weights(w13[:, :, :4096].contiguous(), swiglu=True),
+                                        K.pack_weights(w2[:, :4096].contiguous(), swiglu=False), plan, k)
     finally:
         K.TUNING.update(old)
     close(K.moe_experts(x, pw13, pw2, plan, k), P.moe_gemm2(P.moe_gemm1(x, w13, plan, k), w2, plan), torch.bfloat16)
