@@ -31,6 +31,7 @@
 // order, k groups added in order), never on the batch or on which CTA took the item.  Every
 // wait is bounded; the first to give up records a code and the CTA leaves.
 #define NF_CHAIN_CLASS 0x20
+#include "router_device.cuh"
 #include "tcgen05.cuh"
 
 namespace nf {
@@ -45,9 +46,12 @@ constexpr int kMsMaxPairs = 512;                         // (token, expert) pair
 constexpr int kMsRows = 8;                               // rows of a group
 constexpr int kMsFifo = 64;                              // item ids between producer, loader and consumers
 constexpr unsigned kMsCountPolls = 1u << 20;             // polls of a group's counter (about a second)
+// `work`: 0 the item ticket, 1 CTAs that have finished, 2 the routing's unit ticket, 3 its units done,
+// then the row groups' counters
+constexpr int kMsWork = 8;
 
 // 1-3 ring waits, 4 the wait for a group's activations, 5-7 a plan that does not fit, 8 the
-// consumers' barrier, 9-11 the loader's waits, 12 the consumers' wait for an item's rows
+// consumers' barrier, 9-11 the loader's waits, 12 the consumers' wait for an item's rows, 14 the wait for the router's logits
 __device__ int g_moe_stream_error = 0;
 __device__ __align__(16) unsigned char g_ms_zeros[128];   // source of the zeros behind a row's last k
 
@@ -71,7 +75,15 @@ struct MsArgs {
   const int* offsets;          // [E + 1]
   const int* order;            // [M] sorted pair -> pair index (token * k + slot)
   const int* active;           // [n_mapped] experts with rows, ascending, -1 padded
-  int* work;                   // [2 + kMsMaxGroups]: ticket, finished CTAs, items done per row group; all zero between launches
+  int* work;                   // [kMsWork + kMsMaxGroups]: counters (see kMsWork) and items done per row group; all zero between launches
+  // routing inside the launch (Wr != null): offsets, order and active are then written here too
+  const float* Wr;             // [E + extra, H] float32 router rows, then the rows whose raw logits are handed back
+  float* logits;               // [T, E + extra] scratch
+  int* topk_idx;               // [T, k]
+  float* topk_w;               // [T, k]
+  float* extra_out;            // [T, extra] or null
+  int* inv;                    // [M] pair -> sorted position
+  int extra, norm_topk;
   long long gs13, gs2;         // group strides in elements
   int ldx, M, T, H, I, E, k, n_mapped;
   int b_stride;                // bytes between rows of X (hidden rows or activations) in shared memory
@@ -99,6 +111,11 @@ __device__ __forceinline__ void add_release(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // what the kernel before wrote is read from L2, never through a cache that may hold an older line
+__device__ __forceinline__ uint4 ld_l2(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ int ld_l2_int(const int* p) {
   int v;
   asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -206,74 +223,203 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     hd->loaded = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  {
-    // the row buffers start as zeros: a row that no copy has written yet must not hold a NaN
-    const int n16 = (int)((size_t)2 * kMsRows * p.b_stride / 16);
-    uint4* z = reinterpret_cast<uint4*>(xs);
-    for (int i = threadIdx.x; i < n16 && reinterpret_cast<unsigned char*>(z + i + 1) <= smem_end; i += blockDim.x)
-      z[i] = make_uint4(0, 0, 0, 0);
-    fence_async_smem();                               // bulk copies will write over these zeros
-  }
   const int* offsets = p.offsets;
   const int* active = p.active;
   const int* order = p.order;
   const __nv_bfloat16* X = p.X;
   int* ticket = p.work;
   int* finished = p.work + 1;
-  int* done = p.work + 2;
+  int* done = p.work + kMsWork;
   chain_wait(offsets, active, order, X, ticket);
   __syncthreads();
 
-  // ---- the step: its row groups and its pairs (read from L2: the kernel before wrote them) ---------
+  // ---- the step's row groups and pairs: from the plan the kernel before wrote, or from routing done here ----
   int first_id = 0;
-  if (warp == kMsConsumers && lane == 0) first_id = atomicAdd(ticket, 1);      // under way while the plan is read
-  if (warp == 0) {
-    int n = 0, most = 1;
-    for (int i0 = 0; i0 < p.n_mapped; i0 += 32) {
-      const int i = i0 + lane;
-      int e = i < p.n_mapped ? ld_l2_int(active + i) : -1;
-      int rb = 0, cnt = 0;
-      if (e >= p.E) { atomicCAS(&g_moe_stream_error, 0, 5); e = -1; }
-      if (e >= 0) {
-        rb = ld_l2_int(offsets + e);
-        const int re = ld_l2_int(offsets + e + 1);
-        if (rb < 0 || re > p.M) atomicCAS(&g_moe_stream_error, 0, 6);
-        else cnt = max(re - rb, 0);
-      }
-      // an expert's rows, eight at a time
-      const int ng = (cnt + kMsRows - 1) / kMsRows;
-      int incl = ng;
+  if (warp == kMsConsumers && lane == 0) first_id = atomicAdd(ticket, 1);      // under way meanwhile
+  if (p.Wr) {
+    // Logits by whoever takes a unit (8 router rows x 1 token, a warp a row, the sums in
+    // `lane_dot`'s order as in the router's own kernels); once all are written, every CTA selects
+    // and builds the plan for itself in shared memory - the same values everywhere, and no
+    // second hand-over through global memory.  CTA 0 also writes them out for the kernels after.
+    // (Everything behind the header is free until then: x as float32, then the tables.)
+    float* xf = reinterpret_cast<float*>(xs);
+    __shared__ int s_unit;
+    const int rows = p.E + p.extra, nblk = (rows + 7) >> 3, n_units = nblk * p.T, n = p.M;
+    int unit = blockIdx.x;                       // the first unit needs no ticket
+    while (unit < n_units) {
+      const int t = unit / nblk, e = (unit - t * nblk) * 8 + warp;
+      for (int i = threadIdx.x; i < (p.H >> 3); i += blockDim.x) {
+        const uint4 v = ld_l2(X + (size_t)t * p.ldx + i * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += o;
-      }
-      const int at = n + incl - ng;
-      for (int j = 0; j < ng; ++j)
-        if (at + j < kMsMaxGroups) {
-          hd->expert[at + j] = e;
-          hd->row_begin[at + j] = rb + j * kMsRows;
-          hd->rows[at + j] = min(kMsRows, cnt - j * kMsRows);
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          xf[i * 8 + 2 * j] = f.x;
+          xf[i * 8 + 2 * j + 1] = f.y;
         }
-      most = max(most, min(cnt, kMsRows));
-      n += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      __syncthreads();
+      if (warp < kMsConsumers && e < rows) {
+        const float v = warp_sum(lane_dot(xf, p.Wr + (size_t)e * p.H, p.H, lane));
+        if (lane == 0) p.logits[(size_t)t * rows + e] = v;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();                           // the unit's logits, before it is counted
+        atomicAdd(p.work + 3, 1);
+        s_unit = (int)gridDim.x + atomicAdd(p.work + 2, 1);
+      }
+      __syncthreads();
+      unit = s_unit;
     }
+    if (threadIdx.x == 0) {
+      bool there = false;
+      for (unsigned i = 0; i < kMsCountPolls; ++i)
+        if (ld_acquire(p.work + 3) >= n_units) { there = true; break; }
+      if (!there) {
+        hd->stop = 1;
+        atomicCAS(&g_moe_stream_error, 0, 14);
+      }
+    }
+    __syncthreads();
+    const bool writer = blockIdx.x == 0;
+    float* lg = xf;                                                                  // [8 warps][E]
+    unsigned short* chosen = reinterpret_cast<unsigned short*>(lg + kMsConsumers * p.E);   // [n] expert of each pair
+    unsigned short* rank = chosen + n;                                               // [n] its rank inside the expert
+    int* counts = reinterpret_cast<int*>(((uintptr_t)(rank + n) + 15) & ~(uintptr_t)15);    // [E + 1]
+    if (!hd->stop) {
+      if (warp < kMsConsumers)
+        for (int tt = warp; tt < p.T; tt += kMsConsumers)
+          select_token(p.logits + (size_t)tt * rows, 1, lg + warp * p.E, tt, p.E, p.extra, p.k, p.norm_topk,
+                       writer ? p.topk_idx : nullptr, writer ? p.topk_w : nullptr, writer ? p.extra_out : nullptr,
+                       lane, chosen);
+      __syncthreads();
+      // stable counting sort of the pairs by expert, in shared memory
+      for (int e = warp; e < p.E; e += kMsThreads / 32) {
+        int running = 0;
+        for (int base = 0; base < n; base += 32) {
+          const int i = base + lane;
+          const bool mine = i < n && (int)chosen[i] == e;
+          const unsigned b = __ballot_sync(0xffffffffu, mine);
+          if (mine) rank[i] = (unsigned short)(running + __popc(b & ((1u << lane) - 1u)));
+          running += __popc(b);
+        }
+        if (lane == 0) counts[e] = running;
+      }
+      __syncthreads();
+      if (warp == 0) {
+        // 32 experts a round: offsets (exclusive prefix of the counts), the experts that have pairs
+        // (ascending, then -1), and their rows eight at a time
+        int run = 0, na = 0, ng = 0, most = 1;
+        for (int base = 0; base <= p.E; base += 32) {
+          const int e = base + lane;
+          const int c = e < p.E ? counts[e] : 0;
+          int incl = c;
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
-    if (lane == 0) {
-      if (n > kMsMaxGroups) { atomicCAS(&g_moe_stream_error, 0, 7); n = kMsMaxGroups; }
-      hd->n_groups = n;
-      hd->max_rows = most;
+          for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+          }
+          const int off = run + incl - c;
+          if (e <= p.E) {
+            counts[e] = off;
+            if (writer) const_cast<int*>(offsets)[e] = off;
+          }
+          run += __shfl_sync(0xffffffffu, incl, 31);
+          const unsigned b = __ballot_sync(0xffffffffu, c > 0);
+          if (writer) {
+            const int at = na + __popc(b & ((1u << lane) - 1u));
+            if (c > 0 && at < p.n_mapped) const_cast<int*>(active)[at] = e;
+          }
+          na += __popc(b);
+          const int g = (c + kMsRows - 1) / kMsRows;
+          int gi = g;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, gi, o);
+            if (lane >= o) gi += up;
+          }
+          const int at = ng + gi - g;
+          for (int j = 0; j < g; ++j)
+            if (at + j < kMsMaxGroups) {
+              hd->expert[at + j] = e;
+              hd->row_begin[at + j] = off + j * kMsRows;
+              hd->rows[at + j] = min(kMsRows, c - j * kMsRows);
+            }
+          most = max(most, min(c, kMsRows));
+          ng += __shfl_sync(0xffffffffu, gi, 31);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
+        if (writer)
+          for (int i = min(na, p.n_mapped) + lane; i < p.n_mapped; i += 32) const_cast<int*>(active)[i] = -1;
+        if (lane == 0) {
+          if (ng > kMsMaxGroups) { atomicCAS(&g_moe_stream_error, 0, 7); ng = kMsMaxGroups; }
+          hd->n_groups = ng;
+          hd->max_rows = most;
+        }
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int pos = counts[chosen[i]] + rank[i];
+        if (pos < kMsMaxPairs) hd->order[pos] = i / p.k;
+        if (writer) {
+          p.inv[i] = pos;
+          const_cast<int*>(order)[pos] = i;
+        }
+      }
     }
-  } else if (warp >= 1 && warp < kMsConsumers) {
-    for (int i = threadIdx.x - 32; i < p.M && i < kMsMaxPairs; i += (kMsConsumers - 1) * 32) {
-      const int pair = ld_l2_int(order + i);
-      int tok = pair / p.k;
-      if (pair < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = -1; }     // no row is copied for it
-      hd->order[i] = tok;
+    fence_async_smem();                             // bulk copies will write where these tables were
+    __syncthreads();
+  } else {
+    if (warp == 0) {
+      int n = 0, most = 1;
+      for (int i0 = 0; i0 < p.n_mapped; i0 += 32) {
+        const int i = i0 + lane;
+        int e = i < p.n_mapped ? ld_l2_int(active + i) : -1;
+        int rb = 0, cnt = 0;
+        if (e >= p.E) { atomicCAS(&g_moe_stream_error, 0, 5); e = -1; }
+        if (e >= 0) {
+          rb = ld_l2_int(offsets + e);
+          const int re = ld_l2_int(offsets + e + 1);
+          if (rb < 0 || re > p.M) atomicCAS(&g_moe_stream_error, 0, 6);
+          else cnt = max(re - rb, 0);
+        }
+        // an expert's rows, eight at a time
+        const int ng = (cnt + kMsRows - 1) / kMsRows;
+        int incl = ng;
+  #pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += o;
+        }
+        const int at = n + incl - ng;
+        for (int j = 0; j < ng; ++j)
+          if (at + j < kMsMaxGroups) {
+            hd->expert[at + j] = e;
+            hd->row_begin[at + j] = rb + j * kMsRows;
+            hd->rows[at + j] = min(kMsRows, cnt - j * kMsRows);
+          }
+        most = max(most, min(cnt, kMsRows));
+        n += __shfl_sync(0xffffffffu, incl, 31);
+      }
+  #pragma unroll
+      for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
+      if (lane == 0) {
+        if (n > kMsMaxGroups) { atomicCAS(&g_moe_stream_error, 0, 7); n = kMsMaxGroups; }
+        hd->n_groups = n;
+        hd->max_rows = most;
+      }
+    } else if (warp >= 1 && warp < kMsConsumers) {
+      for (int i = threadIdx.x - 32; i < p.M && i < kMsMaxPairs; i += (kMsConsumers - 1) * 32) {
+        const int pair = ld_l2_int(order + i);
+        int tok = pair / p.k;
+        if (pair < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = -1; }     // no row is copied for it
+        hd->order[i] = tok;
+      }
     }
+    __syncthreads();
   }
-  __syncthreads();
   const int n_groups = hd->n_groups;
   const int kt1 = (p.H + 63) >> 6, kt2 = (p.I + 63) >> 6;               // k tiles of the two products
   const int n1 = (p.I + 16 * Q - 1) / (16 * Q), n2 = (p.H + 16 * Q - 1) / (16 * Q);     // items a row group
@@ -286,7 +432,9 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   const int n_bufs = room >= 2 * buf_bytes + 1024 + (size_t)(kMsMinStages + 1) * kMsSlotBytes ? 2 : 1;
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)(xs + n_bufs * buf_bytes) + 1023) & ~(uintptr_t)1023);
   const int stages = min(kMsMaxStages, (int)((smem_end - ring) / kMsSlotBytes));
-  if (smem_end < ring || stages < 2) {             // (the host's check of the sizes rules this out)
+  if (hd->stop) {
+    // no plan: nothing to do
+  } else if (smem_end < ring || stages < 2) {             // (the host's check of the sizes rules this out)
     if (threadIdx.x == 0) atomicCAS(&g_moe_stream_error, 0, 7);
   } else if (warp == kMsConsumers) {
     // ---- weight producer -----------------------------------------------------------------------------
@@ -491,6 +639,8 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     __syncthreads();
     if (threadIdx.x == 0) {
       *ticket = 0;
+      p.work[2] = 0;
+      p.work[3] = 0;
       __threadfence();
       *finished = 0;
     }
@@ -511,13 +661,21 @@ static int launch_ms(const MsArgs& a, int grid, size_t smem, cudaStream_t stream
 
 // The row stride and the k groups' meeting place of a launch, and whether the header, one buffer
 // of eight rows and a ring of the smallest size fit into `budget` bytes of shared memory.
-static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a) {
+static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a, int route_experts = 0, int pairs = 0) {
   const int widest = H > I ? H : I;
   const int b_stride = (widest + 63) / 64 * 64 * 2 + 16;      // + 16: rows eight apart do not share a bank
   const int red = q < 8 ? 2 * kMsConsumers * 2 * 4 * 32 * 4 : 0;
   const size_t worst = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red + (size_t)kMsRows * b_stride + 1024 +
                        (size_t)kMsMinStages * kMsSlotBytes;
   if (worst > budget) return false;
+  if (route_experts) {
+    // the routing's tables live where the row buffers and the ring will be
+    const size_t head = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red;
+    size_t need = (size_t)H * 4;                  // x as float32, then: selection tables, pairs' experts and ranks, counts
+    const size_t tables = (size_t)kMsConsumers * route_experts * 4 + (size_t)pairs * 4 + 16 + (size_t)(route_experts + 1) * 4;
+    if (tables > need) need = tables;
+    if (head + need > budget) return false;
+  }
   if (a) { a->b_stride = b_stride; a->red_bytes = red; a->smem_bytes = (int)budget; }
   return true;
 }
@@ -527,15 +685,17 @@ static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a) {
 using namespace nf;
 
 // How many ints of zeroed device memory a launch needs as `work`.
-extern "C" int nf_moe_stream_work_ints() { return 2 + kMsMaxGroups; }
+extern "C" int nf_moe_stream_work_ints() { return kMsWork + kMsMaxGroups; }
 
 // 1 if the sizes fit the kernel: `pairs` (token, expert) pairs, `n_mapped` listed experts, and
 // room for a row buffer and a ring inside `smem_bytes` of shared memory.
-extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, int smem_bytes) {
+// route_experts: 0, or E if the launch also routes (its tables then need room too, and E < 65536).
+extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, int smem_bytes, int route_experts) {
   if (!(q == 2 || q == 4 || q == 8) || pairs < 1 || pairs > kMsMaxPairs) return 0;
   if (n_mapped + pairs / kMsRows > kMsMaxGroups) return 0;           // row groups at worst
   if (H % 8 || I % 8 || smem_bytes > 227 * 1024) return 0;
-  return ms_layout(q, H, I, (size_t)smem_bytes, nullptr) ? 1 : 0;
+  if (route_experts < 0 || route_experts > 65535) return 0;
+  return ms_layout(q, H, I, (size_t)smem_bytes, nullptr, route_experts, pairs) ? 1 : 0;
 }
 
 // act[M, I] = silu(x Wgate_e^T) * (x Wup_e^T) and Y[M, H] = act Wdown_e^T for the sorted pairs of
@@ -544,13 +704,21 @@ extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, 
 // pairs.  q: an item is 16 q features (2, 4, 8).  `work`: nf_moe_stream_work_ints() ints, zero
 // before the first launch; the kernel leaves them zero.  smem_bytes: shared memory the launch
 // takes (what is left stays free for kernels of other streams on the same SM).
+// Wr != null: the launch routes first - logits[t, e] = x[t] . Wr[e] in float32 for the E router
+// rows and `extra` further rows, softmax, the k largest (ties to the lower index), weights
+// p_e or p_e / sum(selected) - and writes topk_idx [T, k], topk_w [T, k], extra_out [T, extra]
+// (the further rows' raw logits), offsets, order, inv [M] and active itself; `logits`
+// [T, E + extra] is scratch.  The values are those of the router kernels (router.cu).
 extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long gs13, const void* W2, long long gs2,
                              void* act, void* Y, int M, int T, int H, int I, int E, int k, const int* offsets,
                              const int* order, const int* active, int n_mapped, int* work, int q,
-                             int smem_bytes, cudaStream_t stream) {
+                             int smem_bytes, const float* Wr, int extra, int norm_topk, float* logits, int* topk_idx,
+                             float* topk_w, float* extra_out, int* inv, cudaStream_t stream) {
   if (M == 0) return 0;
   NF_REQUIRE(M > 0 && T > 0 && k > 0 && E > 0 && ldx % 8 == 0, "moe_stream: bad sizes");
-  NF_REQUIRE(nf_moe_stream_fits(H, I, M, n_mapped, q, smem_bytes), "moe_stream: sizes do not fit (H=%d I=%d pairs=%d experts=%d q=%d smem=%d)",
+  NF_REQUIRE(!Wr || (logits && topk_idx && topk_w && inv && extra >= 0 && (extra == 0 || extra_out) && M == T * k && k <= E),
+             "moe_stream: routing needs its outputs");
+  NF_REQUIRE(nf_moe_stream_fits(H, I, M, n_mapped, q, smem_bytes, Wr ? E : 0), "moe_stream: sizes do not fit (H=%d I=%d pairs=%d experts=%d q=%d smem=%d)",
              H, I, M, n_mapped, q, smem_bytes);
   NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W13 % 16 == 0) && ((uintptr_t)W2 % 16 == 0) && ((uintptr_t)act % 16 == 0) &&
              gs13 % 8 == 0 && gs2 % 8 == 0, "moe_stream: operands must be 16-byte aligned");
@@ -559,6 +727,8 @@ extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long 
   a.act = (__nv_bfloat16*)act; a.Y = (__nv_bfloat16*)Y;
   a.offsets = offsets; a.order = order; a.active = active; a.work = work;
   a.gs13 = gs13; a.gs2 = gs2;
+  a.Wr = Wr; a.logits = logits; a.topk_idx = topk_idx; a.topk_w = topk_w; a.extra_out = extra_out; a.inv = inv;
+  a.extra = Wr ? extra : 0; a.norm_topk = norm_topk;
   a.ldx = ldx; a.M = M; a.T = T; a.H = H; a.I = I; a.E = E; a.k = k; a.n_mapped = n_mapped;
   ms_layout(q, H, I, (size_t)smem_bytes, &a);
   static int n_sm = 0;

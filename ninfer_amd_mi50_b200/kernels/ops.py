@@ -73,6 +73,9 @@ TUNING = {
     # instead of 192: the same up to 16 tokens, 2 % slower at 32 and 64)
     "moe_stream_min_tokens": 6,
     "moe_stream_max_tokens": 64,
+    # ... and up to this many tokens that launch routes as well (logits, selection and plan by
+    # its own CTAs before the products); 0: the router's kernels run before it
+    "moe_stream_route_max_tokens": 64,
     "moe_stream_smem_kb": 192,
 }
 
@@ -716,28 +719,39 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
 _STREAM_WORK = {}
 
 
-def _stream_items(x: torch.Tensor, w13, w2, plan: MoePlan, k: int) -> int:
+def _stream_items(x: torch.Tensor, w13, w2, E: int, k: int, routes: bool = False) -> int:
     """Sixteen-feature groups an item of the persistent experts' kernel covers (8, 4 or 2), or 0 if
     the step does not fit the kernel.  The fewer experts a step selects, the finer the items, so
-    that every SM has some; a finer item also needs a smaller ring."""
+    that every SM has some; a finer item also needs a smaller ring.  `routes`: the launch is to
+    route as well."""
     T, H = x.shape
-    if not (isinstance(w13, PackedWeights) and isinstance(w2, PackedWeights) and x.is_cuda and plan.active is not None):
+    if not (isinstance(w13, PackedWeights) and isinstance(w2, PackedWeights) and x.is_cuda):
         return 0
     if T < max(TUNING["moe_stream_min_tokens"], 1) or T > TUNING["moe_stream_max_tokens"] or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        return 0
+    if routes and T > TUNING["moe_stream_route_max_tokens"]:
         return 0
     if w13.K != H or w2.n_features != H or w2.K != w13.n_features or not w13.swiglu or w2.swiglu:
         return 0
     pairs = T * k
     q = 8 if pairs >= 16 else (4 if pairs >= 8 else 2)
     fits = _lib.load().nf_moe_stream_fits
-    while q >= 2 and not fits(H, w13.n_features, pairs, plan.active.numel(), q, TUNING["moe_stream_smem_kb"] * 1024):
+    while q >= 2 and not fits(H, w13.n_features, pairs, min(E, pairs), q, TUNING["moe_stream_smem_kb"] * 1024,
+                              E if routes else 0):
         q //= 2
     return q if q >= 2 else 0
 
 
 def moe_experts_fit_stream(x: torch.Tensor, w13, w2, plan: MoePlan, k: int) -> bool:
     """Whether `moe_experts` serves this step with the one persistent launch."""
-    return _stream_items(x, w13, w2, plan, k) > 0
+    return plan.active is not None and _stream_items(x, w13, w2, plan.num_experts, k) > 0
+
+
+def _stream_work(device: torch.device) -> torch.Tensor:
+    key = str(device)
+    if key not in _STREAM_WORK:
+        _STREAM_WORK[key] = torch.zeros((int(_lib.load().nf_moe_stream_work_ints()),), dtype=torch.int32, device=device)
+    return _STREAM_WORK[key]
 
 
 def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
@@ -748,22 +762,55 @@ def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
     A decode step with packed bfloat16 weights is one persistent launch that streams the weights
     of both products through one ring (`moe_stream.cu`); everything else is `moe_gemm1` followed
     by `moe_gemm2`."""
-    q = _stream_items(x, w13, w2, plan, k)
+    q = _stream_items(x, w13, w2, plan.num_experts, k) if plan.active is not None else 0
     if not q:
         return moe_gemm2(moe_gemm1(x, w13, plan, k, gathered=gathered), w2, plan, plan_is_older=True)
     T, H = x.shape
     inner = w13.n_features
-    key = str(x.device)
-    if key not in _STREAM_WORK:
-        _STREAM_WORK[key] = torch.zeros((int(_lib.load().nf_moe_stream_work_ints()),), dtype=torch.int32, device=x.device)
     act = torch.empty((T * k, inner), dtype=x.dtype, device=x.device)
     y = torch.empty((T * k, H), dtype=x.dtype, device=x.device)
     _lib.call("nf_moe_stream", _p(x), c_int(x.stride(0)), _p(w13.data), c_longlong(w13.group_stride), _p(w2.data),
               c_longlong(w2.group_stride), _p(act), _p(y), c_int(T * k), c_int(T), c_int(H), c_int(inner),
               c_int(w13.groups), c_int(k), _p(plan.offsets), _p(plan.order), _p(plan.active),
-              c_int(plan.active.numel()), _p(_STREAM_WORK[key]), c_int(q),
-              c_int(TUNING["moe_stream_smem_kb"] * 1024), _stream())
+              c_int(plan.active.numel()), _p(_stream_work(x.device)), c_int(q),
+              c_int(TUNING["moe_stream_smem_kb"] * 1024), None, c_int(0), c_int(0), None, None, None, None, None,
+              _stream())
     return y
+
+
+def can_route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, w13, w2, E: int, k: int) -> bool:
+    """Whether `route_and_run_experts` serves this step (else: `route`, then `moe_experts`)."""
+    return (w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1]
+            and _stream_items(x, w13, w2, E, k, routes=True) > 0)
+
+
+def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool, w13, w2):
+    """`route` and `moe_experts` in the one persistent launch: its CTAs compute the router logits
+    between them, the last to finish selects and writes the plan, and all go on to the experts'
+    products.  Returns (idx, weights, extra, plan, y) as the two calls would."""
+    q = _stream_items(x, w13, w2, E, k, routes=True)
+    if not q:
+        raise ValueError("route_and_run_experts: the step does not fit the launch")
+    T, H = x.shape
+    dev = x.device
+    inner = w13.n_features
+    extra = w_router.shape[0] - E
+    idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+    ext = torch.empty((T, extra), dtype=torch.float32, device=dev) if extra > 0 else None
+    logits = torch.empty((T, E + extra), dtype=torch.float32, device=dev)
+    offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    order = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    active = torch.empty((min(E, T * k),), dtype=torch.int32, device=dev)
+    act = torch.empty((T * k, inner), dtype=x.dtype, device=dev)
+    y = torch.empty((T * k, H), dtype=x.dtype, device=dev)
+    _lib.call("nf_moe_stream", _p(x), c_int(x.stride(0)), _p(w13.data), c_longlong(w13.group_stride), _p(w2.data),
+              c_longlong(w2.group_stride), _p(act), _p(y), c_int(T * k), c_int(T), c_int(H), c_int(inner),
+              c_int(E), c_int(k), _p(offsets), _p(order), _p(active), c_int(active.numel()),
+              _p(_stream_work(dev)), c_int(q), c_int(TUNING["moe_stream_smem_kb"] * 1024), _p(w_router),
+              c_int(extra), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(inv), _stream())
+    return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active), y
 
 
 def moe_combine(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optional[torch.Tensor],

@@ -803,11 +803,48 @@ def _persistent_experts_case(K, x, w13, w2, pw13, pw2, idx, plan, T, E, k, dtype
         xh, plan_h = x[:half].contiguous(), K.moe_plan(idx[:half].contiguous(), E)
         yh = K.moe_experts(xh, pw13, pw2, plan_h, k)
         pairs = torch.arange(half * k, device="cuda")
-        if ops._stream_items(xh, pw13, pw2, plan_h, k) == ops._stream_items(x, pw13, pw2, plan, k):
+        if ops._stream_items(xh, pw13, pw2, E, k) == ops._stream_items(x, pw13, pw2, E, k):
             assert torch.equal(yh[plan_h.inv.long()[pairs]], y[plan.inv.long()[pairs]])
         else:
             close(yh[plan_h.inv.long()[pairs]], y[plan.inv.long()[pairs]], dtype)
     assert K.tensor_core_status() == 0 and K.index_status() == 0
+    assert int(ops._STREAM_WORK[str(x.device)].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("T,H,I,E,k,extra", [(8, 2048, 1408, 60, 4, 1), (1, 256, 128, 4, 2, 0), (5, 200, 136, 6, 3, 1),
+                                             (16, 512, 264, 7, 2, 1), (64, 2048, 1408, 60, 4, 1), (33, 328, 72, 70, 8, 2)])
+def test_persistent_launch_that_routes_as_well(K, T, H, I, E, k, extra):
+    """The same launch with the routing inside: its CTAs compute the logits, the last one to
+    finish selects and writes the plan, all go on to the products.  Selection, weights, raw
+    logits of the further rows, plan and outputs have the bits of `route` followed by
+    `moe_experts`; run twice, the same again; counters back at zero."""
+    dtype = torch.bfloat16
+    x = rnd((T, H), dtype, 87)
+    wr = rnd((E + extra, H), torch.float32, 88, 0.05)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 82, 0.1), rnd((E, H, I), dtype, 83, 0.1)
+    pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
+    old = dict(K.TUNING)
+    K.TUNING.update(moe_stream_min_tokens=1, moe_stream_max_tokens=64, moe_stream_route_max_tokens=64)
+    try:
+        assert K.can_route_and_run_experts(x, wr, pw13, pw2, E, k)
+        idx, wts, ext, plan, y = K.route_and_run_experts(x, wr, E, k, True, pw13, pw2)
+        idx2, wts2, ext2, plan2, y2 = K.route_and_run_experts(x, wr, E, k, True, pw13, pw2)
+        ridx, rwts, rext, rplan = K.route(x, wr, E, k, True)
+        ry = K.moe_experts(x, pw13, pw2, rplan, k)
+    finally:
+        K.TUNING.update(old)
+    for a, b, c in ((idx, idx2, ridx), (wts, wts2, rwts), (plan.offsets, plan2.offsets, rplan.offsets),
+                    (plan.order, plan2.order, rplan.order), (plan.inv, plan2.inv, rplan.inv),
+                    (plan.active, plan2.active, rplan.active), (y, y2, ry)):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    if extra:
+        assert torch.equal(ext, ext2) and torch.equal(ext, rext)
+    pidx, pwts, pext = P.router_topk(x, wr, E, k, True)
+    same = (idx == pidx).all(dim=1)
+    assert same.float().mean() > 0.97
+    torch.testing.assert_close(wts[same], pwts[same], rtol=2e-4, atol=1e-6)
+    assert K.tensor_core_status() == 0 and K.index_status() == 0
+    from ninfer_amd_mi50_b200.kernels import ops
     assert int(ops._STREAM_WORK[str(x.device)].abs().sum()) == 0
 
 
