@@ -42,7 +42,7 @@ constexpr int kMsMaxStages = 32;
 constexpr int kMsSlotBytes = 16 * 1024;                  // a stage: 128 weight rows x 64 k, or 64 x 128, or 32 x 256
 constexpr int kMsMinStages = 4;
 constexpr int kMsMaxGroups = 512;                        // row groups (an expert's rows, eight at a time) of one step
-constexpr int kMsMaxPairs = 512;                         // (token, expert) pairs of one step
+constexpr int kMsMaxPairs = 1024;                        // rows of X of one step: (token, expert) pairs + the shared expert's
 constexpr int kMsRows = 8;                               // rows of a group
 constexpr int kMsFifo = 64;                              // item ids between producer, loader and consumers
 constexpr unsigned kMsCountPolls = 1u << 20;             // polls of a group's counter (about a second)
@@ -60,8 +60,8 @@ struct MsHeader {
   unsigned long long meet;                 // the consumer warps' own barrier
   unsigned long long xfull[2], xempty[2];  // row buffers: filled by the loader, released by the consumers
   int fifo[kMsFifo];
-  int stop, n_groups, published, loaded;   // published / loaded: items the producer has named / the loader has read
-  int max_rows, pad0, pad1, pad2;
+  int stop, n_routed, published, loaded;   // routed row groups; items the producer has named / the loader has read
+  int pad0, pad1, pad2, pad3;
   int expert[kMsMaxGroups], row_begin[kMsMaxGroups], rows[kMsMaxGroups];
   int order[kMsMaxPairs];                  // sorted pair -> token
 };
@@ -84,10 +84,18 @@ struct MsArgs {
   float* extra_out;            // [T, extra] or null
   int* inv;                    // [M] pair -> sorted position
   int extra, norm_topk;
+  // a shared expert inside the launch (n_shared > 0, with routing only): its intermediate features in
+  // n_shared chunks of I, packed like n_shared further experts; chunk c takes rows M + c T .. of act and Y
+  const __nv_bfloat16* Ws13;   // packed [n_shared][...] like W13
+  const __nv_bfloat16* Ws2;    // packed [n_shared][...] like W2
+  long long gss13, gss2;
+  float* cw;                   // [T, k + n_shared] weights of the k experts, then sigmoid(gate) (or 1) for every chunk
+  int* cinv;                   // [T, k + n_shared] rows of Y that belong to them
+  int n_shared;
   long long gs13, gs2;         // group strides in elements
   int ldx, M, T, H, I, E, k, n_mapped;
   int b_stride;                // bytes between rows of X (hidden rows or activations) in shared memory
-  int red_bytes, smem_bytes;   // the k groups' meeting place; all of the launch's dynamic shared memory
+  int red_bytes, scratch_bytes, smem_bytes;   // the k groups' meeting place; the routing's tables; all of the launch's dynamic shared memory
 };
 
 __device__ __forceinline__ void ldsm4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
@@ -141,16 +149,19 @@ struct MsRing {
   }
 };
 
-// An item id -> (product, row group, sub-tile of 16 Q features).
+// An item id -> (product, row group, sub-tile of 16 Q features).  Items in ticket order: the
+// first product of the shared expert's ns row groups (they need no plan), of the nr routed ones,
+// then the second product of the shared and of the routed ones.  n1, n2: items a group.
 struct MsItem {
   int second, a, sub;
 };
-__device__ __forceinline__ MsItem ms_decode(int id, int n1, int n2, int items1) {
+__device__ __forceinline__ MsItem ms_decode(int id, int ns, int nr, int n1, int n2) {
   MsItem it;
-  it.second = id >= items1;
-  const int r = it.second ? id - items1 : id;
+  const int first = (ns + nr) * n1;
+  it.second = id >= first;
+  const int r = it.second ? id - first : id;
   const int per = it.second ? n2 : n1;
-  it.a = r / per;
+  it.a = r / per;                  // shared groups come first in the table as well
   it.sub = r - it.a * per;
   return it;
 }
@@ -192,9 +203,118 @@ __device__ __forceinline__ bool ms_k_loop(MsHeader* hd, unsigned char* ring, MsR
   return true;
 }
 
+__device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kMsConsumers * 32) : "memory"); }
+
+// The routing, by the consumer warps of every CTA before they turn to the products: logits by
+// whoever takes a unit (8 router rows x 1 token, a warp a row, the sums in `lane_dot`'s order as
+// in the router's own kernels); the CTA whose unit is counted last selects for every token,
+// builds the plan and writes both out, then raises the flag that the producers wait for.
+// `scratch`: x as float32, then the selection's and the plan's tables.
+__device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s_unit, int* s_last, int warp, int lane) {
+  const int tid = threadIdx.x;                    // consumer threads: 0 .. 255
+  const int rows = p.E + p.extra, nblk = (rows + 7) >> 3, n_units = nblk * p.T, n = p.M;
+  float* xf = scratch;
+  int unit = blockIdx.x;                          // the first unit needs no ticket
+  while (unit < n_units) {
+    const int t = unit / nblk, e = (unit - t * nblk) * 8 + warp;
+    for (int i = tid; i < (p.H >> 3); i += kMsConsumers * 32) {
+      const uint4 v = ld_l2(p.X + (size_t)t * p.ldx + i * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        xf[i * 8 + 2 * j] = f.x;
+        xf[i * 8 + 2 * j + 1] = f.y;
+      }
+    }
+    consumers_sync();
+    if (e < rows) {
+      const float v = warp_sum(lane_dot(xf, p.Wr + (size_t)e * p.H, p.H, lane));
+      if (lane == 0) p.logits[(size_t)t * rows + e] = v;
+    }
+    consumers_sync();
+    if (tid == 0) {
+      __threadfence();                             // the unit's logits, before it is counted
+      *s_last = atomicAdd(p.work + 3, 1) == n_units - 1;
+      *s_unit = (int)gridDim.x + atomicAdd(p.work + 2, 1);
+    }
+    consumers_sync();
+    if (*s_last) {
+      __threadfence();
+      float* lg = xf;                                                                  // [8 warps][E]
+      unsigned short* chosen = reinterpret_cast<unsigned short*>(lg + kMsConsumers * p.E);   // [n] expert of each pair
+      unsigned short* rank = chosen + n;                                               // [n] its rank inside the expert
+      int* counts = reinterpret_cast<int*>(((uintptr_t)(rank + n) + 15) & ~(uintptr_t)15);    // [E + 1]
+      for (int tt = warp; tt < p.T; tt += kMsConsumers)
+        select_token(p.logits + (size_t)tt * rows, 1, lg + warp * p.E, tt, p.E, p.extra, p.k, p.norm_topk, p.topk_idx,
+                     p.topk_w, p.extra_out, lane, chosen);
+      consumers_sync();
+      // stable counting sort of the pairs by expert, in shared memory
+      for (int e2 = warp; e2 < p.E; e2 += kMsConsumers) {
+        int running = 0;
+        for (int base = 0; base < n; base += 32) {
+          const int i = base + lane;
+          const bool mine = i < n && (int)chosen[i] == e2;
+          const unsigned bits = __ballot_sync(0xffffffffu, mine);
+          if (mine) rank[i] = (unsigned short)(running + __popc(bits & ((1u << lane) - 1u)));
+          running += __popc(bits);
+        }
+        if (lane == 0) counts[e2] = running;
+      }
+      consumers_sync();
+      if (warp == 0) {
+        // 32 experts a round: offsets (exclusive prefix of the counts) and the experts that have pairs
+        int run = 0, na = 0;
+        for (int base = 0; base <= p.E; base += 32) {
+          const int e2 = base + lane;
+          const int c = e2 < p.E ? counts[e2] : 0;
+          int incl = c;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+          }
+          if (e2 <= p.E) {
+            counts[e2] = run + incl - c;
+            const_cast<int*>(p.offsets)[e2] = run + incl - c;
+          }
+          run += __shfl_sync(0xffffffffu, incl, 31);
+          const unsigned bits = __ballot_sync(0xffffffffu, c > 0);
+          const int at = na + __popc(bits & ((1u << lane) - 1u));
+          if (c > 0 && at < p.n_mapped) const_cast<int*>(p.active)[at] = e2;
+          na += __popc(bits);
+        }
+        for (int i = min(na, p.n_mapped) + lane; i < p.n_mapped; i += 32) const_cast<int*>(p.active)[i] = -1;
+      }
+      consumers_sync();
+      const int kk = p.k + p.n_shared;
+      for (int i = tid; i < n; i += kMsConsumers * 32) {
+        const int pos = counts[chosen[i]] + rank[i];
+        p.inv[i] = pos;
+        const_cast<int*>(p.order)[pos] = i;
+        if (p.cinv) {
+          const int t = i / p.k, j = i - t * p.k;
+          p.cinv[t * kk + j] = pos;
+          p.cw[t * kk + j] = *reinterpret_cast<volatile float*>(p.topk_w + i);
+        }
+      }
+      if (p.cinv)
+        for (int i = tid; i < p.T * p.n_shared; i += kMsConsumers * 32) {
+          const int t = i / p.n_shared, c = i - t * p.n_shared;
+          p.cinv[t * kk + p.k + c] = p.M + c * p.T + t;
+          p.cw[t * kk + p.k + c] = p.extra > 0 ? 1.f / (1.f + expf(-*reinterpret_cast<volatile float*>(p.extra_out + (size_t)t * p.extra))) : 1.f;
+        }
+      __threadfence();
+      consumers_sync();
+      if (tid == 0) add_release(p.work + 4, 1);
+    }
+    unit = *s_unit;
+  }
+}
+
 // Q: an item is 16 Q features (2, 4 or 8 sixteen-row groups); the 8 consumer warps are Q row
-// groups x 8 / Q k groups.  (At most 102 registers a thread, so that kernels of another stream -
-// the shared expert's - still find room on the SM.)
+// groups x 8 / Q k groups.  (At most 102 registers a thread, so that kernels of another stream
+// still find room on the SM.)
 template <int Q>
 __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs p) {
   extern __shared__ unsigned char ms_smem_raw[];
@@ -205,11 +325,18 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   constexpr int HEADER_BYTES = (sizeof(MsHeader) + 1023) & ~1023;
   MsHeader* hd = reinterpret_cast<MsHeader*>(smem);
   float* red = reinterpret_cast<float*>(smem + HEADER_BYTES);
-  unsigned char* xs = smem + HEADER_BYTES + p.red_bytes;                  // [buffers][rows][b_stride], then the ring
+  float* scratch = reinterpret_cast<float*>(smem + HEADER_BYTES + p.red_bytes);
+  unsigned char* xs = smem + HEADER_BYTES + p.red_bytes + p.scratch_bytes;     // [buffers][8 rows][b_stride], then the ring
   unsigned char* smem_end = ms_smem_raw + p.smem_bytes;
   volatile int* stop = &hd->stop;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __shared__ int s_last;
+  __shared__ int s_last, s_unit, s_last_unit;
+  const int kt1 = (p.H + 63) >> 6, kt2 = (p.I + 63) >> 6;               // k tiles of the two products
+  const int n1 = (p.I + 16 * Q - 1) / (16 * Q), n2 = (p.H + 16 * Q - 1) / (16 * Q);     // items a row group
+  const int target = n1 * kMsConsumers;                                 // counts that say "this group's activations are complete"
+  const int spt = (p.T + kMsRows - 1) / kMsRows;                        // row groups of one chunk of the shared expert
+  const int ns = p.n_shared * spt;                                      // the shared expert's row groups: first in the table
+  const int items_s1 = ns * n1;                                         // items that need no plan
 
   // ---- set-up that needs nothing from the kernel before ------------------------------------------
   if (threadIdx.x == 0) {
@@ -217,12 +344,18 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     mbar_init(&hd->meet, kMsConsumers);
     for (int b = 0; b < 2; ++b) { mbar_init(&hd->xfull[b], 1); mbar_init(&hd->xempty[b], kMsConsumers); }
     hd->stop = 0;
-    hd->n_groups = 0;
-    hd->max_rows = 1;
+    hd->n_routed = 0;
     hd->published = 0;
     hd->loaded = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  for (int g = threadIdx.x; g < ns; g += blockDim.x) {
+    const int c = g / spt, j = g - c * spt;
+    hd->expert[g] = p.E + c;
+    hd->row_begin[g] = p.M + c * p.T + j * kMsRows;
+    hd->rows[g] = min(kMsRows, p.T - j * kMsRows);
+  }
+  for (int i = threadIdx.x; i < p.n_shared * p.T; i += blockDim.x) hd->order[p.M + i] = i % p.T;
   const int* offsets = p.offsets;
   const int* active = p.active;
   const int* order = p.order;
@@ -233,147 +366,81 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   chain_wait(offsets, active, order, X, ticket);
   __syncthreads();
 
-  // ---- the step's row groups and pairs: from the plan the kernel before wrote, or from routing done here ----
-  int first_id = 0;
-  if (warp == kMsConsumers && lane == 0) first_id = atomicAdd(ticket, 1);      // under way meanwhile
-  if (p.Wr) {
-    // Logits by whoever takes a unit (8 router rows x 1 token, a warp a row, the sums in
-    // `lane_dot`'s order as in the router's own kernels); once all are written, every CTA selects
-    // and builds the plan for itself in shared memory - the same values everywhere, and no
-    // second hand-over through global memory.  CTA 0 also writes them out for the kernels after.
-    // (Everything behind the header is free until then: x as float32, then the tables.)
-    float* xf = reinterpret_cast<float*>(xs);
-    __shared__ int s_unit;
-    const int rows = p.E + p.extra, nblk = (rows + 7) >> 3, n_units = nblk * p.T, n = p.M;
-    int unit = blockIdx.x;                       // the first unit needs no ticket
-    while (unit < n_units) {
-      const int t = unit / nblk, e = (unit - t * nblk) * 8 + warp;
-      for (int i = threadIdx.x; i < (p.H >> 3); i += blockDim.x) {
-        const uint4 v = ld_l2(X + (size_t)t * p.ldx + i * 8);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(h[j]);
-          xf[i * 8 + 2 * j] = f.x;
-          xf[i * 8 + 2 * j + 1] = f.y;
+  // two buffers of eight rows of X if the ring keeps enough stages beside them, else one
+  const size_t buf_bytes = (size_t)kMsRows * p.b_stride;
+  const size_t room = (size_t)(smem_end - xs);
+  const int n_bufs = room >= 2 * buf_bytes + 1024 + (size_t)(kMsMinStages + 1) * kMsSlotBytes ? 2 : 1;
+  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)(xs + n_bufs * buf_bytes) + 1023) & ~(uintptr_t)1023);
+  const int stages = min(kMsMaxStages, (int)((smem_end - ring) / kMsSlotBytes));
+  if (smem_end < ring || stages < 2) {             // (the host's check of the sizes rules this out)
+    if (threadIdx.x == 0) atomicCAS(&g_moe_stream_error, 0, 7);
+  } else if (warp == kMsConsumers) {
+    // ---- weight producer -----------------------------------------------------------------------------
+    // Lane 0 streams the items; in between, once, the whole warp reads the plan into the table
+    // (the routed row groups behind the shared expert's, the tokens of the pairs).
+    MsRing at = {0, 1, stages};               // parity of the "empty" wait: a fresh slot counts as released
+    int issued = 0, seq = 0, pending = -1, total = 0x7fffffff;
+    bool ok = true, ended = false;
+    auto stream_items = [&](int nr) {
+      // takes tickets and streams their items; returns with `pending` set at the first item that needs the plan
+      while (ok && !ended) {
+        const int id = pending >= 0 ? pending : atomicAdd(ticket, 1);
+        pending = -1;
+        if (nr < 0 && id >= items_s1) { pending = id; return; }
+        const bool last = id >= total;
+        // name the item for the loader and the consumers (the loader must have read the slot's last tenant)
+        if (seq >= kMsFifo && !spin_above(&hd->loaded, seq - kMsFifo, stop, 9)) { ok = false; return; }
+        hd->fifo[seq % kMsFifo] = last ? -1 : id;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&hd->published) = seq + 1;
+        ++seq;
+        if (last) {
+          if (mbar_wait(&hd->empty[at.s], at.parity, stop, 1, &g_moe_stream_error)) mbar_arrive(&hd->full[at.s]);   // an empty stage that carries the end mark
+          ended = true;
+          return;
+        }
+        const MsItem item = ms_decode(id, ns, max(nr, 0), n1, n2);
+        const int e = hd->expert[item.a];
+        const int f0 = item.sub * 16 * Q, ft = f0 >> 7, r0 = f0 & 127;
+        // first product: tile (ft, kt) holds 256 rows, gate rows at r0, up rows at 128 + r0; second: 128 rows
+        const int kt = item.second ? kt2 : kt1;
+        const size_t tile = item.second ? 128 * 64 : 256 * 64;
+        const __nv_bfloat16* w = e < p.E ? (item.second ? p.W2 + (size_t)e * p.gs2 : p.W13 + (size_t)e * p.gs13)
+                                         : (item.second ? p.Ws2 + (size_t)(e - p.E) * p.gss2 : p.Ws13 + (size_t)(e - p.E) * p.gss13);
+        const __nv_bfloat16* src = w + ((size_t)ft * kt * (item.second ? 128 : 256) + r0) * 64;
+        for (int t0 = 0; t0 < kt && ok; t0 += G) {
+          const int nblk = min(G, kt - t0);
+          for (int half = 0; half < (item.second ? 1 : 2); ++half) {
+            if (!mbar_wait(&hd->empty[at.s], at.parity, stop, 1, &g_moe_stream_error)) { ok = false; break; }
+            unsigned char* dst = ring + (size_t)at.s * kMsSlotBytes;
+            mbar_expect_tx(&hd->full[at.s], nblk * BLOCK_BYTES);
+            for (int b = 0; b < nblk; ++b)
+              bulk_load(dst + b * BLOCK_BYTES, src + (size_t)(t0 + b) * tile + half * (128 * 64), BLOCK_BYTES, &hd->full[at.s]);
+            at.next();
+            ++issued;
+          }
         }
       }
-      __syncthreads();
-      if (warp < kMsConsumers && e < rows) {
-        const float v = warp_sum(lane_dot(xf, p.Wr + (size_t)e * p.H, p.H, lane));
-        if (lane == 0) p.logits[(size_t)t * rows + e] = v;
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        __threadfence();                           // the unit's logits, before it is counted
-        atomicAdd(p.work + 3, 1);
-        s_unit = (int)gridDim.x + atomicAdd(p.work + 2, 1);
-      }
-      __syncthreads();
-      unit = s_unit;
-    }
-    if (threadIdx.x == 0) {
-      bool there = false;
-      for (unsigned i = 0; i < kMsCountPolls; ++i)
-        if (ld_acquire(p.work + 3) >= n_units) { there = true; break; }
-      if (!there) {
-        hd->stop = 1;
-        atomicCAS(&g_moe_stream_error, 0, 14);
-      }
-    }
-    __syncthreads();
-    const bool writer = blockIdx.x == 0;
-    float* lg = xf;                                                                  // [8 warps][E]
-    unsigned short* chosen = reinterpret_cast<unsigned short*>(lg + kMsConsumers * p.E);   // [n] expert of each pair
-    unsigned short* rank = chosen + n;                                               // [n] its rank inside the expert
-    int* counts = reinterpret_cast<int*>(((uintptr_t)(rank + n) + 15) & ~(uintptr_t)15);    // [E + 1]
-    if (!hd->stop) {
-      if (warp < kMsConsumers)
-        for (int tt = warp; tt < p.T; tt += kMsConsumers)
-          select_token(p.logits + (size_t)tt * rows, 1, lg + warp * p.E, tt, p.E, p.extra, p.k, p.norm_topk,
-                       writer ? p.topk_idx : nullptr, writer ? p.topk_w : nullptr, writer ? p.extra_out : nullptr,
-                       lane, chosen);
-      __syncthreads();
-      // stable counting sort of the pairs by expert, in shared memory
-      for (int e = warp; e < p.E; e += kMsThreads / 32) {
-        int running = 0;
-        for (int base = 0; base < n; base += 32) {
-          const int i = base + lane;
-          const bool mine = i < n && (int)chosen[i] == e;
-          const unsigned b = __ballot_sync(0xffffffffu, mine);
-          if (mine) rank[i] = (unsigned short)(running + __popc(b & ((1u << lane) - 1u)));
-          running += __popc(b);
-        }
-        if (lane == 0) counts[e] = running;
-      }
-      __syncthreads();
-      if (warp == 0) {
-        // 32 experts a round: offsets (exclusive prefix of the counts), the experts that have pairs
-        // (ascending, then -1), and their rows eight at a time
-        int run = 0, na = 0, ng = 0, most = 1;
-        for (int base = 0; base <= p.E; base += 32) {
-          const int e = base + lane;
-          const int c = e < p.E ? counts[e] : 0;
-          int incl = c;
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const int up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
-          }
-          const int off = run + incl - c;
-          if (e <= p.E) {
-            counts[e] = off;
-            if (writer) const_cast<int*>(offsets)[e] = off;
-          }
-          run += __shfl_sync(0xffffffffu, incl, 31);
-          const unsigned b = __ballot_sync(0xffffffffu, c > 0);
-          if (writer) {
-            const int at = na + __popc(b & ((1u << lane) - 1u));
-            if (c > 0 && at < p.n_mapped) const_cast<int*>(active)[at] = e;
-          }
-          na += __popc(b);
-          const int g = (c + kMsRows - 1) / kMsRows;
-          int gi = g;
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const int up = __shfl_up_sync(0xffffffffu, gi, o);
-            if (lane >= o) gi += up;
-          }
-          const int at = ng + gi - g;
-          for (int j = 0; j < g; ++j)
-            if (at + j < kMsMaxGroups) {
-              hd->expert[at + j] = e;
-              hd->row_begin[at + j] = off + j * kMsRows;
-              hd->rows[at + j] = min(kMsRows, c - j * kMsRows);
-            }
-          most = max(most, min(c, kMsRows));
-          ng += __shfl_sync(0xffffffffu, gi, 31);
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
-        if (writer)
-          for (int i = min(na, p.n_mapped) + lane; i < p.n_mapped; i += 32) const_cast<int*>(active)[i] = -1;
-        if (lane == 0) {
-          if (ng > kMsMaxGroups) { atomicCAS(&g_moe_stream_error, 0, 7); ng = kMsMaxGroups; }
-          hd->n_groups = ng;
-          hd->max_rows = most;
-        }
-      }
-      __syncthreads();
-      for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int pos = counts[chosen[i]] + rank[i];
-        if (pos < kMsMaxPairs) hd->order[pos] = i / p.k;
-        if (writer) {
-          p.inv[i] = pos;
-          const_cast<int*>(order)[pos] = i;
+    };
+    if (lane == 0) stream_items(-1);          // the shared expert's first product needs no plan
+    __syncwarp();
+    // ---- the plan: wait for it if this launch routes, then the routed row groups and the pairs' tokens ----
+    int have = 1;
+    if (lane == 0) {
+      have = ok && !*stop;
+      if (have && p.Wr) {
+        have = 0;
+        for (unsigned i = 0; i < kMsCountPolls; ++i)
+          if (ld_acquire(p.work + 4) > 0) { have = 1; break; }
+        if (!have) {
+          *stop = 1;
+          atomicCAS(&g_moe_stream_error, 0, 14);
         }
       }
     }
-    fence_async_smem();                             // bulk copies will write where these tables were
-    __syncthreads();
-  } else {
-    if (warp == 0) {
-      int n = 0, most = 1;
+    have = __shfl_sync(0xffffffffu, have, 0);
+    int nr = 0;
+    if (have) {
       for (int i0 = 0; i0 < p.n_mapped; i0 += 32) {
         const int i = i0 + lane;
         int e = i < p.n_mapped ? ld_l2_int(active + i) : -1;
@@ -388,101 +455,54 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
         // an expert's rows, eight at a time
         const int ng = (cnt + kMsRows - 1) / kMsRows;
         int incl = ng;
-  #pragma unroll
+#pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
           const int o = __shfl_up_sync(0xffffffffu, incl, d);
           if (lane >= d) incl += o;
         }
-        const int at = n + incl - ng;
+        const int first = ns + nr + incl - ng;
         for (int j = 0; j < ng; ++j)
-          if (at + j < kMsMaxGroups) {
-            hd->expert[at + j] = e;
-            hd->row_begin[at + j] = rb + j * kMsRows;
-            hd->rows[at + j] = min(kMsRows, cnt - j * kMsRows);
+          if (first + j < kMsMaxGroups) {
+            hd->expert[first + j] = e;
+            hd->row_begin[first + j] = rb + j * kMsRows;
+            hd->rows[first + j] = min(kMsRows, cnt - j * kMsRows);
           }
-        most = max(most, min(cnt, kMsRows));
-        n += __shfl_sync(0xffffffffu, incl, 31);
+        nr += __shfl_sync(0xffffffffu, incl, 31);
       }
-  #pragma unroll
-      for (int d = 16; d > 0; d >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, d));
-      if (lane == 0) {
-        if (n > kMsMaxGroups) { atomicCAS(&g_moe_stream_error, 0, 7); n = kMsMaxGroups; }
-        hd->n_groups = n;
-        hd->max_rows = most;
+      if (ns + nr > kMsMaxGroups) {
+        if (lane == 0) atomicCAS(&g_moe_stream_error, 0, 7);
+        nr = kMsMaxGroups - ns;
       }
-    } else if (warp >= 1 && warp < kMsConsumers) {
-      for (int i = threadIdx.x - 32; i < p.M && i < kMsMaxPairs; i += (kMsConsumers - 1) * 32) {
-        const int pair = ld_l2_int(order + i);
-        int tok = pair / p.k;
-        if (pair < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = -1; }     // no row is copied for it
-        hd->order[i] = tok;
+      for (int i0 = 0; i0 < p.M; i0 += 4 * 32) {
+        int pr[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) pr[u] = i0 + u * 32 + lane < p.M ? ld_l2_int(order + i0 + u * 32 + lane) : 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 32 + lane;
+          if (i < p.M) {
+            int tok = pr[u] / p.k;
+            if (pr[u] < 0 || tok >= p.T) { atomicCAS(&g_moe_stream_error, 0, 6); tok = -1; }     // no row is copied for it
+            hd->order[i] = tok;
+          }
+        }
       }
+      if (lane == 0) *reinterpret_cast<volatile int*>(&hd->n_routed) = nr;
     }
-    __syncthreads();
-  }
-  const int n_groups = hd->n_groups;
-  const int kt1 = (p.H + 63) >> 6, kt2 = (p.I + 63) >> 6;               // k tiles of the two products
-  const int n1 = (p.I + 16 * Q - 1) / (16 * Q), n2 = (p.H + 16 * Q - 1) / (16 * Q);     // items a row group
-  const int items1 = n_groups * n1, total = items1 + n_groups * n2;
-  const int target = n1 * kMsConsumers;                                 // counts that say "this group's activations are complete"
-  // row buffers of as many rows as the largest group has: two if the ring keeps enough stages beside them
-  const int b_rows = hd->max_rows;
-  const size_t buf_bytes = (size_t)b_rows * p.b_stride;
-  const size_t room = (size_t)(smem_end - xs);
-  const int n_bufs = room >= 2 * buf_bytes + 1024 + (size_t)(kMsMinStages + 1) * kMsSlotBytes ? 2 : 1;
-  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)(xs + n_bufs * buf_bytes) + 1023) & ~(uintptr_t)1023);
-  const int stages = min(kMsMaxStages, (int)((smem_end - ring) / kMsSlotBytes));
-  if (hd->stop) {
-    // no plan: nothing to do
-  } else if (smem_end < ring || stages < 2) {             // (the host's check of the sizes rules this out)
-    if (threadIdx.x == 0) atomicCAS(&g_moe_stream_error, 0, 7);
-  } else if (warp == kMsConsumers) {
-    // ---- weight producer -----------------------------------------------------------------------------
+    __threadfence_block();
+    __syncwarp();
     if (lane == 0) {
-      MsRing at = {0, 1, stages};               // parity of the "empty" wait: a fresh slot counts as released
-      int issued = 0, seq = 0;
-      bool ok = true;
-      while (ok) {
-        const int id = seq == 0 ? first_id : atomicAdd(ticket, 1);
-        const bool last = id >= total;
-        // name the item for the loader and the consumers (the loader must have read the slot's last tenant)
-        if (seq >= kMsFifo && !spin_above(&hd->loaded, seq - kMsFifo, stop, 9)) break;
-        hd->fifo[seq % kMsFifo] = last ? -1 : id;
-        __threadfence_block();
-        *reinterpret_cast<volatile int*>(&hd->published) = seq + 1;
-        ++seq;
-        if (last) {
-          if (mbar_wait(&hd->empty[at.s], at.parity, stop, 1, &g_moe_stream_error)) mbar_arrive(&hd->full[at.s]);   // an empty stage that carries the end mark
-          break;
-        }
-        const MsItem item = ms_decode(id, n1, n2, items1);
-        const int e = hd->expert[item.a];
-        const int f0 = item.sub * 16 * Q, ft = f0 >> 7, r0 = f0 & 127;
-        // first product: tile (ft, kt) holds 256 rows, gate rows at r0, up rows at 128 + r0; second: 128 rows
-        const int kt = item.second ? kt2 : kt1;
-        const size_t tile = item.second ? 128 * 64 : 256 * 64;
-        const __nv_bfloat16* src = item.second ? p.W2 + (size_t)e * p.gs2 + ((size_t)ft * kt2 * 128 + r0) * 64
-                                               : p.W13 + (size_t)e * p.gs13 + ((size_t)ft * kt1 * 256 + r0) * 64;
-        for (int t0 = 0; t0 < kt && ok; t0 += G) {
-          const int nblk = min(G, kt - t0);
-          for (int half = 0; half < (item.second ? 1 : 2); ++half) {
-            if (!mbar_wait(&hd->empty[at.s], at.parity, stop, 1, &g_moe_stream_error)) { ok = false; break; }
-            unsigned char* dst = ring + (size_t)at.s * kMsSlotBytes;
-            mbar_expect_tx(&hd->full[at.s], nblk * BLOCK_BYTES);
-            for (int b = 0; b < nblk; ++b)
-              bulk_load(dst + b * BLOCK_BYTES, src + (size_t)(t0 + b) * tile + half * (128 * 64), BLOCK_BYTES, &hd->full[at.s]);
-            at.next();
-            ++issued;
-          }
-        }
+      if (have) {
+        total = (ns + nr) * (n1 + n2);
+        stream_items(nr);
       }
-      if (!ok) {
+      if (!ok || !have) {
         // gave up: let every copy that was started land before the CTA's shared memory goes away
-        int s = at.s, parity = at.parity ^ 1;       // "full" parity of the slot issued last is the "empty" parity it was waited with, flipped
+        int s2 = at.s, parity = at.parity ^ 1;       // "full" parity of the slot issued last is the "empty" parity it was waited with, flipped
         for (int j = 0; j < min(issued, stages); ++j) {
-          if (--s < 0) { s = stages - 1; parity ^= 1; }
+          if (--s2 < 0) { s2 = stages - 1; parity ^= 1; }
           for (unsigned i = 0; i < (1u << 20); ++i)
-            if (mbar_try(&hd->full[s], parity)) break;
+            if (mbar_try(&hd->full[s2], parity)) break;
         }
       }
     }
@@ -499,7 +519,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
         ++seq;
         *reinterpret_cast<volatile int*>(&hd->loaded) = seq;
         if (id < 0) break;
-        const MsItem item = ms_decode(id, n1, n2, items1);
+        const MsItem item = ms_decode(id, ns, *reinterpret_cast<volatile int*>(&hd->n_routed), n1, n2);
         const int buf = n % n_bufs, use = n / n_bufs;
         if (!mbar_wait(&hd->xempty[buf], (use & 1) ^ 1, stop, 11, &g_moe_stream_error)) break;
         const int rows = hd->rows[item.a], row_begin = hd->row_begin[item.a];
@@ -543,7 +563,8 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
       }
     }
   } else {
-    // ---- consumers --------------------------------------------------------------------------------
+    // ---- consumers: the routing first, if the launch has it --------------------------------------------
+    if (p.Wr) ms_route(p, scratch, &s_unit, &s_last_unit, warp, lane);
     const int rg = warp % Q, kg = warp / Q;
     const int g = lane >> 2, t = lane & 3;
     // ldmatrix addresses inside a block of 16 Q rows x 64 k: this lane's row and 16-byte piece parity
@@ -551,7 +572,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     const int a_hi = lane >> 4;                  // second pair of matrices: k + 8
     // B: matrices (rows 0-7, k..k+7), (rows 0-7, k+8..): this lane's row and k half.  (Rows beyond
     // the group's last hold what an earlier item left: they only reach columns that are not stored.)
-    const unsigned b_off = (unsigned)min(lane & 7, b_rows - 1) * p.b_stride + ((lane >> 3) & 1) * 16;
+    const unsigned b_off = (unsigned)(lane & 7) * p.b_stride + ((lane >> 3) & 1) * 16;
     MsRing at = {0, 0, stages};
     int seq = 0;
     unsigned meets = 0;                          // how often the consumers have met
@@ -561,7 +582,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
       const int buf = seq % n_bufs, use = seq / n_bufs;
       ++seq;
       if (id < 0) break;
-      const MsItem item = ms_decode(id, n1, n2, items1);
+      const MsItem item = ms_decode(id, ns, *reinterpret_cast<volatile int*>(&hd->n_routed), n1, n2);
       const int row_begin = hd->row_begin[item.a], rows = hd->rows[item.a];
 
       float acc[2][4];
@@ -641,6 +662,7 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
       *ticket = 0;
       p.work[2] = 0;
       p.work[3] = 0;
+      p.work[4] = 0;
       __threadfence();
       *finished = 0;
     }
@@ -659,24 +681,25 @@ static int launch_ms(const MsArgs& a, int grid, size_t smem, cudaStream_t stream
   return check_launch("moe_stream");
 }
 
-// The row stride and the k groups' meeting place of a launch, and whether the header, one buffer
-// of eight rows and a ring of the smallest size fit into `budget` bytes of shared memory.
+// The row stride, the k groups' meeting place and the routing's tables of a launch, and whether
+// they, one buffer of eight rows and a ring of the smallest size fit into `budget` bytes of
+// shared memory.
 static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a, int route_experts = 0, int pairs = 0) {
   const int widest = H > I ? H : I;
   const int b_stride = (widest + 63) / 64 * 64 * 2 + 16;      // + 16: rows eight apart do not share a bank
   const int red = q < 8 ? 2 * kMsConsumers * 2 * 4 * 32 * 4 : 0;
-  const size_t worst = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red + (size_t)kMsRows * b_stride + 1024 +
+  size_t scratch = 0;
+  if (route_experts) {
+    // x as float32, then: selection tables, the pairs' experts and ranks, counts
+    scratch = (size_t)H * 4;
+    const size_t tables = (size_t)kMsConsumers * route_experts * 4 + (size_t)pairs * 4 + 16 + (size_t)(route_experts + 1) * 4;
+    if (tables > scratch) scratch = tables;
+    scratch = (scratch + 1023) & ~(size_t)1023;
+  }
+  const size_t worst = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red + scratch + (size_t)kMsRows * b_stride + 1024 +
                        (size_t)kMsMinStages * kMsSlotBytes;
   if (worst > budget) return false;
-  if (route_experts) {
-    // the routing's tables live where the row buffers and the ring will be
-    const size_t head = 1024 + ((sizeof(MsHeader) + 1023) & ~(size_t)1023) + red;
-    size_t need = (size_t)H * 4;                  // x as float32, then: selection tables, pairs' experts and ranks, counts
-    const size_t tables = (size_t)kMsConsumers * route_experts * 4 + (size_t)pairs * 4 + 16 + (size_t)(route_experts + 1) * 4;
-    if (tables > need) need = tables;
-    if (head + need > budget) return false;
-  }
-  if (a) { a->b_stride = b_stride; a->red_bytes = red; a->smem_bytes = (int)budget; }
+  if (a) { a->b_stride = b_stride; a->red_bytes = red; a->scratch_bytes = (int)scratch; a->smem_bytes = (int)budget; }
   return true;
 }
 
@@ -687,14 +710,16 @@ using namespace nf;
 // How many ints of zeroed device memory a launch needs as `work`.
 extern "C" int nf_moe_stream_work_ints() { return kMsWork + kMsMaxGroups; }
 
-// 1 if the sizes fit the kernel: `pairs` (token, expert) pairs, `n_mapped` listed experts, and
-// room for a row buffer and a ring inside `smem_bytes` of shared memory.
+// 1 if the sizes fit the kernel: `pairs` (token, expert) pairs, `n_mapped` listed experts,
+// `shared_rows` rows of the shared expert's chunks (chunks x tokens), and room for a row buffer
+// and a ring inside `smem_bytes` of shared memory.
 // route_experts: 0, or E if the launch also routes (its tables then need room too, and E < 65536).
-extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, int smem_bytes, int route_experts) {
-  if (!(q == 2 || q == 4 || q == 8) || pairs < 1 || pairs > kMsMaxPairs) return 0;
-  if (n_mapped + pairs / kMsRows > kMsMaxGroups) return 0;           // row groups at worst
+extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, int smem_bytes, int route_experts,
+                                  int shared_rows) {
+  if (!(q == 2 || q == 4 || q == 8) || pairs < 1 || shared_rows < 0 || pairs + shared_rows > kMsMaxPairs) return 0;
+  if (n_mapped + pairs / kMsRows + shared_rows > kMsMaxGroups) return 0;           // row groups at worst
   if (H % 8 || I % 8 || smem_bytes > 227 * 1024) return 0;
-  if (route_experts < 0 || route_experts > 65535) return 0;
+  if (route_experts < 0 || route_experts > 65535 || (shared_rows && !route_experts)) return 0;
   return ms_layout(q, H, I, (size_t)smem_bytes, nullptr, route_experts, pairs) ? 1 : 0;
 }
 
@@ -709,17 +734,29 @@ extern "C" int nf_moe_stream_fits(int H, int I, int pairs, int n_mapped, int q, 
 // p_e or p_e / sum(selected) - and writes topk_idx [T, k], topk_w [T, k], extra_out [T, extra]
 // (the further rows' raw logits), offsets, order, inv [M] and active itself; `logits`
 // [T, E + extra] is scratch.  The values are those of the router kernels (router.cu).
+// n_shared > 0 (with routing only): a shared expert as well, its intermediate features cut into
+// n_shared chunks of I and packed like n_shared experts (Ws13, Ws2); chunk c writes rows
+// M + c T .. M + (c + 1) T of act and Y, which then have M + n_shared T rows.  Its products are
+// under way while the routing is still being computed.  cw / cinv [T, k + n_shared]: for every
+// token the weights and rows of Y to add up - the k experts', then every chunk's with
+// sigmoid(extra_out[t, 0]) (1 without further rows).
 extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long gs13, const void* W2, long long gs2,
                              void* act, void* Y, int M, int T, int H, int I, int E, int k, const int* offsets,
                              const int* order, const int* active, int n_mapped, int* work, int q,
                              int smem_bytes, const float* Wr, int extra, int norm_topk, float* logits, int* topk_idx,
-                             float* topk_w, float* extra_out, int* inv, cudaStream_t stream) {
+                             float* topk_w, float* extra_out, int* inv, const void* Ws13, long long gss13,
+                             const void* Ws2, long long gss2, int n_shared, float* cw, int* cinv,
+                             cudaStream_t stream) {
   if (M == 0) return 0;
-  NF_REQUIRE(M > 0 && T > 0 && k > 0 && E > 0 && ldx % 8 == 0, "moe_stream: bad sizes");
+  NF_REQUIRE(M > 0 && T > 0 && k > 0 && E > 0 && ldx % 8 == 0 && n_shared >= 0, "moe_stream: bad sizes");
   NF_REQUIRE(!Wr || (logits && topk_idx && topk_w && inv && extra >= 0 && (extra == 0 || extra_out) && M == T * k && k <= E),
              "moe_stream: routing needs its outputs");
-  NF_REQUIRE(nf_moe_stream_fits(H, I, M, n_mapped, q, smem_bytes, Wr ? E : 0), "moe_stream: sizes do not fit (H=%d I=%d pairs=%d experts=%d q=%d smem=%d)",
-             H, I, M, n_mapped, q, smem_bytes);
+  NF_REQUIRE(n_shared == 0 || (Wr && Ws13 && Ws2 && cw && cinv && gss13 % 8 == 0 && gss2 % 8 == 0 &&
+                               (uintptr_t)Ws13 % 16 == 0 && (uintptr_t)Ws2 % 16 == 0),
+             "moe_stream: a shared expert needs the routing inside the launch, its packed weights and cw / cinv");
+  NF_REQUIRE(nf_moe_stream_fits(H, I, M, n_mapped, q, smem_bytes, Wr ? E : 0, n_shared * T),
+             "moe_stream: sizes do not fit (H=%d I=%d pairs=%d experts=%d q=%d smem=%d shared chunks=%d)",
+             H, I, M, n_mapped, q, smem_bytes, n_shared);
   NF_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W13 % 16 == 0) && ((uintptr_t)W2 % 16 == 0) && ((uintptr_t)act % 16 == 0) &&
              gs13 % 8 == 0 && gs2 % 8 == 0, "moe_stream: operands must be 16-byte aligned");
   MsArgs a;
@@ -729,8 +766,10 @@ extern "C" int nf_moe_stream(const void* X, int ldx, const void* W13, long long 
   a.gs13 = gs13; a.gs2 = gs2;
   a.Wr = Wr; a.logits = logits; a.topk_idx = topk_idx; a.topk_w = topk_w; a.extra_out = extra_out; a.inv = inv;
   a.extra = Wr ? extra : 0; a.norm_topk = norm_topk;
+  a.Ws13 = (const __nv_bfloat16*)Ws13; a.Ws2 = (const __nv_bfloat16*)Ws2; a.gss13 = gss13; a.gss2 = gss2;
+  a.n_shared = n_shared; a.cw = n_shared ? cw : nullptr; a.cinv = n_shared ? cinv : nullptr;
   a.ldx = ldx; a.M = M; a.T = T; a.H = H; a.I = I; a.E = E; a.k = k; a.n_mapped = n_mapped;
-  ms_layout(q, H, I, (size_t)smem_bytes, &a);
+  ms_layout(q, H, I, (size_t)smem_bytes, &a, Wr ? E : 0, M);
   static int n_sm = 0;
   if (!n_sm) {
     int dev = 0;

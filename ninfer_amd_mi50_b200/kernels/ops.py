@@ -76,6 +76,15 @@ TUNING = {
     # ... and up to this many tokens that launch routes as well (logits, selection and plan by
     # its own CTAs before the products); 0: the router's kernels run before it
     "moe_stream_route_max_tokens": 64,
+    # ... and up to `moe_stream_shared_max_tokens` tokens it serves a shared expert as well (a
+    # second, packed copy of its matrices is then kept: `pack_shared_expert`; 0: no such copy, the
+    # shared expert always runs beside the launch on a second stream).  Measured at A2.7B sizes,
+    # whole decode steps against the router's kernels + the launch + the second stream: 3 % faster
+    # at 6 tokens, 2 % at 8, the same at 16, 3 % slower at 32, 6 % at 64 (the routing inside the
+    # launch takes 15 us, and only the CTAs that hold an item of the shared expert have work
+    # until it is done); with fewer than 6 tokens the separate kernels win as well
+    "moe_stream_shared": 1,
+    "moe_stream_shared_max_tokens": 16,
     "moe_stream_smem_kb": 192,
 }
 
@@ -719,7 +728,7 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
 _STREAM_WORK = {}
 
 
-def _stream_items(x: torch.Tensor, w13, w2, E: int, k: int, routes: bool = False) -> int:
+def _stream_items(x: torch.Tensor, w13, w2, E: int, k: int, routes: bool = False, shared_chunks: int = 0) -> int:
     """Sixteen-feature groups an item of the persistent experts' kernel covers (8, 4 or 2), or 0 if
     the step does not fit the kernel.  The fewer experts a step selects, the finer the items, so
     that every SM has some; a finer item also needs a smaller ring.  `routes`: the launch is to
@@ -737,7 +746,7 @@ def _stream_items(x: torch.Tensor, w13, w2, E: int, k: int, routes: bool = False
     q = 8 if pairs >= 16 else (4 if pairs >= 8 else 2)
     fits = _lib.load().nf_moe_stream_fits
     while q >= 2 and not fits(H, w13.n_features, pairs, min(E, pairs), q, TUNING["moe_stream_smem_kb"] * 1024,
-                              E if routes else 0):
+                              E if routes else 0, shared_chunks * T):
         q //= 2
     return q if q >= 2 else 0
 
@@ -774,27 +783,67 @@ def moe_experts(x: torch.Tensor, w13, w2, plan: MoePlan, k: int,
               c_int(w13.groups), c_int(k), _p(plan.offsets), _p(plan.order), _p(plan.active),
               c_int(plan.active.numel()), _p(_stream_work(x.device)), c_int(q),
               c_int(TUNING["moe_stream_smem_kb"] * 1024), None, c_int(0), c_int(0), None, None, None, None, None,
-              _stream())
+              None, c_longlong(0), None, c_longlong(0), c_int(0), None, None, _stream())
     return y
 
 
-def can_route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, w13, w2, E: int, k: int) -> bool:
+def pack_shared_expert(w_gate_up: torch.Tensor, w_down: torch.Tensor, chunk: int) -> Tuple[PackedWeights, PackedWeights]:
+    """A shared expert's matrices ([2 Is, H] gate rows first, and [H, Is]) as ceil(Is / chunk)
+    experts of `chunk` intermediate features each, packed like the routed ones (the last chunk
+    padded with zero features, which contribute nothing).  Its output is then the sum of the
+    chunks' outputs, and the persistent experts' launch can serve it."""
+    _chk(w_gate_up, "w_gate_up", torch.bfloat16); _chk(w_down, "w_down", torch.bfloat16)
+    two_is, H = w_gate_up.shape
+    inner = two_is // 2
+    n = (inner + chunk - 1) // chunk
+    g = torch.zeros((n, 2 * chunk, H), dtype=w_gate_up.dtype, device=w_gate_up.device)
+    d = torch.zeros((n, H, chunk), dtype=w_down.dtype, device=w_down.device)
+    for c in range(n):
+        lo, hi = c * chunk, min(inner, (c + 1) * chunk)
+        g[c, :hi - lo] = w_gate_up[lo:hi]
+        g[c, chunk:chunk + hi - lo] = w_gate_up[inner + lo:inner + hi]
+        d[c, :, :hi - lo] = w_down[:, lo:hi]
+    return pack_weights(g, swiglu=True), pack_weights(d, swiglu=False)
+
+
+def can_route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, w13, w2, E: int, k: int,
+                              shared: Optional[Tuple[PackedWeights, PackedWeights]] = None) -> bool:
     """Whether `route_and_run_experts` serves this step (else: `route`, then `moe_experts`)."""
-    return (w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1]
-            and _stream_items(x, w13, w2, E, k, routes=True) > 0)
+    if not (w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == x.shape[1]):
+        return False
+    chunks = 0
+    if shared is not None:
+        s13, s2 = shared
+        if not (isinstance(w13, PackedWeights) and s13.n_features == w13.n_features and s13.K == w13.K
+                and s2.n_features == x.shape[1] and s2.K == w13.n_features and k + s13.groups <= 32):
+            return False
+        chunks = s13.groups
+        if x.shape[0] > TUNING["moe_stream_shared_max_tokens"]:
+            return False
+    return _stream_items(x, w13, w2, E, k, routes=True, shared_chunks=chunks) > 0
 
 
-def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool, w13, w2):
+def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bool, w13, w2,
+                          shared: Optional[Tuple[PackedWeights, PackedWeights]] = None):
     """`route` and `moe_experts` in the one persistent launch: its CTAs compute the router logits
-    between them, the last to finish selects and writes the plan, and all go on to the experts'
-    products.  Returns (idx, weights, extra, plan, y) as the two calls would."""
-    q = _stream_items(x, w13, w2, E, k, routes=True)
+    between them, the one that finishes last selects and writes the plan, and all go on to the
+    experts' products.  Returns (idx, weights, extra, plan, y) as the two calls would.
+
+    With `shared` (`pack_shared_expert`) the launch serves the shared expert too, as further
+    experts that every token has - their weights are on their way while the routing is still
+    being computed.  Then y has T * (k + chunks) rows, and two more values are returned: the
+    weights [T, k + chunks] (the k experts', then sigmoid of the first further logit for every
+    chunk, or 1 without one) and a plan whose `inv` [T * (k + chunks)] names the rows of y to add
+    up for every token - what `moe_combine` and the fused norm take."""
+    chunks = shared[0].groups if shared is not None else 0
+    q = _stream_items(x, w13, w2, E, k, routes=True, shared_chunks=chunks)
     if not q:
         raise ValueError("route_and_run_experts: the step does not fit the launch")
     T, H = x.shape
     dev = x.device
     inner = w13.n_features
     extra = w_router.shape[0] - E
+    rows = T * (k + chunks)
     idx = torch.empty((T, k), dtype=torch.int32, device=dev)
     wts = torch.empty((T, k), dtype=torch.float32, device=dev)
     ext = torch.empty((T, extra), dtype=torch.float32, device=dev) if extra > 0 else None
@@ -803,14 +852,23 @@ def route_and_run_experts(x: torch.Tensor, w_router: torch.Tensor, E: int, k: in
     order = torch.empty((T * k,), dtype=torch.int32, device=dev)
     inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
     active = torch.empty((min(E, T * k),), dtype=torch.int32, device=dev)
-    act = torch.empty((T * k, inner), dtype=x.dtype, device=dev)
-    y = torch.empty((T * k, H), dtype=x.dtype, device=dev)
+    act = torch.empty((rows, inner), dtype=x.dtype, device=dev)
+    y = torch.empty((rows, H), dtype=x.dtype, device=dev)
+    cw = torch.empty((T, k + chunks), dtype=torch.float32, device=dev) if chunks else None
+    cinv = torch.empty((rows,), dtype=torch.int32, device=dev) if chunks else None
+    s13, s2 = shared if shared is not None else (None, None)
     _lib.call("nf_moe_stream", _p(x), c_int(x.stride(0)), _p(w13.data), c_longlong(w13.group_stride), _p(w2.data),
               c_longlong(w2.group_stride), _p(act), _p(y), c_int(T * k), c_int(T), c_int(H), c_int(inner),
               c_int(E), c_int(k), _p(offsets), _p(order), _p(active), c_int(active.numel()),
               _p(_stream_work(dev)), c_int(q), c_int(TUNING["moe_stream_smem_kb"] * 1024), _p(w_router),
-              c_int(extra), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(inv), _stream())
-    return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active), y
+              c_int(extra), c_int(1 if norm_topk else 0), _p(logits), _p(idx), _p(wts), _p(ext), _p(inv),
+              _p(s13.data) if chunks else None, c_longlong(s13.group_stride if chunks else 0),
+              _p(s2.data) if chunks else None, c_longlong(s2.group_stride if chunks else 0), c_int(chunks),
+              _p(cw), _p(cinv), _stream())
+    plan = MoePlan(offsets, order, inv, E, T, k, active)
+    if not chunks:
+        return idx, wts, ext, plan, y
+    return idx, wts, ext, plan, y, cw, MoePlan(offsets, order, cinv, E, T, k + chunks, active)
 
 
 def moe_combine(y: torch.Tensor, plan: MoePlan, wts: torch.Tensor, shared: Optional[torch.Tensor],

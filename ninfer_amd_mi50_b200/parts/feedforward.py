@@ -81,7 +81,7 @@ class SparseMoeSwiglu(FeedForward):
         self.moe_intermediate_size = int(moe_intermediate_size)
         self.shared_intermediate_size = int(shared_intermediate_size)
         self.prefix = prefix
-        self.w_router = self.w13 = self.w2 = self.ws13 = self.ws2 = None
+        self.w_router = self.w13 = self.w2 = self.ws13 = self.ws2 = self.ws_packed = None
         self.w_router_split = None
 
     @property
@@ -131,6 +131,13 @@ class SparseMoeSwiglu(FeedForward):
             self.ws13 = torch.cat([fetch(q + "gate_proj.weight"), fetch(q + "up_proj.weight")],
                                   dim=0).contiguous()
             self.ws2 = fetch(q + "down_proj.weight")
+            # a second copy in the experts' tile layout, cut into chunks of the experts' width: decode
+            # steps then serve the shared expert inside the experts' persistent launch (prompt steps
+            # keep the row-major form for the library's products)
+            self.ws_packed = None
+            if (isinstance(self.w13, kernels.PackedWeights) and kernels.TUNING["moe_stream_shared"]
+                    and self.ws13.dtype == torch.bfloat16):
+                self.ws_packed = kernels.pack_shared_expert(self.ws13, self.ws2.contiguous(), I)
 
     def weight_bytes(self) -> int:
         n = self.w_router.numel() * 4 + self._expert_total_bytes()
@@ -152,6 +159,14 @@ class SparseMoeSwiglu(FeedForward):
         # The shared expert needs nothing from the router, so on small steps (where kernels are
         # too short to fill the device) it runs beside the routed path on a second stream;
         # inside a captured graph that becomes a parallel branch.
+        if (self.ws_packed is not None and x.is_cuda
+                and kernels.can_route_and_run_experts(x, self.w_router, self.w13, self.w2, E, k, shared=self.ws_packed)):
+            # a decode step: routing, the experts' products and the shared expert's are one persistent launch
+            idx, wts, gate, plan, y, sum_wts, sum_plan = kernels.route_and_run_experts(
+                x, self.w_router, E, k, self.norm_topk_prob, self.w13, self.w2, shared=self.ws_packed)
+            if SparseMoeSwiglu.record_routing is not None:
+                SparseMoeSwiglu.record_routing.append(idx.clone())
+            return RoutedSum(y, sum_plan, sum_wts, None, None, x.dtype)
         fork = self.has_shared and x.is_cuda and x.shape[0] <= kernels.TUNING["shared_fork_max_rows"]
         shared = None
 

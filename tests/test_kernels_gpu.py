@@ -848,6 +848,54 @@ def test_persistent_launch_that_routes_as_well(K, T, H, I, E, k, extra):
     assert int(ops._STREAM_WORK[str(x.device)].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("T,H,I,E,k,Is", [(8, 2048, 1408, 60, 4, 5632), (1, 256, 128, 4, 2, 256), (5, 200, 136, 6, 3, 104),
+                                          (16, 512, 264, 7, 2, 600), (64, 2048, 1408, 60, 4, 5632), (2, 2048, 1408, 60, 4, 5632)])
+def test_persistent_launch_with_the_shared_expert_inside(K, T, H, I, E, k, Is):
+    """Routing, the experts' products and the shared expert's (cut into chunks of the experts'
+    width, also where that does not divide it) in the one launch: the sum over the rows and
+    weights it names is the plain feed-forward, the routed part has the bits of the launch
+    without the shared expert, and a second run gives the same bits."""
+    dtype = torch.bfloat16
+    x = rnd((T, H), dtype, 87)
+    wr = rnd((E + 1, H), torch.float32, 88, 0.05)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 82, 0.1), rnd((E, H, I), dtype, 83, 0.1)
+    ws13, ws2 = rnd((2 * Is, H), dtype, 84, 0.1), rnd((H, Is), dtype, 85, 0.1)
+    pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
+    shared = K.pack_shared_expert(ws13, ws2, I)
+    chunks = shared[0].groups
+    assert chunks == (Is + I - 1) // I
+    old = dict(K.TUNING)
+    K.TUNING.update(moe_stream_min_tokens=1, moe_stream_max_tokens=64, moe_stream_route_max_tokens=64,
+                    moe_stream_shared_max_tokens=64)
+    try:
+        assert K.can_route_and_run_experts(x, wr, pw13, pw2, E, k, shared=shared)
+        idx, wts, ext, plan, y, cw, cplan = K.route_and_run_experts(x, wr, E, k, True, pw13, pw2, shared=shared)
+        again = K.route_and_run_experts(x, wr, E, k, True, pw13, pw2, shared=shared)
+        ridx, rwts, rext, rplan, ry = K.route_and_run_experts(x, wr, E, k, True, pw13, pw2)
+    finally:
+        K.TUNING.update(old)
+    assert torch.equal(y, again[4]) and torch.equal(cw, again[5]) and torch.equal(cplan.inv, again[6].inv)
+    assert torch.equal(idx, ridx) and torch.equal(wts, rwts) and torch.equal(plan.inv, rplan.inv)
+    assert torch.equal(y[:T * k], ry)
+    assert torch.equal(cw[:, :k], wts) and torch.equal(cplan.inv.view(T, k + chunks)[:, :k], plan.inv.view(T, k))
+    torch.testing.assert_close(cw[:, k:], torch.sigmoid(ext[:, :1]).expand(T, chunks), rtol=1e-6, atol=1e-7)
+    got = K.moe_combine(y, cplan, cw, None, None, dtype)
+    # the plain twin, chunk by chunk as the launch does it (every chunk's output is rounded to bfloat16) ...
+    parts = [P.moe_gemm2(P.moe_gemm1(x, w13, plan, k), w2, plan)]
+    for c in range(chunks):
+        lo, hi = c * I, min(Is, (c + 1) * I)
+        gu = torch.cat([ws13[lo:hi], ws13[Is + lo:Is + hi]])
+        parts.append(P.linear(P.linear_swiglu(x, gu), ws2[:, lo:hi].contiguous()))
+    close(y, torch.cat(parts), dtype)
+    # ... and in one piece: the chunks' roundings add up to a few bfloat16 steps of the largest value
+    pshared = P.linear(P.linear_swiglu(x, ws13), ws2)
+    want = P.moe_combine(parts[0], plan, wts, pshared, ext, dtype).float()
+    assert (got.float() - want).abs().max().item() <= 2 ** -7 * want.abs().max().item()
+    assert K.tensor_core_status() == 0 and K.index_status() == 0
+    from ninfer_amd_mi50_b200.kernels import ops
+    assert int(ops._STREAM_WORK[str(x.device)].abs().sum()) == 0
+
+
 def test_persistent_experts_launch_is_refused_where_it_does_not_fit(K):
     """Eight rows of a very wide model leave too little shared memory for the ring: the
     two-launch path serves the step, with the same answer."""
