@@ -9,7 +9,7 @@ sizes come from a named set (`--sizes`, by default those of Qwen1.5-MoE-A2.7B):
 a profiler locks the clocks of a GPU that others share.)
 
 Each case warms its kernels up and then runs them a few times; with `--time` it prints the
-median time per call from CUDA events with an L2 flush between calls.  A case holds about
+median time per call from CUDA events (launch included) with an L2 flush between calls.  A case holds about
 1.5 GB on the device, larger than L2, so DRAM figures mean something.
 """
 
@@ -60,6 +60,23 @@ def case_moe(tokens: int, device):
     act = moe_gemm1(x, w13, plan, K_TOP)
     return [("moe_gemm1", lambda: moe_gemm1(x, w13, plan, K_TOP)),
             ("moe_gemm2", lambda: moe_gemm2(act, w2, plan))]
+
+
+def case_moe_stream(tokens: int, device, whole_block: bool):
+    """The persistent launch of a decode step: both products of the routed experts for `tokens`
+    tokens (plan given), or with `whole_block` the routing and the shared expert as well."""
+    from . import TUNING, moe_experts, moe_plan, pack_shared_expert, route_and_run_experts
+    TUNING.update(moe_stream_min_tokens=1, moe_stream_max_tokens=64, moe_stream_route_max_tokens=64,
+                  moe_stream_shared_max_tokens=64)
+    w13, w2 = _experts(device)
+    x = torch.randn(tokens, H, device=device).bfloat16()
+    if not whole_block:
+        plan = moe_plan(_routing(tokens, tokens, device), E)
+        return [("moe_experts", lambda: moe_experts(x, w13, w2, plan, K_TOP))]
+    wr = torch.randn(E + 1, H, device=device) * 0.05
+    shared = pack_shared_expert((torch.randn(2 * IS, H, device=device) * 0.02).bfloat16(),
+                                (torch.randn(H, IS, device=device) * 0.02).bfloat16(), I)
+    return [("route_experts_shared", lambda: route_and_run_experts(x, wr, E, K_TOP, False, w13, w2, shared=shared))]
 
 
 def case_attention_prefill(tokens: int, device):
@@ -125,6 +142,10 @@ CASES = {
     "moe_prefill": lambda dev: case_moe(2048, dev),
     "moe_decode8": lambda dev: case_moe(8, dev),
     "moe_decode64": lambda dev: case_moe(64, dev),
+    "moe_stream_decode8": lambda dev: case_moe_stream(8, dev, False),
+    "moe_stream_decode16": lambda dev: case_moe_stream(16, dev, False),
+    "moe_stream_decode64": lambda dev: case_moe_stream(64, dev, False),
+    "moe_block_decode8": lambda dev: case_moe_stream(8, dev, True),
     "attention_prefill": lambda dev: case_attention_prefill(2048, dev),
     "attention_decode8": lambda dev: case_attention_decode(8, 2048, dev),
     "attention_decode64": lambda dev: case_attention_decode(64, 2048, dev),
@@ -149,12 +170,16 @@ def main(argv=None) -> int:
         for _ in range(2):
             fn()
     torch.cuda.synchronize()
+    # L2 is flushed by writing one buffer larger than it and then reading another: the read pushes
+    # the written lines out, so that the timed call does not pay for their write-back
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if args.time else None
+    clean = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda") if args.time else None
     for name, fn in ops:
         times = []
         for _ in range(args.repeat if not args.time else max(args.repeat, 15)):
             if flush is not None:
                 flush.zero_()
+                clean.sum()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             fn()
