@@ -47,8 +47,12 @@ constexpr int kMsRows = 8;                               // rows of a group
 constexpr int kMsFifo = 64;                              // item ids between producer, loader and consumers
 constexpr unsigned kMsCountPolls = 1u << 20;             // polls of a group's counter (about a second)
 // `work`: 0 the item ticket, 1 CTAs that have finished, 2 the routing's unit ticket, 3 its units done,
-// then the row groups' counters
+// 4 "the routed row groups are written"; then the row groups' counters; then, written by the
+// routing of a launch and read by its producers, the routed row groups (their number, expert,
+// first row and rows of each) and the token of every pair
 constexpr int kMsWork = 8;
+constexpr int kMsTable = kMsWork + kMsMaxGroups;     // n, expert[], row_begin[], rows[], token[]
+constexpr int kMsWorkInts = kMsTable + 1 + 3 * kMsMaxGroups + kMsMaxPairs;
 
 // 1-3 ring waits, 4 the wait for a group's activations, 5-7 a plan that does not fit, 8 the
 // consumers' barrier, 9-11 the loader's waits, 12 the consumers' wait for an item's rows, 14 the wait for the router's logits
@@ -241,15 +245,20 @@ __device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s
     consumers_sync();
     if (*s_last) {
       __threadfence();
+      // everything in shared memory first: what the producers wait for (the routed row groups and
+      // the pairs' tokens) goes out before what only the kernels after this launch read
       float* lg = xf;                                                                  // [8 warps][E]
-      unsigned short* chosen = reinterpret_cast<unsigned short*>(lg + kMsConsumers * p.E);   // [n] expert of each pair
+      float* sw = lg + kMsConsumers * p.E;                                             // [n] weight of each pair
+      float* sext = sw + n;                                                            // [T, extra] raw logits of the further rows
+      int* counts = reinterpret_cast<int*>(sext + p.T * p.extra);                      // [E + 1] rows an expert, then offsets
+      unsigned short* chosen = reinterpret_cast<unsigned short*>(counts + p.E + 1);    // [n] expert of each pair
       unsigned short* rank = chosen + n;                                               // [n] its rank inside the expert
-      int* counts = reinterpret_cast<int*>(((uintptr_t)(rank + n) + 15) & ~(uintptr_t)15);    // [E + 1]
+      int* table = p.work + kMsTable;
       for (int tt = warp; tt < p.T; tt += kMsConsumers)
-        select_token(p.logits + (size_t)tt * rows, 1, lg + warp * p.E, tt, p.E, p.extra, p.k, p.norm_topk, p.topk_idx,
-                     p.topk_w, p.extra_out, lane, chosen);
+        select_token(p.logits + (size_t)tt * rows, 1, lg + warp * p.E, tt, p.E, p.extra, p.k, p.norm_topk, nullptr,
+                     sw, p.extra > 0 ? sext : nullptr, lane, chosen);
       consumers_sync();
-      // stable counting sort of the pairs by expert, in shared memory
+      // stable counting sort of the pairs by expert
       for (int e2 = warp; e2 < p.E; e2 += kMsConsumers) {
         int running = 0;
         for (int base = 0; base < n; base += 32) {
@@ -263,8 +272,9 @@ __device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s
       }
       consumers_sync();
       if (warp == 0) {
-        // 32 experts a round: offsets (exclusive prefix of the counts) and the experts that have pairs
-        int run = 0, na = 0;
+        // 32 experts a round: offsets (exclusive prefix of the counts), the experts that have pairs,
+        // and their rows eight at a time
+        int run = 0, na = 0, ng = 0;
         for (int base = 0; base <= p.E; base += 32) {
           const int e2 = base + lane;
           const int c = e2 < p.E ? counts[e2] : 0;
@@ -274,39 +284,66 @@ __device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s
             const int up = __shfl_up_sync(0xffffffffu, incl, o);
             if (lane >= o) incl += up;
           }
-          if (e2 <= p.E) {
-            counts[e2] = run + incl - c;
-            const_cast<int*>(p.offsets)[e2] = run + incl - c;
-          }
+          const int off = run + incl - c;
+          __syncwarp();
+          if (e2 <= p.E) counts[e2] = off;
           run += __shfl_sync(0xffffffffu, incl, 31);
+          const int gcount = (c + kMsRows - 1) / kMsRows;
+          int gi = gcount;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, gi, o);
+            if (lane >= o) gi += up;
+          }
+          const int first = ng + gi - gcount;
+          for (int j = 0; j < gcount; ++j)
+            if (first + j < kMsMaxGroups) {
+              table[1 + first + j] = e2;
+              table[1 + kMsMaxGroups + first + j] = off + j * kMsRows;
+              table[1 + 2 * kMsMaxGroups + first + j] = min(kMsRows, c - j * kMsRows);
+            }
+          ng += __shfl_sync(0xffffffffu, gi, 31);
+          // (for the kernels after this launch)
+          if (e2 <= p.E) const_cast<int*>(p.offsets)[e2] = off;
           const unsigned bits = __ballot_sync(0xffffffffu, c > 0);
           const int at = na + __popc(bits & ((1u << lane) - 1u));
           if (c > 0 && at < p.n_mapped) const_cast<int*>(p.active)[at] = e2;
           na += __popc(bits);
         }
         for (int i = min(na, p.n_mapped) + lane; i < p.n_mapped; i += 32) const_cast<int*>(p.active)[i] = -1;
+        if (lane == 0) table[0] = min(ng, kMsMaxGroups);
       }
       consumers_sync();
-      const int kk = p.k + p.n_shared;
       for (int i = tid; i < n; i += kMsConsumers * 32) {
         const int pos = counts[chosen[i]] + rank[i];
+        if (pos < kMsMaxPairs) table[1 + 3 * kMsMaxGroups + pos] = i / p.k;
+        rank[i] = (unsigned short)pos;                 // (n <= 1024: a position fits)
+      }
+      __threadfence();
+      consumers_sync();
+      if (tid == 0) add_release(p.work + 4, 1);
+      // ---- the producers are on their way; now what the kernels after this launch read ----------------
+      const int kk = p.k + p.n_shared;
+      for (int i = tid; i < n; i += kMsConsumers * 32) {
+        const int pos = rank[i];
         p.inv[i] = pos;
         const_cast<int*>(p.order)[pos] = i;
+        p.topk_idx[i] = chosen[i];
+        p.topk_w[i] = sw[i];
         if (p.cinv) {
           const int t = i / p.k, j = i - t * p.k;
           p.cinv[t * kk + j] = pos;
-          p.cw[t * kk + j] = *reinterpret_cast<volatile float*>(p.topk_w + i);
+          p.cw[t * kk + j] = sw[i];
         }
       }
+      if (p.extra_out)
+        for (int i = tid; i < p.T * p.extra; i += kMsConsumers * 32) p.extra_out[i] = sext[i];
       if (p.cinv)
         for (int i = tid; i < p.T * p.n_shared; i += kMsConsumers * 32) {
           const int t = i / p.n_shared, c = i - t * p.n_shared;
           p.cinv[t * kk + p.k + c] = p.M + c * p.T + t;
-          p.cw[t * kk + p.k + c] = p.extra > 0 ? 1.f / (1.f + expf(-*reinterpret_cast<volatile float*>(p.extra_out + (size_t)t * p.extra))) : 1.f;
+          p.cw[t * kk + p.k + c] = p.extra > 0 ? 1.f / (1.f + expf(-sext[(size_t)t * p.extra])) : 1.f;
         }
-      __threadfence();
-      consumers_sync();
-      if (tid == 0) add_release(p.work + 4, 1);
     }
     unit = *s_unit;
   }
@@ -440,7 +477,30 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     }
     have = __shfl_sync(0xffffffffu, have, 0);
     int nr = 0;
-    if (have) {
+    if (have && p.Wr) {
+      // the routing of this launch has written the routed row groups and the pairs' tokens as they are needed
+      const int* table = p.work + kMsTable;
+      nr = min(ld_l2_int(table), kMsMaxGroups - ns);
+      for (int g0 = 0; g0 < nr; g0 += 32) {
+        const int g2 = g0 + lane;
+        if (g2 < nr) {
+          const int e = ld_l2_int(table + 1 + g2), rb = ld_l2_int(table + 1 + kMsMaxGroups + g2);
+          const int rw = ld_l2_int(table + 1 + 2 * kMsMaxGroups + g2);
+          hd->expert[ns + g2] = e;
+          hd->row_begin[ns + g2] = rb;
+          hd->rows[ns + g2] = rw;
+        }
+      }
+      for (int i0 = 0; i0 < p.M; i0 += 4 * 32) {
+        int tk[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) tk[u] = i0 + u * 32 + lane < p.M ? ld_l2_int(table + 1 + 3 * kMsMaxGroups + i0 + u * 32 + lane) : 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i0 + u * 32 + lane < p.M) hd->order[i0 + u * 32 + lane] = tk[u];
+      }
+      if (lane == 0) *reinterpret_cast<volatile int*>(&hd->n_routed) = nr;
+    } else if (have) {
       for (int i0 = 0; i0 < p.n_mapped; i0 += 32) {
         const int i = i0 + lane;
         int e = i < p.n_mapped ? ld_l2_int(active + i) : -1;
@@ -690,9 +750,9 @@ static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a, int route_e
   const int red = q < 8 ? 2 * kMsConsumers * 2 * 4 * 32 * 4 : 0;
   size_t scratch = 0;
   if (route_experts) {
-    // x as float32, then: selection tables, the pairs' experts and ranks, counts
+    // x as float32, then: selection tables, the pairs' weights, experts and ranks, further logits, counts
     scratch = (size_t)H * 4;
-    const size_t tables = (size_t)kMsConsumers * route_experts * 4 + (size_t)pairs * 4 + 16 + (size_t)(route_experts + 1) * 4;
+    const size_t tables = (size_t)kMsConsumers * route_experts * 4 + (size_t)pairs * 16 + 64 + (size_t)(route_experts + 1) * 4;
     if (tables > scratch) scratch = tables;
     scratch = (scratch + 1023) & ~(size_t)1023;
   }
@@ -707,8 +767,11 @@ static bool ms_layout(int q, int H, int I, size_t budget, MsArgs* a, int route_e
 
 using namespace nf;
 
-// How many ints of zeroed device memory a launch needs as `work`.
-extern "C" int nf_moe_stream_work_ints() { return kMsWork + kMsMaxGroups; }
+// How many ints of zeroed device memory a launch needs as `work` (its counters are zero again
+// when it has finished; the rest is scratch).
+extern "C" int nf_moe_stream_work_ints() { return kMsWorkInts; }
+// ... and how many of them, from the first on, are the counters.
+extern "C" int nf_moe_stream_counter_ints() { return kMsTable; }
 
 // 1 if the sizes fit the kernel: `pairs` (token, expert) pairs, `n_mapped` listed experts,
 // `shared_rows` rows of the shared expert's chunks (chunks x tokens), and room for a row buffer
