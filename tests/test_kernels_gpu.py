@@ -896,6 +896,35 @@ def test_persistent_launch_with_the_shared_expert_inside(K, T, H, I, E, k, Is):
     assert int(ops._STREAM_WORK[str(x.device)][:K.load().nf_moe_stream_counter_ints()].abs().sum()) == 0
 
 
+def test_persistent_launch_gives_up_cleanly_when_activations_never_complete(K):
+    """The second product waits for a count that the first product raises.  With the counters
+    set so that the count can never be reached, every wait of the launch runs out (within about
+    a second), its three kinds of warps leave, the copies in flight land, the launch returns, the
+    status names the wait, the counters are back at zero, and the next launch is right."""
+    from ninfer_amd_mi50_b200.kernels import lib as klib, ops
+    T, H, I, E, k = 8, 512, 264, 7, 2
+    dtype = torch.bfloat16
+    x = rnd((T, H), dtype, 87)
+    w13, w2 = rnd((E, 2 * I, H), dtype, 82, 0.1), rnd((E, H, I), dtype, 83, 0.1)
+    pw13, pw2 = K.pack_weights(w13, swiglu=True), K.pack_weights(w2, swiglu=False)
+    g = torch.Generator().manual_seed(5)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+    plan = K.moe_plan(idx, E)
+    good = K.moe_experts(x, pw13, pw2, plan, k)
+    assert K.moe_experts_fit_stream(x, pw13, pw2, plan, k) and K.tensor_core_status() == 0
+    work = ops._STREAM_WORK[str(x.device)]
+    counters = K.load().nf_moe_stream_counter_ints()
+    work[8:counters] = -(1 << 20)                      # the row groups' counters: no count will reach its mark
+    K.moe_experts(x, pw13, pw2, plan, k)
+    torch.cuda.synchronize()
+    with pytest.raises(klib.KernelError, match="gave up on a wait .code 4(04|12)."):
+        K.check_status("test")
+    K.check_status("test")
+    assert int(work[:counters].abs().sum()) == 0
+    assert torch.equal(K.moe_experts(x, pw13, pw2, plan, k), good)
+    assert K.tensor_core_status() == 0
+
+
 def test_persistent_experts_launch_is_refused_where_it_does_not_fit(K):
     """Eight rows of a very wide model leave too little shared memory for the ring: the
     two-launch path serves the step, with the same answer."""
