@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
     python bench.py --config 57b           # Qwen2-57B-A14B layer sizes: decode at batch 1 / 8 / 32 after 1,024-token contexts
-    python bench.py --long-prefill         # adds prefill of 8,192 and 32,768 tokens in portions of 2,048
+    python bench.py --long-prefill         # adds prefill of 8,192 and 32,768 tokens in portions of 2,048 (--portion)
     python bench.py --config check-fp32    # the whole model in 32-bit at A2.7B sizes against the plain model
 
 One JSON line on stdout.  A "step" is one decode step of a batch of 8 requests, each
@@ -200,6 +200,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers, for a quick look")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--long-prefill", action="store_true", help="also time prompts of 8,192 and 32,768 tokens")
+    ap.add_argument("--portion", type=int, default=2048,
+                    help="tokens a step of the long prompts (the 2,048-token prompt is always one step)")
     ap.add_argument("--requests", type=int, default=64, help="check-fp32: number of requests")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -233,9 +235,9 @@ def main() -> int:
     pk = peaks()
     cfg = dict(CONFIG, num_hidden_layers=args.layers)
     max_batch = max(point_batches + (args.batch,)) if not args.skip_points else args.batch
-    opts = EngineOptions(dtype="bfloat16", max_context=long_context, prefill_chunk=2048,
+    opts = EngineOptions(dtype="bfloat16", max_context=long_context, prefill_chunk=max(2048, args.portion),
                          num_sequences=max_batch, page_size=64, cache_tokens=max_batch * CONTEXT,
-                         max_batched_tokens=2048)
+                         max_batched_tokens=max(2048, args.portion))
     t0 = time.time()
     engine = Engine(config=cfg, random_seed=2, options=opts)
     runner, cache, model = engine.runner, engine.cache, engine.runner.model
@@ -321,12 +323,13 @@ def main() -> int:
     PREFILL = 2048
     ptoks = torch.randint(0, V, (32768 if args.long_prefill else PREFILL,), generator=g).tolist()
 
-    def prefill_once(tokens=PREFILL):
+    def prefill_once(tokens=PREFILL, portion=PREFILL):
         cache.open("prefill")
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for a in range(0, tokens, PREFILL):
-            runner.step([StepEntry("prefill", ptoks[a:a + PREFILL], [PREFILL - 1] if a + PREFILL >= tokens else [])])
+        for a in range(0, tokens, portion):
+            part = ptoks[a:min(a + portion, tokens)]
+            runner.step([StepEntry("prefill", part, [len(part) - 1] if a + portion >= tokens else [])])
         e1.record()
         torch.cuda.synchronize()
         cache.close("prefill")
@@ -350,9 +353,9 @@ def main() -> int:
                "frac": round(prefill_flops(PREFILL) / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
     if args.long_prefill:
         for n in (8192, 32768):
-            prefill_once(n)
-            lms = min(prefill_once(n) for _ in range(2))
-            prefill[f"tokens_{n}"] = {"value": round(n / (lms / 1e3), 1), "ms": round(lms, 3), "frac": round(
+            prefill_once(n, args.portion)
+            lms = min(prefill_once(n, args.portion) for _ in range(2))
+            prefill[f"tokens_{n}"] = {"value": round(n / (lms / 1e3), 1), "ms": round(lms, 3), "portion": args.portion, "frac": round(
                 prefill_flops(n) / (lms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at batch 1 and 64 ----------------------------------------------------------
