@@ -27,6 +27,16 @@
 //     the two products.  Tickets are handed out in order and first-product items never wait, so
 //     the wait for activations cannot deadlock as long as the grid's CTAs run.
 //
+// Two optional parts in front of that (see `nf_moe_stream`):
+//
+//   * the routing: the consumer warps of every CTA first compute router logits (a unit is 8
+//     router rows x 1 token, taken by ticket), the CTA whose unit is counted last selects for
+//     every token, builds the plan in shared memory and publishes the routed row groups; the
+//     producers wait (bounded) for that before their first routed item;
+//   * a shared expert, cut into chunks of the experts' width and packed like further experts:
+//     its row groups stand first in the table and need no plan, so their weights stream while
+//     the routing is still being computed.
+//
 // The sums of a row are formed in an order that depends on the sizes and on Q only (k tiles in
 // order, k groups added in order), never on the batch or on which CTA took the item.  Every
 // wait is bounded; the first to give up records a code and the CTA leaves.
