@@ -93,7 +93,7 @@ class Session:
 
 class Ninfer:
     def __init__(self, model_dir: Optional[str] = None, max_context: int = 32768,
-                 prefill_chunk: int = 512, num_sequences: int = 1, *, dtype: str = "bfloat16",
+                 prefill_chunk: int = 2048, num_sequences: int = 1, *, dtype: str = "bfloat16",
                  page_size: int = 64, cache_tokens: Optional[int] = None,
                  max_batched_tokens: Optional[int] = None, use_graph: bool = True,
                  run_ahead: bool = True,

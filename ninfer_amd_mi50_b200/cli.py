@@ -2,7 +2,8 @@
 
 Reference: src/apps/ninfer.cpp:55-119.  Kept with their meanings and defaults:
 ``<model_dir>``, ``--prompt``, ``--raw``, ``--system``, ``--max-context`` (32768),
-``--prefill-chunk`` (512), ``--max-new`` (512), ``--temperature`` (0.7; 0 = greedy),
+``--prefill-chunk`` (2048; the reference's 512 suits its GPU, not this one), ``--max-new`` (512),
+``--temperature`` (0.7; 0 = greedy),
 ``--top-k`` (50), ``--top-p`` (0.95), ``--repeat-penalty`` (1.05), ``--seed`` (0 -> 1234 for a
 one-shot run, ninfer.cpp:205), ``--graph``, ``--log-level``.  Dropped: ``--gpus``, ``--quant``,
 ``--parallel``, ``--verify`` (one GPU, no quantisation), ``--no-thinking`` (Qwen3 only).
@@ -40,7 +41,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt-ids-file", help="file with one prompt of token ids per line")
     ap.add_argument("--print-ids", action="store_true", help="print generated token ids, not text")
     ap.add_argument("--max-context", type=int, default=32768, help="KV capacity in tokens per request")
-    ap.add_argument("--prefill-chunk", type=int, default=512, help="prefill chunk size")
+    ap.add_argument("--prefill-chunk", type=int, default=2048, help="prefill chunk size")
     ap.add_argument("--max-new", type=int, default=512, help="new tokens per generation")
     ap.add_argument("--temperature", type=float, default=0.7, help="sampling temperature (0 = greedy)")
     ap.add_argument("--top-k", type=int, default=50)

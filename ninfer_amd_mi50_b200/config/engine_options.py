@@ -1,8 +1,10 @@
 """Engine options: what a user chooses at start-up, as opposed to what config.json fixes.
 
-`max_context`, `prefill_chunk` and `num_sequences` keep the names, meanings and defaults
-of the reference's ``ModelOptions`` (src/models/model.h:37-50) and C options struct
-(src/api/ninfer_c_api.h:20-28).  The paged cache adds `page_size` and `cache_tokens`,
+`max_context`, `prefill_chunk` and `num_sequences` keep the names and meanings of the
+reference's ``ModelOptions`` (src/models/model.h:37-50) and C options struct
+(src/api/ninfer_c_api.h:20-28), and its defaults but one: a prompt's portion is 2,048 tokens,
+not 512.  Every portion reads every expert's weights once, so on a B200 a prompt in portions of
+512 runs at 63 K tokens/s, in portions of 2,048 at 149-167 K, of 8,192 at 185 K (A2.7B sizes).  The paged cache adds `page_size` and `cache_tokens`,
 the scheduler adds `max_batched_tokens`, and `dtype` picks the bfloat16 serving path or
 the all-32-bit path.
 """
@@ -19,7 +21,7 @@ DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp3
 class EngineOptions:
     dtype: str = "bfloat16"          # "bfloat16" | "float32"
     max_context: int = 32768         # most tokens one request may hold
-    prefill_chunk: int = 512         # largest portion of one prompt in one step
+    prefill_chunk: int = 2048        # largest portion of one prompt in one step
     num_sequences: int = 1           # most live requests
     page_size: int = 64              # tokens per cache page
     cache_tokens: Optional[int] = None   # pool size in tokens (default: num_sequences * max_context)
@@ -39,7 +41,7 @@ class EngineOptions:
         if self.max_context <= 0:
             self.max_context = 32768
         if self.prefill_chunk <= 0:
-            self.prefill_chunk = 512
+            self.prefill_chunk = 2048
         if self.num_sequences <= 0:
             self.num_sequences = 1
         if self.page_size <= 0 or self.page_size % 16:

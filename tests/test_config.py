@@ -111,7 +111,8 @@ def test_registry():
 
 def test_engine_options():
     o = EngineOptions(max_context=0, prefill_chunk=-1, num_sequences=0)
-    assert (o.max_context, o.prefill_chunk, o.num_sequences) == (32768, 512, 1)   # c_api.cpp:54-82
+    # the reference's defaults (c_api.cpp:54-82), but for the portion of a prompt: 2,048 instead of 512
+    assert (o.max_context, o.prefill_chunk, o.num_sequences) == (32768, 2048, 1)
     assert EngineOptions(dtype="fp32").dtype == "float32"
     with pytest.raises(ValueError):
         EngineOptions(dtype="int4")
