@@ -359,11 +359,13 @@ def main() -> int:
                 prefill_flops(n) / (lms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at batch 1 and 64 ----------------------------------------------------------
-    points = {}
+    points, points_frac = {}, {}
     if not args.skip_points:
         for b in point_batches:
             pm, _ = time_decode(b, max(8, K // 2), W)
             points[f"decode_b{b}"] = round(b / (pm / 1e3), 1)
+            pw, pkv = decode_bytes(b)
+            points_frac[f"decode_b{b}"] = round((pw + pkv) / (pm / 1e3) / 1e9 / pk["hbm_gbs"], 4)
 
     # ---- end to end through the entry point's engine -----------------------------------------
     e2e = None
@@ -408,7 +410,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"],
                      "weight_bytes": wbytes, "cache_bytes": kvbytes},
-        "points": points, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
+        "points": points, "points_roofline_frac": points_frac, "e2e": e2e, "gpu_launches": launches, "clocks": clk,
     }
     print(json.dumps(out))
     return 0
