@@ -54,10 +54,12 @@ TUNING = {
     "fuse_combine_norm_max_rows": 64,
     # a shared expert runs beside the routed path, on a second stream, in steps of up to
     # `shared_fork_max_rows` rows (larger steps fill the device with either alone); it is started
-    # beside the router up to `shared_fork_late_rows` rows and after it beyond (measured on decode
-    # steps at A2.7B sizes: starting late is 3 % faster at 48 and 64 rows, 5 % slower at 16)
+    # beside the router up to `shared_fork_late_rows` rows and after it beyond.  (With the
+    # experts as two launches, starting after the router was 3 % faster at 48 and 64 rows; with
+    # their persistent launch, starting beside the router is 2 % faster at 40 to 64 rows too, so
+    # the second threshold now equals the first.)
     "shared_fork_max_rows": 64,
-    "shared_fork_late_rows": 32,
+    "shared_fork_late_rows": 64,
     # in steps of at least this many rows the routing (logits, selection, plan, gather: short
     # kernels of a few CTAs, one waiting for the other) runs on a second stream of higher
     # priority while the shared expert's products fill the device; 0 turns it off

@@ -177,9 +177,8 @@ class SparseMoeSwiglu(FeedForward):
                 kernels.chain_break()       # its input comes from the other stream
                 return main, side, kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
 
-        # With few rows the shared expert starts beside the router (whose kernels leave the memory
-        # idle); from some tens of rows on it is better started after it, beside the experts'
-        # products (measured on decode steps: 3 % faster at 48 and 64 rows, 5 % slower at 16).
+        # The shared expert starts beside the router (whose kernels leave the memory idle) up to
+        # `shared_fork_late_rows` rows, beyond that after it, beside the experts' products.
         late = x.shape[0] > kernels.TUNING["shared_fork_late_rows"]
         # In large steps it is the other way round: the shared expert's products fill the device,
         # and the routing - a chain of short kernels of a few CTAs - runs beside them.
