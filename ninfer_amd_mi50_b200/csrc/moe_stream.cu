@@ -129,6 +129,11 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ int add_acq_rel(int* p, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
 __device__ __forceinline__ void add_release(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -248,13 +253,15 @@ __device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s
     }
     consumers_sync();
     if (tid == 0) {
-      __threadfence();                             // the unit's logits, before it is counted
-      *s_last = atomicAdd(p.work + 3, 1) == n_units - 1;
-      *s_unit = (int)gridDim.x + atomicAdd(p.work + 2, 1);
+      // The barrier before this orders the warps' stores of the unit's logits before the count
+      // (release), and for the CTA that counts last, the barrier after it orders every unit's
+      // logits before its reads (acquire): one thread's atomic does for the CTA what a grid-wide
+      // barrier's does.
+      *s_unit = n_units > (int)gridDim.x ? (int)gridDim.x + atomicAdd(p.work + 2, 1) : n_units;
+      *s_last = add_acq_rel(p.work + 3, 1) == n_units - 1;
     }
     consumers_sync();
     if (*s_last) {
-      __threadfence();
       // everything in shared memory first: what the producers wait for (the routed row groups and
       // the pairs' tokens) goes out before what only the kernels after this launch read
       float* lg = xf;                                                                  // [8 warps][E]
@@ -329,9 +336,8 @@ __device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s
         if (pos < kMsMaxPairs) table[1 + 3 * kMsMaxGroups + pos] = i / p.k;
         rank[i] = (unsigned short)pos;                 // (n <= 1024: a position fits)
       }
-      __threadfence();
       consumers_sync();
-      if (tid == 0) add_release(p.work + 4, 1);
+      if (tid == 0) add_release(p.work + 4, 1);          // (after the barrier: it covers every thread's stores)
       // ---- the producers are on their way; now what the kernels after this launch read ----------------
       const int kk = p.k + p.n_shared;
       for (int i = tid; i < n; i += kMsConsumers * 32) {
@@ -403,6 +409,16 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     hd->rows[g] = min(kMsRows, p.T - j * kMsRows);
   }
   for (int i = threadIdx.x; i < p.n_shared * p.T; i += blockDim.x) hd->order[p.M + i] = i % p.T;
+  if (p.Wr && warp < kMsConsumers) {
+    // the router rows of this CTA's first unit are weights: asked into L2 before the dependency wait
+    const int rows = p.E + p.extra, nblk = (rows + 7) >> 3;
+    if ((int)blockIdx.x < nblk * p.T) {
+      const int e = ((int)blockIdx.x % nblk) * 8 + warp;
+      if (e < rows)
+        for (int off = lane * 128; off < p.H * 4; off += 32 * 128)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.Wr + (size_t)e * p.H) + off));
+    }
+  }
   const int* offsets = p.offsets;
   const int* active = p.active;
   const int* order = p.order;
@@ -485,13 +501,27 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
         }
       }
     }
+    __syncwarp();                                // lane 0's acquire comes before the other lanes' reads of the table
     have = __shfl_sync(0xffffffffu, have, 0);
     int nr = 0;
     if (have && p.Wr) {
       // the routing of this launch has written the routed row groups and the pairs' tokens as they are needed
       const int* table = p.work + kMsTable;
+      // (the first groups are asked for together with their number: one trip to L2 instead of two)
+      const int most = min(p.n_mapped + p.M / kMsRows, kMsMaxGroups - ns);      // routed row groups at worst
+      int e0 = 0, rb0 = 0, rw0 = 0;
+      if (lane < most) {
+        e0 = ld_l2_int(table + 1 + lane);
+        rb0 = ld_l2_int(table + 1 + kMsMaxGroups + lane);
+        rw0 = ld_l2_int(table + 1 + 2 * kMsMaxGroups + lane);
+      }
       nr = min(ld_l2_int(table), kMsMaxGroups - ns);
-      for (int g0 = 0; g0 < nr; g0 += 32) {
+      if (lane < nr) {
+        hd->expert[ns + lane] = e0;
+        hd->row_begin[ns + lane] = rb0;
+        hd->rows[ns + lane] = rw0;
+      }
+      for (int g0 = 32; g0 < nr; g0 += 32) {
         const int g2 = g0 + lane;
         if (g2 < nr) {
           const int e = ld_l2_int(table + 1 + g2), rb = ld_l2_int(table + 1 + kMsMaxGroups + g2);

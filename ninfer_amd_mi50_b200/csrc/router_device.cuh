@@ -54,11 +54,13 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
                                              int extra, int k, int norm_topk, int* __restrict__ topk_idx,
                                              float* __restrict__ topk_w, float* __restrict__ extra_out,
                                              int lane, unsigned short* chosen = nullptr) {
-  if (extra_out)
-    for (int g = lane; g < extra; g += 32) {
-      const float* p = row + (size_t)(E + g) * exp_stride;
-      extra_out[(size_t)t * extra + g] = GLOBAL ? __ldcg(p) : *p;
-    }
+  // (the further rows' logits are asked for together with the experts', and stored once those are in)
+  const bool has_extra = extra_out && lane < extra;
+  float extra_v = 0.f;
+  if (has_extra) {
+    const float* p = row + (size_t)(E + lane) * exp_stride;
+    extra_v = GLOBAL ? __ldcg(p) : *p;
+  }
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
     const float* p = row + (size_t)e * exp_stride;
@@ -67,6 +69,12 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
     mx = fmaxf(mx, v);
   }
   mx = warp_max(mx);
+  if (has_extra) extra_out[(size_t)t * extra + lane] = extra_v;
+  if (extra_out)
+    for (int g = lane + 32; g < extra; g += 32) {
+      const float* p = row + (size_t)(E + g) * exp_stride;
+      extra_out[(size_t)t * extra + g] = GLOBAL ? __ldcg(p) : *p;
+    }
   // A logit that is not a number (a broken checkpoint, an overflow upstream) must not become an
   // index: such a probability counts as zero in the selection, so the k experts chosen are
   // always valid ones, and the row's weights are made NaN so that its output shows the fault
