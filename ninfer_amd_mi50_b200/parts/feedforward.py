@@ -155,10 +155,14 @@ class SparseMoeSwiglu(FeedForward):
         return self._expert_total_bytes() // self.num_experts
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """The same arithmetic in four arrangements, chosen by the number of rows (thresholds in
+        `kernels.TUNING`, each with the measurement behind it):
+        6 to 16 rows - routing, experts and shared expert in one persistent launch;
+        up to 64 rows - the shared expert on a second stream beside the router and the experts
+        (which are one persistent launch from 6 rows on);
+        up to 255 rows - one kernel after the other;
+        256 rows and more - the routing on a second stream beside the shared expert's products."""
         E, k = self.num_experts, self.top_k
-        # The shared expert needs nothing from the router, so on small steps (where kernels are
-        # too short to fill the device) it runs beside the routed path on a second stream;
-        # inside a captured graph that becomes a parallel branch.
         if (self.ws_packed is not None and x.is_cuda
                 and kernels.can_route_and_run_experts(x, self.w_router, self.w13, self.w2, E, k, shared=self.ws_packed)):
             # a decode step: routing, the experts' products and the shared expert's are one persistent launch
@@ -167,6 +171,9 @@ class SparseMoeSwiglu(FeedForward):
             if SparseMoeSwiglu.record_routing is not None:
                 SparseMoeSwiglu.record_routing.append(idx.clone())
             return RoutedSum(y, sum_plan, sum_wts, None, None, x.dtype)
+        # The shared expert needs nothing from the router, so on small steps (where kernels are
+        # too short to fill the device) it runs beside the routed path on a second stream;
+        # inside a captured graph that becomes a parallel branch.
         fork = self.has_shared and x.is_cuda and x.shape[0] <= kernels.TUNING["shared_fork_max_rows"]
         shared = None
 
