@@ -62,10 +62,12 @@ TUNING = {
     # the second threshold now equals the first.)
     "shared_fork_max_rows": 64,
     "shared_fork_late_rows": 64,
-    # in steps of at least this many rows the routing (logits, selection, plan, gather: short
-    # kernels of a few CTAs, one waiting for the other) runs on a second stream of higher
-    # priority while the shared expert's products fill the device; 0 turns it off
-    "route_beside_shared_min_rows": 256,
+    # in steps of at least this many rows (and more than `shared_fork_max_rows`) the routing
+    # (logits, selection, plan, gather: short kernels of a few CTAs, one waiting for the other)
+    # runs on a second stream of higher priority while the shared expert's products fill the
+    # device; 0 turns it off.  (A prompt of 2,048 tokens: 3 % faster; decode steps of 72 to 128
+    # tokens: 1.3 %.)
+    "route_beside_shared_min_rows": 65,
     # steps of `moe_stream_min_tokens` to `moe_stream_max_tokens` tokens run both products of the
     # routed experts in one persistent launch (packed bfloat16 weights); a max of 0: always two
     # launches.  Measured at A2.7B sizes, whole decode steps against the two launches (the

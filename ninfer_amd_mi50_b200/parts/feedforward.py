@@ -160,8 +160,8 @@ class SparseMoeSwiglu(FeedForward):
         6 to 16 rows - routing, experts and shared expert in one persistent launch;
         up to 64 rows - the shared expert on a second stream beside the router and the experts
         (which are one persistent launch from 6 rows on);
-        up to 255 rows - one kernel after the other;
-        256 rows and more - the routing on a second stream beside the shared expert's products."""
+        more rows - the routing on a second stream beside the shared expert's products.
+        (Without a shared expert, or with the thresholds moved: one kernel after the other.)"""
         E, k = self.num_experts, self.top_k
         if (self.ws_packed is not None and x.is_cuda
                 and kernels.can_route_and_run_experts(x, self.w_router, self.w13, self.w2, E, k, shared=self.ws_packed)):
