@@ -233,7 +233,9 @@ __device__ __forceinline__ void ms_route(const MsArgs& p, float* scratch, int* s
   const int tid = threadIdx.x;                    // consumer threads: 0 .. 255
   const int rows = p.E + p.extra, nblk = (rows + 7) >> 3, n_units = nblk * p.T, n = p.M;
   float* xf = scratch;
-  int unit = blockIdx.x;                          // the first unit needs no ticket
+  // The first unit needs no ticket; they go to the CTAs from the end of the grid, the first items
+  // of the shared expert to those from its start: a CTA then rarely has both.
+  int unit = (int)gridDim.x - 1 - (int)blockIdx.x;
   while (unit < n_units) {
     const int t = unit / nblk, e = (unit - t * nblk) * 8 + warp;
     for (int i = tid; i < (p.H >> 3); i += kMsConsumers * 32) {
@@ -412,8 +414,9 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
   if (p.Wr && warp < kMsConsumers) {
     // the router rows of this CTA's first unit are weights: asked into L2 before the dependency wait
     const int rows = p.E + p.extra, nblk = (rows + 7) >> 3;
-    if ((int)blockIdx.x < nblk * p.T) {
-      const int e = ((int)blockIdx.x % nblk) * 8 + warp;
+    const int unit = (int)gridDim.x - 1 - (int)blockIdx.x;
+    if (unit < nblk * p.T) {
+      const int e = (unit % nblk) * 8 + warp;
       if (e < rows)
         for (int off = lane * 128; off < p.H * 4; off += 32 * 128)
           asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.Wr + (size_t)e * p.H) + off));
@@ -442,12 +445,15 @@ __global__ void __launch_bounds__(kMsThreads, 2) moe_stream_kernel(const MsArgs 
     // Lane 0 streams the items; in between, once, the whole warp reads the plan into the table
     // (the routed row groups behind the shared expert's, the tokens of the pairs).
     MsRing at = {0, 1, stages};               // parity of the "empty" wait: a fresh slot counts as released
-    int issued = 0, seq = 0, pending = -1, total = 0x7fffffff;
+    int issued = 0, seq = 0, total = 0x7fffffff;
+    // items that need no plan go to the CTAs in order, without a ticket; tickets count on from there
+    const int untaken = min(items_s1, (int)gridDim.x);
+    int pending = (int)blockIdx.x < untaken ? (int)blockIdx.x : -1;
     bool ok = true, ended = false;
     auto stream_items = [&](int nr) {
       // takes tickets and streams their items; returns with `pending` set at the first item that needs the plan
       while (ok && !ended) {
-        const int id = pending >= 0 ? pending : atomicAdd(ticket, 1);
+        const int id = pending >= 0 ? pending : untaken + atomicAdd(ticket, 1);
         pending = -1;
         if (nr < 0 && id >= items_s1) { pending = id; return; }
         const bool last = id >= total;
