@@ -763,6 +763,9 @@ def moe_experts_fit_stream(x: torch.Tensor, w13, w2, plan: MoePlan, k: int) -> b
 
 
 def _stream_work(device: torch.device) -> torch.Tensor:
+    """The persistent launch's counters and tables: one buffer a device, so its launches must not
+    overlap one another - they are issued to one stream (the step's), eagerly or inside its
+    graphs, and each leaves the counters at zero."""
     key = str(device)
     if key not in _STREAM_WORK:
         _STREAM_WORK[key] = torch.zeros((int(_lib.load().nf_moe_stream_work_ints()),), dtype=torch.int32, device=device)
