@@ -75,7 +75,6 @@ struct MsHeader {
   unsigned long long xfull[2], xempty[2];  // row buffers: filled by the loader, released by the consumers
   int fifo[kMsFifo];
   int stop, n_routed, published, loaded;   // routed row groups; items the producer has named / the loader has read
-  int pad0, pad1, pad2, pad3;
   int expert[kMsMaxGroups], row_begin[kMsMaxGroups], rows[kMsMaxGroups];
   int order[kMsMaxPairs];                  // sorted pair -> token
 };
